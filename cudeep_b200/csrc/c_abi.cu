@@ -1,0 +1,268 @@
+// extern "C" surface of libcudeep_b200.so (declared in include/cudeep_b200.h).
+// Each function forwards to the C++ launcher of the same operation and turns
+// exceptions into a status code plus a thread-local message.
+#include "cudeep_b200.h"
+
+#include "cudeep/kernels/conv.cuh"
+#include "cudeep/kernels/matmul.cuh"
+#include "cudeep/memory.cuh"
+#include "conv_igemm.h"
+#include "gemm_tf32.h"
+
+#include <string>
+
+namespace {
+
+thread_local std::string g_last_error;
+
+template <typename F>
+int guarded(F&& f) {
+    try {
+        f();
+        return CUDEEP_B200_OK;
+    } catch (const std::exception& e) {
+        g_last_error = e.what();
+    } catch (...) {
+        g_last_error = "unknown C++ exception";
+    }
+    return CUDEEP_B200_ERROR;
+}
+
+cudaStream_t as_stream(cudeep_b200_stream_t s) { return static_cast<cudaStream_t>(s); }
+
+cudeep::kernels::GemmEpilogue as_epilogue(int code) {
+    CB200_REQUIRE(code >= 0 && code <= 4, "unknown epilogue code");
+    return static_cast<cudeep::kernels::GemmEpilogue>(code);
+}
+
+// Device buffer from the pool, returned on scope exit.
+struct PoolBuffer {
+    void* ptr = nullptr;
+    explicit PoolBuffer(size_t bytes) : ptr(cudeep::device_malloc(bytes)) {}
+    ~PoolBuffer() { cudeep::device_free(ptr); }
+    PoolBuffer(const PoolBuffer&) = delete;
+    PoolBuffer& operator=(const PoolBuffer&) = delete;
+    template <typename T> T* as() const { return static_cast<T*>(ptr); }
+};
+
+// One private stream per thread for the host-buffer entry points, so their
+// copies and kernels do not serialise against the legacy default stream.
+cudaStream_t host_call_stream() {
+    thread_local cudaStream_t stream = nullptr;
+    thread_local int stream_device = -1;
+    int dev = 0;
+    CB200_CUDA(cudaGetDevice(&dev));
+    if (stream == nullptr || stream_device != dev) {
+        CB200_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+        stream_device = dev;
+    }
+    return stream;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cudeep_b200_version(void) { return 100; }
+
+const char* cudeep_b200_last_error(void) { return g_last_error.c_str(); }
+
+int cudeep_b200_device_status(int clear, uint32_t* status) {
+    return guarded([&] {
+        CB200_REQUIRE(status != nullptr, "status pointer is null");
+        *status = cudeep_b200::read_device_status(clear != 0);
+    });
+}
+
+int cudeep_b200_matmul_f32(const float* A, const float* B, float* C, int M, int N, int K,
+                           cudeep_b200_stream_t stream) {
+    return guarded([&] { cudeep::kernels::launch_matmul_kernel<float>(A, B, C, M, N, K, as_stream(stream)); });
+}
+
+int cudeep_b200_matmul_f32_strict(const float* A, const float* B, float* C, int M, int N, int K,
+                                  cudeep_b200_stream_t stream) {
+    return guarded(
+        [&] { cudeep::kernels::launch_matmul_kernel_fp32<float>(A, B, C, M, N, K, as_stream(stream)); });
+}
+
+int cudeep_b200_matmul_f64(const double* A, const double* B, double* C, int M, int N, int K,
+                           cudeep_b200_stream_t stream) {
+    return guarded([&] { cudeep::kernels::launch_matmul_kernel<double>(A, B, C, M, N, K, as_stream(stream)); });
+}
+
+int cudeep_b200_matmul_fused_act(const float* A, const float* B, float* C, int M, int N, int K,
+                                 int epilogue, cudeep_b200_stream_t stream) {
+    return guarded([&] {
+        cudeep::kernels::launch_matmul_fused_act(A, B, C, M, N, K, as_epilogue(epilogue), as_stream(stream));
+    });
+}
+
+int cudeep_b200_linear_forward_f32(const float* x, const float* W, const float* bias, float* y,
+                                   int M, int N, int K, int epilogue, cudeep_b200_stream_t stream) {
+    return guarded([&] {
+        cudeep::kernels::launch_linear_forward(x, W, bias, y, M, N, K, as_epilogue(epilogue), as_stream(stream));
+    });
+}
+
+int cudeep_b200_linear_forward_f64(const double* x, const double* W, const double* bias, double* y,
+                                   int M, int N, int K, int epilogue, cudeep_b200_stream_t stream) {
+    return guarded([&] {
+        cudeep::kernels::launch_linear_forward(x, W, bias, y, M, N, K, as_epilogue(epilogue), as_stream(stream));
+    });
+}
+
+int cudeep_b200_gemm_tf32_tuned(const float* A, const float* B, int b_is_nk, float* C, int M, int N,
+                                int K, const float* bias, int bias_per_row, int epilogue, int ctas,
+                                int bn, int raster_group, int max_ctas, uint32_t b_lbo,
+                                uint32_t b_sbo, cudeep_b200_stream_t stream) {
+    return guarded([&] {
+        CB200_REQUIRE(A != nullptr && B != nullptr && C != nullptr, "gemm: null operand pointer");
+        CB200_REQUIRE(epilogue >= 0 && epilogue <= 4, "unknown epilogue code");
+        cudeep_b200::GemmTuning tune;
+        tune.ctas = ctas;
+        tune.bn = bn;
+        tune.raster_group = raster_group;
+        tune.max_ctas = max_ctas;
+        tune.b_lbo = b_lbo;
+        tune.b_sbo = b_sbo;
+        cudeep_b200::gemm_tf32(A, B, b_is_nk != 0, C, M, N, K, bias, bias_per_row != 0, epilogue, tune,
+                               as_stream(stream));
+    });
+}
+
+int cudeep_b200_conv2d_forward_f32(const float* input, const float* weight, const float* bias,
+                                   float* output, int batch, int in_channels, int out_channels,
+                                   int in_h, int in_w, int kernel_h, int kernel_w, int stride_h,
+                                   int stride_w, int pad_h, int pad_w, cudeep_b200_stream_t stream) {
+    return guarded([&] {
+        cudeep::kernels::launch_conv2d_forward_kernel<float>(input, weight, bias, output, batch, in_channels,
+                                                             out_channels, in_h, in_w, kernel_h, kernel_w,
+                                                             stride_h, stride_w, pad_h, pad_w,
+                                                             as_stream(stream));
+    });
+}
+
+int cudeep_b200_conv2d_forward_fused_f32(const float* input, const float* weight, const float* bias,
+                                         float* output, int batch, int in_channels, int out_channels,
+                                         int in_h, int in_w, int kernel_h, int kernel_w, int stride_h,
+                                         int stride_w, int pad_h, int pad_w, int epilogue,
+                                         cudeep_b200_stream_t stream) {
+    return guarded([&] {
+        cudeep::kernels::launch_conv2d_forward_fused(input, weight, bias, output, batch, in_channels,
+                                                     out_channels, in_h, in_w, kernel_h, kernel_w, stride_h,
+                                                     stride_w, pad_h, pad_w, as_epilogue(epilogue),
+                                                     as_stream(stream));
+    });
+}
+
+int cudeep_b200_conv2d_forward_f64(const double* input, const double* weight, const double* bias,
+                                   double* output, int batch, int in_channels, int out_channels,
+                                   int in_h, int in_w, int kernel_h, int kernel_w, int stride_h,
+                                   int stride_w, int pad_h, int pad_w, cudeep_b200_stream_t stream) {
+    return guarded([&] {
+        cudeep::kernels::launch_conv2d_forward_kernel<double>(input, weight, bias, output, batch, in_channels,
+                                                              out_channels, in_h, in_w, kernel_h, kernel_w,
+                                                              stride_h, stride_w, pad_h, pad_w,
+                                                              as_stream(stream));
+    });
+}
+
+// ---------------------------------------------------------------- host-buffer entry points
+
+int cudeep_b200_matmul_host_f32(const float* A, const float* B, float* C, int M, int N, int K, int strict) {
+    return guarded([&] {
+        CB200_REQUIRE(A != nullptr && B != nullptr && C != nullptr, "matmul: null host pointer");
+        CB200_REQUIRE(M > 0 && N > 0 && K > 0, "matmul: M, N and K must be positive");
+        const size_t a_bytes = size_t(M) * K * sizeof(float);
+        const size_t b_bytes = size_t(K) * N * sizeof(float);
+        const size_t c_bytes = size_t(M) * N * sizeof(float);
+        PoolBuffer da(a_bytes), db(b_bytes), dc(c_bytes);
+        cudaStream_t s = host_call_stream();
+        cudeep::memcpy_h2d(da.ptr, A, a_bytes, s);
+        cudeep::memcpy_h2d(db.ptr, B, b_bytes, s);
+        if (strict)
+            cudeep::kernels::launch_matmul_kernel_fp32<float>(da.as<float>(), db.as<float>(), dc.as<float>(),
+                                                              M, N, K, s);
+        else
+            cudeep::kernels::launch_matmul_kernel<float>(da.as<float>(), db.as<float>(), dc.as<float>(), M,
+                                                         N, K, s);
+        cudeep::memcpy_d2h(C, dc.ptr, c_bytes, s);
+        CB200_CUDA(cudaStreamSynchronize(s));
+    });
+}
+
+int cudeep_b200_linear_forward_host_f32(const float* x, const float* W, const float* bias, float* y,
+                                        int M, int N, int K, int epilogue) {
+    return guarded([&] {
+        CB200_REQUIRE(x != nullptr && W != nullptr && y != nullptr, "linear: null host pointer");
+        CB200_REQUIRE(M > 0 && N > 0 && K > 0, "linear: M, N and K must be positive");
+        const size_t x_bytes = size_t(M) * K * sizeof(float);
+        const size_t w_bytes = size_t(N) * K * sizeof(float);
+        const size_t y_bytes = size_t(M) * N * sizeof(float);
+        PoolBuffer dx(x_bytes), dw(w_bytes), dy(y_bytes), dbias(size_t(N) * sizeof(float));
+        cudaStream_t s = host_call_stream();
+        cudeep::memcpy_h2d(dx.ptr, x, x_bytes, s);
+        cudeep::memcpy_h2d(dw.ptr, W, w_bytes, s);
+        if (bias != nullptr) cudeep::memcpy_h2d(dbias.ptr, bias, size_t(N) * sizeof(float), s);
+        cudeep::kernels::launch_linear_forward(dx.as<float>(), dw.as<float>(),
+                                               bias != nullptr ? dbias.as<float>() : nullptr,
+                                               dy.as<float>(), M, N, K, as_epilogue(epilogue), s);
+        cudeep::memcpy_d2h(y, dy.ptr, y_bytes, s);
+        CB200_CUDA(cudaStreamSynchronize(s));
+    });
+}
+
+int cudeep_b200_conv2d_forward_host_f32(const float* input, const float* weight, const float* bias,
+                                        float* output, int batch, int in_channels, int out_channels,
+                                        int in_h, int in_w, int kernel_h, int kernel_w, int stride_h,
+                                        int stride_w, int pad_h, int pad_w, int epilogue) {
+    return guarded([&] {
+        CB200_REQUIRE(input != nullptr && weight != nullptr && output != nullptr,
+                      "conv2d: null host pointer");
+        const cudeep_b200::ConvShape shape{batch, in_channels, out_channels, in_h, in_w, kernel_h,
+                                           kernel_w, stride_h, stride_w, pad_h, pad_w};
+        cudeep_b200::check_conv_shape(shape);
+        const size_t x_bytes = size_t(batch) * in_channels * in_h * in_w * sizeof(float);
+        const size_t w_bytes = size_t(out_channels) * in_channels * kernel_h * kernel_w * sizeof(float);
+        const size_t y_bytes = size_t(batch) * out_channels * shape.out_h() * shape.out_w() * sizeof(float);
+        PoolBuffer dx(x_bytes), dw(w_bytes), dy(y_bytes), dbias(size_t(out_channels) * sizeof(float));
+        cudaStream_t s = host_call_stream();
+        cudeep::memcpy_h2d(dx.ptr, input, x_bytes, s);
+        cudeep::memcpy_h2d(dw.ptr, weight, w_bytes, s);
+        if (bias != nullptr) cudeep::memcpy_h2d(dbias.ptr, bias, size_t(out_channels) * sizeof(float), s);
+        cudeep::kernels::launch_conv2d_forward_fused(dx.as<float>(), dw.as<float>(),
+                                                     bias != nullptr ? dbias.as<float>() : nullptr,
+                                                     dy.as<float>(), batch, in_channels, out_channels, in_h,
+                                                     in_w, kernel_h, kernel_w, stride_h, stride_w, pad_h,
+                                                     pad_w, as_epilogue(epilogue), s);
+        cudeep::memcpy_d2h(output, dy.ptr, y_bytes, s);
+        CB200_CUDA(cudaStreamSynchronize(s));
+    });
+}
+
+// ---------------------------------------------------------------- memory pool
+
+int cudeep_b200_pool_alloc(size_t nbytes, void** ptr) {
+    return guarded([&] {
+        CB200_REQUIRE(ptr != nullptr, "pool_alloc: null result pointer");
+        *ptr = cudeep::device_malloc(nbytes);
+    });
+}
+
+int cudeep_b200_pool_free(void* ptr) {
+    return guarded([&] { cudeep::device_free(ptr); });
+}
+
+int cudeep_b200_pool_release_cached(void) {
+    return guarded([&] { cudeep::MemoryPool::instance().release_cached(); });
+}
+
+int cudeep_b200_pool_stats(size_t* allocated_bytes, size_t* cached_bytes) {
+    return guarded([&] {
+        cudeep::MemoryPool& pool = cudeep::MemoryPool::instance();
+        if (allocated_bytes) *allocated_bytes = pool.allocated_bytes();
+        if (cached_bytes) *cached_bytes = pool.cached_bytes();
+    });
+}
+
+}  // extern "C"

@@ -1,0 +1,363 @@
+// Conv2d forward as an implicit GEMM on tcgen05 (stride 1).
+//
+//   out[n, oc, oh, ow] = act( sum_{kh,kw,c} w[oc, c, kh, kw] * x[n, c, oh+kh-ph, ow+kw-pw] + bias[oc] )
+//
+// is computed as D[OC, pixels] = Wp[OC, K] * X[K, pixels] with K ordered
+// (kh, kw, c).  Nothing of size K x pixels is ever written to memory:
+//   * filters are packed once per call to Wp[OC][KH*KW][Cp] (Cp = C rounded up
+//     to 32, zero filled), a K-major A operand;
+//   * the input is re-laid once per call as NHWC (channels padded to a
+//     multiple of 4).  A K block is then "32 channels of one filter tap", and
+//     the B tile of a block of output pixels is a 4-D TMA box
+//     {32 channels, box_w, box_h, 1 image} whose start coordinate carries the
+//     tap offset (ow0+kw-pw, oh0+kh-ph); padding is TMA's out-of-range zero
+//     fill.  The box lands in shared memory as one 128-byte row per pixel,
+//     which is a K-major B operand as is.
+// Accumulator rows are output channels and columns are output pixels, so the
+// epilogue writes NCHW directly with bias and activation fused.
+//
+// The reference takes this shape through Winograd F(4,3) with three global
+// temporaries and 36 GEMMs, or through im2col + GEMM + transpose
+// (src/kernels/conv_kernel.cu:225-335, :735-789).
+#include "conv_igemm.h"
+#include "umma_gemm.cuh"
+
+namespace cudeep_b200 {
+
+namespace {
+
+// ------------------------------------------------------------------ layout transforms
+
+// x[N][C][HW] -> xt[N][HW][Cx], Cx >= C (extra channels written as zero).
+// 32 x 32 tiles through shared memory: reads coalesce along HW, writes along C.
+__global__ void nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, int hw,
+                                    int cx) {
+    __shared__ float tile[32][33];
+    const int n = blockIdx.z;
+    const int p0 = blockIdx.x * 32;
+    const int c0 = blockIdx.y * 32;
+    const float* xn = x + static_cast<long long>(n) * c * hw;
+    float* xtn = xt + static_cast<long long>(n) * hw * cx;
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int ch = c0 + i, p = p0 + threadIdx.x;
+        tile[i][threadIdx.x] = (ch < c && p < hw) ? xn[static_cast<long long>(ch) * hw + p] : 0.0f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int p = p0 + i, ch = c0 + threadIdx.x;
+        if (p < hw && ch < cx) xtn[static_cast<long long>(p) * cx + ch] = tile[threadIdx.x][i];
+    }
+}
+
+// w[OC][C][KH*KW] -> wp[OC][KH*KW][Cp], zero for c >= C.
+__global__ void pack_filters_kernel(const float* __restrict__ w, float* __restrict__ wp, int oc_n,
+                                    int c, int taps, int cp) {
+    const long long total = static_cast<long long>(oc_n) * taps * cp;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int ch = static_cast<int>(i % cp);
+        const long long r = i / cp;
+        const int tap = static_cast<int>(r % taps);
+        const long long oc = r / taps;
+        wp[i] = ch < c ? w[(oc * c + ch) * taps + tap] : 0.0f;
+    }
+}
+
+// ------------------------------------------------------------------ problem policy
+
+template <int CTAS>
+struct ConvProblem {
+    CUtensorMap map_w;     // packed filters: dims {KH*KW*Cp, OC}, box {32, 128}
+    CUtensorMap map_x;     // NHWC input: dims {Cx, W, H, N}, box {32, box_w, box_h / CTAS, 1}
+    float* out;
+    int oc_n, oh_n, ow_n;
+    int box_w, box_h;      // output pixels per tile: box_h rows of box_w
+    int tiles_w, tiles_h;  // tiles per image
+    int c_blocks;          // Cp / 32
+    int k_w;
+    int p_h, p_w;
+    int contig;            // box_w == OW: the tile's pixels are contiguous in the output plane
+    int vec_ok;            // 128-bit stores are aligned for every tile
+
+    struct Tile {
+        int oc0;           // first output channel of this CTA
+        int n, oh0, ow0;   // image and first output pixel of the tile
+        int hb0;           // first output row whose pixels this CTA stages as B
+    };
+
+    __device__ __forceinline__ void prefetch_maps() const {
+        ptx::prefetch_tensormap(&map_w);
+        ptx::prefetch_tensormap(&map_x);
+    }
+    __device__ __forceinline__ Tile decode(int tm, int tn, uint32_t cta_rank) const {
+        Tile t;
+        t.oc0 = (tm * CTAS + int(cta_rank)) * UMMA_BM;
+        const int per_image = tiles_h * tiles_w;
+        t.n = tn / per_image;
+        const int r = tn - t.n * per_image;
+        const int th = r / tiles_w;
+        t.oh0 = th * box_h;
+        t.ow0 = (r - th * tiles_w) * box_w;
+        t.hb0 = t.oh0 + int(cta_rank) * (box_h / CTAS);
+        return t;
+    }
+    template <int C>
+    __device__ __forceinline__ void load(const Tile& t, int kb, uint32_t a_smem, uint32_t b_smem,
+                                         uint32_t bar) const {
+        const int tap = kb / c_blocks;
+        const int c0 = (kb - tap * c_blocks) * UMMA_BK;
+        const int kh = tap / k_w;
+        const int kw = tap - kh * k_w;
+        if constexpr (C == 1) {
+            ptx::tma_load_2d(a_smem, &map_w, bar, kb * UMMA_BK, t.oc0);
+            ptx::tma_load_4d(b_smem, &map_x, bar, c0, t.ow0 + kw - p_w, t.hb0 + kh - p_h, t.n);
+        } else {
+            ptx::tma_load_2d_pair(a_smem, &map_w, bar, kb * UMMA_BK, t.oc0);
+            ptx::tma_load_4d_pair(b_smem, &map_x, bar, c0, t.ow0 + kw - p_w, t.hb0 + kh - p_h, t.n);
+        }
+    }
+    __device__ __forceinline__ void store(const Tile& t, int row_in_cta, int c0, float (&v)[32],
+                                          const UmmaEpilogueArgs& epi) const {
+        const int oc = t.oc0 + row_in_cta;
+        if (oc >= oc_n) return;
+        if (epi.bias != nullptr) {
+            const float b = __ldg(epi.bias + oc);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += b;
+        }
+        apply_activation(v, epi.act);
+        float* plane = out + (static_cast<long long>(t.n) * oc_n + oc) * oh_n * ow_n;
+        if (contig) {
+            const int rows = min(box_h, oh_n - t.oh0);
+            const int limit = rows * ow_n;                 // valid accumulator columns
+            float* dst = plane + static_cast<long long>(t.oh0) * ow_n + c0;
+            if (vec_ok && c0 + 32 <= limit) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (c0 + j < limit) dst[j] = v[j];
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int col = c0 + j;
+                const int r = col / box_w;
+                const int q = col - r * box_w;
+                const int oh = t.oh0 + r, ow = t.ow0 + q;
+                if (oh < oh_n && ow < ow_n) plane[static_cast<long long>(oh) * ow_n + ow] = v[j];
+            }
+        }
+    }
+};
+
+struct TilePlan {
+    int box_w = 0, box_h = 0;
+};
+
+// Output-pixel box of one tile: box_h rows of box_w pixels, box_w * box_h a
+// multiple of 32 and at most 256, box_h a multiple of the CTAs that split it;
+// picked to waste the fewest accumulator columns, then to be as large as possible.
+TilePlan plan_tile(int oh, int ow, int ctas) {
+    TilePlan best;
+    double best_eff = -1.0;
+    const int w_lo = ow < 256 ? ow : 256;
+    const int w_hi = (w_lo + 31 < 256) ? w_lo + 31 : 256;
+    for (int bw = w_lo; bw <= w_hi; ++bw) {
+        for (int bh = ctas; bh * bw <= 256; bh += ctas) {
+            if ((bh * bw) % 32 != 0) continue;
+            if (bh > 256 || bw > 256) continue;
+            const int tiles_w = (ow + bw - 1) / bw;
+            const int tiles_h = (oh + bh - 1) / bh;
+            const double eff = double(oh) * ow / (double(tiles_w) * tiles_h * bw * bh);
+            const double score = eff + 1e-4 * (bw * bh) / 256.0;
+            if (score > best_eff) {
+                best_eff = score;
+                best.box_w = bw;
+                best.box_h = bh;
+            }
+        }
+    }
+    return best;
+}
+
+template <int CTAS>
+void launch_conv(const float* xt, const float* wp, const float* bias, float* out, const ConvShape& s,
+                 int cx, int cp, const TilePlan& plan, int act, cudaStream_t stream) {
+    using Cfg = UmmaConfig<CTAS, 256, false>;
+    using Prob = ConvProblem<CTAS>;
+    const DeviceInfo& dev = device_info();
+    const int oh = s.out_h(), ow = s.out_w();
+    const int taps = s.k_h * s.k_w;
+
+    Prob prob;
+    {
+        const uint64_t dims[2] = {uint64_t(taps) * cp, uint64_t(s.out_c)};
+        const uint64_t strides[1] = {uint64_t(taps) * cp * 4};
+        const uint32_t box[2] = {UMMA_BK, UMMA_BM};
+        encode_tensor_map(&prob.map_w, wp, 2, dims, strides, box, TmaSwizzle::B128);
+    }
+    {
+        const uint64_t dims[4] = {uint64_t(cx), uint64_t(s.in_w), uint64_t(s.in_h), uint64_t(s.batch)};
+        const uint64_t strides[3] = {uint64_t(cx) * 4, uint64_t(s.in_w) * cx * 4,
+                                     uint64_t(s.in_h) * s.in_w * cx * 4};
+        const uint32_t box[4] = {UMMA_BK, uint32_t(plan.box_w), uint32_t(plan.box_h / CTAS), 1};
+        encode_tensor_map(&prob.map_x, xt, 4, dims, strides, box, TmaSwizzle::B128);
+    }
+    prob.out = out;
+    prob.oc_n = s.out_c;
+    prob.oh_n = oh;
+    prob.ow_n = ow;
+    prob.box_w = plan.box_w;
+    prob.box_h = plan.box_h;
+    prob.tiles_w = (ow + plan.box_w - 1) / plan.box_w;
+    prob.tiles_h = (oh + plan.box_h - 1) / plan.box_h;
+    prob.c_blocks = cp / UMMA_BK;
+    prob.k_w = s.k_w;
+    prob.p_h = s.p_h;
+    prob.p_w = s.p_w;
+    prob.contig = (plan.box_w == ow) ? 1 : 0;
+    prob.vec_ok = (prob.contig && ((plan.box_h * ow) % 4 == 0) && ((oh * ow) % 4 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(out) & 15u) == 0)) ? 1 : 0;
+
+    UmmaSchedule sched;
+    sched.tiles_m = (s.out_c + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS);
+    sched.tiles_n = s.batch * prob.tiles_h * prob.tiles_w;
+    sched.k_blocks = taps * prob.c_blocks;
+    // Consecutive tiles walk the output-channel tiles of one pixel block, so
+    // concurrent CTAs read the same input pixels from L2.
+    sched.raster_group = sched.tiles_m;
+    sched.status = dev.status_word;
+    sched.wait_limit_ns = 2000000000ull;
+    sched.b_lbo = 0;
+    sched.b_sbo = 0;
+    sched.umma_n = plan.box_w * plan.box_h;
+    sched.tx_bytes = (Cfg::A_BYTES + uint32_t(sched.umma_n / CTAS) * UMMA_BK * 4) * CTAS;
+
+    const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;
+    CB200_REQUIRE(num_tiles < (1LL << 30), "conv2d: too many tiles");
+    long long groups = dev.num_sms / CTAS;
+    if (groups < 1) groups = 1;
+    if (groups > num_tiles) groups = num_tiles;
+
+    auto kernel = umma_tf32_kernel<CTAS, 256, false, Prob>;
+    ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), Cfg::SMEM_BYTES);
+
+    UmmaEpilogueArgs epi{bias, 1, act};
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(groups * CTAS), 1, 1);
+    cfg.blockDim = dim3(UMMA_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, prob, sched, epi));
+}
+
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+}  // namespace
+
+bool conv2d_igemm_supported(const ConvShape& s) {
+    if (device_info().cc_major != 10) return false;
+    if (s.s_h != 1 || s.s_w != 1) return false;
+    if (s.p_h >= s.k_h || s.p_w >= s.k_w) return false;     // keeps every box start within TMA's signed range
+    const int oh = s.out_h(), ow = s.out_w();
+    if (oh < 1 || ow < 1) return false;
+    // Worth a 128-row tensor-core tile only with enough channels and pixels.
+    if (s.out_c < 32 || static_cast<long long>(s.in_c) * s.k_h * s.k_w < 32) return false;
+    if (static_cast<long long>(s.batch) * oh * ow < 64) return false;
+    return true;
+}
+
+size_t conv2d_igemm_scratch_bytes(const ConvShape& s, size_t* nhwc_bytes, size_t* filter_bytes) {
+    const int cx = round_up(s.in_c, 4);
+    const int cp = round_up(s.in_c, UMMA_BK);
+    const size_t a = static_cast<size_t>(s.batch) * s.in_h * s.in_w * cx * sizeof(float);
+    const size_t b = static_cast<size_t>(s.out_c) * s.k_h * s.k_w * cp * sizeof(float);
+    // Both regions start on 1 KiB boundaries.
+    const size_t a_pad = (a + 1023) / 1024 * 1024;
+    const size_t b_pad = (b + 1023) / 1024 * 1024;
+    if (nhwc_bytes) *nhwc_bytes = a_pad;
+    if (filter_bytes) *filter_bytes = b_pad;
+    return a_pad + b_pad;
+}
+
+void conv2d_igemm_with_scratch(const float* input, const float* weight, const float* bias,
+                               float* output, const ConvShape& s, int act, void* scratch,
+                               int force_ctas, cudaStream_t stream) {
+    check_conv_shape(s);
+    CB200_REQUIRE(conv2d_igemm_supported(s), "conv2d: shape not supported by the tensor-core path");
+    CB200_REQUIRE(scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0,
+                  "conv2d: scratch must be 256-byte aligned");
+    const int cx = round_up(s.in_c, 4);
+    const int cp = round_up(s.in_c, UMMA_BK);
+    const int hw = s.in_h * s.in_w;
+    const int taps = s.k_h * s.k_w;
+    size_t nhwc_bytes = 0;
+    conv2d_igemm_scratch_bytes(s, &nhwc_bytes, nullptr);
+    float* xt = static_cast<float*>(scratch);
+    float* wp = reinterpret_cast<float*>(static_cast<char*>(scratch) + nhwc_bytes);
+
+    {
+        dim3 grid((hw + 31) / 32, (cx + 31) / 32, s.batch);
+        dim3 block(32, 8);
+        CB200_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "conv2d: too many channels or images");
+        nchw_to_nhwc_kernel<<<grid, block, 0, stream>>>(input, xt, s.in_c, hw, cx);
+        CB200_CHECK_LAUNCH();
+    }
+    {
+        const long long total = static_cast<long long>(s.out_c) * taps * cp;
+        long long blocks = (total + 255) / 256;
+        if (blocks > 4096) blocks = 4096;
+        pack_filters_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(weight, wp, s.out_c,
+                                                                               s.in_c, taps, cp);
+        CB200_CHECK_LAUNCH();
+    }
+
+    const int oh = s.out_h(), ow = s.out_w();
+    int ctas = force_ctas;
+    if (ctas == 0) ctas = (s.out_c > UMMA_BM) ? 2 : 1;
+    TilePlan plan = plan_tile(oh, ow, ctas);
+    if (plan.box_w == 0 && ctas == 2) {
+        ctas = 1;
+        plan = plan_tile(oh, ow, 1);
+    }
+    CB200_REQUIRE(plan.box_w > 0, "conv2d: no tile shape fits this output size");
+    if (ctas == 2) launch_conv<2>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+    else launch_conv<1>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+}
+
+void conv2d_igemm(const float* input, const float* weight, const float* bias, float* output,
+                  const ConvShape& s, int act, cudaStream_t stream) {
+    const size_t bytes = conv2d_igemm_scratch_bytes(s, nullptr, nullptr);
+    // Stream-ordered scratch, as the reference does for its temporaries
+    // (conv_kernel.cu:282,314,748-754): safe when calls on several streams overlap.
+    static thread_local int pool_ready_device = -1;
+    const int dev = device_info().device;
+    if (pool_ready_device != dev) {
+        cudaMemPool_t pool;
+        CB200_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+        uint64_t keep = UINT64_MAX;   // keep freed scratch cached instead of returning it at every sync
+        CB200_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+        pool_ready_device = dev;
+    }
+    void* scratch = nullptr;
+    CB200_CUDA(cudaMallocAsync(&scratch, bytes, stream));
+    try {
+        conv2d_igemm_with_scratch(input, weight, bias, output, s, act, scratch, 0, stream);
+    } catch (...) {
+        cudaFreeAsync(scratch, stream);
+        throw;
+    }
+    CB200_CUDA(cudaFreeAsync(scratch, stream));
+}
+
+}  // namespace cudeep_b200

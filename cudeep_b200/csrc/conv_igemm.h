@@ -1,0 +1,27 @@
+// Host entry of the implicit-GEMM convolution (see conv_igemm.cu).
+#pragma once
+
+#include "conv_direct.h"
+
+namespace cudeep_b200 {
+
+// True when the tensor-core path takes this shape: sm_100 device, stride 1,
+// padding smaller than the filter, at least 32 output channels, C*KH*KW >= 32
+// and at least 64 output pixels.
+bool conv2d_igemm_supported(const ConvShape& s);
+
+// Bytes of scratch one call needs: the NHWC copy of the input followed by the
+// packed filters.  The two optional outputs receive the size of each part.
+size_t conv2d_igemm_scratch_bytes(const ConvShape& s, size_t* nhwc_bytes, size_t* filter_bytes);
+
+// Convolution with caller-provided scratch (256-byte aligned, at least
+// conv2d_igemm_scratch_bytes).  force_ctas: 0 = choose, 1 or 2 = CTAs per MMA.
+void conv2d_igemm_with_scratch(const float* input, const float* weight, const float* bias,
+                               float* output, const ConvShape& s, int act, void* scratch,
+                               int force_ctas, cudaStream_t stream);
+
+// Convolution with stream-ordered scratch (cudaMallocAsync / cudaFreeAsync on `stream`).
+void conv2d_igemm(const float* input, const float* weight, const float* bias, float* output,
+                  const ConvShape& s, int act, cudaStream_t stream);
+
+}  // namespace cudeep_b200

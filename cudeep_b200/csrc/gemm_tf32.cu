@@ -1,0 +1,228 @@
+// Dense TF32 GEMM on tcgen05: C[M,N] = act(A[M,K] * B + bias).
+//
+// Two B layouts share one kernel:
+//   * B[K,N] row-major (the layout of Tensor.matmul, reference
+//     src/tensor.cu:384-420 / matmul_kernel.cu:1785-1841): an MN-major UMMA
+//     operand, staged as 32-column x 32-row TMA boxes in the 128-byte swizzle
+//     with 32-byte atoms (the one layout tcgen05 takes for MN-major 32-bit data).
+//   * W[N,K] row-major (nn.Linear's weight as stored, reference
+//     python/cuDeep/nn.py:110-115): a K-major operand, so Linear needs no
+//     transposed copy of W.
+// Operands are read as raw FP32 words; the tensor core ignores the low 13
+// mantissa bits, the same truncation the reference's mma.sync path applies
+// (matmul_kernel.cu:186-201).
+#include "gemm_tf32.h"
+#include "umma_gemm.cuh"
+
+namespace cudeep_b200 {
+
+namespace {
+
+template <int CTAS, int BN, bool B_MN_MAJOR>
+struct GemmProblem {
+    CUtensorMap map_a;     // dims {K, M}, box {32, 128}
+    CUtensorMap map_b;     // K-major: dims {K, N}, box {32, BN/CTAS};  MN-major: dims {N, K}, box {32, 32}
+    float* c;
+    long long ldc;
+    int m, n;
+    int vec_ok;            // rows of C are 16-byte aligned
+
+    struct Tile {
+        int m0;            // first C row of this CTA
+        int n0;            // first C column of the tile
+        int nb0;           // first B row (K-major) / column (MN-major) this CTA stages
+    };
+
+    __device__ __forceinline__ void prefetch_maps() const {
+        ptx::prefetch_tensormap(&map_a);
+        ptx::prefetch_tensormap(&map_b);
+    }
+    __device__ __forceinline__ Tile decode(int tm, int tn, uint32_t cta_rank) const {
+        Tile t;
+        t.m0 = (tm * CTAS + int(cta_rank)) * UMMA_BM;
+        t.n0 = tn * BN;
+        t.nb0 = t.n0 + int(cta_rank) * (BN / CTAS);
+        return t;
+    }
+    template <int C>
+    __device__ __forceinline__ void load(const Tile& t, int kb, uint32_t a_smem, uint32_t b_smem,
+                                         uint32_t bar) const {
+        const int k0 = kb * UMMA_BK;
+        if constexpr (C == 1) {
+            ptx::tma_load_2d(a_smem, &map_a, bar, k0, t.m0);
+            if constexpr (B_MN_MAJOR) {
+#pragma unroll
+                for (int j = 0; j < BN / CTAS / 32; ++j)
+                    ptx::tma_load_2d(b_smem + j * 4096, &map_b, bar, t.nb0 + j * 32, k0);
+            } else {
+                ptx::tma_load_2d(b_smem, &map_b, bar, k0, t.nb0);
+            }
+        } else {
+            ptx::tma_load_2d_pair(a_smem, &map_a, bar, k0, t.m0);
+            if constexpr (B_MN_MAJOR) {
+#pragma unroll
+                for (int j = 0; j < BN / CTAS / 32; ++j)
+                    ptx::tma_load_2d_pair(b_smem + j * 4096, &map_b, bar, t.nb0 + j * 32, k0);
+            } else {
+                ptx::tma_load_2d_pair(b_smem, &map_b, bar, k0, t.nb0);
+            }
+        }
+    }
+    __device__ __forceinline__ void store(const Tile& t, int row_in_cta, int c0, float (&v)[32],
+                                          const UmmaEpilogueArgs& epi) const {
+        const int row = t.m0 + row_in_cta;
+        const int col = t.n0 + c0;
+        if (row >= m || col >= n) return;
+        if (epi.bias != nullptr) {
+            if (epi.bias_per_row) {
+                const float b = __ldg(epi.bias + row);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += b;
+            } else if (col + 32 <= n) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += __ldg(epi.bias + col + j);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col + j < n) v[j] += __ldg(epi.bias + col + j);
+            }
+        }
+        apply_activation(v, epi.act);
+        float* dst = c + static_cast<long long>(row) * ldc + col;
+        if (vec_ok && col + 32 <= n) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col + j < n) dst[j] = v[j];
+        }
+    }
+};
+
+template <int CTAS, int BN, bool B_MN_MAJOR>
+void launch_variant(const float* a, const float* b, float* c, int m, int n, int k,
+                    const UmmaEpilogueArgs& epi, const GemmTuning& tune, cudaStream_t stream) {
+    using Cfg = UmmaConfig<CTAS, BN, B_MN_MAJOR>;
+    using Prob = GemmProblem<CTAS, BN, B_MN_MAJOR>;
+    const DeviceInfo& dev = device_info();
+
+    Prob prob;
+    {
+        const uint64_t dims[2] = {uint64_t(k), uint64_t(m)};
+        const uint64_t strides[1] = {uint64_t(k) * 4};
+        const uint32_t box[2] = {UMMA_BK, UMMA_BM};
+        encode_tensor_map(&prob.map_a, a, 2, dims, strides, box, TmaSwizzle::B128);
+    }
+    if (B_MN_MAJOR) {
+        const uint64_t dims[2] = {uint64_t(n), uint64_t(k)};
+        const uint64_t strides[1] = {uint64_t(n) * 4};
+        const uint32_t box[2] = {32, UMMA_BK};
+        encode_tensor_map(&prob.map_b, b, 2, dims, strides, box, TmaSwizzle::B128Atom32);
+    } else {
+        const uint64_t dims[2] = {uint64_t(k), uint64_t(n)};
+        const uint64_t strides[1] = {uint64_t(k) * 4};
+        const uint32_t box[2] = {UMMA_BK, uint32_t(Cfg::BN_CTA)};
+        encode_tensor_map(&prob.map_b, b, 2, dims, strides, box, TmaSwizzle::B128);
+    }
+    prob.c = c;
+    prob.ldc = n;
+    prob.m = m;
+    prob.n = n;
+    prob.vec_ok = ((n % 4) == 0) && ((reinterpret_cast<uintptr_t>(c) & 15u) == 0);
+
+    UmmaSchedule sched;
+    sched.tiles_m = (m + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS);
+    sched.tiles_n = (n + BN - 1) / BN;
+    sched.k_blocks = (k + UMMA_BK - 1) / UMMA_BK;
+    sched.raster_group = tune.raster_group > 0 ? tune.raster_group : (CTAS == 2 ? 4 : 8);
+    sched.status = dev.status_word;
+    sched.wait_limit_ns = 2000000000ull;
+    sched.b_lbo = tune.b_lbo;
+    sched.b_sbo = tune.b_sbo;
+    sched.umma_n = BN;
+    sched.tx_bytes = Cfg::TX_BYTES;
+
+    const int num_tiles = sched.tiles_m * sched.tiles_n;
+    int max_ctas = tune.max_ctas > 0 ? tune.max_ctas : dev.num_sms;
+    int groups = max_ctas / CTAS;
+    if (groups < 1) groups = 1;
+    if (groups > num_tiles) groups = num_tiles;
+
+    auto kernel = umma_tf32_kernel<CTAS, BN, B_MN_MAJOR, Prob>;
+    ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), Cfg::SMEM_BYTES);
+
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(groups * CTAS), 1, 1);
+    cfg.blockDim = dim3(UMMA_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, prob, sched, epi));
+}
+
+template <bool B_MN_MAJOR>
+void dispatch(const float* a, const float* b, float* c, int m, int n, int k,
+              const UmmaEpilogueArgs& epi, const GemmTuning& tune, cudaStream_t stream) {
+    const DeviceInfo& dev = device_info();
+    int ctas = tune.ctas;
+    int bn = tune.bn;
+    if (ctas == 0 || bn == 0) {
+        // Largest tile that still gives every SM work; small problems take
+        // narrower tiles so more CTAs run.
+        const long long sms = dev.num_sms;
+        auto tiles = [&](int tile_m, int tile_n) {
+            return static_cast<long long>((m + tile_m - 1) / tile_m) * ((n + tile_n - 1) / tile_n);
+        };
+        int pick_ctas = 1, pick_bn = 64;
+        if (tiles(256, 256) * 2 >= sms) { pick_ctas = 2; pick_bn = 256; }
+        else if (tiles(128, 256) >= sms) { pick_ctas = 1; pick_bn = 256; }
+        else if (tiles(128, 128) >= sms) { pick_ctas = 1; pick_bn = 128; }
+        if (ctas == 0) ctas = pick_ctas;
+        if (bn == 0) bn = pick_bn;
+    }
+#define CB200_CASE(C, N)                                                                  \
+    if (ctas == C && bn == N) {                                                           \
+        launch_variant<C, N, B_MN_MAJOR>(a, b, c, m, n, k, epi, tune, stream);            \
+        return;                                                                           \
+    }
+    CB200_CASE(1, 256)
+    CB200_CASE(1, 128)
+    CB200_CASE(1, 64)
+    CB200_CASE(2, 256)
+    CB200_CASE(2, 128)
+#undef CB200_CASE
+    CB200_REQUIRE(false, "unsupported TF32 GEMM tile configuration");
+}
+
+}  // namespace
+
+bool gemm_tf32_supported(const float* a, const float* b, const float* c, int m, int n, int k,
+                         bool b_is_nk) {
+    if (m < 1 || n < 1 || k < 1) return false;
+    if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(b) & 15u)) return false;
+    (void)c;
+    if (k % 4 != 0) return false;               // A rows (and W rows) must be 16-byte multiples
+    if (!b_is_nk && n % 4 != 0) return false;   // B[K,N] rows likewise
+    return device_info().cc_major == 10;
+}
+
+void gemm_tf32(const float* a, const float* b, bool b_is_nk, float* c, int m, int n, int k,
+               const float* bias, bool bias_per_row, int act, const GemmTuning& tune,
+               cudaStream_t stream) {
+    CB200_REQUIRE(gemm_tf32_supported(a, b, c, m, n, k, b_is_nk),
+                  "TF32 tensor-core GEMM needs an sm_100 device, 16-byte aligned operands and "
+                  "row lengths that are multiples of 4");
+    UmmaEpilogueArgs epi{bias, bias_per_row ? 1 : 0, act};
+    if (b_is_nk) dispatch<false>(a, b, c, m, n, k, epi, tune, stream);
+    else dispatch<true>(a, b, c, m, n, k, epi, tune, stream);
+}
+
+}  // namespace cudeep_b200

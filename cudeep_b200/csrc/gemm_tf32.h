@@ -1,0 +1,31 @@
+// Host entry of the tcgen05 TF32 GEMM (see gemm_tf32.cu).
+#pragma once
+
+#include "runtime.h"
+
+namespace cudeep_b200 {
+
+// Optional overrides; zero means "let the launcher choose".
+struct GemmTuning {
+    int ctas = 0;            // 1 or 2 CTAs per MMA
+    int bn = 0;              // tile columns: 64, 128 or 256
+    int raster_group = 0;    // tile rows walked together
+    int max_ctas = 0;        // cap on resident CTAs (default: one per SM)
+    uint32_t b_lbo = 0;      // B shared-memory descriptor overrides (bring-up aid)
+    uint32_t b_sbo = 0;
+};
+
+// True when the tensor-core path can take this problem (sm_100 device,
+// 16-byte aligned bases, K % 4 == 0, and N % 4 == 0 for B[K,N]).
+bool gemm_tf32_supported(const float* a, const float* b, const float* c, int m, int n, int k,
+                         bool b_is_nk);
+
+// C[M,N] = act(A[M,K] * B + bias), TF32 multiply, FP32 accumulate.
+//   b_is_nk == false: B is [K,N] row-major;  true: B is [N,K] row-major (y = x W^T).
+//   bias: nullptr, or N values (bias_per_row == false), or M values (bias_per_row == true).
+// Asynchronous on `stream`.  Throws std::runtime_error on bad arguments or launch failure.
+void gemm_tf32(const float* a, const float* b, bool b_is_nk, float* c, int m, int n, int k,
+               const float* bias, bool bias_per_row, int act, const GemmTuning& tune,
+               cudaStream_t stream);
+
+}  // namespace cudeep_b200

@@ -1,0 +1,134 @@
+#include "runtime.h"
+
+#include <mutex>
+#include <unordered_set>
+#include <vector>
+#include <memory>
+
+namespace cudeep_b200 {
+
+// One status word per device image of this library.  Kernels write a non-zero
+// code here when a bounded wait gives up; the host reads it on request.
+__device__ uint32_t g_status_word[4];
+
+static const char* base_name(const char* path) {
+    const char* base = path;
+    for (const char* p = path; *p; ++p)
+        if (*p == '/') base = p + 1;
+    return base;
+}
+
+void throw_cuda(cudaError_t err, const char* what, const char* file, int line) {
+    throw std::runtime_error(std::string("CUDA error: ") + cudaGetErrorString(err) + " in " + what +
+                             " (" + base_name(file) + ":" + std::to_string(line) + ")");
+}
+void throw_msg(const std::string& msg, const char* file, int line) {
+    throw std::runtime_error("cudeep_b200: " + msg + " (" + base_name(file) + ":" +
+                             std::to_string(line) + ")");
+}
+
+namespace {
+
+struct DeviceState {
+    DeviceInfo info;
+    std::mutex mu;
+    std::unordered_set<const void*> smem_done;
+};
+
+std::mutex g_mu;
+std::vector<std::unique_ptr<DeviceState>> g_devices;
+
+DeviceState& state() {
+    int dev = 0;
+    CB200_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (dev >= static_cast<int>(g_devices.size())) g_devices.resize(dev + 1);
+    if (!g_devices[dev]) {
+        auto st = std::make_unique<DeviceState>();
+        cudaDeviceProp prop{};
+        CB200_CUDA(cudaGetDeviceProperties(&prop, dev));
+        st->info.device = dev;
+        st->info.num_sms = prop.multiProcessorCount;
+        st->info.cc_major = prop.major;
+        st->info.cc_minor = prop.minor;
+        st->info.smem_optin = prop.sharedMemPerBlockOptin;
+        void* p = nullptr;
+        CB200_CUDA(cudaGetSymbolAddress(&p, g_status_word));
+        st->info.status_word = static_cast<uint32_t*>(p);
+        CB200_CUDA(cudaMemset(p, 0, sizeof(uint32_t) * 4));
+        g_devices[dev] = std::move(st);
+    }
+    return *g_devices[dev];
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q{};
+        CB200_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        CB200_REQUIRE(p != nullptr && q == cudaDriverEntryPointSuccess,
+                      "driver does not provide cuTensorMapEncodeTiled");
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+}  // namespace
+
+const DeviceInfo& device_info() { return state().info; }
+
+void ensure_dynamic_smem(const void* func, size_t bytes) {
+    DeviceState& st = state();
+    std::lock_guard<std::mutex> lock(st.mu);
+    if (st.smem_done.count(func)) return;
+    CB200_REQUIRE(bytes <= st.info.smem_optin, "kernel needs more shared memory than the device offers");
+    CB200_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(bytes)));
+    st.smem_done.insert(func);
+}
+
+uint32_t read_device_status(bool clear) {
+    const DeviceInfo& info = device_info();
+    CB200_CUDA(cudaDeviceSynchronize());
+    uint32_t v = 0;
+    CB200_CUDA(cudaMemcpy(&v, info.status_word, sizeof(v), cudaMemcpyDeviceToHost));
+    if (clear && v != 0) CB200_CUDA(cudaMemset(info.status_word, 0, sizeof(uint32_t)));
+    return v;
+}
+
+void encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint64_t* dims,
+                       const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle) {
+    CB200_REQUIRE(rank >= 1 && rank <= 4, "tensor map rank must be 1..4");
+    CB200_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15u) == 0, "TMA base address must be 16-byte aligned");
+    cuuint64_t gdim[4];
+    cuuint64_t gstride[3];
+    cuuint32_t gbox[4];
+    cuuint32_t estride[4];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        gbox[i] = box[i];
+        estride[i] = 1;
+        CB200_REQUIRE(box[i] >= 1 && box[i] <= 256, "TMA box extent must be 1..256");
+    }
+    for (int i = 0; i + 1 < rank; ++i) {
+        gstride[i] = strides_bytes[i];
+        CB200_REQUIRE((strides_bytes[i] & 15u) == 0, "TMA strides must be multiples of 16 bytes");
+    }
+    if (swizzle != TmaSwizzle::None)
+        CB200_REQUIRE(box[0] * 4 == 128, "128-byte swizzle needs a 128-byte inner box");
+    const CUtensorMapSwizzle sw = swizzle == TmaSwizzle::B128         ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : swizzle == TmaSwizzle::B128Atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                                                      : CU_TENSOR_MAP_SWIZZLE_NONE;
+    CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, static_cast<cuuint32_t>(rank),
+                             const_cast<float*>(base), gdim, gstride, gbox, estride,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CB200_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+}
+
+}  // namespace cudeep_b200

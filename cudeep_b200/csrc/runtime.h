@@ -1,0 +1,63 @@
+// Host-side plumbing shared by all launchers: error convention, per-device
+// state (SM count, status word, opt-in shared memory), TMA descriptor encoding.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda.h>
+#include <stdint.h>
+#include <stdexcept>
+#include <string>
+
+namespace cudeep_b200 {
+
+// Errors are C++ exceptions (std::runtime_error), the convention of the
+// reference's CUDEEP_CHECK_CUDA / CUDEEP_ASSERT (include/cudeep/error.cuh:11-40).
+// The C ABI converts them to status codes.
+[[noreturn]] void throw_cuda(cudaError_t err, const char* what, const char* file, int line);
+[[noreturn]] void throw_msg(const std::string& msg, const char* file, int line);
+
+#define CB200_CUDA(call)                                                        \
+    do {                                                                        \
+        cudaError_t cb200_err_ = (call);                                        \
+        if (cb200_err_ != cudaSuccess)                                          \
+            ::cudeep_b200::throw_cuda(cb200_err_, #call, __FILE__, __LINE__);   \
+    } while (0)
+
+#define CB200_REQUIRE(cond, msg)                                                \
+    do {                                                                        \
+        if (!(cond)) ::cudeep_b200::throw_msg((msg), __FILE__, __LINE__);       \
+    } while (0)
+
+#define CB200_CHECK_LAUNCH() CB200_CUDA(cudaGetLastError())
+
+struct DeviceInfo {
+    int device = -1;
+    int num_sms = 0;
+    int cc_major = 0, cc_minor = 0;
+    size_t smem_optin = 0;
+    uint32_t* status_word = nullptr;   // device address of this device's status word
+};
+
+// State of the current device, created on first use (thread-safe).
+const DeviceInfo& device_info();
+
+// Raise the dynamic shared-memory limit of `func` on the current device once.
+void ensure_dynamic_smem(const void* func, size_t bytes);
+
+// Read-and-clear the current device's kernel status word (synchronises the device).
+uint32_t read_device_status(bool clear);
+
+enum class TmaSwizzle {
+    None,
+    B128,          // 16-byte chunks XOR-ed within each 128-byte row, period 8 rows
+    B128Atom32,    // 32-byte chunks XOR-ed within each 128-byte row, period 4 rows
+};
+
+// 64-byte aligned TMA descriptor for a row-major fp32 tensor of rank <= 4.
+// dims[0] is the contiguous dimension; strides_bytes[i] is the stride of
+// dims[i+1].  Out-of-range elements read as zero.  With a swizzle the inner
+// box must span exactly 128 bytes.
+void encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint64_t* dims,
+                       const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle);
+
+}  // namespace cudeep_b200

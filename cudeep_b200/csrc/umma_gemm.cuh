@@ -1,0 +1,282 @@
+// Persistent, warp-specialised TF32 GEMM mainloop for sm_100a.
+//
+//   warp 0      TMA producer   (one lane issues cp.async.bulk.tensor loads)
+//   warp 1      MMA issuer     (one lane issues tcgen05.mma; the warp owns TMEM)
+//   warps 2..5  epilogue       (tcgen05.ld -> bias/activation -> 128-bit stores)
+//
+// A CTA owns 128 accumulator rows.  With CTAS == 2 two CTAs of a cluster form a
+// pair: the tile is 256 x BN, each CTA stages its own 128 rows of A and its own
+// half of B, and the pair's leader (cluster rank 0) issues cta_group::2 MMAs
+// that read both CTAs' shared memory.  No load is multicast.
+//
+// The accumulator lives in TMEM and is double-buffered (2 x BN columns) so the
+// epilogue of tile i overlaps the mainloop of tile i+1.
+//
+// The kernel is shared by the dense GEMM / Linear forward and the
+// implicit-GEMM convolution through a `Problem` policy that supplies the tile
+// decode, the TMA loads of one K block and the output store.
+#pragma once
+
+#include "sm100_ptx.cuh"
+#include "epilogue_math.cuh"
+
+namespace cudeep_b200 {
+
+// Codes written to the device status word when a bounded wait runs out.
+enum UmmaStatus : uint32_t {
+    UMMA_OK = 0,
+    UMMA_TIMEOUT_PRODUCER = 1,   // producer waited for a free stage
+    UMMA_TIMEOUT_MMA_FULL = 2,   // MMA issuer waited for operand data
+    UMMA_TIMEOUT_MMA_ACC = 3,    // MMA issuer waited for a free accumulator
+    UMMA_TIMEOUT_EPILOGUE = 4,   // epilogue waited for a finished accumulator
+};
+
+constexpr int UMMA_BM = 128;        // accumulator rows per CTA
+constexpr int UMMA_BK = 32;         // fp32 elements per K block = one 128-byte swizzle row
+constexpr int UMMA_K = 8;           // K of one tcgen05.mma kind::tf32
+constexpr int UMMA_THREADS = 192;
+
+struct UmmaEpilogueArgs {
+    const float* bias;     // nullptr = none
+    int bias_per_row;      // 0: bias[column], 1: bias[row]
+    int act;               // cudeep_b200 epilogue code (0 none, 1 relu, 2 gelu, 3 silu, 4 sigmoid)
+};
+
+struct UmmaSchedule {
+    int tiles_m;           // tile rows  (tile = 128*CTAS rows)
+    int tiles_n;           // tile columns
+    int k_blocks;          // ceil(K / 32)
+    int raster_group;      // tile rows walked together so concurrent CTAs share B columns in L2
+    uint32_t* status;      // device status word
+    unsigned long long wait_limit_ns;
+    uint32_t b_lbo, b_sbo; // non-zero: override the B descriptor offsets (bring-up aid)
+    int umma_n;            // N of one MMA (<= BN, multiple of 32): accumulator columns in use
+    uint32_t tx_bytes;     // bytes all CTAs of the group deliver per stage
+};
+
+template <int CTAS, int BN, bool B_MN_MAJOR>
+struct UmmaConfig {
+    static constexpr int BN_CTA = BN / CTAS;                       // B rows staged by one CTA
+    static constexpr uint32_t A_BYTES = UMMA_BM * UMMA_BK * 4;
+    static constexpr uint32_t B_BYTES = BN_CTA * UMMA_BK * 4;
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr uint32_t TX_BYTES = STAGE_BYTES * CTAS;       // counted on the leader's barrier
+    // 227 KB of shared memory per CTA, minus alignment slack and the barriers.
+    static constexpr uint32_t SMEM_BUDGET = 232448 - 1024 - 512;
+    static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES > 8 ? 8 : SMEM_BUDGET / STAGE_BYTES;
+    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + alignment slack
+    static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;      // 128 / 256 / 512
+    static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
+    static_assert(CTAS == 1 || CTAS == 2, "CTAS must be 1 or 2");
+};
+
+// Problem policy contract:
+//   struct Tile;                                             decoded tile coordinates
+//   __device__ Tile decode(int tm, int tn, uint32_t cta_rank) const;
+//   __device__ void load(tile, kb, a_smem, b_smem, bar) const;     one lane, issues all TMA loads of a stage
+//   __device__ void store(tile, row_in_cta, col0, float (&v)[32]) const;   32 consecutive columns of one row
+template <int CTAS, int BN, bool B_MN_MAJOR, class Problem>
+__global__ void __launch_bounds__(UMMA_THREADS, 1)
+umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
+                 const UmmaEpilogueArgs epi) {
+#if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM101_ALL) || \
+    defined(__CUDA_ARCH_FEAT_SM103_ALL)
+    using Cfg = UmmaConfig<CTAS, BN, B_MN_MAJOR>;
+    constexpr int STAGES = Cfg::STAGES;
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[STAGES];
+    __shared__ __align__(8) uint64_t bar_empty[STAGES];
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ uint32_t tmem_base_holder;
+    __shared__ uint32_t abort_flag;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t cta_rank = (CTAS == 2) ? ptx::cluster_ctarank() : 0u;
+    const bool is_leader = (cta_rank == 0);
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+
+    ptx::WaitCtx wctx{&abort_flag, sched.status, sched.wait_limit_ns};
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        prob.prefetch_maps();
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&bar_full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bar_empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(ptx::smem_u32(&bar_acc_full[a]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bar_acc_empty[a]), 4 * CTAS);
+        }
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<CTAS>(ptx::smem_u32(&tmem_base_holder), Cfg::TMEM_COLS);
+        ptx::tmem_relinquish<CTAS>();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if constexpr (CTAS == 2) {   // the peer's barriers must exist before anything signals them
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = tmem_base_holder;
+
+    const int num_tiles = sched.tiles_m * sched.tiles_n;
+    const int tile_stride = gridDim.x / CTAS;
+    const int first_tile = blockIdx.x / CTAS;
+    const int group_tiles = sched.raster_group * sched.tiles_n;
+
+    auto tile_coords = [&](int t, int& tm, int& tn) {
+        const int group = t / group_tiles;
+        const int first_m = group * sched.raster_group;
+        const int rows = min(sched.raster_group, sched.tiles_m - first_m);
+        const int in_group = t - group * group_tiles;
+        tm = first_m + in_group % rows;
+        tn = in_group / rows;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            for (int t = first_tile; t < num_tiles; t += tile_stride) {
+                int tm, tn;
+                tile_coords(t, tm, tn);
+                const auto tile = prob.decode(tm, tn, cta_rank);
+                for (int kb = 0; kb < sched.k_blocks; ++kb) {
+                    if (!ptx::mbar_wait(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, wctx,
+                                        UMMA_TIMEOUT_PRODUCER))
+                        goto producer_done;
+                    const uint32_t full_local = ptx::smem_u32(&bar_full[stage]);
+                    if (is_leader) ptx::mbar_arrive_expect_tx(full_local, sched.tx_bytes);
+                    const uint32_t full_bar = (CTAS == 2) ? ptx::mapa(full_local, 0) : full_local;
+                    const uint32_t a_smem = smem_base + stage * Cfg::STAGE_BYTES;
+                    prob.template load<CTAS>(tile, kb, a_smem, a_smem + Cfg::A_BYTES, full_bar);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    producer_done:
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0 && is_leader) {
+            const uint32_t idesc =
+                ptx::idesc_tf32(UMMA_BM * CTAS, sched.umma_n, /*a_mn=*/0, /*b_mn=*/B_MN_MAJOR ? 1 : 0);
+            // K-major operand: rows are 128 B, 8-row swizzle atoms 1024 B apart.
+            const uint64_t a_base = ptx::smem_desc(16, 1024, ptx::SMEM_LAYOUT_SW128);
+            // MN-major B (32-bit elements): the only layout the tensor core accepts is
+            // the 128-byte swizzle with 32-byte atoms, whose pattern repeats every 4
+            // K rows.  Each TMA box is 32 columns x 32 K rows (4096 B): column chunks
+            // are 4096 B apart (LBO), 4-row K groups 512 B apart (SBO), and one MMA
+            // (K = 8) advances the start address by 8 rows = 1024 B.
+            const uint32_t b_lbo = sched.b_lbo ? sched.b_lbo : (B_MN_MAJOR ? 4096u : 16u);
+            const uint32_t b_sbo = sched.b_sbo ? sched.b_sbo : (B_MN_MAJOR ? 512u : 1024u);
+            const uint64_t b_base = ptx::smem_desc(
+                b_lbo, b_sbo, B_MN_MAJOR ? ptx::SMEM_LAYOUT_SW128_ATOM32 : ptx::SMEM_LAYOUT_SW128);
+            constexpr uint32_t b_kstep = B_MN_MAJOR ? 1024u : UMMA_K * 4u;
+
+            uint32_t stage = 0, phase = 0;
+            int it = 0;
+            for (int t = first_tile; t < num_tiles; t += tile_stride, ++it) {
+                const uint32_t acc = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                if (!ptx::mbar_wait(ptx::smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, wctx,
+                                    UMMA_TIMEOUT_MMA_ACC))
+                    goto mma_done;
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < sched.k_blocks; ++kb) {
+                    if (!ptx::mbar_wait(ptx::smem_u32(&bar_full[stage]), phase, wctx,
+                                        UMMA_TIMEOUT_MMA_FULL))
+                        goto mma_done;
+                    ptx::tc_fence_after();
+                    const uint32_t a_smem = smem_base + stage * Cfg::STAGE_BYTES;
+                    const uint32_t b_smem = a_smem + Cfg::A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < UMMA_BK / UMMA_K; ++kk) {
+                        const uint64_t a_desc = ptx::smem_desc_at(a_base, a_smem + kk * UMMA_K * 4);
+                        const uint64_t b_desc = ptx::smem_desc_at(b_base, b_smem + kk * b_kstep);
+                        ptx::umma_tf32<CTAS>(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0);
+                    }
+                    // Free the stage once these MMAs have read it (in both CTAs of a pair).
+                    const uint32_t empty_local = ptx::smem_u32(&bar_empty[stage]);
+                    ptx::umma_commit<CTAS>(empty_local);
+                    if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(empty_local, 1));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                const uint32_t accf_local = ptx::smem_u32(&bar_acc_full[acc]);
+                ptx::umma_commit<CTAS>(accf_local);
+                if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(accf_local, 1));
+            }
+        }
+    mma_done:
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const uint32_t quarter = warp & 3u;            // TMEM lanes [32*quarter, +32) belong to this warp
+        const int row_in_cta = quarter * 32 + lane;
+        int it = 0;
+        bool ok = true;
+        for (int t = first_tile; t < num_tiles && ok; t += tile_stride, ++it) {
+            int tm, tn;
+            tile_coords(t, tm, tn);
+            const auto tile = prob.decode(tm, tn, cta_rank);
+            const uint32_t acc = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            ok = ptx::mbar_wait(ptx::smem_u32(&bar_acc_full[acc]), acc_phase, wctx,
+                                UMMA_TIMEOUT_EPILOGUE);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const uint32_t t_row = tmem_base + acc * BN + ((quarter * 32u) << 16);
+#pragma unroll 1
+            for (int c = 0; c < sched.umma_n; c += 32) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(t_row + c, r);
+                ptx::tmem_ld_wait();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                prob.store(tile, row_in_cta, c, v, epi);
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                const uint32_t acce_local = ptx::smem_u32(&bar_acc_empty[acc]);
+                if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(ptx::mapa(acce_local, 0));
+                else ptx::mbar_arrive(acce_local);
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        // A wait ran out: give copies still in flight a bounded time to land
+        // before this CTA's shared memory is handed to the next one.
+        const uint64_t t0 = ptx::globaltimer_ns();
+        while (ptx::globaltimer_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if constexpr (CTAS == 2) {
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
+    }
+#else
+    // Compiled for an architecture without tcgen05: report instead of running.
+    if (threadIdx.x == 0 && blockIdx.x == 0) atomicCAS(sched.status, 0u, 0xdeadu);
+#endif
+}
+
+}  // namespace cudeep_b200

@@ -1,0 +1,42 @@
+// C++ launchers of the Conv2d forward path, Blackwell (sm_100a) build.
+//
+// launch_conv2d_forward_kernel keeps the name, argument list and mangled
+// symbol of the reference's include/cudeep/kernels/conv.cuh:8-16.  Tensors are
+// contiguous: input [N, C, H, W], weight [OC, C, KH, KW], bias [OC] or
+// nullptr, output [N, OC, OH, OW] with OH = (H + 2*pad_h - KH) / stride_h + 1.
+// The operation is a cross-correlation with zero padding, no dilation, no
+// groups.  Launches are asynchronous on `stream`; errors are std::runtime_error.
+//
+// Dispatch of the float launcher:
+//   * implicit-GEMM on tcgen05 (TF32 multiply, FP32 accumulate) for stride 1
+//     with C % 4 == 0 and an output row of at most 256 pixels; the input is
+//     re-laid as NHWC once per call and gathered tap by tap with TMA, filters
+//     are packed [OC][KH][KW][C]; no im2col matrix is materialised;
+//   * direct strict-FP32 convolution otherwise.
+// The double instantiation is a direct FP64 convolution.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "matmul.cuh"
+
+namespace cudeep {
+namespace kernels {
+
+// (reference conv.cuh:8-16, conv_kernel.cu:225-335)
+template <typename T>
+void launch_conv2d_forward_kernel(const T* input, const T* weight, const T* bias, T* output,
+                                  int batch, int in_channels, int out_channels, int in_h, int in_w,
+                                  int kernel_h, int kernel_w, int stride_h, int stride_w, int pad_h,
+                                  int pad_w, cudaStream_t stream = nullptr);
+
+// Addition: the same convolution with bias and an activation applied in the
+// GEMM epilogue (one pass over the output instead of conv + bias + activation).
+void launch_conv2d_forward_fused(const float* input, const float* weight, const float* bias,
+                                 float* output, int batch, int in_channels, int out_channels,
+                                 int in_h, int in_w, int kernel_h, int kernel_w, int stride_h,
+                                 int stride_w, int pad_h, int pad_w, GemmEpilogue epilogue,
+                                 cudaStream_t stream = nullptr);
+
+}  // namespace kernels
+}  // namespace cudeep

@@ -1,0 +1,158 @@
+/* C ABI of libcudeep_b200.so: the dense-contraction hot path of cuDeep
+ * (matmul, Linear forward, Conv2d forward) for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain pointers and sizes, returns 0 on success and a
+ * non-zero code on failure; cudeep_b200_last_error() then describes the
+ * failure for the calling thread.  Device-pointer entry points are
+ * asynchronous on `stream` (NULL = the legacy default stream) and never
+ * synchronise.  All matrices are row-major and contiguous, images are NCHW,
+ * filters OIHW, as in the reference.
+ *
+ * Each declaration names the reference interface it stands in for
+ * (paths are relative to the cuDeep source tree).
+ */
+#ifndef CUDEEP_B200_H
+#define CUDEEP_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Return codes. */
+#define CUDEEP_B200_OK 0
+#define CUDEEP_B200_ERROR 1          /* bad argument or CUDA failure; see cudeep_b200_last_error() */
+
+/* Epilogue codes; values equal cudeep::kernels::GemmEpilogue
+ * (include/cudeep/kernels/matmul.cuh:32-38). */
+#define CUDEEP_B200_EPI_NONE 0
+#define CUDEEP_B200_EPI_RELU 1
+#define CUDEEP_B200_EPI_GELU 2       /* tanh form, include/cudeep/ptx_intrinsics.cuh:545-549 */
+#define CUDEEP_B200_EPI_SILU 3
+#define CUDEEP_B200_EPI_SIGMOID 4
+
+typedef void* cudeep_b200_stream_t;  /* a cudaStream_t */
+
+/* ---- library ---------------------------------------------------------------------- */
+
+/* Library version, major*100 + minor. */
+int cudeep_b200_version(void);
+
+/* Message of the last failure on this thread ("" if none).  The pointer stays
+ * valid until the next failing call on the same thread. */
+const char* cudeep_b200_last_error(void);
+
+/* Reads the current device's kernel status word into *status (0 = no kernel
+ * abandoned a wait; 1..4 name the pipeline role that timed out) and clears it
+ * when `clear` is non-zero.  Synchronises the device. */
+int cudeep_b200_device_status(int clear, uint32_t* status);
+
+/* ---- matmul (device pointers) -------------------------------------------------------- */
+
+/* C[M,N] = A[M,K] * B[K,N], float.  TF32 tensor cores (FP32 accumulate) for
+ * M,N >= 64, K >= 32 with K % 4 == 0, N % 4 == 0 and 16-byte aligned A, B;
+ * strict FP32 otherwise.
+ * Replaces cudeep::kernels::launch_matmul_kernel<float>
+ * (include/cudeep/kernels/matmul.cuh:8-12, src/kernels/matmul_kernel.cu:1785-1841). */
+int cudeep_b200_matmul_f32(const float* A, const float* B, float* C, int M, int N, int K,
+                           cudeep_b200_stream_t stream);
+
+/* Same product, always strict FP32 (fused multiply-add, no tensor cores).
+ * Replaces launch_matmul_kernel_fp32<float>
+ * (matmul.cuh:14-18, matmul_kernel.cu:1851-1863). */
+int cudeep_b200_matmul_f32_strict(const float* A, const float* B, float* C, int M, int N, int K,
+                                  cudeep_b200_stream_t stream);
+
+/* FP64 product.  Replaces launch_matmul_kernel<double> (matmul_kernel.cu:1843-1849). */
+int cudeep_b200_matmul_f64(const double* A, const double* B, double* C, int M, int N, int K,
+                           cudeep_b200_stream_t stream);
+
+/* C = act(A * B).  Replaces launch_matmul_fused_act
+ * (matmul.cuh:40-44, matmul_kernel.cu:1884-1924). */
+int cudeep_b200_matmul_fused_act(const float* A, const float* B, float* C, int M, int N, int K,
+                                 int epilogue, cudeep_b200_stream_t stream);
+
+/* y[M,N] = act(x[M,K] * W[N,K]^T + bias[N]); bias may be NULL.  One kernel for
+ * what nn.Linear.forward runs as transpose-copy + GEMM + broadcast_add (+ a
+ * separate activation): python/cuDeep/nn.py:110-115,
+ * src/bindings/module.cpp:664-694, src/tensor.cu:256-281. */
+int cudeep_b200_linear_forward_f32(const float* x, const float* W, const float* bias, float* y,
+                                   int M, int N, int K, int epilogue,
+                                   cudeep_b200_stream_t stream);
+int cudeep_b200_linear_forward_f64(const double* x, const double* W, const double* bias, double* y,
+                                   int M, int N, int K, int epilogue,
+                                   cudeep_b200_stream_t stream);
+
+/* The TF32 tensor-core GEMM with explicit tile choices, for benchmarks and
+ * bring-up.  b_is_nk: 0 = B is [K,N], 1 = B is [N,K].  bias: NULL, N values, or
+ * M values when bias_per_row != 0.  ctas (1|2), bn (64|128|256), raster_group,
+ * max_ctas: 0 selects the default.  b_lbo / b_sbo: 0, or a byte offset that
+ * overrides the B shared-memory descriptor fields.  Fails instead of falling
+ * back when the tensor-core path cannot take the problem. */
+int cudeep_b200_gemm_tf32_tuned(const float* A, const float* B, int b_is_nk, float* C, int M, int N,
+                                int K, const float* bias, int bias_per_row, int epilogue, int ctas,
+                                int bn, int raster_group, int max_ctas, uint32_t b_lbo,
+                                uint32_t b_sbo, cudeep_b200_stream_t stream);
+
+/* ---- conv2d forward (device pointers) -------------------------------------------------- */
+
+/* output[N,OC,OH,OW] = conv(input[N,C,H,W], weight[OC,C,KH,KW]) + bias[OC]
+ * (cross-correlation, zero padding, no dilation or groups; bias may be NULL),
+ * OH = (H + 2*pad_h - KH) / stride_h + 1.  Replaces
+ * launch_conv2d_forward_kernel<float> (include/cudeep/kernels/conv.cuh:8-16,
+ * src/kernels/conv_kernel.cu:225-335). */
+int cudeep_b200_conv2d_forward_f32(const float* input, const float* weight, const float* bias,
+                                   float* output, int batch, int in_channels, int out_channels,
+                                   int in_h, int in_w, int kernel_h, int kernel_w, int stride_h,
+                                   int stride_w, int pad_h, int pad_w,
+                                   cudeep_b200_stream_t stream);
+
+/* Same with an activation applied to conv + bias in the epilogue. */
+int cudeep_b200_conv2d_forward_fused_f32(const float* input, const float* weight, const float* bias,
+                                         float* output, int batch, int in_channels,
+                                         int out_channels, int in_h, int in_w, int kernel_h,
+                                         int kernel_w, int stride_h, int stride_w, int pad_h,
+                                         int pad_w, int epilogue, cudeep_b200_stream_t stream);
+
+/* FP64 convolution.  Replaces launch_conv2d_forward_kernel<double>. */
+int cudeep_b200_conv2d_forward_f64(const double* input, const double* weight, const double* bias,
+                                   double* output, int batch, int in_channels, int out_channels,
+                                   int in_h, int in_w, int kernel_h, int kernel_w, int stride_h,
+                                   int stride_w, int pad_h, int pad_w,
+                                   cudeep_b200_stream_t stream);
+
+/* ---- host-buffer entry points ---------------------------------------------------------- */
+
+/* The reference's Python call sequence Tensor.from_numpy(a).matmul(
+ * Tensor.from_numpy(b)).numpy() as one call on host memory: copies A and B to
+ * the device, multiplies, copies C back and waits for it
+ * (src/bindings/module.cpp:106,116-146; src/tensor.cu:208-223,384-420).
+ * strict != 0 selects the strict FP32 kernel.  Device buffers come from the
+ * library's memory pool and are reused by later calls of the same sizes. */
+int cudeep_b200_matmul_host_f32(const float* A, const float* B, float* C, int M, int N, int K,
+                                int strict);
+
+/* nn.Linear forward on host memory (x, W, bias in; y out). */
+int cudeep_b200_linear_forward_host_f32(const float* x, const float* W, const float* bias, float* y,
+                                        int M, int N, int K, int epilogue);
+
+/* conv2d forward on host memory. */
+int cudeep_b200_conv2d_forward_host_f32(const float* input, const float* weight, const float* bias,
+                                        float* output, int batch, int in_channels, int out_channels,
+                                        int in_h, int in_w, int kernel_h, int kernel_w, int stride_h,
+                                        int stride_w, int pad_h, int pad_w, int epilogue);
+
+/* ---- memory pool (cudeep::MemoryPool, include/cudeep/memory.cuh:13-46) ------------------- */
+
+int cudeep_b200_pool_alloc(size_t nbytes, void** ptr);     /* MemoryPool::allocate   */
+int cudeep_b200_pool_free(void* ptr);                      /* MemoryPool::deallocate */
+int cudeep_b200_pool_release_cached(void);                 /* MemoryPool::release_cached */
+int cudeep_b200_pool_stats(size_t* allocated_bytes, size_t* cached_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* CUDEEP_B200_H */
