@@ -1,0 +1,373 @@
+#!/usr/bin/env python
+"""Headline benchmark: TF32 GEMM TFLOP/s at 8192^3, on 1..8 B200s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one C = A @ B with A[8192, 8192], B[8192, 8192] float32 (N(0,1), seeded),
+TF32 tensor-core multiply, FP32 accumulate, through the library's C ABI.  With N > 1
+(launched under torchrun, one rank per GPU) the job is the row-sharded GEMM
+C[N*8192, 8192] = A[N*8192, 8192] @ B: every rank owns 8192 rows of A and C and a
+replica of B, so per-GPU work is fixed (weak scaling) and no collective is on the
+data path.  At N = 8 that is the 65536 x 8192 x 8192 sharded configuration.
+
+Prints one JSON line (rank 0).  `value` is device-resident throughput (CUDA events,
+max over ranks); `e2e` is the same product through the host-buffer entry point with
+pinned host inputs and outputs, copies inside the timed region.
+
+--impl reference times the reference's own CUDA kernels (cuDeep's matmul sources
+rebuilt unmodified for sm_100, oracle/_ref) on the same GPU, inputs and protocol; the
+reference has no CPU implementation of this path.  If that library is absent the arm
+falls back to the CPU oracle port and says so.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SIZE = 8192
+METRIC = "TF32 GEMM TFLOP/s at 8192^3"
+FALLBACK_BF16_TFLOPS = 1590.0       # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+NOMINAL_TF32_TFLOPS = 1125.0        # half the nominal dense bf16 rate of a B200
+
+# DRAM bytes one 8192^3 launch moves (dram__bytes_read.sum + dram__bytes_write.sum from the
+# ncu capture summarised in profiles/); None until a capture exists.
+NCU_DRAM_BYTES_PER_LAUNCH = None
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons through NVML (read-only) while timing runs."""
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+            "hw_power_brake": getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------- helpers
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            d = json.loads(path.read_text())
+            return float(d["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_BF16_TFLOPS, "fallback"
+
+
+def dist_setup(n_gpus: int):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+    return rank, world, local, dist
+
+
+def barrier_sync(dist):
+    import torch
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(dist, value: float) -> float:
+    import torch
+    if dist is None:
+        return value
+    t = torch.tensor([value], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def shard_inputs(rank: int):
+    """This rank's 8192 rows of A (seeded per rank) and the replicated B."""
+    from cudeep_b200 import workloads
+    a, b = workloads.c2_gemm(SIZE)                 # rank 0 runs exactly the 8192^3 benchmark configuration
+    if rank != 0:
+        a = np.random.default_rng([SIZE, rank]).standard_normal((SIZE, SIZE), dtype=np.float32)
+    return a, b
+
+
+def time_device_steps(launch, steps: int, warmup: int, dist, sampler_index: int):
+    """K launches timed with CUDA events on the current stream; returns (seconds, per-launch ms, clocks)."""
+    import torch
+    for _ in range(warmup):
+        launch()
+    barrier_sync(dist)
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    with ClockSampler(sampler_index) as clocks:
+        events[0].record()
+        for i in range(steps):
+            launch()
+            events[i + 1].record()
+        barrier_sync(dist)
+    total_ms = events[0].elapsed_time(events[-1])
+    per_launch = [events[i].elapsed_time(events[i + 1]) for i in range(steps)]
+    return total_ms / 1e3, per_launch, clocks.summary()
+
+
+def time_e2e_steps(step, steps: int, dist):
+    """Host-to-host steps; wall-clock per step is taken between device-synchronised points."""
+    import torch
+    step()
+    barrier_sync(dist)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier_sync(dist)
+    wall = time.perf_counter() - t0
+    return max(wall, e0.elapsed_time(e1) / 1e3)
+
+
+def cpu_baseline_leg():
+    """The oracle port's host GEMM (NumPy / OpenBLAS sgemm, FP32) on a bounded sample."""
+    from oracle import oracle as o
+    rows = 2048
+    rng = np.random.default_rng(SIZE)
+    a = rng.standard_normal((rows, SIZE), dtype=np.float32)
+    b = rng.standard_normal((SIZE, SIZE), dtype=np.float32)
+    o.cpu_sgemm(a[:256], b)
+    best = float("inf")
+    spent = 0.0
+    while spent < 12.0:
+        t0 = time.perf_counter()
+        o.cpu_sgemm(a, b)
+        dt = time.perf_counter() - t0
+        best = min(best, dt)
+        spent += dt
+    return {"value": 2.0 * rows * SIZE * SIZE / best / 1e12, "unit": "TFLOP/s", "cores": o.cpu_threads(),
+            "kind": "port",
+            "sample": f"rows 0..{rows - 1} of the 8192^3 product, FP32 sgemm (NumPy/OpenBLAS), best of ~12 s"}
+
+
+# ---------------------------------------------------------------------------- arms
+
+def run_ours(args):
+    import torch
+    from cudeep_b200 import _lib
+    lib = _lib.load()
+    rank, world, local, dist = dist_setup(args.gpus)
+    a_np, b_np = shard_inputs(rank)
+    a = torch.from_numpy(a_np).cuda()
+    b = torch.from_numpy(b_np).cuda()
+    c = torch.empty((SIZE, SIZE), device="cuda", dtype=torch.float32)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    pa, pb, pc = (ctypes.c_void_p(t.data_ptr()) for t in (a, b, c))
+
+    def launch():
+        rc = lib.cudeep_b200_matmul_f32(pa, pb, pc, SIZE, SIZE, SIZE, stream)
+        if rc != 0:
+            raise RuntimeError(lib.cudeep_b200_last_error().decode())
+
+    seconds, per_launch, clocks = time_device_steps(launch, args.steps, args.warmup, dist, local)
+    status = _lib.device_status(True)
+    if status != 0:
+        raise RuntimeError(f"kernel status word {status}: a pipeline wait was abandoned")
+    seconds = max_over_ranks(dist, seconds)
+    flops_step = 2.0 * SIZE ** 3 * world
+    value = flops_step * args.steps / seconds / 1e12
+
+    # end to end: pinned host buffers in, pinned host buffer out, through the host entry point
+    ha = torch.from_numpy(a_np).pin_memory()
+    hb = torch.from_numpy(b_np).pin_memory()
+    hc = torch.empty((SIZE, SIZE), dtype=torch.float32).pin_memory()
+    pha, phb, phc = (ctypes.c_void_p(t.data_ptr()) for t in (ha, hb, hc))
+
+    def e2e_step():
+        rc = lib.cudeep_b200_matmul_host_f32(pha, phb, phc, SIZE, SIZE, SIZE, 0)
+        if rc != 0:
+            raise RuntimeError(lib.cudeep_b200_last_error().decode())
+
+    e2e_seconds = max_over_ranks(dist, time_e2e_steps(e2e_step, args.e2e_steps, dist))
+    e2e_value = flops_step * args.e2e_steps / e2e_seconds / 1e12
+    checksum = float(hc[0, :8].sum())      # the step's result is read on the host
+
+    if rank != 0:
+        return
+    bf16_peak, peak_kind = measured_peaks()
+    kernel_ms = float(np.mean(per_launch))
+    achieved = 2.0 * SIZE ** 3 / (kernel_ms * 1e-3) / 1e12
+    peak = bf16_peak / 2.0
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "tf32 multiply, f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"C = A[{SIZE * world},{SIZE}] @ B[{SIZE},{SIZE}] float32 N(0,1), "
+                               f"{SIZE} rows of A and C per GPU, B replicated",
+                   "flop_per_step": flops_step, "l2": "operands and result (805 MB per GPU) exceed the 126 MB L2; no flush",
+                   "parallelism": f"rows sharded over {world} GPU(s), no data-path collective"},
+        "pct_of_nominal_tf32_peak": 100.0 * value / world / NOMINAL_TF32_TFLOPS,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * SIZE * SIZE * 4 * world,
+                "d2h_bytes_per_step": SIZE * SIZE * 4 * world, "steps": args.e2e_steps,
+                "result_probe": checksum},
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / peak,
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                     "peak_source": f"{peak_kind} dense bf16 cuBLAS burst ({bf16_peak} TFLOP/s) / 2: "
+                                    "TF32 issues at half the bf16 rate",
+                     "kernel": "umma_tf32_kernel", "kernel_ms": kernel_ms},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_leg()
+    print(json.dumps(line), flush=True)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return                                   # the reference is single-device: rank 0 alone measures
+    from oracle import oracle as o
+    flops_step = 2.0 * SIZE ** 3
+    base = {"impl": "reference", "metric": METRIC, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "data": "synthetic"}
+    use_gpu = o.REF_LIB_PATH.exists()
+    if use_gpu:
+        try:
+            import torch
+            use_gpu = torch.cuda.is_available()
+        except Exception:
+            use_gpu = False
+    if use_gpu:
+        import torch
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        ref = ctypes.CDLL(str(o.REF_LIB_PATH))
+        a_np, b_np = shard_inputs(0)
+        a, b = torch.from_numpy(a_np).cuda(), torch.from_numpy(b_np).cuda()
+        c = torch.empty((SIZE, SIZE), device="cuda", dtype=torch.float32)
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        pa, pb, pc = (ctypes.c_void_p(t.data_ptr()) for t in (a, b, c))
+
+        def launch():
+            if ref.cudeep_ref_matmul_f32(pa, pb, pc, SIZE, SIZE, SIZE, stream) != 0:
+                raise RuntimeError("reference launcher failed")
+
+        steps = min(args.steps, 50)
+        seconds, per_launch, clocks = time_device_steps(launch, steps, min(args.warmup, 5), None, 0)
+        value = flops_step * steps / seconds / 1e12
+        ha, hb = torch.from_numpy(a_np).pin_memory(), torch.from_numpy(b_np).pin_memory()
+        hc = torch.empty((SIZE, SIZE), dtype=torch.float32).pin_memory()
+
+        def e2e_step():                            # from_numpy -> matmul -> numpy, as the reference's Python API does
+            a.copy_(ha, non_blocking=True)
+            b.copy_(hb, non_blocking=True)
+            launch()
+            hc.copy_(c, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        e2e_seconds = time_e2e_steps(e2e_step, args.e2e_steps, None)
+        line = dict(base, steps=steps, value=value, ms_per_step=seconds / steps * 1e3,
+                    dtype="tf32 multiply, f32 accumulate",
+                    config={"workload": f"C = A[{SIZE},{SIZE}] @ B[{SIZE},{SIZE}] float32 N(0,1)",
+                            "device": "the reference's CUDA kernels (mma.sync TF32) on the same B200",
+                            "flop_per_step": flops_step},
+                    e2e={"value": flops_step * args.e2e_steps / e2e_seconds / 1e12, "unit": "TFLOP/s",
+                         "h2d_bytes_per_step": 2 * SIZE * SIZE * 4, "d2h_bytes_per_step": SIZE * SIZE * 4},
+                    cpu_baseline={"value": value, "unit": "TFLOP/s", "cores": 0, "kind": "reference",
+                                  "sample": "not a CPU run: the reference has no CPU implementation of this path; "
+                                            "its own GPU kernels were timed on the full workload"},
+                    gpu_launches=steps, clocks=clocks)
+    else:
+        cpu = cpu_baseline_leg()
+        line = dict(base, value=cpu["value"], ms_per_step=flops_step / (cpu["value"] * 1e12) * 1e3,
+                    dtype="f32", config={"workload": f"C = A[{SIZE},{SIZE}] @ B[{SIZE},{SIZE}] float32 N(0,1)",
+                                         "device": "host CPU (oracle port); reference kernels not built",
+                                         "flop_per_step": flops_step},
+                    cpu_baseline=cpu,
+                    e2e={"value": cpu["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

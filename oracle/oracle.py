@@ -188,6 +188,24 @@ def sgemm_f32(a, b) -> np.ndarray:
     return c
 
 
+def cpu_sgemm(a, b) -> np.ndarray:
+    """FP32 host GEMM through NumPy's BLAS (all host threads): the timed CPU baseline."""
+    return _f32(a) @ _f32(b)
+
+
+def cpu_threads() -> int:
+    """Threads the BLAS behind cpu_sgemm uses."""
+    try:
+        from threadpoolctl import threadpool_info
+        counts = [int(i.get("num_threads", 0)) for i in threadpool_info() if i.get("user_api") == "blas"]
+        if counts:
+            return max(counts)
+    except Exception:
+        pass
+    import os
+    return os.cpu_count() or 1
+
+
 # ---- error measures used by the parity tests -------------------------------------------
 
 def rel_frobenius(got, want) -> float:

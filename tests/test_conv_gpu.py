@@ -1,0 +1,139 @@
+"""GPU parity of Conv2d forward against the float64 CPU oracle, through the C ABI."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from cudeep_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-5
+TF32_TOL = 5e-3
+TF32_MODEL_TOL = 2e-5
+
+
+def test_reference_known_answers(dev):
+    # cuDeep tests/unit/test_kernels.cu:324-425
+    x = np.arange(1, 17, dtype=np.float32).reshape(1, 1, 4, 4)
+    y = dev.conv2d(x, np.ones((1, 1, 1, 1), np.float32), np.zeros(1, np.float32))
+    assert np.max(np.abs(y - x)) < 1e-4
+    ones = np.ones((1, 1, 3, 3), np.float32)
+    assert abs(dev.conv2d(ones, ones)[0, 0, 0, 0] - 9) < 1e-4
+    assert abs(dev.conv2d(ones, ones, np.array([10], np.float32))[0, 0, 0, 0] - 19) < 1e-4
+    y = dev.conv2d(ones, ones, None, (1, 1), (1, 1))
+    assert abs(y[0, 0, 1, 1] - 9) < 1e-4 and abs(y[0, 0, 0, 0] - 4) < 1e-4 and abs(y[0, 0, 0, 1] - 6) < 1e-4
+
+
+def test_reference_layer_shapes(dev):
+    # cuDeep tests/unit/test_layers.py:58-75
+    rng = np.random.default_rng(0)
+    y = dev.conv2d(rng.standard_normal((2, 3, 8, 8), dtype=np.float32),
+                   rng.standard_normal((16, 3, 3, 3), dtype=np.float32), None, (1, 1), (1, 1))
+    assert y.shape == (2, 16, 8, 8) and np.isfinite(y).all()
+    y = dev.conv2d(rng.standard_normal((1, 1, 8, 8), dtype=np.float32),
+                   rng.standard_normal((4, 1, 3, 3), dtype=np.float32))
+    assert y.shape == (1, 4, 6, 6)
+    y = dev.conv2d(rng.standard_normal((1, 3, 8, 8), dtype=np.float32),
+                   rng.standard_normal((8, 3, 3, 3), dtype=np.float32), None, (2, 2), (1, 1))
+    assert y.shape == (1, 8, 4, 4)
+
+
+def test_golden_fixtures(dev, oracle):
+    g = np.load(Path(__file__).resolve().parent / "golden" / "dense_golden.npz")
+    for tag in ("p1", "s2", "k1", "k5"):
+        sh, sw, ph, pw = (int(v) for v in g[f"conv_{tag}_meta"])
+        y = dev.conv2d(g[f"conv_{tag}_x"], g[f"conv_{tag}_w"], g[f"conv_{tag}_bias"], (sh, sw), (ph, pw), act=1)
+        assert oracle.rel_frobenius(y, g[f"conv_{tag}_y"]) <= FP32_TOL     # small shapes: strict FP32 path
+
+
+@pytest.mark.parametrize("shape,oc,k,stride,padding", [
+    ((1, 1, 5, 5), 1, (3, 3), (1, 1), (0, 0)),
+    ((2, 3, 9, 11), 8, (3, 3), (2, 2), (1, 1)),
+    ((1, 16, 12, 12), 8, (5, 3), (1, 2), (2, 0)),
+    ((2, 64, 14, 14), 64, (3, 3), (2, 2), (1, 1)),      # strided: direct path even with many channels
+])
+def test_direct_path_shapes(dev, oracle, shape, oc, k, stride, padding):
+    rng = np.random.default_rng(sum(shape) + oc)
+    x = rng.standard_normal(shape, dtype=np.float32)
+    w = rng.standard_normal((oc, shape[1], *k), dtype=np.float32) * np.float32(0.2)
+    bias = rng.standard_normal(oc, dtype=np.float32)
+    for act in (0, 1):
+        got = dev.conv2d(x, w, bias, stride, padding, act=act)
+        assert oracle.rel_frobenius(got, oracle.conv2d(x, w, bias, stride, padding, act=act)) <= FP32_TOL
+
+
+@pytest.mark.parametrize("shape,oc,k,padding", [
+    ((2, 32, 8, 8), 128, (3, 3), (1, 1)),        # one CTA per tile, box narrower than 256 pixels
+    ((1, 64, 14, 14), 64, (3, 3), (1, 1)),       # fewer output channels than a tile has rows
+    ((2, 48, 9, 13), 96, (3, 3), (1, 1)),        # odd width: padded pixel box, channel count not a multiple of 32
+    ((1, 32, 56, 56), 128, (1, 1), (0, 0)),      # 1x1
+    ((2, 32, 8, 8), 256, (3, 3), (1, 1)),        # CTA pair
+    ((1, 64, 56, 56), 256, (3, 3), (1, 1)),      # C4's image size and filter, one image
+    ((2, 40, 10, 12), 200, (5, 5), (2, 2)),      # 5x5, ragged channels on both sides
+    ((1, 36, 20, 20), 160, (3, 3), (0, 0)),      # no padding: output smaller than input
+    ((3, 6, 16, 16), 64, (3, 3), (1, 1)),        # few input channels (C*KH*KW >= 32 still holds)
+    ((1, 32, 6, 300), 64, (3, 3), (1, 1)),       # rows wider than one tile
+])
+@pytest.mark.parametrize("act", [0, 1])
+def test_tensor_core_path_shapes(dev, oracle, shape, oc, k, padding, act):
+    rng = np.random.default_rng(sum(shape) + oc + act)
+    x = rng.standard_normal(shape, dtype=np.float32)
+    w = rng.standard_normal((oc, shape[1], *k), dtype=np.float32) * np.float32(0.1)
+    bias = rng.standard_normal(oc, dtype=np.float32)
+    got = dev.conv2d(x, w, bias, (1, 1), padding, act=act)
+    assert not np.isnan(got).any()
+    exact = oracle.conv2d(x, w, bias, (1, 1), padding, act=act)
+    model = oracle.conv2d(x, w, bias, (1, 1), padding, act=act, input_mode=oracle.INPUT_TF32_TRUNC)
+    assert got.shape == exact.shape
+    assert oracle.rel_frobenius(got, exact) <= TF32_TOL
+    assert oracle.rel_frobenius(got, model) <= TF32_MODEL_TOL
+
+
+def test_no_bias_and_bias_differ_by_bias(dev):
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((1, 32, 8, 8), dtype=np.float32)
+    w = rng.standard_normal((64, 32, 3, 3), dtype=np.float32) * np.float32(0.1)
+    bias = rng.standard_normal(64, dtype=np.float32)
+    y0 = dev.conv2d(x, w, None, (1, 1), (1, 1))
+    y1 = dev.conv2d(x, w, bias, (1, 1), (1, 1))
+    assert np.allclose(y1 - y0, bias[None, :, None, None], atol=1e-5)
+
+
+def test_c4_reduced_batch(dev, oracle):
+    """C4's layer (256 -> 256, 3x3, 56x56, bias + ReLU) on 2 images; the oracle checks all of it."""
+    x, w, bias = workloads.c4_conv(batch=2)
+    got = dev.conv2d(x, w, bias, (1, 1), (1, 1), act=1)
+    exact = oracle.conv2d(x, w, bias, (1, 1), (1, 1), act=1)
+    model = oracle.conv2d(x, w, bias, (1, 1), (1, 1), act=1, input_mode=oracle.INPUT_TF32_TRUNC)
+    assert oracle.rel_frobenius(got, exact) <= TF32_TOL
+    assert oracle.rel_frobenius(got, model) <= TF32_MODEL_TOL
+    k = 256 * 9
+    pre = oracle.conv2d(x, w, bias, (1, 1), (1, 1))
+    got_pre = dev.conv2d(x, w, bias, (1, 1), (1, 1))
+    assert np.max(np.abs(got_pre - pre)) <= oracle.tf32_elementwise_bound(x, w, k)
+
+
+def test_c4_full_batch_properties(dev, oracle):
+    """C4 at full size (64 images): batch independence and a sampled check against the oracle."""
+    x, w, bias = workloads.c4_conv()
+    got = dev.conv2d(x, w, bias, (1, 1), (1, 1), act=1)
+    assert got.shape == (64, 256, 56, 56) and not np.isnan(got).any()
+    # images are independent: recomputing images 17 and 63 alone gives the same bits
+    for i in (17, 63):
+        alone = dev.conv2d(x[i:i + 1], w, bias, (1, 1), (1, 1), act=1)
+        assert np.array_equal(alone[0], got[i])
+    exact = oracle.conv2d(x[40:41], w, bias, (1, 1), (1, 1), act=1)
+    assert oracle.rel_frobenius(got[40:41], exact) <= TF32_TOL
+
+
+def test_conv_host_buffers(lib, cuda, oracle):
+    import ctypes
+    from cudeep_b200 import _lib
+    x, w, bias = workloads.c4_conv(batch=1, channels=64, out_channels=128, size=28)
+    y = np.full((1, 128, 28, 28), np.nan, np.float32)
+    p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    _lib.check(lib.cudeep_b200_conv2d_forward_host_f32(p(x), p(w), p(bias), p(y), 1, 64, 128, 28, 28, 3, 3,
+                                                       1, 1, 1, 1, 1))
+    assert _lib.device_status() == 0
+    assert oracle.rel_frobenius(y, oracle.conv2d(x, w, bias, (1, 1), (1, 1), act=1)) <= TF32_TOL

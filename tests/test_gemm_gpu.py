@@ -1,0 +1,216 @@
+"""GPU parity of the matmul / Linear path against the float64 CPU oracle, through the C ABI.
+
+Bars (from the benchmark specification):
+  strict FP32 path  : relative Frobenius error <= 1e-5
+  TF32 path         : relative Frobenius error <= 5e-3 and every element within
+                      2^-9 * K * max|a| * max|b| of the float64 product
+and, stronger, the TF32 path must agree with the float64 product of the
+TF32-truncated inputs to FP32-accumulation accuracy (<= 2e-5 relative), which pins
+the operand handling to the reference's (raw FP32 words into the TF32 MMA).
+"""
+import numpy as np
+import pytest
+
+from cudeep_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-5
+TF32_TOL = 5e-3
+TF32_MODEL_TOL = 2e-5
+
+
+def check_tf32(oracle, got, a, b, k, *, b_is_nk=False, bias=None, act=0, rows=None):
+    sel = slice(None) if rows is None else rows
+    exact = oracle.gemm(a[sel], b, b_is_nk=b_is_nk, bias=bias, act=act)
+    model = oracle.gemm(a[sel], b, b_is_nk=b_is_nk, bias=bias, act=act, input_mode=oracle.INPUT_TF32_TRUNC)
+    g = got[sel]
+    assert not np.isnan(g).any()
+    assert oracle.rel_frobenius(g, exact) <= TF32_TOL
+    assert oracle.rel_frobenius(g, model) <= TF32_MODEL_TOL
+    if act == 0:
+        assert np.max(np.abs(g - exact)) <= oracle.tf32_elementwise_bound(a, b, k)
+
+
+# ---- reference known-answer cases through the library -------------------------------------
+
+def test_known_answers(dev, oracle):
+    a = np.array([[1, 2], [3, 4]], np.float32)
+    b = np.array([[5, 6], [7, 8]], np.float32)
+    assert np.allclose(dev.matmul(a, b), [[19, 22], [43, 50]], atol=1e-5)      # test_matmul.cu:42-66
+    d = np.diag(np.arange(1, 5)).astype(np.float32)
+    assert np.allclose(dev.matmul(d, np.eye(4, dtype=np.float32)), d, atol=1e-5)  # test_matmul.cu:13-40
+    rng = np.random.default_rng(0)
+    r = rng.standard_normal((8, 8), dtype=np.float32)
+    assert np.allclose(dev.matmul(r, np.eye(8, dtype=np.float32)), r, rtol=1e-5)  # test_tensor_ops.py:220-227
+    a35, b57 = rng.standard_normal((3, 5), dtype=np.float32), rng.standard_normal((5, 7), dtype=np.float32)
+    assert np.allclose(dev.matmul(a35, b57), a35 @ b57, rtol=1e-4, atol=1e-6)     # test_tensor_ops.py:229-237
+    a1, b1 = rng.standard_normal((64, 128), dtype=np.float32), rng.standard_normal((128, 32), dtype=np.float32)
+    assert np.allclose(dev.matmul(a1, b1), a1 @ b1, rtol=1e-3, atol=1e-3)         # test_tensor_ops.py:239-245
+
+
+def test_known_answers_f64(dev, lib):
+    import torch
+    a = np.array([[1.5, 2.5], [3.5, 4.5]])
+    b = np.array([[0.5, 1.5], [2.5, 3.5]])
+    ta, tb = dev.to_dev(a), dev.to_dev(b)
+    tc = dev.empty((2, 2), dtype=torch.float64)
+    dev.check(lib.cudeep_b200_matmul_f64(dev.ptr(ta), dev.ptr(tb), dev.ptr(tc), 2, 2, 2, None))
+    assert dev.sync_status() == 0
+    assert np.max(np.abs(tc.cpu().numpy() - a @ b)) < 1e-10                    # test_tensor.cu:368-381
+
+
+# ---- C1: strict FP32 ---------------------------------------------------------------------
+
+def test_c1_fp32_512(dev, oracle):
+    a, b = workloads.c1_sgemm()
+    got = dev.matmul(a, b, strict=True)
+    assert oracle.rel_frobenius(got, oracle.gemm(a, b)) <= FP32_TOL
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (2, 2, 2), (3, 7, 5), (70, 33, 45), (129, 257, 65), (300, 130, 1000)])
+def test_fp32_shapes(dev, oracle, m, n, k):
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    assert oracle.rel_frobenius(dev.matmul(a, b, strict=True), oracle.gemm(a, b)) <= FP32_TOL
+
+
+def test_small_and_unaligned_dispatch_is_fp32_exact(dev, oracle):
+    """Shapes the tensor-core path does not take must come out at FP32 accuracy."""
+    rng = np.random.default_rng(11)
+    for m, n, k in [(8, 8, 8), (63, 200, 64), (200, 63, 64), (128, 130, 64), (128, 128, 30)]:
+        a = rng.standard_normal((m, k), dtype=np.float32)
+        b = rng.standard_normal((k, n), dtype=np.float32)
+        assert oracle.rel_frobenius(dev.matmul(a, b), oracle.gemm(a, b)) <= FP32_TOL
+
+
+def test_golden_fixtures_fp32(dev, oracle):
+    from pathlib import Path
+    g = np.load(Path(__file__).resolve().parent / "golden" / "dense_golden.npz")
+    for tag in ("aligned", "ragged"):
+        a, b, w, bias = (g[f"gemm_{tag}_{s}"] for s in ("a", "b", "w", "bias"))
+        assert oracle.rel_frobenius(dev.matmul(a, b, strict=True), g[f"gemm_{tag}_c"]) <= FP32_TOL
+        for act in range(5):
+            got = dev.linear(a, w, bias, act=act)
+            assert oracle.rel_frobenius(got, g[f"linear_{tag}_act{act}"]) <= 2e-5   # SFU-approximate activations
+
+
+# ---- C2: TF32 tensor-core GEMM, B as [K, N] --------------------------------------------------
+
+@pytest.mark.parametrize("n", [1024, 2048])
+def test_c2_tf32_full(dev, oracle, n):
+    a, b = workloads.c2_gemm(n)
+    got = dev.matmul(a, b)
+    check_tf32(oracle, got, a, b, n)
+
+
+@pytest.mark.parametrize("n", [4096, 8192])
+def test_c2_tf32_sampled_rows(dev, oracle, n):
+    """Full-size products; the float64 oracle checks 96 random rows (all columns) of each."""
+    a, b = workloads.c2_gemm(n)
+    got = dev.matmul(a, b)
+    rows = np.sort(np.random.default_rng(n).choice(n, size=96, replace=False))
+    check_tf32(oracle, got, a, b, n, rows=rows)
+    # every tile took part: no row of the output is left poisoned, and a column checksum of
+    # the whole product matches the one formed from the operands (sum_i C[i,:] = (sum_i A[i,:]) B)
+    assert not np.isnan(got).any()
+    colsum = got.sum(axis=0, dtype=np.float64)
+    want = a.sum(axis=0, dtype=np.float64) @ b.astype(np.float64)
+    assert np.linalg.norm(colsum - want) / np.linalg.norm(want) <= TF32_TOL
+
+
+@pytest.mark.parametrize("ctas,bn", [(1, 256), (1, 128), (1, 64), (2, 256), (2, 128)])
+@pytest.mark.parametrize("b_is_nk", [False, True])
+def test_tf32_every_tile_configuration(dev, oracle, ctas, bn, b_is_nk):
+    rng = np.random.default_rng(ctas * 1000 + bn + int(b_is_nk))
+    m, n, k = 640, 768, 416          # several tiles per CTA, K not a multiple of 32
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((n, k) if b_is_nk else (k, n), dtype=np.float32)
+    got = dev.gemm_tuned(a, b, b_is_nk, ctas=ctas, bn=bn, max_ctas=8)   # 8 CTAs: each walks many tiles
+    check_tf32(oracle, got, a, b, k, b_is_nk=b_is_nk)
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 64, 32), (100, 260, 36), (129, 132, 200), (1000, 72, 64), (257, 1028, 516)])
+@pytest.mark.parametrize("b_is_nk", [False, True])
+def test_tf32_ragged_shapes(dev, oracle, m, n, k, b_is_nk):
+    rng = np.random.default_rng(m * 7 + n * 3 + k)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((n, k) if b_is_nk else (k, n), dtype=np.float32)
+    got = dev.gemm_tuned(a, b, b_is_nk)
+    check_tf32(oracle, got, a, b, k, b_is_nk=b_is_nk)
+
+
+def test_tf32_is_deterministic(dev):
+    a, b = workloads.c2_gemm(1024)
+    assert np.array_equal(dev.matmul(a, b), dev.matmul(a, b))
+
+
+def test_tf32_linearity(dev, oracle):
+    """(2A)B == 2(AB) exactly: scaling by a power of two commutes with truncation and rounding."""
+    a, b = workloads.c2_gemm(1024)
+    assert np.array_equal(dev.matmul(2 * a, b), 2 * dev.matmul(a, b))
+
+
+# ---- fused epilogues and Linear -----------------------------------------------------------
+
+@pytest.mark.parametrize("act", [0, 1, 2, 3, 4])
+def test_fused_activation(dev, lib, oracle, act):
+    rng = np.random.default_rng(act)
+    m, n, k = 256, 512, 128
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32) * np.float32(0.2)
+    ta, tb = dev.to_dev(a), dev.to_dev(b)
+    tc = dev.empty((m, n))
+    dev.check(lib.cudeep_b200_matmul_fused_act(dev.ptr(ta), dev.ptr(tb), dev.ptr(tc), m, n, k, act, None))
+    assert dev.sync_status() == 0
+    check_tf32(oracle, tc.cpu().numpy(), a, b, k, act=act)
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 512, 128), (130, 100, 72), (8, 10, 6)])
+@pytest.mark.parametrize("act", [0, 2])
+def test_linear_forward(dev, oracle, m, n, k, act):
+    rng = np.random.default_rng(m + act)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.uniform(-0.3, 0.3, (n, k)).astype(np.float32)
+    bias = rng.uniform(-0.5, 0.5, n).astype(np.float32)
+    got = dev.linear(x, w, bias, act=act)
+    if m >= 64 and n >= 64 and k >= 32 and k % 4 == 0:
+        check_tf32(oracle, got, x, w, k, b_is_nk=True, bias=bias, act=act)
+    else:
+        assert oracle.rel_frobenius(got, oracle.linear(x, w, bias, act=act)) <= 2e-5
+
+
+def test_linear_known_weights(dev):
+    w = np.array([[1, 0, 0], [0, 1, 0]], np.float32)
+    x = np.array([[1, 2, 3], [4, 5, 6]], np.float32)
+    assert np.allclose(dev.linear(x, w), [[1, 2], [4, 5]], rtol=1e-5)               # test_nn.py:50-62
+    y = dev.linear(np.array([[1, 2]], np.float32), np.eye(2, dtype=np.float32), np.array([100, 200], np.float32))
+    assert np.allclose(y, [[101, 202]], rtol=1e-5)                                   # test_nn.py:64-76
+
+
+def test_c3_linear_stack_reduced_batch(dev, oracle):
+    """C3's layer widths and initialisation at batch 256 (the oracle finishes in seconds)."""
+    x, w1, b1, w2, b2 = workloads.c3_linear_stack(batch=256)
+    h = dev.linear(x, w1, b1, act=2)
+    y = dev.linear(h, w2, b2)
+    h_ref = oracle.linear(x, w1, b1, act=2)
+    assert oracle.rel_frobenius(h, h_ref) <= TF32_TOL
+    y_ref = oracle.linear(h_ref.astype(np.float32), w2, b2)
+    assert oracle.rel_frobenius(y, y_ref) <= TF32_TOL
+
+
+# ---- host-buffer entry point ---------------------------------------------------------------
+
+def test_matmul_host_buffers(lib, cuda, oracle):
+    import ctypes
+    from cudeep_b200 import _lib
+    a, b = workloads.c2_gemm(1024)
+    c = np.full((1024, 1024), np.nan, np.float32)
+    p = lambda x: x.ctypes.data_as(ctypes.c_void_p)
+    _lib.check(lib.cudeep_b200_matmul_host_f32(p(a), p(b), p(c), 1024, 1024, 1024, 0))
+    assert _lib.device_status() == 0
+    assert oracle.rel_frobenius(c, oracle.gemm(a, b)) <= TF32_TOL
+    c2 = np.empty_like(c)
+    _lib.check(lib.cudeep_b200_matmul_host_f32(p(a), p(b), p(c2), 1024, 1024, 1024, 1))
+    assert oracle.rel_frobenius(c2, oracle.gemm(a, b)) <= FP32_TOL
