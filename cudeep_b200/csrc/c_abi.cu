@@ -122,7 +122,11 @@ int cudeep_b200_gemm_tf32_tuned(const float* A, const float* B, int b_is_nk, flo
         tune.ctas = ctas;
         tune.bn = bn;
         tune.raster_group = raster_group;
-        tune.max_ctas = max_ctas;
+        tune.max_ctas = max_ctas & 0xffff;
+        tune.stages = (max_ctas >> 16) & 0xff;      // packed: see cudeep_b200.h
+        tune.debug = static_cast<uint32_t>(max_ctas >> 24) & 0xfu;
+        tune.b_chunked = ((max_ctas >> 28) & 1) ? -1 : 0;
+        tune.katoms = (max_ctas >> 29) & 3;
         tune.b_lbo = b_lbo;
         tune.b_sbo = b_sbo;
         cudeep_b200::gemm_tf32(A, B, b_is_nk != 0, C, M, N, K, bias, bias_per_row != 0, epilogue, tune,

@@ -186,7 +186,7 @@ TilePlan plan_tile(int oh, int ow, int ctas) {
 template <int CTAS>
 void launch_conv(const float* xt, const float* wp, const float* bias, float* out, const ConvShape& s,
                  int cx, int cp, const TilePlan& plan, int act, cudaStream_t stream) {
-    using Cfg = UmmaConfig<CTAS, 256, false>;
+    using Cfg = UmmaConfig<CTAS, 256, false, 1>;
     using Prob = ConvProblem<CTAS>;
     const DeviceInfo& dev = device_info();
     const int oh = s.out_h(), ow = s.out_w();
@@ -235,6 +235,8 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     sched.b_sbo = 0;
     sched.umma_n = plan.box_w * plan.box_h;
     sched.tx_bytes = (Cfg::A_BYTES + uint32_t(sched.umma_n / CTAS) * UMMA_BK * 4) * CTAS;
+    sched.stages = Cfg::STAGES;
+    sched.debug = 0;
 
     const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;
     CB200_REQUIRE(num_tiles < (1LL << 30), "conv2d: too many tiles");
@@ -242,7 +244,7 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     if (groups < 1) groups = 1;
     if (groups > num_tiles) groups = num_tiles;
 
-    auto kernel = umma_tf32_kernel<CTAS, 256, false, Prob>;
+    auto kernel = umma_tf32_kernel<CTAS, 256, false, 1, Prob>;
     ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), Cfg::SMEM_BYTES);
 
     UmmaEpilogueArgs epi{bias, 1, act};

@@ -26,6 +26,7 @@ struct GemmProblem {
     long long ldc;
     int m, n;
     int vec_ok;            // rows of C are 16-byte aligned
+    int b_chunked;         // MN-major B described as {32, K, N/32}: one load brings every column chunk
 
     struct Tile {
         int m0;            // first C row of this CTA
@@ -51,18 +52,26 @@ struct GemmProblem {
         if constexpr (C == 1) {
             ptx::tma_load_2d(a_smem, &map_a, bar, k0, t.m0);
             if constexpr (B_MN_MAJOR) {
+                if (b_chunked) {
+                    ptx::tma_load_3d(b_smem, &map_b, bar, 0, k0, t.nb0 / 32);
+                } else {
 #pragma unroll
-                for (int j = 0; j < BN / CTAS / 32; ++j)
-                    ptx::tma_load_2d(b_smem + j * 4096, &map_b, bar, t.nb0 + j * 32, k0);
+                    for (int j = 0; j < BN / CTAS / 32; ++j)
+                        ptx::tma_load_2d(b_smem + j * 4096, &map_b, bar, t.nb0 + j * 32, k0);
+                }
             } else {
                 ptx::tma_load_2d(b_smem, &map_b, bar, k0, t.nb0);
             }
         } else {
             ptx::tma_load_2d_pair(a_smem, &map_a, bar, k0, t.m0);
             if constexpr (B_MN_MAJOR) {
+                if (b_chunked) {
+                    ptx::tma_load_3d_pair(b_smem, &map_b, bar, 0, k0, t.nb0 / 32);
+                } else {
 #pragma unroll
-                for (int j = 0; j < BN / CTAS / 32; ++j)
-                    ptx::tma_load_2d_pair(b_smem + j * 4096, &map_b, bar, t.nb0 + j * 32, k0);
+                    for (int j = 0; j < BN / CTAS / 32; ++j)
+                        ptx::tma_load_2d_pair(b_smem + j * 4096, &map_b, bar, t.nb0 + j * 32, k0);
+                }
             } else {
                 ptx::tma_load_2d_pair(b_smem, &map_b, bar, k0, t.nb0);
             }
@@ -101,10 +110,10 @@ struct GemmProblem {
     }
 };
 
-template <int CTAS, int BN, bool B_MN_MAJOR>
+template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS>
 void launch_variant(const float* a, const float* b, float* c, int m, int n, int k,
                     const UmmaEpilogueArgs& epi, const GemmTuning& tune, cudaStream_t stream) {
-    using Cfg = UmmaConfig<CTAS, BN, B_MN_MAJOR>;
+    using Cfg = UmmaConfig<CTAS, BN, B_MN_MAJOR, KATOMS>;
     using Prob = GemmProblem<CTAS, BN, B_MN_MAJOR>;
     const DeviceInfo& dev = device_info();
 
@@ -115,7 +124,17 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
         const uint32_t box[2] = {UMMA_BK, UMMA_BM};
         encode_tensor_map(&prob.map_a, a, 2, dims, strides, box, TmaSwizzle::B128);
     }
-    if (B_MN_MAJOR) {
+    prob.b_chunked = 0;
+    if (B_MN_MAJOR && n % 32 == 0 && tune.b_chunked >= 0) {
+        // B[K,N] seen as N/32 column chunks of 32 floats: {32, K, N/32} with strides
+        // {row pitch, 128 B}.  One box {32, 32, chunks} fills the stage in the order the
+        // MMA descriptors expect (chunk-major, 4096 B per chunk).
+        const uint64_t dims[3] = {32, uint64_t(k), uint64_t(n / 32)};
+        const uint64_t strides[2] = {uint64_t(n) * 4, 128};
+        const uint32_t box[3] = {32, UMMA_BK, uint32_t(Cfg::BN_CTA / 32)};
+        encode_tensor_map(&prob.map_b, b, 3, dims, strides, box, TmaSwizzle::B128Atom32);
+        prob.b_chunked = 1;
+    } else if (B_MN_MAJOR) {
         const uint64_t dims[2] = {uint64_t(n), uint64_t(k)};
         const uint64_t strides[1] = {uint64_t(n) * 4};
         const uint32_t box[2] = {32, UMMA_BK};
@@ -136,13 +155,15 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     sched.tiles_m = (m + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS);
     sched.tiles_n = (n + BN - 1) / BN;
     sched.k_blocks = (k + UMMA_BK - 1) / UMMA_BK;
-    sched.raster_group = tune.raster_group > 0 ? tune.raster_group : (CTAS == 2 ? 4 : 8);
+    sched.raster_group = tune.raster_group > 0 ? tune.raster_group : 16;
     sched.status = dev.status_word;
     sched.wait_limit_ns = 2000000000ull;
     sched.b_lbo = tune.b_lbo;
     sched.b_sbo = tune.b_sbo;
     sched.umma_n = BN;
     sched.tx_bytes = Cfg::TX_BYTES;
+    sched.stages = (tune.stages > 0 && tune.stages < Cfg::STAGES) ? tune.stages : Cfg::STAGES;
+    sched.debug = tune.debug;
 
     const int num_tiles = sched.tiles_m * sched.tiles_n;
     int max_ctas = tune.max_ctas > 0 ? tune.max_ctas : dev.num_sms;
@@ -150,7 +171,7 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     if (groups < 1) groups = 1;
     if (groups > num_tiles) groups = num_tiles;
 
-    auto kernel = umma_tf32_kernel<CTAS, BN, B_MN_MAJOR, Prob>;
+    auto kernel = umma_tf32_kernel<CTAS, BN, B_MN_MAJOR, KATOMS, Prob>;
     ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), Cfg::SMEM_BYTES);
 
     cudaLaunchConfig_t cfg{};
@@ -188,16 +209,22 @@ void dispatch(const float* a, const float* b, float* c, int m, int n, int k,
         if (ctas == 0) ctas = pick_ctas;
         if (bn == 0) bn = pick_bn;
     }
-#define CB200_CASE(C, N)                                                                  \
-    if (ctas == C && bn == N) {                                                           \
-        launch_variant<C, N, B_MN_MAJOR>(a, b, c, m, n, k, epi, tune, stream);            \
+    int katoms = tune.katoms;
+    if (katoms == 0) katoms = (ctas == 2 && bn == 256) ? 2 : 1;
+#define CB200_CASE(C, N, KA)                                                              \
+    if (ctas == C && bn == N && katoms == KA) {                                           \
+        launch_variant<C, N, B_MN_MAJOR, KA>(a, b, c, m, n, k, epi, tune, stream);        \
         return;                                                                           \
     }
-    CB200_CASE(1, 256)
-    CB200_CASE(1, 128)
-    CB200_CASE(1, 64)
-    CB200_CASE(2, 256)
-    CB200_CASE(2, 128)
+    CB200_CASE(1, 256, 1)
+    CB200_CASE(1, 128, 1)
+    CB200_CASE(1, 128, 2)
+    CB200_CASE(1, 64, 1)
+    CB200_CASE(1, 64, 2)
+    CB200_CASE(2, 256, 1)
+    CB200_CASE(2, 256, 2)
+    CB200_CASE(2, 128, 1)
+    CB200_CASE(2, 128, 2)
 #undef CB200_CASE
     CB200_REQUIRE(false, "unsupported TF32 GEMM tile configuration");
 }

@@ -51,15 +51,29 @@ struct UmmaSchedule {
     unsigned long long wait_limit_ns;
     uint32_t b_lbo, b_sbo; // non-zero: override the B descriptor offsets (bring-up aid)
     int umma_n;            // N of one MMA (<= BN, multiple of 32): accumulator columns in use
-    uint32_t tx_bytes;     // bytes all CTAs of the group deliver per stage
+    uint32_t tx_bytes;     // bytes all CTAs of the group deliver per stage (all atoms)
+    int stages;            // pipeline stages in use (<= UmmaConfig::STAGES)
+    // Diagnostics for performance bring-up (results are then meaningless):
+    //   bit 0: after the ring has been filled once the producer stops loading and only
+    //          signals the stages, so the MMA side runs without memory traffic;
+    //   bit 1: the MMA issuer skips the MMAs and only recycles stages, so the load side
+    //          runs alone;
+    //   bit 2: the MMA issuer ignores the stage ring (no waits, no stage commits) and the
+    //          producer does nothing: raw MMA issue rate;
+    //   bit 3: the epilogue neither reads TMEM nor stores.
+    uint32_t debug;
 };
 
-template <int CTAS, int BN, bool B_MN_MAJOR>
+// KATOMS: 32-wide K blocks ("atoms") per pipeline stage.  A stage is KATOMS
+// consecutive [A atom][B atom] pairs; barriers are exchanged once per stage, so
+// a larger KATOMS spends fewer of the MMA issuer's cycles on handshakes.
+template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS = 1>
 struct UmmaConfig {
     static constexpr int BN_CTA = BN / CTAS;                       // B rows staged by one CTA
-    static constexpr uint32_t A_BYTES = UMMA_BM * UMMA_BK * 4;
-    static constexpr uint32_t B_BYTES = BN_CTA * UMMA_BK * 4;
-    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr uint32_t A_BYTES = UMMA_BM * UMMA_BK * 4;     // one A atom
+    static constexpr uint32_t B_BYTES = BN_CTA * UMMA_BK * 4;      // one B atom (at most)
+    static constexpr uint32_t ATOM_BYTES = A_BYTES + B_BYTES;
+    static constexpr uint32_t STAGE_BYTES = ATOM_BYTES * KATOMS;
     static constexpr uint32_t TX_BYTES = STAGE_BYTES * CTAS;       // counted on the leader's barrier
     // 227 KB of shared memory per CTA, minus alignment slack and the barriers.
     static constexpr uint32_t SMEM_BUDGET = 232448 - 1024 - 512;
@@ -75,14 +89,15 @@ struct UmmaConfig {
 //   __device__ Tile decode(int tm, int tn, uint32_t cta_rank) const;
 //   __device__ void load(tile, kb, a_smem, b_smem, bar) const;     one lane, issues all TMA loads of a stage
 //   __device__ void store(tile, row_in_cta, col0, float (&v)[32]) const;   32 consecutive columns of one row
-template <int CTAS, int BN, bool B_MN_MAJOR, class Problem>
+template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, class Problem>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
 umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                  const UmmaEpilogueArgs epi) {
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM101_ALL) || \
     defined(__CUDA_ARCH_FEAT_SM103_ALL)
-    using Cfg = UmmaConfig<CTAS, BN, B_MN_MAJOR>;
+    using Cfg = UmmaConfig<CTAS, BN, B_MN_MAJOR, KATOMS>;
     constexpr int STAGES = Cfg::STAGES;
+    const int k_stages = (sched.k_blocks + KATOMS - 1) / KATOMS;   // stages per tile
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[STAGES];
@@ -142,22 +157,33 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
+        if (lane == 0 && !(sched.debug & 4u)) {
+            uint32_t stage = 0, phase = 0, issued = 0;
             for (int t = first_tile; t < num_tiles; t += tile_stride) {
                 int tm, tn;
                 tile_coords(t, tm, tn);
                 const auto tile = prob.decode(tm, tn, cta_rank);
-                for (int kb = 0; kb < sched.k_blocks; ++kb) {
+                for (int ks = 0; ks < k_stages; ++ks) {
                     if (!ptx::mbar_wait(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, wctx,
                                         UMMA_TIMEOUT_PRODUCER))
                         goto producer_done;
                     const uint32_t full_local = ptx::smem_u32(&bar_full[stage]);
-                    if (is_leader) ptx::mbar_arrive_expect_tx(full_local, sched.tx_bytes);
-                    const uint32_t full_bar = (CTAS == 2) ? ptx::mapa(full_local, 0) : full_local;
-                    const uint32_t a_smem = smem_base + stage * Cfg::STAGE_BYTES;
-                    prob.template load<CTAS>(tile, kb, a_smem, a_smem + Cfg::A_BYTES, full_bar);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    if ((sched.debug & 1u) && issued >= uint32_t(sched.stages)) {
+                        if (is_leader) ptx::mbar_arrive(full_local);
+                    } else {
+                        if (is_leader) ptx::mbar_arrive_expect_tx(full_local, sched.tx_bytes);
+                        const uint32_t full_bar = (CTAS == 2) ? ptx::mapa(full_local, 0) : full_local;
+                        // Atoms past the end of K are loaded too; their coordinates are out
+                        // of range, so they arrive as zeros and add nothing.
+#pragma unroll
+                        for (int j = 0; j < KATOMS; ++j) {
+                            const uint32_t a_smem = smem_base + stage * Cfg::STAGE_BYTES + j * Cfg::ATOM_BYTES;
+                            prob.template load<CTAS>(tile, ks * KATOMS + j, a_smem, a_smem + Cfg::A_BYTES,
+                                                     full_bar);
+                        }
+                    }
+                    ++issued;
+                    if (++stage == uint32_t(sched.stages)) { stage = 0; phase ^= 1u; }
                 }
             }
         }
@@ -180,6 +206,8 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
             const uint64_t b_base = ptx::smem_desc(
                 b_lbo, b_sbo, B_MN_MAJOR ? ptx::SMEM_LAYOUT_SW128_ATOM32 : ptx::SMEM_LAYOUT_SW128);
             constexpr uint32_t b_kstep = B_MN_MAJOR ? 1024u : UMMA_K * 4u;
+            const uint64_t a_desc0 = ptx::smem_desc_at(a_base, smem_base);
+            const uint64_t b_desc0 = ptx::smem_desc_at(b_base, smem_base + Cfg::A_BYTES);
 
             uint32_t stage = 0, phase = 0;
             int it = 0;
@@ -191,24 +219,44 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                     goto mma_done;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < sched.k_blocks; ++kb) {
-                    if (!ptx::mbar_wait(ptx::smem_u32(&bar_full[stage]), phase, wctx,
-                                        UMMA_TIMEOUT_MMA_FULL))
-                        goto mma_done;
-                    ptx::tc_fence_after();
-                    const uint32_t a_smem = smem_base + stage * Cfg::STAGE_BYTES;
-                    const uint32_t b_smem = a_smem + Cfg::A_BYTES;
+                const bool free_run = (sched.debug & 4u) != 0;
+                // The issuing thread is the critical path: every instruction between two
+                // MMAs shows up as an idle tensor pipe.  So the barrier of the NEXT stage
+                // is probed before this stage's MMAs are issued, and only waited on if
+                // that early look found it incomplete.
+                bool ready = free_run || ptx::mbar_test(ptx::smem_u32(&bar_full[stage]), phase);
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    if (!ready) {
+                        if (!ptx::mbar_wait(ptx::smem_u32(&bar_full[stage]), phase, wctx,
+                                            UMMA_TIMEOUT_MMA_FULL))
+                            goto mma_done;
+                    }
+                    uint32_t next_stage = stage + 1, next_phase = phase;
+                    if (next_stage == uint32_t(sched.stages)) { next_stage = 0; next_phase ^= 1u; }
+                    ready = free_run || ptx::mbar_test(ptx::smem_u32(&bar_full[next_stage]), next_phase);
+                    if (!(sched.debug & 2u)) {
+                        // Descriptors differ only in the start-address field (address >> 4),
+                        // so each one is the stage's first descriptor plus a constant.
+                        const uint64_t a_stage = a_desc0 + ((stage * Cfg::STAGE_BYTES) >> 4);
+                        const uint64_t b_stage = b_desc0 + ((stage * Cfg::STAGE_BYTES) >> 4);
 #pragma unroll
-                    for (int kk = 0; kk < UMMA_BK / UMMA_K; ++kk) {
-                        const uint64_t a_desc = ptx::smem_desc_at(a_base, a_smem + kk * UMMA_K * 4);
-                        const uint64_t b_desc = ptx::smem_desc_at(b_base, b_smem + kk * b_kstep);
-                        ptx::umma_tf32<CTAS>(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0);
+                        for (int j = 0; j < KATOMS; ++j) {
+#pragma unroll
+                            for (int kk = 0; kk < UMMA_BK / UMMA_K; ++kk) {
+                                const uint64_t a_desc = a_stage + ((j * Cfg::ATOM_BYTES + kk * UMMA_K * 4) >> 4);
+                                const uint64_t b_desc = b_stage + ((j * Cfg::ATOM_BYTES + kk * b_kstep) >> 4);
+                                ptx::umma_tf32<CTAS>(d_tmem, a_desc, b_desc, idesc, (ks | j | kk) != 0);
+                            }
+                        }
                     }
                     // Free the stage once these MMAs have read it (in both CTAs of a pair).
-                    const uint32_t empty_local = ptx::smem_u32(&bar_empty[stage]);
-                    ptx::umma_commit<CTAS>(empty_local);
-                    if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(empty_local, 1));
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    if (!free_run) {
+                        const uint32_t empty_local = ptx::smem_u32(&bar_empty[stage]);
+                        ptx::umma_commit<CTAS>(empty_local);
+                        if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(empty_local, 1));
+                    }
+                    stage = next_stage;
+                    phase = next_phase;
                 }
                 const uint32_t accf_local = ptx::smem_u32(&bar_acc_full[acc]);
                 ptx::umma_commit<CTAS>(accf_local);
@@ -236,7 +284,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
             ptx::tc_fence_after();
             const uint32_t t_row = tmem_base + acc * BN + ((quarter * 32u) << 16);
 #pragma unroll 1
-            for (int c = 0; c < sched.umma_n; c += 32) {
+            for (int c = 0; c < ((sched.debug & 8u) ? 0 : sched.umma_n); c += 32) {
                 uint32_t r[32];
                 ptx::tmem_ld_32x32(t_row + c, r);
                 ptx::tmem_ld_wait();

@@ -88,9 +88,16 @@ int cudeep_b200_linear_forward_f64(const double* x, const double* W, const doubl
 /* The TF32 tensor-core GEMM with explicit tile choices, for benchmarks and
  * bring-up.  b_is_nk: 0 = B is [K,N], 1 = B is [N,K].  bias: NULL, N values, or
  * M values when bias_per_row != 0.  ctas (1|2), bn (64|128|256), raster_group,
- * max_ctas: 0 selects the default.  b_lbo / b_sbo: 0, or a byte offset that
- * overrides the B shared-memory descriptor fields.  Fails instead of falling
- * back when the tensor-core path cannot take the problem. */
+ * max_ctas: 0 selects the default.  max_ctas is a packed field: bits 0-15 cap
+ * the resident CTAs, bits 16-23 limit the pipeline stages (0 = all that fit),
+ * bits 24-27 are performance diagnostics that make the result meaningless
+ * (1: stop loading operands once the stage ring is full, 2: skip the MMAs,
+ * 4: issue MMAs without the stage ring, 8: skip the epilogue's loads and stores);
+ * bit 28 loads B[K,N] as separate 32-column boxes instead of one chunked box;
+ * bits 29-30 set the 32-wide K blocks per pipeline stage (1 or 2, 0 = default).
+ * b_lbo / b_sbo: 0, or a byte offset that overrides the B shared-memory
+ * descriptor fields.  Fails instead of falling back when the tensor-core path
+ * cannot take the problem. */
 int cudeep_b200_gemm_tf32_tuned(const float* A, const float* B, int b_is_nk, float* C, int M, int N,
                                 int K, const float* bias, int bias_per_row, int epilogue, int ctas,
                                 int bn, int raster_group, int max_ctas, uint32_t b_lbo,

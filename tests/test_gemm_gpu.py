@@ -120,15 +120,27 @@ def test_c2_tf32_sampled_rows(dev, oracle, n):
     assert np.linalg.norm(colsum - want) / np.linalg.norm(want) <= TF32_TOL
 
 
-@pytest.mark.parametrize("ctas,bn", [(1, 256), (1, 128), (1, 64), (2, 256), (2, 128)])
+@pytest.mark.parametrize("ctas,bn,katoms", [(1, 256, 1), (1, 128, 1), (1, 128, 2), (1, 64, 1), (1, 64, 2),
+                                            (2, 256, 1), (2, 256, 2), (2, 128, 1), (2, 128, 2)])
 @pytest.mark.parametrize("b_is_nk", [False, True])
-def test_tf32_every_tile_configuration(dev, oracle, ctas, bn, b_is_nk):
+def test_tf32_every_tile_configuration(dev, oracle, ctas, bn, katoms, b_is_nk):
     rng = np.random.default_rng(ctas * 1000 + bn + int(b_is_nk))
-    m, n, k = 640, 768, 416          # several tiles per CTA, K not a multiple of 32
+    m, n, k = 640, 768, 416          # several tiles per CTA; 13 K blocks: odd, last one partial
     a = rng.standard_normal((m, k), dtype=np.float32)
     b = rng.standard_normal((n, k) if b_is_nk else (k, n), dtype=np.float32)
-    got = dev.gemm_tuned(a, b, b_is_nk, ctas=ctas, bn=bn, max_ctas=8)   # 8 CTAs: each walks many tiles
+    got = dev.gemm_tuned(a, b, b_is_nk, ctas=ctas, bn=bn, katoms=katoms, max_ctas=8)   # 8 CTAs walk many tiles each
     check_tf32(oracle, got, a, b, k, b_is_nk=b_is_nk)
+
+
+def test_tf32_b_loaded_as_separate_boxes(dev, oracle):
+    """B[K,N] with N a multiple of 32 normally takes one chunked TMA box; the per-chunk path must agree."""
+    rng = np.random.default_rng(77)
+    a = rng.standard_normal((384, 160), dtype=np.float32)
+    b = rng.standard_normal((160, 512), dtype=np.float32)
+    one = dev.gemm_tuned(a, b, False, ctas=2, bn=256)
+    many = dev.gemm_tuned(a, b, False, ctas=2, bn=256, unchunked=True)
+    assert np.array_equal(one, many)
+    check_tf32(oracle, one, a, b, 160)
 
 
 @pytest.mark.parametrize("m,n,k", [(64, 64, 32), (100, 260, 36), (129, 132, 200), (1000, 72, 64), (257, 1028, 516)])
