@@ -53,6 +53,9 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--suite", action="store_true",
+                    help="instead of the headline line, time every benchmark configuration next to "
+                         "cuBLAS / cuDNN (through torch) and the reference's kernels; one JSON line each")
     return ap.parse_args()
 
 
@@ -361,8 +364,131 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------- suite
+
+def run_suite(args):
+    """All single-GPU configurations side by side.  Device-resident inputs, CUDA events, an L2
+    flush before every timed launch (several inputs are smaller than the 126 MB L2)."""
+    import torch
+    import torch.nn.functional as F
+    from cudeep_b200 import _lib, workloads
+    from oracle import oracle as o
+    lib = _lib.load()
+    torch.cuda.set_device(0)
+    ref = ctypes.CDLL(str(o.REF_LIB_PATH)) if o.REF_LIB_PATH.exists() else None
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    flush = torch.empty(256 * 1024 * 1024 // 4, device="cuda")
+    P = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return float(np.median(ts)), float(np.min(ts))
+
+    def emit(name, flops, rows, **extra):
+        line = {"suite": name, "gflop": flops / 1e9}
+        for key, (med, mn) in rows.items():
+            line[key] = {"ms_median": med, "ms_min": mn, "tflops": flops / (med * 1e-3) / 1e12}
+        for key in rows:
+            if key != "ours":
+                line[f"ours_over_{key}"] = rows[key][0] / rows["ours"][0]
+        line.update(extra)
+        print(json.dumps(line), flush=True)
+
+    def ok(rc):
+        if rc != 0:
+            raise RuntimeError(lib.cudeep_b200_last_error().decode())
+
+    # C1: strict FP32 512^3
+    a_np, b_np = workloads.c1_sgemm()
+    a, b = torch.from_numpy(a_np).cuda(), torch.from_numpy(b_np).cuda()
+    c = torch.empty((512, 512), device="cuda")
+    rows = {"ours": timed(lambda: ok(lib.cudeep_b200_matmul_f32_strict(P(a), P(b), P(c), 512, 512, 512, stream)), 50)}
+    torch.backends.cuda.matmul.allow_tf32 = False
+    rows["cublas_fp32"] = timed(lambda: torch.matmul(a, b, out=c), 50)
+    if ref is not None:
+        rows["reference"] = timed(lambda: ref.cudeep_ref_matmul_f32_strict(P(a), P(b), P(c), 512, 512, 512, stream), 50)
+    emit("C1 FP32 SGEMM 512^3", 2.0 * 512 ** 3, rows)
+
+    # C2: TF32 square GEMMs
+    torch.backends.cuda.matmul.allow_tf32 = True
+    for n in workloads.C2_SIZES:
+        a = torch.randn((n, n), device="cuda")
+        b = torch.randn((n, n), device="cuda")
+        c = torch.empty((n, n), device="cuda")
+        iters = 30 if n <= 4096 else 15
+        rows = {"ours": timed(lambda: ok(lib.cudeep_b200_matmul_f32(P(a), P(b), P(c), n, n, n, stream)), iters),
+                "cublas_tf32": timed(lambda: torch.matmul(a, b, out=c), iters)}
+        if ref is not None:
+            rows["reference"] = timed(lambda: ref.cudeep_ref_matmul_f32(P(a), P(b), P(c), n, n, n, stream), max(3, iters // 5))
+        emit(f"C2 TF32 GEMM {n}^3", 2.0 * n ** 3, rows)
+
+    # C3: Linear(4096 -> 16384, GELU) -> Linear(16384 -> 4096), batch 8192
+    m, d_in, d_h, d_out = 8192, 4096, 16384, 4096
+    x = torch.randn((m, d_in), device="cuda")
+    w1 = (torch.rand((d_h, d_in), device="cuda") * 2 - 1) * (6.0 / d_in) ** 0.5
+    b1 = (torch.rand(d_h, device="cuda") * 2 - 1) * 0.01
+    w2 = (torch.rand((d_out, d_h), device="cuda") * 2 - 1) * (6.0 / d_h) ** 0.5
+    b2 = (torch.rand(d_out, device="cuda") * 2 - 1) * 0.01
+    h = torch.empty((m, d_h), device="cuda")
+    y = torch.empty((m, d_out), device="cuda")
+
+    def ours_c3():
+        ok(lib.cudeep_b200_linear_forward_f32(P(x), P(w1), P(b1), P(h), m, d_h, d_in, 2, stream))
+        ok(lib.cudeep_b200_linear_forward_f32(P(h), P(w2), P(b2), P(y), m, d_out, d_h, 0, stream))
+
+    def torch_c3():
+        F.linear(F.gelu(F.linear(x, w1, b1), approximate="tanh"), w2, b2)
+
+    rows = {"ours": timed(ours_c3, 8), "cublas_tf32_torch": timed(torch_c3, 8)}
+    if ref is not None:
+        w1t, w2t = w1.t().contiguous(), w2.t().contiguous()
+
+        def ref_c3():       # the reference's two GEMMs only: its transpose copies, bias and GELU passes are not counted
+            ref.cudeep_ref_matmul_f32(P(x), P(w1t), P(h), m, d_h, d_in, stream)
+            ref.cudeep_ref_matmul_f32(P(h), P(w2t), P(y), m, d_out, d_h, stream)
+
+        rows["reference_gemms_only"] = timed(ref_c3, 3)
+    emit("C3 Linear 8192x4096 -> 16384 (GELU) -> 4096", 2.0 * m * d_in * d_h * 2, rows)
+    del x, w1, w2, h, y
+
+    # C4: conv 3x3, 64 x 256 x 56 x 56 -> 256, bias + ReLU
+    nb, ch, size, oc = 64, 256, 56, 256
+    xc = torch.randn((nb, ch, size, size), device="cuda")
+    wc = torch.randn((oc, ch, 3, 3), device="cuda") * (2.0 / (ch * 9)) ** 0.5
+    bc = (torch.rand(oc, device="cuda") * 2 - 1) * 0.01
+    yc = torch.empty((nb, oc, size, size), device="cuda")
+    torch.backends.cudnn.allow_tf32 = True
+    torch.backends.cudnn.benchmark = True
+    rows = {"ours": timed(lambda: ok(lib.cudeep_b200_conv2d_forward_fused_f32(
+        P(xc), P(wc), P(bc), P(yc), nb, ch, oc, size, size, 3, 3, 1, 1, 1, 1, 1, stream)), 15),
+            "cudnn_tf32_torch": timed(lambda: F.relu(F.conv2d(xc, wc, bc, padding=1)), 15)}
+    xl = xc.contiguous(memory_format=torch.channels_last)
+    rows["cudnn_tf32_torch_nhwc_input"] = timed(lambda: F.relu(F.conv2d(xl, wc, bc, padding=1)), 15)
+    if ref is not None:
+        rows["reference_no_relu"] = timed(lambda: ref.cudeep_ref_conv2d_forward_f32(
+            P(xc), P(wc), P(bc), P(yc), nb, ch, oc, size, size, 3, 3, 1, 1, 1, 1, stream), 5)
+    emit("C4 conv 3x3 64x256x56x56 -> 256, bias + ReLU", workloads.conv_flops(nb, ch, oc, size, size, 3, 3), rows)
+    status = _lib.device_status(True)
+    if status != 0:
+        raise RuntimeError(f"kernel status word {status}")
+
+
 def main():
     args = parse_args()
+    if args.suite:
+        run_suite(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

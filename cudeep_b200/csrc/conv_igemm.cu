@@ -76,6 +76,8 @@ struct ConvProblem {
     int c_blocks;          // Cp / 32
     int k_w;
     int p_h, p_w;
+    int total_kb;          // K blocks of the reduction: KH * KW * c_blocks
+    int batch;
     int contig;            // box_w == OW: the tile's pixels are contiguous in the output plane
     int vec_ok;            // 128-bit stores are aligned for every tile
 
@@ -108,12 +110,16 @@ struct ConvProblem {
         const int c0 = (kb - tap * c_blocks) * UMMA_BK;
         const int kh = tap / k_w;
         const int kw = tap - kh * k_w;
+        // A K block past the end of the reduction (a stage's padding) must read zeros on
+        // both sides: the filter coordinate is out of range by itself, the image index is
+        // pushed out of range here.
+        const int n = kb < total_kb ? t.n : batch;
         if constexpr (C == 1) {
             ptx::tma_load_2d(a_smem, &map_w, bar, kb * UMMA_BK, t.oc0);
-            ptx::tma_load_4d(b_smem, &map_x, bar, c0, t.ow0 + kw - p_w, t.hb0 + kh - p_h, t.n);
+            ptx::tma_load_4d(b_smem, &map_x, bar, c0, t.ow0 + kw - p_w, t.hb0 + kh - p_h, n);
         } else {
             ptx::tma_load_2d_pair(a_smem, &map_w, bar, kb * UMMA_BK, t.oc0);
-            ptx::tma_load_4d_pair(b_smem, &map_x, bar, c0, t.ow0 + kw - p_w, t.hb0 + kh - p_h, t.n);
+            ptx::tma_load_4d_pair(b_smem, &map_x, bar, c0, t.ow0 + kw - p_w, t.hb0 + kh - p_h, n);
         }
     }
     __device__ __forceinline__ void store(const Tile& t, int row_in_cta, int c0, float (&v)[32],
@@ -183,7 +189,7 @@ TilePlan plan_tile(int oh, int ow, int ctas) {
     return best;
 }
 
-template <int CTAS>
+template <int CTAS, int KATOMS>
 void launch_conv(const float* xt, const float* wp, const float* bias, float* out, const ConvShape& s,
                  int cx, int cp, const TilePlan& plan, int act, cudaStream_t stream) {
     using Cfg = UmmaConfig<CTAS, 256, false, 1>;
@@ -218,6 +224,8 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     prob.k_w = s.k_w;
     prob.p_h = s.p_h;
     prob.p_w = s.p_w;
+    prob.total_kb = taps * prob.c_blocks;
+    prob.batch = s.batch;
     prob.contig = (plan.box_w == ow) ? 1 : 0;
     prob.vec_ok = (prob.contig && ((plan.box_h * ow) % 4 == 0) && ((oh * ow) % 4 == 0) &&
                    ((reinterpret_cast<uintptr_t>(out) & 15u) == 0)) ? 1 : 0;
@@ -234,7 +242,7 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     sched.b_lbo = 0;
     sched.b_sbo = 0;
     sched.umma_n = plan.box_w * plan.box_h;
-    sched.tx_bytes = (Cfg::A_BYTES + uint32_t(sched.umma_n / CTAS) * UMMA_BK * 4) * CTAS;
+    sched.tx_bytes = (Cfg::A_BYTES + uint32_t(sched.umma_n / CTAS) * UMMA_BK * 4) * CTAS * KATOMS;
     sched.stages = Cfg::STAGES;
     sched.debug = 0;
 
@@ -333,8 +341,10 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
         plan = plan_tile(oh, ow, 1);
     }
     CB200_REQUIRE(plan.box_w > 0, "conv2d: no tile shape fits this output size");
-    if (ctas == 2) launch_conv<2>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
-    else launch_conv<1>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+    // A CTA pair stages at most 32 KB per K block, so two blocks share a pipeline
+    // stage and the barrier handshake is paid half as often.
+    if (ctas == 2) launch_conv<2, 2>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+    else launch_conv<1, 1>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
 }
 
 void conv2d_igemm(const float* input, const float* weight, const float* bias, float* output,
