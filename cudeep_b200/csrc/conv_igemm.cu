@@ -192,7 +192,7 @@ TilePlan plan_tile(int oh, int ow, int ctas) {
 template <int CTAS, int KATOMS>
 void launch_conv(const float* xt, const float* wp, const float* bias, float* out, const ConvShape& s,
                  int cx, int cp, const TilePlan& plan, int act, cudaStream_t stream) {
-    using Cfg = UmmaConfig<CTAS, 256, false, 1>;
+    using Cfg = UmmaConfig<CTAS, 256, false, KATOMS>;
     using Prob = ConvProblem<CTAS>;
     const DeviceInfo& dev = device_info();
     const int oh = s.out_h(), ow = s.out_w();
@@ -252,7 +252,7 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     if (groups < 1) groups = 1;
     if (groups > num_tiles) groups = num_tiles;
 
-    auto kernel = umma_tf32_kernel<CTAS, 256, false, 1, Prob>;
+    auto kernel = umma_tf32_kernel<CTAS, 256, false, KATOMS, Prob>;
     ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), Cfg::SMEM_BYTES);
 
     UmmaEpilogueArgs epi{bias, 1, act};
