@@ -8,6 +8,7 @@
 #include "cudeep/memory.cuh"
 #include "conv_igemm.h"
 #include "gemm_tf32.h"
+#include "abi_error.h"
 
 #include <string>
 
@@ -60,6 +61,10 @@ cudaStream_t host_call_stream() {
 }
 
 }  // namespace
+
+namespace cudeep_b200 {
+void set_last_error(const std::string& message) { g_last_error = message; }
+}  // namespace cudeep_b200
 
 extern "C" {
 

@@ -123,6 +123,32 @@ int cudeep_b200_conv2d_forward_fused_f32(const float* input, const float* weight
                                          int kernel_w, int stride_h, int stride_w, int pad_h,
                                          int pad_w, int epilogue, cudeep_b200_stream_t stream);
 
+/* Conv2d forward (+ bias + activation) that allocates nothing.  No counterpart in the
+ * reference: it exists for callers with a fixed device-memory plan - a serving process
+ * whose own allocator owns all free memory, or a loop that cannot take an allocation's
+ * implicit synchronisation or its failure mid-step.  Same arguments and results as
+ * cudeep_b200_conv2d_forward_fused_f32; the scratch (NHWC copy of the input + packed
+ * filters) lives in a 32 MiB array built into the library, which every GPU that loads
+ * the library holds until the process exits.
+ *   - Shapes whose scratch exceeds cudeep_b200_conv2d_noalloc_capacity() are refused
+ *     with an error that states both sizes (C*H*W*batch*4 bytes, channels rounded up
+ *     to 4, plus the filters with channels rounded up to 32).  Shapes the tensor-core
+ *     path does not take (stride > 1, tiny) run the direct kernel and need no scratch.
+ *   - The first call on each device looks up the array's device address; make that
+ *     call before starting any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's
+ *     contents; each call rewrites every byte it later reads, so nothing needs
+ *     clearing, but two calls that overlap on the GPU (different streams, no
+ *     dependency) race on it.  Serialise them. */
+int cudeep_b200_conv2d_forward_noalloc_f32(const float* input, const float* weight, const float* bias,
+                                           float* output, int batch, int in_channels,
+                                           int out_channels, int in_h, int in_w, int kernel_h,
+                                           int kernel_w, int stride_h, int stride_w, int pad_h,
+                                           int pad_w, int epilogue, cudeep_b200_stream_t stream);
+
+/* Bytes of built-in scratch behind cudeep_b200_conv2d_forward_noalloc_f32. */
+size_t cudeep_b200_conv2d_noalloc_capacity(void);
+
 /* FP64 convolution.  Replaces launch_conv2d_forward_kernel<double>. */
 int cudeep_b200_conv2d_forward_f64(const double* input, const double* weight, const double* bias,
                                    double* output, int batch, int in_channels, int out_channels,
