@@ -35,6 +35,27 @@ PROTOTYPES = {
     "cudeep_b200_matmul_host_f32": (c_int, [_fp, _fp, _fp, c_int, c_int, c_int, c_int]),
     "cudeep_b200_linear_forward_host_f32": (c_int, [_fp, _fp, _fp, _fp, c_int, c_int, c_int, c_int]),
     "cudeep_b200_conv2d_forward_host_f32": (c_int, [_fp, _fp, _fp, _fp] + [c_int] * 12),
+    "cudeep_b200_memcpy_h2d": (c_int, [c_void_p, c_void_p, c_size_t, _stream]),
+    "cudeep_b200_memcpy_d2h": (c_int, [c_void_p, c_void_p, c_size_t, _stream]),
+    "cudeep_b200_memcpy_d2d": (c_int, [c_void_p, c_void_p, c_size_t, _stream]),
+    "cudeep_b200_stream_synchronize": (c_int, [_stream]),
+    "cudeep_b200_device_synchronize": (c_int, []),
+    "cudeep_b200_strided_copy": (c_int, [c_void_p, c_void_p, c_int, POINTER(ctypes.c_longlong),
+                                         POINTER(ctypes.c_longlong), c_int, _stream]),
+    "cudeep_b200_fill_f32": (c_int, [c_void_p, c_float, ctypes.c_longlong, _stream]),
+    "cudeep_b200_fill_f64": (c_int, [c_void_p, c_double, ctypes.c_longlong, _stream]),
+    "cudeep_b200_broadcast_add_f32": (c_int, [_fp, _fp, _fp, ctypes.c_longlong, c_int, _stream]),
+    "cudeep_b200_broadcast_add_f64": (c_int, [_fp, _fp, _fp, ctypes.c_longlong, c_int, _stream]),
+    "cudeep_b200_activation_f32": (c_int, [_fp, _fp, ctypes.c_longlong, c_int, _stream]),
+    "cudeep_b200_stream_create": (c_int, [POINTER(c_void_p)]),
+    "cudeep_b200_stream_destroy": (c_int, [_stream]),
+    "cudeep_b200_event_create": (c_int, [POINTER(c_void_p)]),
+    "cudeep_b200_event_destroy": (c_int, [c_void_p]),
+    "cudeep_b200_event_record": (c_int, [c_void_p, _stream]),
+    "cudeep_b200_event_synchronize": (c_int, [c_void_p]),
+    "cudeep_b200_event_elapsed_ms": (c_int, [c_void_p, c_void_p, POINTER(c_float)]),
+    "cudeep_b200_device_info": (c_int, [POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int),
+                                        POINTER(c_size_t)]),
     "cudeep_b200_pool_alloc": (c_int, [c_size_t, POINTER(c_void_p)]),
     "cudeep_b200_pool_free": (c_int, [c_void_p]),
     "cudeep_b200_pool_release_cached": (c_int, []),

@@ -9,6 +9,8 @@
 #include "conv_igemm.h"
 #include "gemm_tf32.h"
 #include "abi_error.h"
+#include "tensor_ops.h"
+#include "cudeep/stream.cuh"
 
 #include <string>
 
@@ -246,6 +248,120 @@ int cudeep_b200_conv2d_forward_host_f32(const float* input, const float* weight,
                                                      pad_w, as_epilogue(epilogue), s);
         cudeep::memcpy_d2h(output, dy.ptr, y_bytes, s);
         CB200_CUDA(cudaStreamSynchronize(s));
+    });
+}
+
+// ---------------------------------------------------------------- tensor plumbing
+
+int cudeep_b200_memcpy_h2d(void* dst, const void* src, size_t nbytes, cudeep_b200_stream_t stream) {
+    return guarded([&] { cudeep::memcpy_h2d(dst, src, nbytes, as_stream(stream)); });
+}
+int cudeep_b200_memcpy_d2h(void* dst, const void* src, size_t nbytes, cudeep_b200_stream_t stream) {
+    return guarded([&] { cudeep::memcpy_d2h(dst, src, nbytes, as_stream(stream)); });
+}
+int cudeep_b200_memcpy_d2d(void* dst, const void* src, size_t nbytes, cudeep_b200_stream_t stream) {
+    return guarded([&] { cudeep::memcpy_d2d(dst, src, nbytes, as_stream(stream)); });
+}
+int cudeep_b200_stream_synchronize(cudeep_b200_stream_t stream) {
+    return guarded([&] { CB200_CUDA(cudaStreamSynchronize(as_stream(stream))); });
+}
+int cudeep_b200_device_synchronize(void) {
+    return guarded([&] { CB200_CUDA(cudaDeviceSynchronize()); });
+}
+
+int cudeep_b200_strided_copy(const void* src, void* dst, int ndim, const long long* shape,
+                             const long long* strides, int elem_size, cudeep_b200_stream_t stream) {
+    return guarded([&] {
+        CB200_REQUIRE(src != nullptr && dst != nullptr && shape != nullptr && strides != nullptr,
+                      "strided copy: null pointer");
+        CB200_REQUIRE(ndim >= 1 && ndim <= cudeep_b200::StridedView::kMaxDims, "strided copy: rank must be 1..8");
+        cudeep_b200::StridedView view{};
+        view.ndim = ndim;
+        for (int d = 0; d < ndim; ++d) {
+            view.shape[d] = shape[d];
+            view.strides[d] = strides[d];
+        }
+        if (elem_size == 4)
+            cudeep_b200::strided_copy<float>(static_cast<const float*>(src), static_cast<float*>(dst), view,
+                                             as_stream(stream));
+        else if (elem_size == 8)
+            cudeep_b200::strided_copy<double>(static_cast<const double*>(src), static_cast<double*>(dst), view,
+                                              as_stream(stream));
+        else
+            CB200_REQUIRE(false, "strided copy: element size must be 4 or 8");
+    });
+}
+
+int cudeep_b200_fill_f32(float* dst, float value, long long count, cudeep_b200_stream_t stream) {
+    return guarded([&] { cudeep_b200::fill<float>(dst, value, count, as_stream(stream)); });
+}
+int cudeep_b200_fill_f64(double* dst, double value, long long count, cudeep_b200_stream_t stream) {
+    return guarded([&] { cudeep_b200::fill<double>(dst, value, count, as_stream(stream)); });
+}
+
+int cudeep_b200_broadcast_add_f32(const float* matrix, const float* row, float* out, long long rows, int cols,
+                                  cudeep_b200_stream_t stream) {
+    return guarded([&] { cudeep_b200::add_row<float>(matrix, row, out, rows, cols, as_stream(stream)); });
+}
+int cudeep_b200_broadcast_add_f64(const double* matrix, const double* row, double* out, long long rows,
+                                  int cols, cudeep_b200_stream_t stream) {
+    return guarded([&] { cudeep_b200::add_row<double>(matrix, row, out, rows, cols, as_stream(stream)); });
+}
+
+int cudeep_b200_activation_f32(const float* x, float* y, long long count, int epilogue,
+                               cudeep_b200_stream_t stream) {
+    return guarded([&] { cudeep_b200::activation(x, y, count, epilogue, as_stream(stream)); });
+}
+
+// ---------------------------------------------------------------- streams and events
+
+int cudeep_b200_stream_create(cudeep_b200_stream_t* stream) {
+    return guarded([&] {
+        CB200_REQUIRE(stream != nullptr, "stream_create: null result pointer");
+        cudaStream_t s = nullptr;
+        CB200_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+        *stream = s;
+    });
+}
+int cudeep_b200_stream_destroy(cudeep_b200_stream_t stream) {
+    return guarded([&] { CB200_CUDA(cudaStreamDestroy(as_stream(stream))); });
+}
+int cudeep_b200_event_create(void** event) {
+    return guarded([&] {
+        CB200_REQUIRE(event != nullptr, "event_create: null result pointer");
+        cudaEvent_t e = nullptr;
+        CB200_CUDA(cudaEventCreate(&e));
+        *event = e;
+    });
+}
+int cudeep_b200_event_destroy(void* event) {
+    return guarded([&] { CB200_CUDA(cudaEventDestroy(static_cast<cudaEvent_t>(event))); });
+}
+int cudeep_b200_event_record(void* event, cudeep_b200_stream_t stream) {
+    return guarded([&] { CB200_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(event), as_stream(stream))); });
+}
+int cudeep_b200_event_synchronize(void* event) {
+    return guarded([&] { CB200_CUDA(cudaEventSynchronize(static_cast<cudaEvent_t>(event))); });
+}
+int cudeep_b200_event_elapsed_ms(void* start, void* end, float* ms) {
+    return guarded([&] {
+        CB200_REQUIRE(ms != nullptr, "event_elapsed_ms: null result pointer");
+        CB200_CUDA(cudaEventElapsedTime(ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(end)));
+    });
+}
+
+int cudeep_b200_device_info(int* device, int* sm_count, int* cc_major, int* cc_minor, size_t* total_mem) {
+    return guarded([&] {
+        const cudeep_b200::DeviceInfo& info = cudeep_b200::device_info();
+        if (device) *device = info.device;
+        if (sm_count) *sm_count = info.num_sms;
+        if (cc_major) *cc_major = info.cc_major;
+        if (cc_minor) *cc_minor = info.cc_minor;
+        if (total_mem) {
+            size_t free_b = 0, total_b = 0;
+            CB200_CUDA(cudaMemGetInfo(&free_b, &total_b));
+            *total_mem = total_b;
+        }
     });
 }
 

@@ -196,21 +196,37 @@ void dispatch(const float* a, const float* b, float* c, int m, int n, int k,
     int ctas = tune.ctas;
     int bn = tune.bn;
     if (ctas == 0 || bn == 0) {
-        // Largest tile that still gives every SM work; small problems take
-        // narrower tiles so more CTAs run.
-        const long long sms = dev.num_sms;
-        auto tiles = [&](int tile_m, int tile_n) {
-            return static_cast<long long>((m + tile_m - 1) / tile_m) * ((n + tile_n - 1) / tile_n);
-        };
+        // Pick the tile by a small cost model.  An MMA costs the issuing thread about the
+        // same time whatever its N (measured on B200: ~150 clk for a CTA pair at N = 256,
+        // ~185 / 143 / 121 clk for one CTA at N = 256 / 128 / 64), so the time of a launch
+        // is waves x MMAs per tile x that cost, plus a fixed start-up that is larger for
+        // clusters.  Wide tiles win as soon as they fill the machine; narrow ones only
+        // help problems too small to give every SM a wide tile.
+        struct Candidate { int ctas, bn; double mma_clk, fixed_clk; };
+        const Candidate candidates[] = {
+            {2, 256, 150.0, 9000.0}, {1, 256, 185.0, 4000.0}, {1, 128, 143.0, 4000.0}, {1, 64, 121.0, 4000.0}};
+        const double k_mmas = 4.0 * ((k + UMMA_BK - 1) / UMMA_BK);
+        double best = 0.0;
         int pick_ctas = 1, pick_bn = 64;
-        if (tiles(256, 256) * 2 >= sms) { pick_ctas = 2; pick_bn = 256; }
-        else if (tiles(128, 256) >= sms) { pick_ctas = 1; pick_bn = 256; }
-        else if (tiles(128, 128) >= sms) { pick_ctas = 1; pick_bn = 128; }
+        for (const Candidate& cand : candidates) {
+            if (ctas != 0 && cand.ctas != ctas) continue;
+            if (bn != 0 && cand.bn != bn) continue;
+            const long long tiles = static_cast<long long>((m + 128 * cand.ctas - 1) / (128 * cand.ctas)) *
+                                    ((n + cand.bn - 1) / cand.bn);
+            const long long slots = dev.num_sms / cand.ctas;
+            const long long waves = (tiles + slots - 1) / slots;
+            const double cost = waves * k_mmas * cand.mma_clk + cand.fixed_clk;
+            if (best == 0.0 || cost < best) {
+                best = cost;
+                pick_ctas = cand.ctas;
+                pick_bn = cand.bn;
+            }
+        }
         if (ctas == 0) ctas = pick_ctas;
         if (bn == 0) bn = pick_bn;
     }
     int katoms = tune.katoms;
-    if (katoms == 0) katoms = (ctas == 2 && bn == 256) ? 2 : 1;
+    if (katoms == 0) katoms = (ctas == 2 || bn <= 128) ? 2 : 1;
 #define CB200_CASE(C, N, KA)                                                              \
     if (ctas == C && bn == N && katoms == KA) {                                           \
         launch_variant<C, N, B_MN_MAJOR, KA>(a, b, c, m, n, k, epi, tune, stream);        \

@@ -177,6 +177,49 @@ int cudeep_b200_conv2d_forward_host_f32(const float* input, const float* weight,
                                         int in_h, int in_w, int kernel_h, int kernel_w, int stride_h,
                                         int stride_w, int pad_h, int pad_w, int epilogue);
 
+/* ---- tensor plumbing ------------------------------------------------------------------- */
+
+/* Copies; asynchronous on `stream`, blocking when stream is NULL
+ * (memcpy_h2d / d2h / d2d, include/cudeep/memory.cuh:41-45, src/memory.cu:75-97). */
+int cudeep_b200_memcpy_h2d(void* dst, const void* src, size_t nbytes, cudeep_b200_stream_t stream);
+int cudeep_b200_memcpy_d2h(void* dst, const void* src, size_t nbytes, cudeep_b200_stream_t stream);
+int cudeep_b200_memcpy_d2d(void* dst, const void* src, size_t nbytes, cudeep_b200_stream_t stream);
+int cudeep_b200_stream_synchronize(cudeep_b200_stream_t stream);   /* Stream::synchronize, stream.cuh:18 */
+int cudeep_b200_device_synchronize(void);
+
+/* dst (contiguous over `shape`) = src read through `strides` (in elements); rank 1..8,
+ * elem_size 4 or 8.  Replaces Tensor::contiguous / launch_strided_copy
+ * (src/tensor.cu:47-68,256-281) without its device allocations and stream synchronisation. */
+int cudeep_b200_strided_copy(const void* src, void* dst, int ndim, const long long* shape,
+                             const long long* strides, int elem_size, cudeep_b200_stream_t stream);
+
+/* Tensor::fill_ (src/tensor.cu:422-446). */
+int cudeep_b200_fill_f32(float* dst, float value, long long count, cudeep_b200_stream_t stream);
+int cudeep_b200_fill_f64(double* dst, double value, long long count, cudeep_b200_stream_t stream);
+
+/* out[i, j] = matrix[i, j] + row[j]: broadcast_add
+ * (src/bindings/module.cpp:664-694, src/kernels/elementwise_kernel.cu:187-204). */
+int cudeep_b200_broadcast_add_f32(const float* matrix, const float* row, float* out, long long rows,
+                                  int cols, cudeep_b200_stream_t stream);
+int cudeep_b200_broadcast_add_f64(const double* matrix, const double* row, double* out, long long rows,
+                                  int cols, cudeep_b200_stream_t stream);
+
+/* y = act(x) as a separate pass, for an activation module that does not follow a Linear or
+ * Conv2d it could be fused into (activation_fwd kernels, src/kernels/activation_kernel.cu:70-95). */
+int cudeep_b200_activation_f32(const float* x, float* y, long long count, int epilogue,
+                               cudeep_b200_stream_t stream);
+
+/* ---- streams, events, device (include/cudeep/stream.cuh:8-44, module.cpp:642-658) ------- */
+
+int cudeep_b200_stream_create(cudeep_b200_stream_t* stream);
+int cudeep_b200_stream_destroy(cudeep_b200_stream_t stream);
+int cudeep_b200_event_create(void** event);
+int cudeep_b200_event_destroy(void* event);
+int cudeep_b200_event_record(void* event, cudeep_b200_stream_t stream);
+int cudeep_b200_event_synchronize(void* event);
+int cudeep_b200_event_elapsed_ms(void* start, void* end, float* ms);
+int cudeep_b200_device_info(int* device, int* sm_count, int* cc_major, int* cc_minor, size_t* total_mem);
+
 /* ---- memory pool (cudeep::MemoryPool, include/cudeep/memory.cuh:13-46) ------------------- */
 
 int cudeep_b200_pool_alloc(size_t nbytes, void** ptr);     /* MemoryPool::allocate   */
