@@ -42,7 +42,7 @@ NOMINAL_TF32_TFLOPS = 1125.0        # half the nominal dense bf16 rate of a B200
 
 # DRAM bytes one 8192^3 launch moves (dram__bytes_read.sum + dram__bytes_write.sum from the
 # ncu capture summarised in profiles/); None until a capture exists.
-NCU_DRAM_BYTES_PER_LAUNCH = None
+NCU_DRAM_BYTES_PER_LAUNCH = 2.84e9
 
 
 def parse_args():
@@ -266,6 +266,9 @@ def run_ours(args):
     e2e_value = flops_step * args.e2e_steps / e2e_seconds / 1e12
     checksum = float(hc[0, :8].sum())      # the step's result is read on the host
 
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         return
     bf16_peak, peak_kind = measured_peaks()

@@ -13,6 +13,7 @@
 #include "cudeep/stream.cuh"
 
 #include <string>
+#include <vector>
 
 namespace {
 
@@ -180,6 +181,43 @@ int cudeep_b200_conv2d_forward_f64(const double* input, const double* weight, co
 
 // ---------------------------------------------------------------- host-buffer entry points
 
+}  // extern "C"
+
+namespace {
+
+// Streams and events of the pipelined host matmul, one set per thread and device.
+struct HostPipeline {
+    cudaStream_t in = nullptr, compute = nullptr, out = nullptr;
+    std::vector<cudaEvent_t> events;
+    int device = -1;
+    cudaEvent_t event(size_t i) {
+        while (events.size() <= i) {
+            cudaEvent_t e = nullptr;
+            CB200_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+            events.push_back(e);
+        }
+        return events[i];
+    }
+};
+
+HostPipeline& host_pipeline() {
+    thread_local HostPipeline p;
+    int dev = 0;
+    CB200_CUDA(cudaGetDevice(&dev));
+    if (p.device != dev) {
+        p = HostPipeline{};
+        CB200_CUDA(cudaStreamCreateWithFlags(&p.in, cudaStreamNonBlocking));
+        CB200_CUDA(cudaStreamCreateWithFlags(&p.compute, cudaStreamNonBlocking));
+        CB200_CUDA(cudaStreamCreateWithFlags(&p.out, cudaStreamNonBlocking));
+        p.device = dev;
+    }
+    return p;
+}
+
+}  // namespace
+
+extern "C" {
+
 int cudeep_b200_matmul_host_f32(const float* A, const float* B, float* C, int M, int N, int K, int strict) {
     return guarded([&] {
         CB200_REQUIRE(A != nullptr && B != nullptr && C != nullptr, "matmul: null host pointer");
@@ -188,17 +226,43 @@ int cudeep_b200_matmul_host_f32(const float* A, const float* B, float* C, int M,
         const size_t b_bytes = size_t(K) * N * sizeof(float);
         const size_t c_bytes = size_t(M) * N * sizeof(float);
         PoolBuffer da(a_bytes), db(b_bytes), dc(c_bytes);
-        cudaStream_t s = host_call_stream();
-        cudeep::memcpy_h2d(da.ptr, A, a_bytes, s);
-        cudeep::memcpy_h2d(db.ptr, B, b_bytes, s);
-        if (strict)
-            cudeep::kernels::launch_matmul_kernel_fp32<float>(da.as<float>(), db.as<float>(), dc.as<float>(),
-                                                              M, N, K, s);
-        else
-            cudeep::kernels::launch_matmul_kernel<float>(da.as<float>(), db.as<float>(), dc.as<float>(), M,
-                                                         N, K, s);
-        cudeep::memcpy_d2h(C, dc.ptr, c_bytes, s);
-        CB200_CUDA(cudaStreamSynchronize(s));
+        // The host link, not the GEMM, bounds this call.  B goes up first (every row of C needs
+        // all of it); A then goes up in row bands, each band is multiplied as soon as it has
+        // landed, and its rows of C go back down while later bands are still going up, so the
+        // two directions of the link and the tensor cores all work at once.
+        int bands = 1;
+        const size_t band_target = size_t(32) << 20;
+        if (a_bytes + c_bytes > 4 * band_target) {
+            bands = static_cast<int>((a_bytes + c_bytes) / 2 / band_target);
+            if (bands > 32) bands = 32;
+            if (bands < 1) bands = 1;
+        }
+        int band_rows = (M + bands - 1) / bands;
+        band_rows = (band_rows + 255) / 256 * 256;          // whole 256-row tiles per band
+        HostPipeline& p = host_pipeline();
+        cudeep::memcpy_h2d(db.ptr, B, b_bytes, p.in);
+        size_t ev = 0;
+        for (int row0 = 0; row0 < M; row0 += band_rows) {
+            const int rows = (M - row0 < band_rows) ? (M - row0) : band_rows;
+            float* a_dev = da.as<float>() + size_t(row0) * K;
+            float* c_dev = dc.as<float>() + size_t(row0) * N;
+            cudeep::memcpy_h2d(a_dev, A + size_t(row0) * K, size_t(rows) * K * sizeof(float), p.in);
+            cudaEvent_t landed = p.event(ev++);
+            CB200_CUDA(cudaEventRecord(landed, p.in));
+            CB200_CUDA(cudaStreamWaitEvent(p.compute, landed, 0));
+            if (strict)
+                cudeep::kernels::launch_matmul_kernel_fp32<float>(a_dev, db.as<float>(), c_dev, rows, N, K,
+                                                                  p.compute);
+            else
+                cudeep::kernels::launch_matmul_kernel<float>(a_dev, db.as<float>(), c_dev, rows, N, K, p.compute);
+            cudaEvent_t done = p.event(ev++);
+            CB200_CUDA(cudaEventRecord(done, p.compute));
+            CB200_CUDA(cudaStreamWaitEvent(p.out, done, 0));
+            cudeep::memcpy_d2h(C + size_t(row0) * N, c_dev, size_t(rows) * N * sizeof(float), p.out);
+        }
+        CB200_CUDA(cudaStreamSynchronize(p.out));
+        CB200_CUDA(cudaStreamSynchronize(p.compute));
+        CB200_CUDA(cudaStreamSynchronize(p.in));
     });
 }
 
