@@ -123,7 +123,7 @@ struct ConvProblem {
         }
     }
     __device__ __forceinline__ void store(const Tile& t, int row_in_cta, int c0, float (&v)[32],
-                                          const UmmaEpilogueArgs& epi) const {
+                                          const UmmaEpilogueArgs& epi, int /*mode: tiles are never split*/) const {
         const int oc = t.oc0 + row_in_cta;
         if (oc >= oc_n) return;
         if (epi.bias != nullptr) {
@@ -244,6 +244,9 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     sched.umma_n = plan.box_w * plan.box_h;
     sched.tx_bytes = (Cfg::A_BYTES + uint32_t(sched.umma_n / CTAS) * UMMA_BK * 4) * CTAS * KATOMS;
     sched.stages = Cfg::STAGES;
+    sched.n_whole = sched.tiles_m * sched.tiles_n;
+    sched.split = 1;
+    sched.kb_per_split = sched.k_blocks;
     sched.debug = 0;
 
     const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;

@@ -110,6 +110,121 @@ gemm_simt_kernel(const TI* __restrict__ a, const TI* __restrict__ b, T* __restri
     }
 }
 
+// Fast path for FP32 when every extent is a multiple of the tile and the operands are
+// 16-byte aligned: 128-bit global loads, the next K slice prefetched into registers
+// while the current one is multiplied out of shared memory (two buffers, one barrier
+// per slice), 128-bit shared-memory reads in the inner loop.  B is [K,N].
+template <int BM, int BN, int BK, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+sgemm_aligned_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
+                     int m, int n, int k, const float* __restrict__ bias, int bias_per_row, int act) {
+    constexpr int THREADS = (BM / TM) * (BN / TN);
+    constexpr int A_VEC = BM * BK / 4 / THREADS;     // float4 loads of A per thread and slice
+    constexpr int B_VEC = BK * BN / 4 / THREADS;
+    static_assert(A_VEC >= 1 && B_VEC >= 1 && TM % 4 == 0 && TN % 4 == 0 && BK % 4 == 0, "tile shape");
+    __shared__ __align__(16) float as[2][BK][BM + 4];
+    __shared__ __align__(16) float bs[2][BK][BN + 4];
+
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN);
+    const int ty = tid / (BN / TN);
+    const float* a_tile = a + static_cast<long long>(blockIdx.y) * BM * k;
+    const float* b_tile = b + static_cast<long long>(blockIdx.x) * BN;
+
+    float4 ra[A_VEC], rb[B_VEC];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < A_VEC; ++i) {
+            const int v = tid + i * THREADS;
+            const int row = v / (BK / 4), kq = (v % (BK / 4)) * 4;
+            ra[i] = *reinterpret_cast<const float4*>(a_tile + static_cast<long long>(row) * k + k0 + kq);
+        }
+#pragma unroll
+        for (int i = 0; i < B_VEC; ++i) {
+            const int v = tid + i * THREADS;
+            const int kk = v / (BN / 4), nq = (v % (BN / 4)) * 4;
+            rb[i] = *reinterpret_cast<const float4*>(b_tile + static_cast<long long>(k0 + kk) * n + nq);
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < A_VEC; ++i) {
+            const int v = tid + i * THREADS;
+            const int row = v / (BK / 4), kq = (v % (BK / 4)) * 4;
+            as[buf][kq + 0][row] = ra[i].x;
+            as[buf][kq + 1][row] = ra[i].y;
+            as[buf][kq + 2][row] = ra[i].z;
+            as[buf][kq + 3][row] = ra[i].w;
+        }
+#pragma unroll
+        for (int i = 0; i < B_VEC; ++i) {
+            const int v = tid + i * THREADS;
+            const int kk = v / (BN / 4), nq = (v % (BN / 4)) * 4;
+            *reinterpret_cast<float4*>(&bs[buf][kk][nq]) = rb[i];
+        }
+    };
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    int buf = 0;
+    for (int k0 = 0; k0 < k; k0 += BK) {
+        const bool more = k0 + BK < k;
+        if (more) fetch(k0 + BK);
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float av[TM], bv[TN];
+#pragma unroll
+            for (int i = 0; i < TM; i += 4)
+                *reinterpret_cast<float4*>(&av[i]) = *reinterpret_cast<const float4*>(&as[buf][kk][ty * TM + i]);
+#pragma unroll
+            for (int j = 0; j < TN; j += 4)
+                *reinterpret_cast<float4*>(&bv[j]) = *reinterpret_cast<const float4*>(&bs[buf][kk][tx * TN + j]);
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        if (more) {
+            stash(buf ^ 1);
+            __syncthreads();
+            buf ^= 1;
+        }
+    }
+
+    const long long row0 = static_cast<long long>(blockIdx.y) * BM + ty * TM;
+    const long long col0 = static_cast<long long>(blockIdx.x) * BN + tx * TN;
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+#pragma unroll
+        for (int j = 0; j < TN; j += 4) {
+            float v[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float x = acc[i][j + q];
+                if (bias != nullptr) x += bias_per_row ? bias[row0 + i] : bias[col0 + j + q];
+                v[q] = apply_activation1(x, act);
+            }
+            *reinterpret_cast<float4*>(c + (row0 + i) * n + col0 + j) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+    }
+}
+
+template <int BM, int BN, int BK, int TM, int TN>
+void launch_aligned(const float* a, const float* b, float* c, int m, int n, int k, const float* bias,
+                    bool bias_per_row, int act, cudaStream_t stream) {
+    dim3 grid(n / BN, m / BM);
+    sgemm_aligned_kernel<BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, stream>>>(
+        a, b, c, m, n, k, bias, bias_per_row ? 1 : 0, act);
+    CB200_CHECK_LAUNCH();
+}
+
 template <typename TI, typename T, int BM, int BN, int BK, int TM, int TN>
 void launch(const TI* a, const TI* b, bool b_is_nk, T* c, int m, int n, int k, const T* bias,
             bool bias_per_row, int act, cudaStream_t stream) {
@@ -131,6 +246,23 @@ void gemm_simt<float>(const float* a, const float* b, bool b_is_nk, float* c, in
                       const float* bias, bool bias_per_row, int act, cudaStream_t stream) {
     CB200_REQUIRE(m > 0 && n > 0 && k > 0, "GEMM extents must be positive");
     const long long big_tiles = static_cast<long long>((m + 127) / 128) * ((n + 127) / 128);
+    const bool aligned16 = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) |
+                             reinterpret_cast<uintptr_t>(c)) & 15u) == 0;
+    if (!b_is_nk && aligned16 && k % 16 == 0) {
+        const long long sms = device_info().num_sms;
+        if (m % 128 == 0 && n % 128 == 0 && big_tiles >= sms) {
+            launch_aligned<128, 128, 16, 8, 8>(a, b, c, m, n, k, bias, bias_per_row, act, stream);
+            return;
+        }
+        if (m % 64 == 0 && n % 64 == 0 && static_cast<long long>(m / 64) * (n / 64) >= sms) {
+            launch_aligned<64, 64, 16, 4, 4>(a, b, c, m, n, k, bias, bias_per_row, act, stream);
+            return;
+        }
+        if (m % 32 == 0 && n % 64 == 0) {
+            launch_aligned<32, 64, 16, 4, 4>(a, b, c, m, n, k, bias, bias_per_row, act, stream);
+            return;
+        }
+    }
     if (big_tiles >= 2LL * device_info().num_sms)
         launch<float, float, 128, 128, 16, 8, 8>(a, b, b_is_nk, c, m, n, k, bias, bias_per_row, act, stream);
     else

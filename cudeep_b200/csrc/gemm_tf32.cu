@@ -78,11 +78,11 @@ struct GemmProblem {
         }
     }
     __device__ __forceinline__ void store(const Tile& t, int row_in_cta, int c0, float (&v)[32],
-                                          const UmmaEpilogueArgs& epi) const {
+                                          const UmmaEpilogueArgs& epi, int mode) const {
         const int row = t.m0 + row_in_cta;
         const int col = t.n0 + c0;
         if (row >= m || col >= n) return;
-        if (epi.bias != nullptr) {
+        if (epi.bias != nullptr && mode != 2) {      // a split tile gets its bias once
             if (epi.bias_per_row) {
                 const float b = __ldg(epi.bias + row);
 #pragma unroll
@@ -96,8 +96,23 @@ struct GemmProblem {
                     if (col + j < n) v[j] += __ldg(epi.bias + col + j);
             }
         }
-        apply_activation(v, epi.act);
         float* dst = c + static_cast<long long>(row) * ldc + col;
+        if (mode != 0) {
+            // Partial sum of a split tile: C was zeroed before the launch and every K range
+            // adds its share.  With two ranges the result does not depend on their order
+            // (0 + p + q == 0 + q + p exactly); more ranges are summed in arrival order.
+            if (vec_ok && col + 32 <= n) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    atomicAdd(reinterpret_cast<float4*>(dst + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col + j < n) atomicAdd(dst + j, v[j]);
+            }
+            return;
+        }
+        apply_activation(v, epi.act);
         if (vec_ok && col + 32 <= n) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4)
@@ -109,6 +124,30 @@ struct GemmProblem {
         }
     }
 };
+
+// Zeroes the C region of tiles [first_tile, first_tile + gridDim.x) (raster order); blockIdx.y
+// selects a band of 16 rows inside the tile.
+__global__ void zero_tiles_kernel(float* __restrict__ c, long long ldc, int m, int n, int tile_m, int tile_n,
+                                  int tiles_m, int tiles_n, int raster_group, int first_tile, int vec_ok) {
+    int tm, tn;
+    raster_coords(first_tile + blockIdx.x, tiles_m, tiles_n, raster_group, tm, tn);
+    const int row0 = tm * tile_m + blockIdx.y * 16, col0 = tn * tile_n;
+    const int rows = min(16, m - row0), cols = min(tile_n, n - col0);
+    if (rows <= 0 || cols <= 0) return;
+    if (vec_ok && cols % 4 == 0) {
+        const int vcols = cols / 4;
+        for (int i = threadIdx.x; i < rows * vcols; i += blockDim.x) {
+            const int r = i / vcols, q = i - r * vcols;
+            *reinterpret_cast<float4*>(c + static_cast<long long>(row0 + r) * ldc + col0 + q * 4) =
+                make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+    } else {
+        for (int i = threadIdx.x; i < rows * cols; i += blockDim.x) {
+            const int r = i / cols, q = i - r * cols;
+            c[static_cast<long long>(row0 + r) * ldc + col0 + q] = 0.0f;
+        }
+    }
+}
 
 template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS>
 void launch_variant(const float* a, const float* b, float* c, int m, int n, int k,
@@ -169,7 +208,37 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     int max_ctas = tune.max_ctas > 0 ? tune.max_ctas : dev.num_sms;
     int groups = max_ctas / CTAS;
     if (groups < 1) groups = 1;
-    if (groups > num_tiles) groups = num_tiles;
+
+    // Split-K: when the last wave of tiles leaves most of the machine idle, cut each of its
+    // tiles into K ranges so that the wave is both full and proportionally shorter.
+    sched.n_whole = num_tiles;
+    sched.split = 1;
+    sched.kb_per_split = sched.k_blocks;
+    const int tail = num_tiles % groups;
+    int want_split = tune.split_k;
+    if (want_split == 0 && epi.act == EPI_NONE && tail > 0 && num_tiles > groups && sched.k_blocks >= 16) {
+        // Only behind at least one full wave (for a problem that does not fill the machine the
+        // zeroing pass and the atomic adds cost more than the shorter K loop saves), and two
+        // ranges at most when choosing automatically: their sum does not depend on the order in
+        // which they arrive, so results stay bitwise reproducible.
+        want_split = groups / tail >= 2 ? 2 : 1;
+    }
+    if (want_split >= 2 && epi.act == EPI_NONE && tail > 0) {
+        int per = (sched.k_blocks + want_split - 1) / want_split;
+        per = (per + KATOMS - 1) / KATOMS * KATOMS;
+        const int parts = (sched.k_blocks + per - 1) / per;
+        if (parts >= 2) {
+            sched.n_whole = num_tiles - tail;
+            sched.split = parts;
+            sched.kb_per_split = per;
+            zero_tiles_kernel<<<dim3(tail, UMMA_BM * CTAS / 16), 256, 0, stream>>>(
+                c, prob.ldc, m, n, UMMA_BM * CTAS, BN, sched.tiles_m, sched.tiles_n, sched.raster_group,
+                sched.n_whole, prob.vec_ok);
+            CB200_CHECK_LAUNCH();
+        }
+    }
+    const int num_units = sched.n_whole + (num_tiles - sched.n_whole) * sched.split;
+    if (groups > num_units) groups = num_units;
 
     auto kernel = umma_tf32_kernel<CTAS, BN, B_MN_MAJOR, KATOMS, Prob>;
     ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), Cfg::SMEM_BYTES);
@@ -214,8 +283,15 @@ void dispatch(const float* a, const float* b, float* c, int m, int n, int k,
             const long long tiles = static_cast<long long>((m + 128 * cand.ctas - 1) / (128 * cand.ctas)) *
                                     ((n + cand.bn - 1) / cand.bn);
             const long long slots = dev.num_sms / cand.ctas;
-            const long long waves = (tiles + slots - 1) / slots;
-            const double cost = waves * k_mmas * cand.mma_clk + cand.fixed_clk;
+            const long long tail = tiles % slots;
+            double waves = static_cast<double>(tiles / slots) + (tail > 0 ? 1.0 : 0.0);
+            double extra = 0.0;
+            if (tail > 0 && tiles > slots && slots / tail >= 2 && epi.act == EPI_NONE && tune.split_k != 1 &&
+                k >= 16 * UMMA_BK) {
+                waves -= 0.5;            // the last wave is split in two K ranges
+                extra = 3000.0;          // zeroing C and adding partial sums
+            }
+            const double cost = waves * k_mmas * cand.mma_clk + cand.fixed_clk + extra;
             if (best == 0.0 || cost < best) {
                 best = cost;
                 pick_ctas = cand.ctas;

@@ -14,6 +14,7 @@ struct GemmTuning {
     uint32_t b_lbo = 0;      // B shared-memory descriptor overrides (bring-up aid)
     uint32_t b_sbo = 0;
     int stages = 0;          // pipeline stages to use (default: all that fit)
+    int split_k = 0;         // K ranges per tile of the ragged last wave: 0 = choose, 1 = never split
     int katoms = 0;          // 32-wide K blocks per pipeline stage: 1 or 2
     int b_chunked = 0;       // -1: load B[K,N] as separate 32-column boxes even when N % 32 == 0
     uint32_t debug = 0;      // diagnostics, see UmmaSchedule::debug

@@ -53,6 +53,13 @@ struct UmmaSchedule {
     int umma_n;            // N of one MMA (<= BN, multiple of 32): accumulator columns in use
     uint32_t tx_bytes;     // bytes all CTAs of the group deliver per stage (all atoms)
     int stages;            // pipeline stages in use (<= UmmaConfig::STAGES)
+    // Split-K for the ragged last wave (or for problems too small to fill the machine): the
+    // first n_whole tiles (in raster order) are computed whole; each remaining tile is cut
+    // into `split` K ranges of kb_per_split blocks (a multiple of KATOMS), one work unit
+    // each, whose partial sums are added into a zeroed C.  split == 1: every tile is whole.
+    int n_whole;
+    int split;
+    int kb_per_split;
     // Diagnostics for performance bring-up (results are then meaningless):
     //   bit 0: after the ring has been filled once the producer stops loading and only
     //          signals the stages, so the MMA side runs without memory traffic;
@@ -67,6 +74,27 @@ struct UmmaSchedule {
 // KATOMS: 32-wide K blocks ("atoms") per pipeline stage.  A stage is KATOMS
 // consecutive [A atom][B atom] pairs; barriers are exchanged once per stage, so
 // a larger KATOMS spends fewer of the MMA issuer's cycles on handshakes.
+// Tile index -> tile coordinates: groups of `raster_group` tile rows are walked column by
+// column, so CTAs working on consecutive tiles share operand slabs in L2.
+__host__ __device__ inline void raster_coords(int t, int tiles_m, int tiles_n, int raster_group, int& tm,
+                                              int& tn) {
+    const int group_tiles = raster_group * tiles_n;
+    const int group = t / group_tiles;
+    const int first_m = group * raster_group;
+    const int rows = (tiles_m - first_m) < raster_group ? (tiles_m - first_m) : raster_group;
+    const int in_group = t - group * group_tiles;
+    tm = first_m + in_group % rows;
+    tn = in_group / rows;
+}
+
+// One unit of work of the persistent loop: a tile and a range of its K blocks.
+struct WorkUnit {
+    int tile;
+    int kb0;        // first K block
+    int kb_count;   // K blocks in this unit
+    int mode;       // 0: whole tile, plain store; 1: first K range of a split tile; 2: a later range
+};
+
 template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS = 1>
 struct UmmaConfig {
     static constexpr int BN_CTA = BN / CTAS;                       // B rows staged by one CTA
@@ -88,7 +116,8 @@ struct UmmaConfig {
 //   struct Tile;                                             decoded tile coordinates
 //   __device__ Tile decode(int tm, int tn, uint32_t cta_rank) const;
 //   __device__ void load(tile, kb, a_smem, b_smem, bar) const;     one lane, issues all TMA loads of a stage
-//   __device__ void store(tile, row_in_cta, col0, float (&v)[32]) const;   32 consecutive columns of one row
+//   __device__ void store(tile, row_in_cta, col0, float (&v)[32], epi, mode) const;   32 consecutive
+//       columns of one row; mode as WorkUnit::mode (1, 2: add the partial sum into C)
 template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, class Problem>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
 umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
@@ -97,7 +126,6 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
     defined(__CUDA_ARCH_FEAT_SM103_ALL)
     using Cfg = UmmaConfig<CTAS, BN, B_MN_MAJOR, KATOMS>;
     constexpr int STAGES = Cfg::STAGES;
-    const int k_stages = (sched.k_blocks + KATOMS - 1) / KATOMS;   // stages per tile
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[STAGES];
@@ -142,27 +170,41 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
     const uint32_t tmem_base = tmem_base_holder;
 
     const int num_tiles = sched.tiles_m * sched.tiles_n;
-    const int tile_stride = gridDim.x / CTAS;
-    const int first_tile = blockIdx.x / CTAS;
-    const int group_tiles = sched.raster_group * sched.tiles_n;
+    const int num_units = sched.n_whole + (num_tiles - sched.n_whole) * sched.split;
+    const int unit_stride = gridDim.x / CTAS;
+    const int first_unit = blockIdx.x / CTAS;
 
     auto tile_coords = [&](int t, int& tm, int& tn) {
-        const int group = t / group_tiles;
-        const int first_m = group * sched.raster_group;
-        const int rows = min(sched.raster_group, sched.tiles_m - first_m);
-        const int in_group = t - group * group_tiles;
-        tm = first_m + in_group % rows;
-        tn = in_group / rows;
+        raster_coords(t, sched.tiles_m, sched.tiles_n, sched.raster_group, tm, tn);
+    };
+    auto decode_unit = [&](int u) {
+        WorkUnit w;
+        if (u < sched.n_whole) {
+            w.tile = u;
+            w.kb0 = 0;
+            w.kb_count = sched.k_blocks;
+            w.mode = 0;
+        } else {
+            const int r = u - sched.n_whole;
+            const int part = r % sched.split;
+            w.tile = sched.n_whole + r / sched.split;
+            w.kb0 = part * sched.kb_per_split;
+            w.kb_count = min(sched.kb_per_split, sched.k_blocks - w.kb0);
+            w.mode = part == 0 ? 1 : 2;
+        }
+        return w;
     };
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0 && !(sched.debug & 4u)) {
             uint32_t stage = 0, phase = 0, issued = 0;
-            for (int t = first_tile; t < num_tiles; t += tile_stride) {
+            for (int u = first_unit; u < num_units; u += unit_stride) {
+                const WorkUnit w = decode_unit(u);
                 int tm, tn;
-                tile_coords(t, tm, tn);
+                tile_coords(w.tile, tm, tn);
                 const auto tile = prob.decode(tm, tn, cta_rank);
+                const int k_stages = (w.kb_count + KATOMS - 1) / KATOMS;
                 for (int ks = 0; ks < k_stages; ++ks) {
                     if (!ptx::mbar_wait(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, wctx,
                                         UMMA_TIMEOUT_PRODUCER))
@@ -174,12 +216,14 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                         if (is_leader) ptx::mbar_arrive_expect_tx(full_local, sched.tx_bytes);
                         const uint32_t full_bar = (CTAS == 2) ? ptx::mapa(full_local, 0) : full_local;
                         // Atoms past the end of K are loaded too; their coordinates are out
-                        // of range, so they arrive as zeros and add nothing.
+                        // of range, so they arrive as zeros and add nothing.  (A split unit
+                        // that is not the last holds a whole number of stages, so it never
+                        // reaches into its neighbour's K range.)
 #pragma unroll
                         for (int j = 0; j < KATOMS; ++j) {
                             const uint32_t a_smem = smem_base + stage * Cfg::STAGE_BYTES + j * Cfg::ATOM_BYTES;
-                            prob.template load<CTAS>(tile, ks * KATOMS + j, a_smem, a_smem + Cfg::A_BYTES,
-                                                     full_bar);
+                            prob.template load<CTAS>(tile, w.kb0 + ks * KATOMS + j, a_smem,
+                                                     a_smem + Cfg::A_BYTES, full_bar);
                         }
                     }
                     ++issued;
@@ -211,7 +255,8 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
 
             uint32_t stage = 0, phase = 0;
             int it = 0;
-            for (int t = first_tile; t < num_tiles; t += tile_stride, ++it) {
+            for (int u = first_unit; u < num_units; u += unit_stride, ++it) {
+                const int k_stages = (decode_unit(u).kb_count + KATOMS - 1) / KATOMS;
                 const uint32_t acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
                 if (!ptx::mbar_wait(ptx::smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, wctx,
@@ -271,9 +316,10 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
         const int row_in_cta = quarter * 32 + lane;
         int it = 0;
         bool ok = true;
-        for (int t = first_tile; t < num_tiles && ok; t += tile_stride, ++it) {
+        for (int u = first_unit; u < num_units && ok; u += unit_stride, ++it) {
+            const WorkUnit w = decode_unit(u);
             int tm, tn;
-            tile_coords(t, tm, tn);
+            tile_coords(w.tile, tm, tn);
             const auto tile = prob.decode(tm, tn, cta_rank);
             const uint32_t acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
@@ -291,7 +337,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                prob.store(tile, row_in_cta, c, v, epi);
+                prob.store(tile, row_in_cta, c, v, epi, w.mode);
             }
             ptx::tc_fence_before();
             __syncwarp();

@@ -96,7 +96,8 @@ int cudeep_b200_linear_forward_f64(const double* x, const double* W, const doubl
  * bit 28 loads B[K,N] as separate 32-column boxes instead of one chunked box;
  * bits 29-30 set the 32-wide K blocks per pipeline stage (1 or 2, 0 = default).
  * b_lbo / b_sbo: 0, or a byte offset that overrides the B shared-memory
- * descriptor fields.  Fails instead of falling back when the tensor-core path
+ * descriptor fields (b_lbo bits 0-15); bits 16-23 of b_lbo set the split-K factor
+ * of the ragged last wave of tiles (0 = choose, 1 = never split).  Fails instead of falling back when the tensor-core path
  * cannot take the problem. */
 int cudeep_b200_gemm_tf32_tuned(const float* A, const float* B, int b_is_nk, float* C, int M, int N,
                                 int K, const float* bias, int bias_per_row, int epilogue, int ctas,

@@ -153,6 +153,37 @@ def test_tf32_ragged_shapes(dev, oracle, m, n, k, b_is_nk):
     check_tf32(oracle, got, a, b, k, b_is_nk=b_is_nk)
 
 
+@pytest.mark.parametrize("ctas,bn,max_ctas,split_k", [
+    (2, 256, 0, 0),      # 12 tiles on 74 CTA pairs: the launcher splits every tile in two K ranges
+    (2, 256, 0, 4),      # forced four ranges
+    (1, 256, 0, 3),      # one CTA per tile, three ranges (1024 K blocks do not divide evenly)
+    (2, 256, 10, 2),     # 5 pairs, 12 tiles: 10 whole tiles, 2 tail tiles split in two
+    (1, 128, 6, 2),      # narrow tiles, whole tiles and split tiles mixed
+    (2, 256, 0, 1),      # splitting switched off
+])
+@pytest.mark.parametrize("b_is_nk,bias", [(False, False), (True, True)])
+def test_tf32_split_k(dev, oracle, ctas, bn, max_ctas, split_k, b_is_nk, bias):
+    rng = np.random.default_rng(ctas * 100 + bn + split_k)
+    m, n, k = 520, 1500, 2080          # ragged rows and columns: scalar and vector partial-sum paths
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((n, k) if b_is_nk else (k, n), dtype=np.float32)
+    bv = rng.standard_normal(n, dtype=np.float32) if bias else None
+    got = dev.gemm_tuned(a, b, b_is_nk, bias=bv, ctas=ctas, bn=bn, max_ctas=max_ctas, split_k=split_k)
+    check_tf32(oracle, got, a, b, k, b_is_nk=b_is_nk, bias=bv)
+
+
+def test_tf32_split_k_into_prefilled_output(dev, lib, oracle):
+    """Split tiles accumulate into C, so the launcher must clear what the caller left there."""
+    rng = np.random.default_rng(123)
+    a = rng.standard_normal((512, 1024), dtype=np.float32)
+    b = rng.standard_normal((1024, 512), dtype=np.float32)
+    ta, tb = dev.to_dev(a), dev.to_dev(b)
+    tc = dev.torch.full((512, 512), 1.0e6, device=dev.dev)
+    dev.check(lib.cudeep_b200_matmul_f32(dev.ptr(ta), dev.ptr(tb), dev.ptr(tc), 512, 512, 1024, None))
+    assert dev.sync_status() == 0
+    check_tf32(oracle, tc.cpu().numpy(), a, b, 1024)
+
+
 def test_tf32_is_deterministic(dev):
     a, b = workloads.c2_gemm(1024)
     assert np.array_equal(dev.matmul(a, b), dev.matmul(a, b))
