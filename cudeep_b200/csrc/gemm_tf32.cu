@@ -194,7 +194,7 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     sched.tiles_m = (m + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS);
     sched.tiles_n = (n + BN - 1) / BN;
     sched.k_blocks = (k + UMMA_BK - 1) / UMMA_BK;
-    sched.raster_group = tune.raster_group > 0 ? tune.raster_group : 16;
+    sched.raster_group = tune.raster_group > 0 ? tune.raster_group : 8;
     sched.status = dev.status_word;
     sched.wait_limit_ns = 2000000000ull;
     sched.b_lbo = tune.b_lbo;

@@ -154,7 +154,7 @@ def test_tf32_ragged_shapes(dev, oracle, m, n, k, b_is_nk):
 
 
 @pytest.mark.parametrize("ctas,bn,max_ctas,split_k", [
-    (2, 256, 0, 0),      # 12 tiles on 74 CTA pairs: the launcher splits every tile in two K ranges
+    (2, 256, 0, 0),      # 12 tiles on 74 CTA pairs: no full wave, so the launcher does not split
     (2, 256, 0, 4),      # forced four ranges
     (1, 256, 0, 3),      # one CTA per tile, three ranges (1024 K blocks do not divide evenly)
     (2, 256, 10, 2),     # 5 pairs, 12 tiles: 10 whole tiles, 2 tail tiles split in two
@@ -172,16 +172,24 @@ def test_tf32_split_k(dev, oracle, ctas, bn, max_ctas, split_k, b_is_nk, bias):
     check_tf32(oracle, got, a, b, k, b_is_nk=b_is_nk, bias=bv)
 
 
-def test_tf32_split_k_into_prefilled_output(dev, lib, oracle):
-    """Split tiles accumulate into C, so the launcher must clear what the caller left there."""
+def test_tf32_split_k_chosen_by_the_launcher(dev, lib, oracle):
+    """4096 x 4096 x 512: 256 tiles on 74 CTA pairs leave a 34-tile last wave, which the launcher
+    splits in two K ranges that accumulate into C - so it must first clear what the caller left there."""
     rng = np.random.default_rng(123)
-    a = rng.standard_normal((512, 1024), dtype=np.float32)
-    b = rng.standard_normal((1024, 512), dtype=np.float32)
+    a = rng.standard_normal((4096, 512), dtype=np.float32)
+    b = rng.standard_normal((512, 4096), dtype=np.float32)
     ta, tb = dev.to_dev(a), dev.to_dev(b)
-    tc = dev.torch.full((512, 512), 1.0e6, device=dev.dev)
-    dev.check(lib.cudeep_b200_matmul_f32(dev.ptr(ta), dev.ptr(tb), dev.ptr(tc), 512, 512, 1024, None))
+    tc = dev.torch.full((4096, 4096), 1.0e6, device=dev.dev)
+    dev.check(lib.cudeep_b200_matmul_f32(dev.ptr(ta), dev.ptr(tb), dev.ptr(tc), 4096, 4096, 512, None))
     assert dev.sync_status() == 0
-    check_tf32(oracle, tc.cpu().numpy(), a, b, 1024)
+    got = tc.cpu().numpy()
+    rows = np.sort(rng.choice(4096, size=128, replace=False))
+    check_tf32(oracle, got, a, b, 512, rows=rows)
+    colsum = got.sum(axis=0, dtype=np.float64)
+    want = a.sum(axis=0, dtype=np.float64) @ b.astype(np.float64)
+    assert np.linalg.norm(colsum - want) / np.linalg.norm(want) <= TF32_TOL
+    again = dev.matmul(a, b)
+    assert np.array_equal(got, again)          # two K ranges: order-independent, bitwise reproducible
 
 
 def test_tf32_is_deterministic(dev):
