@@ -56,6 +56,10 @@ def parse_args():
     ap.add_argument("--suite", action="store_true",
                     help="instead of the headline line, time every benchmark configuration next to "
                          "cuBLAS / cuDNN (through torch) and the reference's kernels; one JSON line each")
+    ap.add_argument("--only", default="", help="with --suite: run only the configurations whose name starts "
+                                               "with one of these comma-separated tags (C1, C2, C3, C4)")
+    ap.add_argument("--no-comparators", action="store_true",
+                    help="with --suite: time only this library (short runs for profiling)")
     return ap.parse_args()
 
 
@@ -383,7 +387,9 @@ def run_suite(args):
     flush = torch.empty(256 * 1024 * 1024 // 4, device="cuda")
     P = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())
 
-    def timed(fn, iters):
+    def timed(fn, iters, cmp=False):
+        if cmp and args.no_comparators:
+            return None
         for _ in range(3):
             fn()
         torch.cuda.synchronize()
@@ -405,6 +411,7 @@ def run_suite(args):
         for key in rows:
             if key != "ours":
                 line[f"ours_over_{key}"] = rows[key][0] / rows["ours"][0]
+        rows = dict(rows)
         line.update(extra)
         print(json.dumps(line), flush=True)
 
@@ -412,18 +419,45 @@ def run_suite(args):
         if rc != 0:
             raise RuntimeError(lib.cudeep_b200_last_error().decode())
 
+    only = [t.strip() for t in args.only.split(",") if t.strip()]
+    want = lambda tag: not only or tag in only
+    if args.no_comparators:
+        ref = None
+
+    def trim(rows):
+        return {k: v for k, v in rows.items() if v is not None}
+
     # C1: strict FP32 512^3
+    if want("C1"):
+        run_c1(lib, ref, timed, emit, ok, P, stream, trim)
+    if want("C2"):
+        run_c2(lib, ref, timed, emit, ok, P, stream, trim)
+    if want("C3"):
+        run_c3(lib, ref, timed, emit, ok, P, stream, trim)
+    if want("C4"):
+        run_c4(lib, ref, timed, emit, ok, P, stream, trim)
+    status = _lib.device_status(True)
+    if status != 0:
+        raise RuntimeError(f"kernel status word {status}")
+
+
+def run_c1(lib, ref, timed, emit, ok, P, stream, trim):
+    import torch
+    from cudeep_b200 import workloads
     a_np, b_np = workloads.c1_sgemm()
     a, b = torch.from_numpy(a_np).cuda(), torch.from_numpy(b_np).cuda()
     c = torch.empty((512, 512), device="cuda")
     rows = {"ours": timed(lambda: ok(lib.cudeep_b200_matmul_f32_strict(P(a), P(b), P(c), 512, 512, 512, stream)), 50)}
     torch.backends.cuda.matmul.allow_tf32 = False
-    rows["cublas_fp32"] = timed(lambda: torch.matmul(a, b, out=c), 50)
+    rows["cublas_fp32"] = timed(lambda: torch.matmul(a, b, out=c), 50, cmp=True)
     if ref is not None:
-        rows["reference"] = timed(lambda: ref.cudeep_ref_matmul_f32_strict(P(a), P(b), P(c), 512, 512, 512, stream), 50)
-    emit("C1 FP32 SGEMM 512^3", 2.0 * 512 ** 3, rows)
+        rows["reference"] = timed(lambda: ref.cudeep_ref_matmul_f32_strict(P(a), P(b), P(c), 512, 512, 512, stream), 50, cmp=True)
+    emit("C1 FP32 SGEMM 512^3", 2.0 * 512 ** 3, trim(rows))
 
-    # C2: TF32 square GEMMs
+
+def run_c2(lib, ref, timed, emit, ok, P, stream, trim):
+    import torch
+    from cudeep_b200 import workloads
     torch.backends.cuda.matmul.allow_tf32 = True
     for n in workloads.C2_SIZES:
         a = torch.randn((n, n), device="cuda")
@@ -431,12 +465,17 @@ def run_suite(args):
         c = torch.empty((n, n), device="cuda")
         iters = 30 if n <= 4096 else 15
         rows = {"ours": timed(lambda: ok(lib.cudeep_b200_matmul_f32(P(a), P(b), P(c), n, n, n, stream)), iters),
-                "cublas_tf32": timed(lambda: torch.matmul(a, b, out=c), iters)}
+                "cublas_tf32": timed(lambda: torch.matmul(a, b, out=c), iters, cmp=True)}
         if ref is not None:
-            rows["reference"] = timed(lambda: ref.cudeep_ref_matmul_f32(P(a), P(b), P(c), n, n, n, stream), max(3, iters // 5))
-        emit(f"C2 TF32 GEMM {n}^3", 2.0 * n ** 3, rows)
+            rows["reference"] = timed(lambda: ref.cudeep_ref_matmul_f32(P(a), P(b), P(c), n, n, n, stream), max(3, iters // 5), cmp=True)
+        emit(f"C2 TF32 GEMM {n}^3", 2.0 * n ** 3, trim(rows))
 
-    # C3: Linear(4096 -> 16384, GELU) -> Linear(16384 -> 4096), batch 8192
+
+def run_c3(lib, ref, timed, emit, ok, P, stream, trim):
+    """Linear(4096 -> 16384, GELU) -> Linear(16384 -> 4096), batch 8192."""
+    import torch
+    import torch.nn.functional as F
+    torch.backends.cuda.matmul.allow_tf32 = True
     m, d_in, d_h, d_out = 8192, 4096, 16384, 4096
     x = torch.randn((m, d_in), device="cuda")
     w1 = (torch.rand((d_h, d_in), device="cuda") * 2 - 1) * (6.0 / d_in) ** 0.5
@@ -453,7 +492,7 @@ def run_suite(args):
     def torch_c3():
         F.linear(F.gelu(F.linear(x, w1, b1), approximate="tanh"), w2, b2)
 
-    rows = {"ours": timed(ours_c3, 8), "cublas_tf32_torch": timed(torch_c3, 8)}
+    rows = {"ours": timed(ours_c3, 8), "cublas_tf32_torch": timed(torch_c3, 8, cmp=True)}
     if ref is not None:
         w1t, w2t = w1.t().contiguous(), w2.t().contiguous()
 
@@ -461,11 +500,15 @@ def run_suite(args):
             ref.cudeep_ref_matmul_f32(P(x), P(w1t), P(h), m, d_h, d_in, stream)
             ref.cudeep_ref_matmul_f32(P(h), P(w2t), P(y), m, d_out, d_h, stream)
 
-        rows["reference_gemms_only"] = timed(ref_c3, 3)
-    emit("C3 Linear 8192x4096 -> 16384 (GELU) -> 4096", 2.0 * m * d_in * d_h * 2, rows)
-    del x, w1, w2, h, y
+        rows["reference_gemms_only"] = timed(ref_c3, 3, cmp=True)
+    emit("C3 Linear 8192x4096 -> 16384 (GELU) -> 4096", 2.0 * m * d_in * d_h * 2, trim(rows))
 
-    # C4: conv 3x3, 64 x 256 x 56 x 56 -> 256, bias + ReLU
+
+def run_c4(lib, ref, timed, emit, ok, P, stream, trim):
+    """conv 3x3, 64 x 256 x 56 x 56 -> 256, bias + ReLU."""
+    import torch
+    import torch.nn.functional as F
+    from cudeep_b200 import workloads
     nb, ch, size, oc = 64, 256, 56, 256
     xc = torch.randn((nb, ch, size, size), device="cuda")
     wc = torch.randn((oc, ch, 3, 3), device="cuda") * (2.0 / (ch * 9)) ** 0.5
@@ -475,16 +518,14 @@ def run_suite(args):
     torch.backends.cudnn.benchmark = True
     rows = {"ours": timed(lambda: ok(lib.cudeep_b200_conv2d_forward_fused_f32(
         P(xc), P(wc), P(bc), P(yc), nb, ch, oc, size, size, 3, 3, 1, 1, 1, 1, 1, stream)), 15),
-            "cudnn_tf32_torch": timed(lambda: F.relu(F.conv2d(xc, wc, bc, padding=1)), 15)}
+            "cudnn_tf32_torch": timed(lambda: F.relu(F.conv2d(xc, wc, bc, padding=1)), 15, cmp=True)}
     xl = xc.contiguous(memory_format=torch.channels_last)
-    rows["cudnn_tf32_torch_nhwc_input"] = timed(lambda: F.relu(F.conv2d(xl, wc, bc, padding=1)), 15)
+    rows["cudnn_tf32_torch_nhwc_input"] = timed(lambda: F.relu(F.conv2d(xl, wc, bc, padding=1)), 15, cmp=True)
     if ref is not None:
         rows["reference_no_relu"] = timed(lambda: ref.cudeep_ref_conv2d_forward_f32(
-            P(xc), P(wc), P(bc), P(yc), nb, ch, oc, size, size, 3, 3, 1, 1, 1, 1, stream), 5)
-    emit("C4 conv 3x3 64x256x56x56 -> 256, bias + ReLU", workloads.conv_flops(nb, ch, oc, size, size, 3, 3), rows)
-    status = _lib.device_status(True)
-    if status != 0:
-        raise RuntimeError(f"kernel status word {status}")
+            P(xc), P(wc), P(bc), P(yc), nb, ch, oc, size, size, 3, 3, 1, 1, 1, 1, stream), 5, cmp=True)
+    emit("C4 conv 3x3 64x256x56x56 -> 256, bias + ReLU", workloads.conv_flops(nb, ch, oc, size, size, 3, 3),
+         trim(rows))
 
 
 def main():

@@ -29,23 +29,52 @@ namespace {
 // ------------------------------------------------------------------ layout transforms
 
 // x[N][C][HW] -> xt[N][HW][Cx], Cx >= C (extra channels written as zero).
-// 32 x 32 tiles through shared memory: reads coalesce along HW, writes along C.
-__global__ void nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, int hw,
-                                    int cx) {
-    __shared__ float tile[32][33];
+// 32-channel x 64-pixel tiles through shared memory: reads coalesce along HW, writes along C.
+// With HW a multiple of 4 both sides move 128 bits per thread (a warp reads 512 contiguous
+// bytes of one channel and writes four pixels' 128-byte channel runs); otherwise scalars.
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, int hw, int cx) {
+    __shared__ float tile[32][65];
     const int n = blockIdx.z;
-    const int p0 = blockIdx.x * 32;
+    const int p0 = blockIdx.x * 64;
     const int c0 = blockIdx.y * 32;
     const float* xn = x + static_cast<long long>(n) * c * hw;
     float* xtn = xt + static_cast<long long>(n) * hw * cx;
-    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
-        const int ch = c0 + i, p = p0 + threadIdx.x;
-        tile[i][threadIdx.x] = (ch < c && p < hw) ? xn[static_cast<long long>(ch) * hw + p] : 0.0f;
-    }
-    __syncthreads();
-    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
-        const int p = p0 + i, ch = c0 + threadIdx.x;
-        if (p < hw && ch < cx) xtn[static_cast<long long>(p) * cx + ch] = tile[threadIdx.x][i];
+    const int tid = threadIdx.x;
+    if constexpr (VEC) {
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+            const int ch_l = pass * 16 + tid / 16, p_l = (tid % 16) * 4;
+            const int ch = c0 + ch_l, p = p0 + p_l;
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (ch < c && p < hw) v = *reinterpret_cast<const float4*>(xn + static_cast<long long>(ch) * hw + p);
+            tile[ch_l][p_l + 0] = v.x;
+            tile[ch_l][p_l + 1] = v.y;
+            tile[ch_l][p_l + 2] = v.z;
+            tile[ch_l][p_l + 3] = v.w;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+            const int p_l = pass * 32 + tid / 8, ch_l = (tid % 8) * 4;
+            const int p = p0 + p_l, ch = c0 + ch_l;
+            if (p < hw && ch < cx)
+                *reinterpret_cast<float4*>(xtn + static_cast<long long>(p) * cx + ch) =
+                    make_float4(tile[ch_l][p_l], tile[ch_l + 1][p_l], tile[ch_l + 2][p_l], tile[ch_l + 3][p_l]);
+        }
+    } else {
+        for (int i = tid; i < 32 * 64; i += 256) {
+            const int ch_l = i / 64, p_l = i % 64;
+            const int ch = c0 + ch_l, p = p0 + p_l;
+            tile[ch_l][p_l] = (ch < c && p < hw) ? xn[static_cast<long long>(ch) * hw + p] : 0.0f;
+        }
+        __syncthreads();
+        for (int i = tid; i < 32 * 64; i += 256) {
+            const int p_l = i / 32, ch_l = i % 32;
+            const int p = p0 + p_l, ch = c0 + ch_l;
+            if (p < hw && ch < cx) xtn[static_cast<long long>(p) * cx + ch] = tile[ch_l][p_l];
+        }
     }
 }
 
@@ -320,10 +349,11 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
     float* wp = reinterpret_cast<float*>(static_cast<char*>(scratch) + nhwc_bytes);
 
     {
-        dim3 grid((hw + 31) / 32, (cx + 31) / 32, s.batch);
-        dim3 block(32, 8);
+        dim3 grid((hw + 63) / 64, (cx + 31) / 32, s.batch);
         CB200_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "conv2d: too many channels or images");
-        nchw_to_nhwc_kernel<<<grid, block, 0, stream>>>(input, xt, s.in_c, hw, cx);
+        const bool vec = (hw % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
+        if (vec) nchw_to_nhwc_kernel<true><<<grid, 256, 0, stream>>>(input, xt, s.in_c, hw, cx);
+        else nchw_to_nhwc_kernel<false><<<grid, 256, 0, stream>>>(input, xt, s.in_c, hw, cx);
         CB200_CHECK_LAUNCH();
     }
     {
