@@ -329,15 +329,29 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
             if (!ok) break;
             ptx::tc_fence_after();
             const uint32_t t_row = tmem_base + acc * BN + ((quarter * 32u) << 16);
+            // Two register sets: the TMEM load of the next 32 columns is in flight while the
+            // current 32 are converted and stored.
+            const int n_cols = (sched.debug & 8u) ? 0 : sched.umma_n;
+            uint32_t r0[32], r1[32];
+            if (n_cols > 0) ptx::tmem_ld_32x32(t_row, r0);
 #pragma unroll 1
-            for (int c = 0; c < ((sched.debug & 8u) ? 0 : sched.umma_n); c += 32) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32(t_row + c, r);
+            for (int c = 0; c < n_cols; c += 64) {
                 ptx::tmem_ld_wait();
-                float v[32];
+                if (c + 32 < n_cols) ptx::tmem_ld_32x32(t_row + c + 32, r1);
+                {
+                    float v[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                prob.store(tile, row_in_cta, c, v, epi, w.mode);
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
+                    prob.store(tile, row_in_cta, c, v, epi, w.mode);
+                }
+                if (c + 32 < n_cols) {
+                    ptx::tmem_ld_wait();
+                    if (c + 64 < n_cols) ptx::tmem_ld_32x32(t_row + c + 64, r0);
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
+                    prob.store(tile, row_in_cta, c + 32, v, epi, w.mode);
+                }
             }
             ptx::tc_fence_before();
             __syncwarp();
