@@ -151,15 +151,14 @@ struct ConvProblem {
             ptx::tma_load_4d_pair(b_smem, &map_x, bar, c0, t.ow0 + kw - p_w, t.hb0 + kh - p_h, n);
         }
     }
-    __device__ __forceinline__ void store4(const Tile& t, int row_in_cta, int c0, float4 q,
-                                           const UmmaEpilogueArgs& epi, int /*mode: tiles are never split*/) const {
+    __device__ __forceinline__ void store(const Tile& t, int row_in_cta, int c0, float (&v)[32],
+                                          const UmmaEpilogueArgs& epi, int /*mode: tiles are never split*/) const {
         const int oc = t.oc0 + row_in_cta;
         if (oc >= oc_n) return;
-        float v[4] = {q.x, q.y, q.z, q.w};
         if (epi.bias != nullptr) {
             const float b = __ldg(epi.bias + oc);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] += b;
+            for (int j = 0; j < 32; ++j) v[j] += b;
         }
         apply_activation(v, epi.act);
         float* plane = out + (static_cast<long long>(t.n) * oc_n + oc) * oh_n * ow_n;
@@ -167,20 +166,22 @@ struct ConvProblem {
             const int rows = min(box_h, oh_n - t.oh0);
             const int limit = rows * ow_n;                 // valid accumulator columns
             float* dst = plane + static_cast<long long>(t.oh0) * ow_n + c0;
-            if (vec_ok && c0 + 4 <= limit) {
-                *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+            if (vec_ok && c0 + 32 <= limit) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
             } else {
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < 32; ++j)
                     if (c0 + j < limit) dst[j] = v[j];
             }
         } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < 32; ++j) {
                 const int col = c0 + j;
                 const int r = col / box_w;
-                const int qx = col - r * box_w;
-                const int oh = t.oh0 + r, ow = t.ow0 + qx;
+                const int q = col - r * box_w;
+                const int oh = t.oh0 + r, ow = t.ow0 + q;
                 if (oh < oh_n && ow < ow_n) plane[static_cast<long long>(oh) * ow_n + ow] = v[j];
             }
         }

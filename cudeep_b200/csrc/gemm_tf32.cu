@@ -77,22 +77,23 @@ struct GemmProblem {
             }
         }
     }
-    __device__ __forceinline__ void store4(const Tile& t, int row_in_cta, int c0, float4 q,
-                                           const UmmaEpilogueArgs& epi, int mode) const {
+    __device__ __forceinline__ void store(const Tile& t, int row_in_cta, int c0, float (&v)[32],
+                                          const UmmaEpilogueArgs& epi, int mode) const {
         const int row = t.m0 + row_in_cta;
         const int col = t.n0 + c0;
         if (row >= m || col >= n) return;
-        float v[4] = {q.x, q.y, q.z, q.w};
-        const bool full = col + 4 <= n;
         if (epi.bias != nullptr && mode != 2) {      // a split tile gets its bias once
             if (epi.bias_per_row) {
                 const float b = __ldg(epi.bias + row);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] += b;
+                for (int j = 0; j < 32; ++j) v[j] += b;
+            } else if (col + 32 <= n) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += __ldg(epi.bias + col + j);
             } else {
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (full || col + j < n) v[j] += __ldg(epi.bias + col + j);
+                for (int j = 0; j < 32; ++j)
+                    if (col + j < n) v[j] += __ldg(epi.bias + col + j);
             }
         }
         float* dst = c + static_cast<long long>(row) * ldc + col;
@@ -100,21 +101,25 @@ struct GemmProblem {
             // Partial sum of a split tile: C was zeroed before the launch and every K range
             // adds its share.  With two ranges the result does not depend on their order
             // (0 + p + q == 0 + q + p exactly); more ranges are summed in arrival order.
-            if (vec_ok && full) {
-                atomicAdd(reinterpret_cast<float4*>(dst), make_float4(v[0], v[1], v[2], v[3]));
+            if (vec_ok && col + 32 <= n) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    atomicAdd(reinterpret_cast<float4*>(dst + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
             } else {
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < 32; ++j)
                     if (col + j < n) atomicAdd(dst + j, v[j]);
             }
             return;
         }
         apply_activation(v, epi.act);
-        if (vec_ok && full) {
-            *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        if (vec_ok && col + 32 <= n) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
         } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < 32; ++j)
                 if (col + j < n) dst[j] = v[j];
         }
     }

@@ -104,14 +104,9 @@ struct UmmaConfig {
     static constexpr uint32_t STAGE_BYTES = ATOM_BYTES * KATOMS;
     static constexpr uint32_t TX_BYTES = STAGE_BYTES * CTAS;       // counted on the leader's barrier
     // 227 KB of shared memory per CTA, minus alignment slack and the barriers.
-    // Epilogue staging: each of the 4 epilogue warps transposes 32 x 32 accumulator chunks
-    // through 32 rows of 144 B (128 B of data + 16 B of padding against bank conflicts).
-    static constexpr uint32_t EPI_ROW_BYTES = 144;
-    static constexpr uint32_t EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;
-    static constexpr uint32_t EPI_BYTES = 4 * EPI_WARP_BYTES;
-    static constexpr uint32_t SMEM_BUDGET = 232448 - 1024 - 512 - EPI_BYTES;
+    static constexpr uint32_t SMEM_BUDGET = 232448 - 1024 - 512;
     static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES > 8 ? 8 : SMEM_BUDGET / STAGE_BYTES;
-    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024;   // + alignment slack
+    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + alignment slack
     static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;      // 128 / 256 / 512
     static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
     static_assert(CTAS == 1 || CTAS == 2, "CTAS must be 1 or 2");
@@ -121,9 +116,8 @@ struct UmmaConfig {
 //   struct Tile;                                             decoded tile coordinates
 //   __device__ Tile decode(int tm, int tn, uint32_t cta_rank) const;
 //   __device__ void load(tile, kb, a_smem, b_smem, bar) const;     one lane, issues all TMA loads of a stage
-//   __device__ void store4(tile, row_in_cta, col0, float4 v, epi, mode) const;   4 consecutive columns
-//       (col0 a multiple of 4) of one accumulator row; mode as WorkUnit::mode (1, 2: add the
-//       partial sum into C)
+//   __device__ void store(tile, row_in_cta, col0, float (&v)[32], epi, mode) const;   32 consecutive
+//       columns of one row; mode as WorkUnit::mode (1, 2: add the partial sum into C)
 template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, class Problem>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
 umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
@@ -319,6 +313,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
     } else {
         // ------------------------------------------------------------ epilogue
         const uint32_t quarter = warp & 3u;            // TMEM lanes [32*quarter, +32) belong to this warp
+        const int row_in_cta = quarter * 32 + lane;
         int it = 0;
         bool ok = true;
         for (int u = first_unit; u < num_units && ok; u += unit_stride, ++it) {
@@ -334,43 +329,28 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
             if (!ok) break;
             ptx::tc_fence_after();
             const uint32_t t_row = tmem_base + acc * BN + ((quarter * 32u) << 16);
-            // Each thread receives 32 consecutive columns of one accumulator row.  Stored as
-            // they are, a warp's store instruction would touch 32 different rows (32 partial
-            // cache lines); instead the 32 x 32 chunk is transposed through shared memory so
-            // that every store instruction writes 4 rows x 128 contiguous bytes.  Two register
-            // sets keep the TMEM load of the next chunk in flight meanwhile.
+            // Two register sets: the TMEM load of the next 32 columns is in flight while the
+            // current 32 are converted and stored.
             const int n_cols = (sched.debug & 8u) ? 0 : sched.umma_n;
-            uint8_t* stage_ptr = smem_raw + (smem_base - ptx::smem_u32(smem_raw)) + STAGES * Cfg::STAGE_BYTES +
-                                 (warp - 2) * Cfg::EPI_WARP_BYTES;
-            const int sub_row = lane >> 3;            // row within a group of 4 this lane stores
-            const int sub_col = (lane & 7) * 4;       // first of the 4 columns this lane stores
-            auto flush_chunk = [&](const uint32_t (&r)[32], int c) {
-                float4* mine = reinterpret_cast<float4*>(stage_ptr + lane * Cfg::EPI_ROW_BYTES);
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    mine[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                          __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                __syncwarp();
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int r_local = i * 4 + sub_row;
-                    const float4 v = *reinterpret_cast<const float4*>(stage_ptr + r_local * Cfg::EPI_ROW_BYTES +
-                                                                      sub_col * 4);
-                    prob.store4(tile, int(quarter) * 32 + r_local, c + sub_col, v, epi, w.mode);
-                }
-                __syncwarp();
-            };
             uint32_t r0[32], r1[32];
             if (n_cols > 0) ptx::tmem_ld_32x32(t_row, r0);
 #pragma unroll 1
             for (int c = 0; c < n_cols; c += 64) {
                 ptx::tmem_ld_wait();
                 if (c + 32 < n_cols) ptx::tmem_ld_32x32(t_row + c + 32, r1);
-                flush_chunk(r0, c);
+                {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
+                    prob.store(tile, row_in_cta, c, v, epi, w.mode);
+                }
                 if (c + 32 < n_cols) {
                     ptx::tmem_ld_wait();
                     if (c + 64 < n_cols) ptx::tmem_ld_32x32(t_row + c + 64, r0);
-                    flush_chunk(r1, c + 32);
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
+                    prob.store(tile, row_in_cta, c + 32, v, epi, w.mode);
                 }
             }
             ptx::tc_fence_before();
