@@ -8,9 +8,9 @@ The package is a thin host layer over libcudeep_b200.so (build it with
 """
 from . import nn
 from .tensor import (DType, Event, MemoryPool, Stream, Tensor, broadcast_add, conv2d, device_info, gelu, linear,
-                     relu, sigmoid, silu)
+                     matmul_backward, relu, sigmoid, silu)
 
 __version__ = "0.1.0"
 
 __all__ = ["Tensor", "DType", "Stream", "Event", "MemoryPool", "broadcast_add", "conv2d", "linear", "relu", "gelu",
-           "silu", "sigmoid", "device_info", "nn"]
+           "silu", "sigmoid", "device_info", "matmul_backward", "nn"]

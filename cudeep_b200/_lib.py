@@ -25,6 +25,8 @@ PROTOTYPES = {
     "cudeep_b200_matmul_fused_act": (c_int, [_fp, _fp, _fp, c_int, c_int, c_int, c_int, _stream]),
     "cudeep_b200_linear_forward_f32": (c_int, [_fp, _fp, _fp, _fp, c_int, c_int, c_int, c_int, _stream]),
     "cudeep_b200_linear_forward_f64": (c_int, [_fp, _fp, _fp, _fp, c_int, c_int, c_int, c_int, _stream]),
+    "cudeep_b200_matmul_nt_f32": (c_int, [_fp, _fp, _fp, c_int, c_int, c_int, _stream]),
+    "cudeep_b200_matmul_tn_f32": (c_int, [_fp, _fp, _fp, c_int, c_int, c_int, _stream]),
     "cudeep_b200_gemm_tf32_tuned": (c_int, [_fp, _fp, c_int, _fp, c_int, c_int, c_int, _fp, c_int, c_int,
                                             c_int, c_int, c_int, c_int, c_uint32, c_uint32, _stream]),
     "cudeep_b200_conv2d_forward_f32": (c_int, [_fp, _fp, _fp, _fp] + [c_int] * 11 + [_stream]),

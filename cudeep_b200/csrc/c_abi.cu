@@ -119,6 +119,16 @@ int cudeep_b200_linear_forward_f64(const double* x, const double* W, const doubl
     });
 }
 
+int cudeep_b200_matmul_nt_f32(const float* A, const float* B, float* C, int M, int N, int K,
+                              cudeep_b200_stream_t stream) {
+    return guarded([&] { cudeep::kernels::launch_matmul_nt(A, B, C, M, N, K, as_stream(stream)); });
+}
+
+int cudeep_b200_matmul_tn_f32(const float* A, const float* B, float* C, int M, int N, int K,
+                              cudeep_b200_stream_t stream) {
+    return guarded([&] { cudeep::kernels::launch_matmul_tn(A, B, C, M, N, K, as_stream(stream)); });
+}
+
 int cudeep_b200_gemm_tf32_tuned(const float* A, const float* B, int b_is_nk, float* C, int M, int N,
                                 int K, const float* bias, int bias_per_row, int epilogue, int ctas,
                                 int bn, int raster_group, int max_ctas, uint32_t b_lbo,

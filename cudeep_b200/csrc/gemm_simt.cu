@@ -36,7 +36,7 @@ template <typename T, typename TI> __device__ __forceinline__ T widen(TI x) { re
 template <> __device__ __forceinline__ float widen<float, __half>(__half x) { return __half2float(x); }
 
 // TI: element type of A and B in memory; T: accumulate / output type.
-template <typename TI, typename T, int BM, int BN, int BK, int TM, int TN, bool B_NK>
+template <typename TI, typename T, int BM, int BN, int BK, int TM, int TN, bool B_NK, bool A_KM = false>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_simt_kernel(const TI* __restrict__ a, const TI* __restrict__ b, T* __restrict__ c, int m, int n,
                  int k, const T* __restrict__ bias, int bias_per_row, int act) {
@@ -62,7 +62,9 @@ gemm_simt_kernel(const TI* __restrict__ a, const TI* __restrict__ b, T* __restri
             const int r = idx / BK, kk = idx % BK;
             const long long gr = m0 + r;
             const int gk = k0 + kk;
-            as[kk][r] = (gr < m && gk < k) ? widen<T, TI>(a[gr * k + gk]) : T(0);
+            as[kk][r] = (gr < m && gk < k)
+                            ? widen<T, TI>(A_KM ? a[static_cast<long long>(gk) * m + gr] : a[gr * k + gk])
+                            : T(0);
         }
         if (B_NK) {
             for (int idx = tid; idx < BN * BK; idx += THREADS) {
@@ -274,6 +276,14 @@ void gemm_simt<double>(const double* a, const double* b, bool b_is_nk, double* c
                        int k, const double* bias, bool bias_per_row, int act, cudaStream_t stream) {
     CB200_REQUIRE(m > 0 && n > 0 && k > 0, "GEMM extents must be positive");
     launch<double, double, 64, 64, 16, 4, 4>(a, b, b_is_nk, c, m, n, k, bias, bias_per_row, act, stream);
+}
+
+void gemm_simt_tn(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream) {
+    CB200_REQUIRE(m > 0 && n > 0 && k > 0, "GEMM extents must be positive");
+    dim3 grid((n + 63) / 64, (m + 63) / 64);
+    gemm_simt_kernel<float, float, 64, 64, 16, 4, 4, false, true><<<grid, 256, 0, stream>>>(
+        a, b, c, m, n, k, nullptr, 0, EPI_NONE);
+    CB200_CHECK_LAUNCH();
 }
 
 void gemm_simt_half(const __half* a, const __half* b, float* c, int m, int n, int k,

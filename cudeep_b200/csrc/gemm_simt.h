@@ -14,6 +14,9 @@ template <typename T>
 void gemm_simt(const T* a, const T* b, bool b_is_nk, T* c, int m, int n, int k, const T* bias,
                bool bias_per_row, int act, cudaStream_t stream);
 
+// C[M,N] = A^T * B with A stored [K,M], B stored [K,N]; strict FP32.
+void gemm_simt_tn(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream);
+
 // C[M,N] = A[M,K] * B[K,N] with half inputs widened to FP32 and FP32 accumulation.
 void gemm_simt_half(const __half* a, const __half* b, float* c, int m, int n, int k,
                     cudaStream_t stream);

@@ -18,15 +18,16 @@ namespace cudeep_b200 {
 
 namespace {
 
-template <int CTAS, int BN, bool B_MN_MAJOR>
+template <int CTAS, int BN, bool B_MN_MAJOR, bool A_MN_MAJOR = false>
 struct GemmProblem {
-    CUtensorMap map_a;     // dims {K, M}, box {32, 128}
+    CUtensorMap map_a;     // K-major: dims {K, M}, box {32, 128};  MN-major (A stored [K, M]): as map_b
     CUtensorMap map_b;     // K-major: dims {K, N}, box {32, BN/CTAS};  MN-major: dims {N, K}, box {32, 32}
     float* c;
     long long ldc;
     int m, n;
     int vec_ok;            // rows of C are 16-byte aligned
     int b_chunked;         // MN-major B described as {32, K, N/32}: one load brings every column chunk
+    int a_chunked;         // the same for an MN-major A
 
     struct Tile {
         int m0;            // first C row of this CTA
@@ -50,7 +51,17 @@ struct GemmProblem {
                                          uint32_t bar) const {
         const int k0 = kb * UMMA_BK;
         if constexpr (C == 1) {
-            ptx::tma_load_2d(a_smem, &map_a, bar, k0, t.m0);
+            if constexpr (A_MN_MAJOR) {
+                if (a_chunked) {
+                    ptx::tma_load_3d(a_smem, &map_a, bar, 0, k0, t.m0 / 32);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < UMMA_BM / 32; ++j)
+                        ptx::tma_load_2d(a_smem + j * 4096, &map_a, bar, t.m0 + j * 32, k0);
+                }
+            } else {
+                ptx::tma_load_2d(a_smem, &map_a, bar, k0, t.m0);
+            }
             if constexpr (B_MN_MAJOR) {
                 if (b_chunked) {
                     ptx::tma_load_3d(b_smem, &map_b, bar, 0, k0, t.nb0 / 32);
@@ -63,7 +74,17 @@ struct GemmProblem {
                 ptx::tma_load_2d(b_smem, &map_b, bar, k0, t.nb0);
             }
         } else {
-            ptx::tma_load_2d_pair(a_smem, &map_a, bar, k0, t.m0);
+            if constexpr (A_MN_MAJOR) {
+                if (a_chunked) {
+                    ptx::tma_load_3d_pair(a_smem, &map_a, bar, 0, k0, t.m0 / 32);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < UMMA_BM / 32; ++j)
+                        ptx::tma_load_2d_pair(a_smem + j * 4096, &map_a, bar, t.m0 + j * 32, k0);
+                }
+            } else {
+                ptx::tma_load_2d_pair(a_smem, &map_a, bar, k0, t.m0);
+            }
             if constexpr (B_MN_MAJOR) {
                 if (b_chunked) {
                     ptx::tma_load_3d_pair(b_smem, &map_b, bar, 0, k0, t.nb0 / 32);
@@ -149,15 +170,28 @@ __global__ void zero_tiles_kernel(float* __restrict__ c, long long ldc, int m, i
     }
 }
 
-template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS>
+template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, bool A_MN_MAJOR = false>
 void launch_variant(const float* a, const float* b, float* c, int m, int n, int k,
                     const UmmaEpilogueArgs& epi, const GemmTuning& tune, cudaStream_t stream) {
     using Cfg = UmmaConfig<CTAS, BN, B_MN_MAJOR, KATOMS>;
-    using Prob = GemmProblem<CTAS, BN, B_MN_MAJOR>;
+    using Prob = GemmProblem<CTAS, BN, B_MN_MAJOR, A_MN_MAJOR>;
     const DeviceInfo& dev = device_info();
 
     Prob prob;
-    {
+    prob.a_chunked = 0;
+    if (A_MN_MAJOR && m % 32 == 0) {
+        // A stored [K, M]: M/32 column chunks of 32 floats, one box {32, 32, 4} per stage.
+        const uint64_t dims[3] = {32, uint64_t(k), uint64_t(m / 32)};
+        const uint64_t strides[2] = {uint64_t(m) * 4, 128};
+        const uint32_t box[3] = {32, UMMA_BK, uint32_t(UMMA_BM / 32)};
+        encode_tensor_map(&prob.map_a, a, 3, dims, strides, box, TmaSwizzle::B128Atom32);
+        prob.a_chunked = 1;
+    } else if (A_MN_MAJOR) {
+        const uint64_t dims[2] = {uint64_t(m), uint64_t(k)};
+        const uint64_t strides[1] = {uint64_t(m) * 4};
+        const uint32_t box[2] = {32, UMMA_BK};
+        encode_tensor_map(&prob.map_a, a, 2, dims, strides, box, TmaSwizzle::B128Atom32);
+    } else {
         const uint64_t dims[2] = {uint64_t(k), uint64_t(m)};
         const uint64_t strides[1] = {uint64_t(k) * 4};
         const uint32_t box[2] = {UMMA_BK, UMMA_BM};
@@ -240,7 +274,7 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     const int num_units = sched.n_whole + (num_tiles - sched.n_whole) * sched.split;
     if (groups > num_units) groups = num_units;
 
-    auto kernel = umma_tf32_kernel<CTAS, BN, B_MN_MAJOR, KATOMS, Prob>;
+    auto kernel = umma_tf32_kernel<CTAS, BN, B_MN_MAJOR, KATOMS, Prob, A_MN_MAJOR>;
     ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), Cfg::SMEM_BYTES);
 
     cudaLaunchConfig_t cfg{};
@@ -258,7 +292,7 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     CB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, prob, sched, epi));
 }
 
-template <bool B_MN_MAJOR>
+template <bool B_MN_MAJOR, bool A_MN_MAJOR = false>
 void dispatch(const float* a, const float* b, float* c, int m, int n, int k,
               const UmmaEpilogueArgs& epi, const GemmTuning& tune, cudaStream_t stream) {
     const DeviceInfo& dev = device_info();
@@ -305,18 +339,20 @@ void dispatch(const float* a, const float* b, float* c, int m, int n, int k,
     if (katoms == 0) katoms = (ctas == 2 || bn <= 128) ? 2 : 1;
 #define CB200_CASE(C, N, KA)                                                              \
     if (ctas == C && bn == N && katoms == KA) {                                           \
-        launch_variant<C, N, B_MN_MAJOR, KA>(a, b, c, m, n, k, epi, tune, stream);        \
+        launch_variant<C, N, B_MN_MAJOR, KA, A_MN_MAJOR>(a, b, c, m, n, k, epi, tune, stream); \
         return;                                                                           \
     }
     CB200_CASE(1, 256, 1)
-    CB200_CASE(1, 128, 1)
-    CB200_CASE(1, 128, 2)
-    CB200_CASE(1, 64, 1)
-    CB200_CASE(1, 64, 2)
     CB200_CASE(2, 256, 1)
     CB200_CASE(2, 256, 2)
-    CB200_CASE(2, 128, 1)
-    CB200_CASE(2, 128, 2)
+    if constexpr (!A_MN_MAJOR) {      // narrow tiles are built for the forward layouts only
+        CB200_CASE(1, 128, 1)
+        CB200_CASE(1, 128, 2)
+        CB200_CASE(1, 64, 1)
+        CB200_CASE(1, 64, 2)
+        CB200_CASE(2, 128, 1)
+        CB200_CASE(2, 128, 2)
+    }
 #undef CB200_CASE
     CB200_REQUIRE(false, "unsupported TF32 GEMM tile configuration");
 }
@@ -331,6 +367,26 @@ bool gemm_tf32_supported(const float* a, const float* b, const float* c, int m, 
     if (k % 4 != 0) return false;               // A rows (and W rows) must be 16-byte multiples
     if (!b_is_nk && n % 4 != 0) return false;   // B[K,N] rows likewise
     return device_info().cc_major == 10;
+}
+
+bool gemm_tf32_tn_supported(const float* a, const float* b, int m, int n, int k) {
+    if (m < 1 || n < 1 || k < 1) return false;
+    if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(b) & 15u)) return false;
+    if (m % 4 != 0 || n % 4 != 0) return false;      // rows of A[K,M] and B[K,N] must be 16-byte multiples
+    return device_info().cc_major == 10;
+}
+
+void gemm_tf32_tn(const float* a, const float* b, float* c, int m, int n, int k, const GemmTuning& tune,
+                  cudaStream_t stream) {
+    CB200_REQUIRE(gemm_tf32_tn_supported(a, b, m, n, k),
+                  "TF32 tensor-core GEMM (transposed A) needs an sm_100 device, 16-byte aligned operands "
+                  "and M, N multiples of 4");
+    UmmaEpilogueArgs epi{nullptr, 0, EPI_NONE};
+    GemmTuning t = tune;
+    if (t.ctas == 0) t.ctas = (static_cast<long long>((m + 255) / 256) * ((n + 255) / 256) * 2 >= device_info().num_sms) ? 2 : 1;
+    if (t.bn == 0) t.bn = 256;                        // only the 256-wide tiles are built for this layout
+    CB200_REQUIRE(t.bn == 256, "transposed-A GEMM supports 256-wide tiles only");
+    dispatch<true, true>(a, b, c, m, n, k, epi, t, stream);
 }
 
 void gemm_tf32(const float* a, const float* b, bool b_is_nk, float* c, int m, int n, int k,

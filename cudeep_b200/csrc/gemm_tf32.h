@@ -33,4 +33,11 @@ void gemm_tf32(const float* a, const float* b, bool b_is_nk, float* c, int m, in
                const float* bias, bool bias_per_row, int act, const GemmTuning& tune,
                cudaStream_t stream);
 
+// C[M,N] = A^T * B with A stored [K,M] and B stored [K,N] (both row-major): the weight-gradient
+// product dW = X^T dY of a Linear layer, and a^T @ grad of matmul's backward, without a transposed
+// copy of the left operand (reference python/cuDeep/tensor.py:430-443 makes that copy).
+bool gemm_tf32_tn_supported(const float* a, const float* b, int m, int n, int k);
+void gemm_tf32_tn(const float* a, const float* b, float* c, int m, int n, int k, const GemmTuning& tune,
+                  cudaStream_t stream);
+
 }  // namespace cudeep_b200

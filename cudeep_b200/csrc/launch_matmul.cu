@@ -102,6 +102,19 @@ void launch_linear_forward(const float* x, const float* W, const float* bias, fl
     }
 }
 
+void launch_matmul_tn(const float* A, const float* B, float* C, int M, int N, int K, cudaStream_t stream) {
+    check_dims(A, B, C, M, N, K);
+    if (tensor_core_worthwhile(M, N, K) && cudeep_b200::gemm_tf32_tn_supported(A, B, M, N, K)) {
+        cudeep_b200::gemm_tf32_tn(A, B, C, M, N, K, cudeep_b200::GemmTuning{}, stream);
+    } else {
+        cudeep_b200::gemm_simt_tn(A, B, C, M, N, K, stream);
+    }
+}
+
+void launch_matmul_nt(const float* A, const float* B, float* C, int M, int N, int K, cudaStream_t stream) {
+    launch_linear_forward(A, B, nullptr, C, M, N, K, GemmEpilogue::None, stream);
+}
+
 void launch_linear_forward(const double* x, const double* W, const double* bias, double* y, int M,
                            int N, int K, GemmEpilogue epilogue, cudaStream_t stream) {
     check_dims(x, W, y, M, N, K);

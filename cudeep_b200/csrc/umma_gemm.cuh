@@ -118,7 +118,7 @@ struct UmmaConfig {
 //   __device__ void load(tile, kb, a_smem, b_smem, bar) const;     one lane, issues all TMA loads of a stage
 //   __device__ void store(tile, row_in_cta, col0, float (&v)[32], epi, mode) const;   32 consecutive
 //       columns of one row; mode as WorkUnit::mode (1, 2: add the partial sum into C)
-template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, class Problem>
+template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, class Problem, bool A_MN_MAJOR = false>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
 umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                  const UmmaEpilogueArgs epi) {
@@ -237,9 +237,14 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0 && is_leader) {
             const uint32_t idesc =
-                ptx::idesc_tf32(UMMA_BM * CTAS, sched.umma_n, /*a_mn=*/0, /*b_mn=*/B_MN_MAJOR ? 1 : 0);
+                ptx::idesc_tf32(UMMA_BM * CTAS, sched.umma_n, /*a_mn=*/A_MN_MAJOR ? 1 : 0,
+                                /*b_mn=*/B_MN_MAJOR ? 1 : 0);
             // K-major operand: rows are 128 B, 8-row swizzle atoms 1024 B apart.
-            const uint64_t a_base = ptx::smem_desc(16, 1024, ptx::SMEM_LAYOUT_SW128);
+            // An MN-major A (a transposed left operand, stored [K, M]) uses the same layout as
+            // an MN-major B: 32-row chunks 4096 B apart, 4-row K groups 512 B apart.
+            const uint64_t a_base = A_MN_MAJOR ? ptx::smem_desc(4096, 512, ptx::SMEM_LAYOUT_SW128_ATOM32)
+                                               : ptx::smem_desc(16, 1024, ptx::SMEM_LAYOUT_SW128);
+            constexpr uint32_t a_kstep = A_MN_MAJOR ? 1024u : UMMA_K * 4u;
             // MN-major B (32-bit elements): the only layout the tensor core accepts is
             // the 128-byte swizzle with 32-byte atoms, whose pattern repeats every 4
             // K rows.  Each TMA box is 32 columns x 32 K rows (4096 B): column chunks
@@ -288,7 +293,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                         for (int j = 0; j < KATOMS; ++j) {
 #pragma unroll
                             for (int kk = 0; kk < UMMA_BK / UMMA_K; ++kk) {
-                                const uint64_t a_desc = a_stage + ((j * Cfg::ATOM_BYTES + kk * UMMA_K * 4) >> 4);
+                                const uint64_t a_desc = a_stage + ((j * Cfg::ATOM_BYTES + kk * a_kstep) >> 4);
                                 const uint64_t b_desc = b_stage + ((j * Cfg::ATOM_BYTES + kk * b_kstep) >> 4);
                                 ptx::umma_tf32<CTAS>(d_tmem, a_desc, b_desc, idesc, (ks | j | kk) != 0);
                             }

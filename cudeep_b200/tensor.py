@@ -239,6 +239,33 @@ class Tensor:
 
     __matmul__ = matmul
 
+    def _matmul_variant(self, other: "Tensor", which: str) -> "Tensor":
+        if self.ndim() != 2 or other.ndim() != 2 or self._dtype != DType.float32 or other._dtype != DType.float32:
+            raise RuntimeError(f"matmul_{which}: 2-D float32 tensors expected")
+        if not (self.is_contiguous() and other.is_contiguous()):
+            raise RuntimeError(f"matmul_{which} requires contiguous tensors")
+        lib = _lib.load()
+        if which == "nt":            # self [M,K] x other[N,K]^T
+            (m, k), (n, k2) = self._shape, other._shape
+            fn = lib.cudeep_b200_matmul_nt_f32
+        else:                        # self[K,M]^T x other[K,N]
+            (k, m), (k2, n) = self._shape, other._shape
+            fn = lib.cudeep_b200_matmul_tn_f32
+        if k != k2:
+            raise RuntimeError(f"matmul_{which}: inner dimensions do not match")
+        out = Tensor([m, n], self._dtype)
+        out.stream = self.stream
+        _lib.check(fn(self._storage.ptr, other._storage.ptr, out._storage.ptr, m, n, k, self.stream))
+        return out
+
+    def matmul_nt(self, other: "Tensor") -> "Tensor":
+        """self @ other^T without materialising the transpose (other is [N, K])."""
+        return self._matmul_variant(other, "nt")
+
+    def matmul_tn(self, other: "Tensor") -> "Tensor":
+        """self^T @ other without materialising the transpose (self is [K, M])."""
+        return self._matmul_variant(other, "tn")
+
     def _activation(self, act: int) -> "Tensor":
         if self._dtype != DType.float32:
             raise RuntimeError("activations are float32 only")
@@ -277,6 +304,12 @@ def broadcast_add(matrix: Tensor, row: Tensor) -> Tensor:
     _lib.check(fn(m._storage.ptr, r._storage.ptr, out._storage.ptr, matrix.shape()[0], matrix.shape()[1],
                   matrix.stream))
     return out
+
+
+def matmul_backward(a: Tensor, b: Tensor, grad: Tensor):
+    """Gradients of c = a @ b: (grad @ b^T, a^T @ grad), the two products of MatMulOp.backward
+    (python/cuDeep/tensor.py:430-443) without its transposed copies."""
+    return grad.matmul_nt(b), a.matmul_tn(grad)
 
 
 def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None, activation=None) -> Tensor:

@@ -62,5 +62,15 @@ void launch_linear_forward(const float* x, const float* W, const float* bias, fl
 void launch_linear_forward(const double* x, const double* W, const double* bias, double* y, int M,
                            int N, int K, GemmEpilogue epilogue, cudaStream_t stream = nullptr);
 
+// The two products of matmul's backward pass without transposed copies (the reference
+// materialises b^T and a^T first, python/cuDeep/tensor.py:430-443):
+//   launch_matmul_nt: C[M,N] = A[M,K] * B[N,K]^T     (grad_a = grad * b^T)
+//   launch_matmul_tn: C[M,N] = A[K,M]^T * B[K,N]     (grad_b = a^T * grad)
+// Same precision rule as launch_matmul_kernel<float>.
+void launch_matmul_nt(const float* A, const float* B, float* C, int M, int N, int K,
+                      cudaStream_t stream = nullptr);
+void launch_matmul_tn(const float* A, const float* B, float* C, int M, int N, int K,
+                      cudaStream_t stream = nullptr);
+
 }  // namespace kernels
 }  // namespace cudeep

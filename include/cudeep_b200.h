@@ -85,6 +85,16 @@ int cudeep_b200_linear_forward_f64(const double* x, const double* W, const doubl
                                    int M, int N, int K, int epilogue,
                                    cudeep_b200_stream_t stream);
 
+/* The two products of matmul's backward pass, computed without the transposed copies the
+ * reference makes first (MatMulOp.backward, python/cuDeep/tensor.py:430-443):
+ *   nt: C[M,N] = A[M,K] * B[N,K]^T   (grad_a = grad * b^T; also x * W^T of Linear)
+ *   tn: C[M,N] = A[K,M]^T * B[K,N]   (grad_b = a^T * grad; also dW^T = x^T * dy of Linear)
+ * Precision rule as cudeep_b200_matmul_f32 (tn needs M % 4 == 0 and N % 4 == 0 for TF32). */
+int cudeep_b200_matmul_nt_f32(const float* A, const float* B, float* C, int M, int N, int K,
+                              cudeep_b200_stream_t stream);
+int cudeep_b200_matmul_tn_f32(const float* A, const float* B, float* C, int M, int N, int K,
+                              cudeep_b200_stream_t stream);
+
 /* The TF32 tensor-core GEMM with explicit tile choices, for benchmarks and
  * bring-up.  b_is_nk: 0 = B is [K,N], 1 = B is [N,K].  bias: NULL, N values, or
  * M values when bias_per_row != 0.  ctas (1|2), bn (64|128|256), raster_group,

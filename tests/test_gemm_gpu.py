@@ -203,6 +203,67 @@ def test_tf32_linearity(dev, oracle):
     assert np.array_equal(dev.matmul(2 * a, b), 2 * dev.matmul(a, b))
 
 
+# ---- transposed operands (the products of matmul's backward pass) ---------------------------------
+
+@pytest.mark.parametrize("m,n,k", [
+    (512, 512, 256),      # CTA pair, chunked A and B loads
+    (384, 260, 200),      # N not a multiple of 32: B loaded chunk by chunk
+    (132, 512, 96),       # M not a multiple of 32: A loaded chunk by chunk
+    (1024, 2048, 520),    # several tiles, odd number of K blocks with a partial last one
+    (66, 70, 50),         # extents not multiples of 4: strict FP32 path
+    (8, 6, 4),
+])
+def test_matmul_tn(dev, lib, oracle, m, n, k):
+    rng = np.random.default_rng(m + n + k)
+    a_km = rng.standard_normal((k, m), dtype=np.float32)          # A stored transposed
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    ta, tb = dev.to_dev(a_km), dev.to_dev(b)
+    tc = dev.empty((m, n))
+    dev.check(lib.cudeep_b200_matmul_tn_f32(dev.ptr(ta), dev.ptr(tb), dev.ptr(tc), m, n, k, None))
+    assert dev.sync_status() == 0
+    got = tc.cpu().numpy()
+    a = np.ascontiguousarray(a_km.T)
+    if m >= 64 and n >= 64 and k >= 32 and m % 4 == 0 and n % 4 == 0:
+        check_tf32(oracle, got, a, b, k)
+    else:
+        assert oracle.rel_frobenius(got, oracle.gemm(a, b)) <= FP32_TOL
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 768, 256), (130, 100, 72), (8, 10, 6)])
+def test_matmul_nt(dev, lib, oracle, m, n, k):
+    rng = np.random.default_rng(m * 3 + n + k)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b_nk = rng.standard_normal((n, k), dtype=np.float32)
+    ta, tb = dev.to_dev(a), dev.to_dev(b_nk)
+    tc = dev.empty((m, n))
+    dev.check(lib.cudeep_b200_matmul_nt_f32(dev.ptr(ta), dev.ptr(tb), dev.ptr(tc), m, n, k, None))
+    assert dev.sync_status() == 0
+    got = tc.cpu().numpy()
+    if m >= 64 and n >= 64 and k >= 32 and k % 4 == 0:
+        check_tf32(oracle, got, a, b_nk, k, b_is_nk=True)
+    else:
+        assert oracle.rel_frobenius(got, oracle.gemm(a, b_nk, b_is_nk=True)) <= FP32_TOL
+
+
+def test_matmul_backward_products_match_transposed_copies(dev, lib, oracle):
+    """grad_a = grad b^T and grad_b = a^T grad against the reference's way of computing them
+    (explicit transposed copies, then a plain matmul), both through this library."""
+    rng = np.random.default_rng(99)
+    a = rng.standard_normal((640, 384), dtype=np.float32)
+    b = rng.standard_normal((384, 512), dtype=np.float32)
+    grad = rng.standard_normal((640, 512), dtype=np.float32)
+    ta, tb, tg = dev.to_dev(a), dev.to_dev(b), dev.to_dev(grad)
+    ga, gb = dev.empty((640, 384)), dev.empty((384, 512))
+    dev.check(lib.cudeep_b200_matmul_nt_f32(dev.ptr(tg), dev.ptr(tb), dev.ptr(ga), 640, 384, 512, None))
+    dev.check(lib.cudeep_b200_matmul_tn_f32(dev.ptr(ta), dev.ptr(tg), dev.ptr(gb), 384, 512, 640, None))
+    assert dev.sync_status() == 0
+    ga_ref = dev.matmul(grad, np.ascontiguousarray(b.T))
+    gb_ref = dev.matmul(np.ascontiguousarray(a.T), grad)
+    assert oracle.rel_frobenius(ga.cpu().numpy(), ga_ref) <= TF32_MODEL_TOL
+    assert oracle.rel_frobenius(gb.cpu().numpy(), gb_ref) <= TF32_MODEL_TOL
+    assert oracle.rel_frobenius(gb.cpu().numpy(), oracle.gemm(np.ascontiguousarray(a.T), grad)) <= TF32_TOL
+
+
 # ---- fused epilogues and Linear -----------------------------------------------------------
 
 @pytest.mark.parametrize("act", [0, 1, 2, 3, 4])

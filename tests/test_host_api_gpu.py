@@ -75,6 +75,16 @@ class TestMatmul:
         with pytest.raises(RuntimeError):
             cd.Tensor.randn([2, 3, 4]).matmul(t)                      # not 2-D
 
+    def test_matmul_backward(self, cd, oracle):
+        rng = np.random.default_rng(12)
+        a = rng.standard_normal((256, 128)).astype(np.float32)
+        b = rng.standard_normal((128, 192)).astype(np.float32)
+        g = rng.standard_normal((256, 192)).astype(np.float32)
+        ga, gb = cd.matmul_backward(cd.Tensor.from_numpy(a), cd.Tensor.from_numpy(b), cd.Tensor.from_numpy(g))
+        assert ga.shape() == [256, 128] and gb.shape() == [128, 192]
+        assert oracle.rel_frobenius(ga.numpy(), g.astype(np.float64) @ b.T.astype(np.float64)) <= 5e-3
+        assert oracle.rel_frobenius(gb.numpy(), a.T.astype(np.float64) @ g.astype(np.float64)) <= 5e-3
+
     def test_strict_fp32_option(self, cd, oracle):
         rng = np.random.default_rng(4)
         a = rng.standard_normal((256, 256)).astype(np.float32)
