@@ -53,6 +53,9 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", action="store_true",
+                    help="with --gpus N > 1: additionally time steps that end with the optional NCCL "
+                         "all-gather of C's row shards (reported under \"with_gather\")")
     ap.add_argument("--suite", action="store_true",
                     help="instead of the headline line, time every benchmark configuration next to "
                          "cuBLAS / cuDNN (through torch) and the reference's kernels; one JSON line each")
@@ -270,6 +273,24 @@ def run_ours(args):
     e2e_value = flops_step * args.e2e_steps / e2e_seconds / 1e12
     checksum = float(hc[0, :8].sum())      # the step's result is read on the host
 
+    gather_info = None
+    if dist is not None and args.gather:
+        # The optional collective of the sharded GEMM: every rank ends up with all of C.
+        full = torch.empty((SIZE * world, SIZE), device="cuda", dtype=torch.float32)
+
+        def launch_and_gather():
+            launch()
+            dist.all_gather_into_tensor(full, c)
+
+        g_steps = max(5, args.steps // 10)
+        g_seconds, _, _ = time_device_steps(launch_and_gather, g_steps, 3, dist, local)
+        g_seconds = max_over_ranks(dist, g_seconds)
+        payload = (world - 1) * SIZE * SIZE * 4          # bytes each rank receives per step
+        gather_info = {"value": flops_step * g_steps / g_seconds / 1e12, "unit": "TFLOP/s",
+                       "ms_per_step": g_seconds / g_steps * 1e3, "steps": g_steps,
+                       "bytes_received_per_rank": payload,
+                       "note": "GEMM then ncclAllGather of C on the same stream, not overlapped"}
+        del full
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -300,6 +321,8 @@ def run_ours(args):
                                     "TF32 issues at half the bf16 rate",
                      "kernel": "umma_tf32_kernel", "kernel_ms": kernel_ms},
     }
+    if gather_info is not None:
+        line["with_gather"] = gather_info
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_leg()
     print(json.dumps(line), flush=True)
@@ -530,6 +553,12 @@ def run_c4(lib, ref, timed, emit, ok, P, stream, trim):
 
 def main():
     args = parse_args()
+    # Libraries (NCCL's version banner, for one) may print to stdout; the contract is ONE JSON
+    # line there.  Everything else this process prints goes to stderr, the result line to the
+    # real stdout.
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    sys.stdout = real_stdout
     if args.suite:
         run_suite(args)
         return
