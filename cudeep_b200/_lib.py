@@ -34,6 +34,8 @@ PROTOTYPES = {
     "cudeep_b200_conv2d_forward_f64": (c_int, [_fp, _fp, _fp, _fp] + [c_int] * 11 + [_stream]),
     "cudeep_b200_conv2d_forward_noalloc_f32": (c_int, [_fp, _fp, _fp, _fp] + [c_int] * 12 + [_stream]),
     "cudeep_b200_conv2d_noalloc_capacity": (c_size_t, []),
+    "cudeep_b200_conv2d_backward_data_f32": (c_int, [_fp, _fp, _fp] + [c_int] * 11 + [_stream]),
+    "cudeep_b200_conv2d_backward_weight_f32": (c_int, [_fp, _fp, _fp] + [c_int] * 11 + [_stream]),
     "cudeep_b200_matmul_host_f32": (c_int, [_fp, _fp, _fp, c_int, c_int, c_int, c_int]),
     "cudeep_b200_linear_forward_host_f32": (c_int, [_fp, _fp, _fp, _fp, c_int, c_int, c_int, c_int]),
     "cudeep_b200_conv2d_forward_host_f32": (c_int, [_fp, _fp, _fp, _fp] + [c_int] * 12),

@@ -190,6 +190,28 @@ int cudeep_b200_conv2d_forward_f64(const double* input, const double* weight, co
     });
 }
 
+int cudeep_b200_conv2d_backward_data_f32(const float* grad_output, const float* weight, float* grad_input,
+                                         int batch, int in_channels, int out_channels, int in_h, int in_w,
+                                         int kernel_h, int kernel_w, int stride_h, int stride_w, int pad_h,
+                                         int pad_w, cudeep_b200_stream_t stream) {
+    return guarded([&] {
+        cudeep::kernels::launch_conv2d_backward_data_kernel<float>(
+            grad_output, weight, grad_input, batch, in_channels, out_channels, in_h, in_w, kernel_h, kernel_w,
+            stride_h, stride_w, pad_h, pad_w, as_stream(stream));
+    });
+}
+
+int cudeep_b200_conv2d_backward_weight_f32(const float* grad_output, const float* input, float* grad_weight,
+                                           int batch, int in_channels, int out_channels, int in_h, int in_w,
+                                           int kernel_h, int kernel_w, int stride_h, int stride_w, int pad_h,
+                                           int pad_w, cudeep_b200_stream_t stream) {
+    return guarded([&] {
+        cudeep::kernels::launch_conv2d_backward_weight_kernel<float>(
+            grad_output, input, grad_weight, batch, in_channels, out_channels, in_h, in_w, kernel_h, kernel_w,
+            stride_h, stride_w, pad_h, pad_w, as_stream(stream));
+    });
+}
+
 // ---------------------------------------------------------------- host-buffer entry points
 
 }  // extern "C"

@@ -30,6 +30,24 @@ void launch_conv2d_forward_kernel(const T* input, const T* weight, const T* bias
                                   int kernel_h, int kernel_w, int stride_h, int stride_w, int pad_h,
                                   int pad_w, cudaStream_t stream = nullptr);
 
+// Gradient w.r.t. the input, grad_input [N, C, H, W] from grad_output [N, OC, OH, OW]
+// (reference conv.cuh:18-26).  Stride 1 with enough channels runs as a forward implicit-GEMM
+// convolution of grad_output with flipped filters (TF32); everything else, and double, runs a
+// direct strict-precision kernel.
+template <typename T>
+void launch_conv2d_backward_data_kernel(const T* grad_output, const T* weight, T* grad_input, int batch,
+                                        int in_channels, int out_channels, int in_h, int in_w,
+                                        int kernel_h, int kernel_w, int stride_h, int stride_w, int pad_h,
+                                        int pad_w, cudaStream_t stream = nullptr);
+
+// Gradient w.r.t. the filters, grad_weight [OC, C, KH, KW] (reference conv.cuh:28-36); a direct
+// strict-precision kernel.
+template <typename T>
+void launch_conv2d_backward_weight_kernel(const T* grad_output, const T* input, T* grad_weight, int batch,
+                                          int in_channels, int out_channels, int in_h, int in_w,
+                                          int kernel_h, int kernel_w, int stride_h, int stride_w,
+                                          int pad_h, int pad_w, cudaStream_t stream = nullptr);
+
 // Addition: the same convolution with bias and an activation applied in the
 // GEMM epilogue (one pass over the output instead of conv + bias + activation).
 void launch_conv2d_forward_fused(const float* input, const float* weight, const float* bias,

@@ -167,6 +167,20 @@ int cudeep_b200_conv2d_forward_f64(const double* input, const double* weight, co
                                    int stride_w, int pad_h, int pad_w,
                                    cudeep_b200_stream_t stream);
 
+/* Gradients of the convolution.  Replace launch_conv2d_backward_data_kernel<float> and
+ * launch_conv2d_backward_weight_kernel<float> (include/cudeep/kernels/conv.cuh:18-36,
+ * src/kernels/conv_kernel.cu:417-545).  in_h / in_w are the forward input's size.
+ * grad_input runs on the forward tensor-core path for stride 1 (TF32), otherwise both are
+ * strict FP32. */
+int cudeep_b200_conv2d_backward_data_f32(const float* grad_output, const float* weight, float* grad_input,
+                                         int batch, int in_channels, int out_channels, int in_h, int in_w,
+                                         int kernel_h, int kernel_w, int stride_h, int stride_w, int pad_h,
+                                         int pad_w, cudeep_b200_stream_t stream);
+int cudeep_b200_conv2d_backward_weight_f32(const float* grad_output, const float* input, float* grad_weight,
+                                           int batch, int in_channels, int out_channels, int in_h, int in_w,
+                                           int kernel_h, int kernel_w, int stride_h, int stride_w, int pad_h,
+                                           int pad_w, cudeep_b200_stream_t stream);
+
 /* ---- host-buffer entry points ---------------------------------------------------------- */
 
 /* The reference's Python call sequence Tensor.from_numpy(a).matmul(

@@ -178,6 +178,47 @@ def conv2d_np(x, w, bias=None, stride=(1, 1), padding=(0, 0), act: int = EPI_NON
     return activation(out, act)
 
 
+def conv2d_backward_data_np(dy, w, in_hw, stride=(1, 1), padding=(0, 0), input_mode: int = INPUT_EXACT) -> np.ndarray:
+    """float64 gradient of conv2d w.r.t. its input: dx[n,c,ih,iw] = sum dy[n,oc,oh,ow] * w[oc,c,kh,kw]
+    over the (oc, kh, kw) with oh*s - p + kh == ih (restates col2im_kernel + the weight^T GEMM,
+    src/kernels/conv_kernel.cu:345-478)."""
+    dy32, w32 = _f32(dy), _f32(w)
+    if input_mode == INPUT_TF32_TRUNC:
+        dy32, w32 = tf32_truncate(dy32), tf32_truncate(w32)
+    dy64, w64 = dy32.astype(np.float64), w32.astype(np.float64)
+    n, oc, oh, ow = dy64.shape
+    _, c, kh, kw = w64.shape
+    h, wd = in_hw
+    sh, sw = stride
+    ph, pw = padding
+    dxp = np.zeros((n, c, h + 2 * ph, wd + 2 * pw), dtype=np.float64)
+    for r in range(kh):
+        for q in range(kw):
+            contrib = np.einsum("nohw,oc->nchw", dy64, w64[:, :, r, q])
+            dxp[:, :, r:r + sh * (oh - 1) + 1:sh, q:q + sw * (ow - 1) + 1:sw] += contrib
+    return dxp[:, :, ph:ph + h, pw:pw + wd]
+
+
+def conv2d_backward_weight_np(dy, x, k_hw, stride=(1, 1), padding=(0, 0)) -> np.ndarray:
+    """float64 gradient of conv2d w.r.t. its filters: dw[oc,c,kh,kw] = sum over images and output
+    pixels of dy[n,oc,oh,ow] * x[n,c,oh*s-p+kh,ow*s-p+kw] (src/kernels/conv_kernel.cu:486-545)."""
+    dy64 = np.asarray(dy, dtype=np.float64)
+    x64 = np.asarray(x, dtype=np.float64)
+    n, oc, oh, ow = dy64.shape
+    _, c, h, wd = x64.shape
+    kh, kw = k_hw
+    sh, sw = stride
+    ph, pw = padding
+    xp = np.zeros((n, c, h + 2 * ph, wd + 2 * pw), dtype=np.float64)
+    xp[:, :, ph:ph + h, pw:pw + wd] = x64
+    dw = np.zeros((oc, c, kh, kw), dtype=np.float64)
+    for r in range(kh):
+        for q in range(kw):
+            patch = xp[:, :, r:r + sh * (oh - 1) + 1:sh, q:q + sw * (ow - 1) + 1:sw]
+            dw[:, :, r, q] = np.einsum("nohw,nchw->oc", dy64, patch)
+    return dw
+
+
 def sgemm_f32(a, b) -> np.ndarray:
     """FP32-accumulating host GEMM (the timed CPU baseline kernel)."""
     a, b = _f32(a), _f32(b)

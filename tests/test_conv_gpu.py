@@ -127,6 +127,54 @@ def test_c4_full_batch_properties(dev, oracle):
     assert oracle.rel_frobenius(got[40:41], exact) <= TF32_TOL
 
 
+# ---- backward ---------------------------------------------------------------------------------
+
+def conv_backward(dev, lib, dy, w, x, stride, padding):
+    n, c, h, wd = x.shape
+    oc, _, kh, kw = w.shape
+    tdy, tw, tx = dev.to_dev(dy), dev.to_dev(w), dev.to_dev(x)
+    dx, dw = dev.empty(x.shape), dev.empty(w.shape)
+    args = (n, c, oc, h, wd, kh, kw, stride[0], stride[1], padding[0], padding[1], None)
+    dev.check(lib.cudeep_b200_conv2d_backward_data_f32(dev.ptr(tdy), dev.ptr(tw), dev.ptr(dx), *args))
+    dev.check(lib.cudeep_b200_conv2d_backward_weight_f32(dev.ptr(tdy), dev.ptr(tx), dev.ptr(dw), *args))
+    assert dev.sync_status() == 0
+    return dx.cpu().numpy(), dw.cpu().numpy()
+
+
+def test_backward_reference_known_answers(dev, lib):
+    # cuDeep tests/unit/test_advanced_kernels.cu:197-241
+    ones = np.ones((1, 1, 3, 3), np.float32)
+    dx, dw = conv_backward(dev, lib, ones, np.full((1, 1, 1, 1), 2.0, np.float32), ones, (1, 1), (0, 0))
+    assert np.max(np.abs(dx - 2.0)) < 1e-4
+    assert abs(dw[0, 0, 0, 0] - 9.0) < 1e-4
+
+
+@pytest.mark.parametrize("shape,oc,k,stride,padding,tensor_core", [
+    ((2, 3, 9, 11), 8, (3, 3), (2, 2), (1, 1), False),      # strided: direct kernels
+    ((1, 5, 8, 8), 4, (3, 2), (1, 1), (0, 1), False),       # few channels: direct kernels
+    ((2, 64, 14, 14), 96, (3, 3), (1, 1), (1, 1), True),    # grad_input on the implicit-GEMM path
+    ((1, 160, 12, 20), 48, (5, 5), (1, 1), (2, 2), True),   # 5x5, more input than output channels
+    ((2, 32, 10, 10), 64, (3, 3), (1, 1), (0, 0), True),    # no padding: full correlation with pad 2
+])
+def test_backward_against_oracle(dev, lib, oracle, shape, oc, k, stride, padding, tensor_core):
+    rng = np.random.default_rng(sum(shape) + oc)
+    x = rng.standard_normal(shape, dtype=np.float32)
+    w = rng.standard_normal((oc, shape[1], *k), dtype=np.float32) * np.float32(0.1)
+    oh = (shape[2] + 2 * padding[0] - k[0]) // stride[0] + 1
+    ow = (shape[3] + 2 * padding[1] - k[1]) // stride[1] + 1
+    dy = rng.standard_normal((shape[0], oc, oh, ow), dtype=np.float32)
+    dx, dw = conv_backward(dev, lib, dy, w, x, stride, padding)
+    dx_ref = oracle.conv2d_backward_data_np(dy, w, shape[2:], stride, padding)
+    dw_ref = oracle.conv2d_backward_weight_np(dy, x, k, stride, padding)
+    assert oracle.rel_frobenius(dw, dw_ref) <= FP32_TOL
+    if tensor_core:
+        assert oracle.rel_frobenius(dx, dx_ref) <= TF32_TOL
+        model = oracle.conv2d_backward_data_np(dy, w, shape[2:], stride, padding, input_mode=oracle.INPUT_TF32_TRUNC)
+        assert oracle.rel_frobenius(dx, model) <= TF32_MODEL_TOL
+    else:
+        assert oracle.rel_frobenius(dx, dx_ref) <= FP32_TOL
+
+
 def test_conv_host_buffers(lib, cuda, oracle):
     import ctypes
     from cudeep_b200 import _lib

@@ -102,6 +102,33 @@ def test_ref_conv_layer_shapes(oracle):
                          None, (2, 2), (1, 1)).shape == (1, 8, 4, 4)
 
 
+def test_ref_conv_backward_known_answers(oracle):
+    # tests/unit/test_advanced_kernels.cu:197-219: 1x1 kernel of weight 2, grad_output all ones -> grad_input all 2
+    dy = np.ones((1, 1, 3, 3), np.float32)
+    dx = oracle.conv2d_backward_data_np(dy, np.full((1, 1, 1, 1), 2.0, np.float32), (3, 3))
+    assert np.max(np.abs(dx - 2.0)) < 1e-4
+    # :221-241: input all ones, grad_output all ones -> grad_weight = 9
+    dw = oracle.conv2d_backward_weight_np(dy, np.ones((1, 1, 3, 3), np.float32), (1, 1))
+    assert abs(dw[0, 0, 0, 0] - 9.0) < 1e-4
+
+
+def test_conv_backward_is_the_adjoint_of_forward(oracle):
+    """<conv(x, w), dy> == <x, dgrad(dy, w)> == <w, wgrad(dy, x)> for random data, strides and paddings."""
+    rng = np.random.default_rng(31)
+    for (shape, oc, k, stride, padding) in [((2, 3, 7, 8), 4, (3, 3), (1, 1), (1, 1)),
+                                            ((1, 2, 9, 9), 3, (3, 2), (2, 1), (0, 1)),
+                                            ((2, 4, 6, 6), 2, (1, 1), (1, 1), (0, 0))]:
+        x = rng.standard_normal(shape, dtype=np.float32)
+        w = rng.standard_normal((oc, shape[1], *k), dtype=np.float32)
+        y = oracle.conv2d(x, w, None, stride, padding)
+        dy = rng.standard_normal(y.shape).astype(np.float32)
+        lhs = float(np.sum(y * dy))
+        dx = oracle.conv2d_backward_data_np(dy, w, shape[2:], stride, padding)
+        dw = oracle.conv2d_backward_weight_np(dy, x, k, stride, padding)
+        assert abs(lhs - float(np.sum(x.astype(np.float64) * dx))) <= 1e-9 * abs(lhs) + 1e-9
+        assert abs(lhs - float(np.sum(w.astype(np.float64) * dw))) <= 1e-9 * abs(lhs) + 1e-9
+
+
 # ---- 2. C oracle vs NumPy restatement ---------------------------------------------------
 
 @pytest.mark.parametrize("m,n,k", [(1, 1, 1), (5, 3, 7), (64, 48, 80), (33, 129, 17)])
