@@ -113,19 +113,26 @@ gemm_simt_kernel(const TI* __restrict__ a, const TI* __restrict__ b, T* __restri
 }
 
 // Fast path for FP32 when every extent is a multiple of the tile and the operands are
-// 16-byte aligned: 128-bit global loads, the next K slice prefetched into registers
-// while the current one is multiplied out of shared memory (two buffers, one barrier
-// per slice), 128-bit shared-memory reads in the inner loop.  B is [K,N].
-template <int BM, int BN, int BK, int TM, int TN>
-__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+// 16-byte aligned.  K slices of 16 travel global -> shared memory with cp.async, STAGES - 1
+// slices in flight while one is multiplied, so global latency hides behind the FMAs even
+// when only a few warps fit on an SM (512^3 gives each SM one small CTA).  A stays row-major
+// in shared memory ([BM][16 + 4]); a thread reads 4 consecutive k of a row with one 128-bit
+// load, and all threads of a warp that share a row read the same address (broadcast).
+// B is [K,N].  Sums run in ascending k.
+template <int BM, int BN, int TM, int TN, int STAGES>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN), 2)
 sgemm_aligned_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
                      int m, int n, int k, const float* __restrict__ bias, int bias_per_row, int act) {
+    constexpr int BK = 16;
     constexpr int THREADS = (BM / TM) * (BN / TN);
-    constexpr int A_VEC = BM * BK / 4 / THREADS;     // float4 loads of A per thread and slice
-    constexpr int B_VEC = BK * BN / 4 / THREADS;
-    static_assert(A_VEC >= 1 && B_VEC >= 1 && TM % 4 == 0 && TN % 4 == 0 && BK % 4 == 0, "tile shape");
-    __shared__ __align__(16) float as[2][BK][BM + 4];
-    __shared__ __align__(16) float bs[2][BK][BN + 4];
+    constexpr int A_LD = BK + 4;                 // floats per shared-memory row of A
+    constexpr int B_LD = BN + 4;
+    constexpr int A_CHUNKS = BM * BK / 4;        // 16-byte copies per slice
+    constexpr int B_CHUNKS = BK * BN / 4;
+    static_assert(TM % 4 == 0 && TN % 4 == 0, "micro-tile must be a multiple of 4");
+    extern __shared__ __align__(16) float smem_f[];
+    float* as = smem_f;                                   // [STAGES][BM][A_LD]
+    float* bs = smem_f + STAGES * BM * A_LD;              // [STAGES][BK][B_LD]
 
     const int tid = threadIdx.x;
     const int tx = tid % (BN / TN);
@@ -133,36 +140,19 @@ sgemm_aligned_kernel(const float* __restrict__ a, const float* __restrict__ b, f
     const float* a_tile = a + static_cast<long long>(blockIdx.y) * BM * k;
     const float* b_tile = b + static_cast<long long>(blockIdx.x) * BN;
 
-    float4 ra[A_VEC], rb[B_VEC];
-    auto fetch = [&](int k0) {
-#pragma unroll
-        for (int i = 0; i < A_VEC; ++i) {
-            const int v = tid + i * THREADS;
+    auto issue = [&](int slice, int buf) {
+        const int k0 = slice * BK;
+        for (int v = tid; v < A_CHUNKS; v += THREADS) {
             const int row = v / (BK / 4), kq = (v % (BK / 4)) * 4;
-            ra[i] = *reinterpret_cast<const float4*>(a_tile + static_cast<long long>(row) * k + k0 + kq);
+            const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(as + (buf * BM + row) * A_LD + kq));
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
+                         "l"(a_tile + static_cast<long long>(row) * k + k0 + kq));
         }
-#pragma unroll
-        for (int i = 0; i < B_VEC; ++i) {
-            const int v = tid + i * THREADS;
+        for (int v = tid; v < B_CHUNKS; v += THREADS) {
             const int kk = v / (BN / 4), nq = (v % (BN / 4)) * 4;
-            rb[i] = *reinterpret_cast<const float4*>(b_tile + static_cast<long long>(k0 + kk) * n + nq);
-        }
-    };
-    auto stash = [&](int buf) {
-#pragma unroll
-        for (int i = 0; i < A_VEC; ++i) {
-            const int v = tid + i * THREADS;
-            const int row = v / (BK / 4), kq = (v % (BK / 4)) * 4;
-            as[buf][kq + 0][row] = ra[i].x;
-            as[buf][kq + 1][row] = ra[i].y;
-            as[buf][kq + 2][row] = ra[i].z;
-            as[buf][kq + 3][row] = ra[i].w;
-        }
-#pragma unroll
-        for (int i = 0; i < B_VEC; ++i) {
-            const int v = tid + i * THREADS;
-            const int kk = v / (BN / 4), nq = (v % (BN / 4)) * 4;
-            *reinterpret_cast<float4*>(&bs[buf][kk][nq]) = rb[i];
+            const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(bs + (buf * BK + kk) * B_LD + nq));
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
+                         "l"(b_tile + static_cast<long long>(k0 + kk) * n + nq));
         }
     };
 
@@ -172,31 +162,39 @@ sgemm_aligned_kernel(const float* __restrict__ a, const float* __restrict__ b, f
 #pragma unroll
         for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
 
-    fetch(0);
-    stash(0);
-    __syncthreads();
-    int buf = 0;
-    for (int k0 = 0; k0 < k; k0 += BK) {
-        const bool more = k0 + BK < k;
-        if (more) fetch(k0 + BK);
+    const int slices = k / BK;
 #pragma unroll
-        for (int kk = 0; kk < BK; ++kk) {
-            float av[TM], bv[TN];
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < slices) issue(s, s);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int s = 0; s < slices; ++s) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+        __syncthreads();                      // slice s has landed; buffer (s - 1) % STAGES is free again
+        if (s + STAGES - 1 < slices) issue(s + STAGES - 1, (s + STAGES - 1) % STAGES);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const float* as_s = as + (s % STAGES) * BM * A_LD;
+        const float* bs_s = bs + (s % STAGES) * BK * B_LD;
 #pragma unroll
-            for (int i = 0; i < TM; i += 4)
-                *reinterpret_cast<float4*>(&av[i]) = *reinterpret_cast<const float4*>(&as[buf][kk][ty * TM + i]);
-#pragma unroll
-            for (int j = 0; j < TN; j += 4)
-                *reinterpret_cast<float4*>(&bv[j]) = *reinterpret_cast<const float4*>(&bs[buf][kk][tx * TN + j]);
+        for (int k4 = 0; k4 < BK; k4 += 4) {
+            float4 av[TM];
 #pragma unroll
             for (int i = 0; i < TM; ++i)
+                av[i] = *reinterpret_cast<const float4*>(as_s + (ty * TM + i) * A_LD + k4);
 #pragma unroll
-                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
-        }
-        if (more) {
-            stash(buf ^ 1);
-            __syncthreads();
-            buf ^= 1;
+            for (int kk = 0; kk < 4; ++kk) {
+                float bv[TN];
+#pragma unroll
+                for (int j = 0; j < TN; j += 4)
+                    *reinterpret_cast<float4*>(&bv[j]) =
+                        *reinterpret_cast<const float4*>(bs_s + (k4 + kk) * B_LD + tx * TN + j);
+#pragma unroll
+                for (int i = 0; i < TM; ++i) {
+                    const float ai = kk == 0 ? av[i].x : kk == 1 ? av[i].y : kk == 2 ? av[i].z : av[i].w;
+#pragma unroll
+                    for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(ai, bv[j], acc[i][j]);
+                }
+            }
         }
     }
 
@@ -218,12 +216,14 @@ sgemm_aligned_kernel(const float* __restrict__ a, const float* __restrict__ b, f
     }
 }
 
-template <int BM, int BN, int BK, int TM, int TN>
+template <int BM, int BN, int TM, int TN, int STAGES>
 void launch_aligned(const float* a, const float* b, float* c, int m, int n, int k, const float* bias,
                     bool bias_per_row, int act, cudaStream_t stream) {
+    constexpr size_t smem = sizeof(float) * STAGES * (BM * (16 + 4) + 16 * (BN + 4));
+    auto kernel = sgemm_aligned_kernel<BM, BN, TM, TN, STAGES>;
+    ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     dim3 grid(n / BN, m / BM);
-    sgemm_aligned_kernel<BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, stream>>>(
-        a, b, c, m, n, k, bias, bias_per_row ? 1 : 0, act);
+    kernel<<<grid, (BM / TM) * (BN / TN), smem, stream>>>(a, b, c, m, n, k, bias, bias_per_row ? 1 : 0, act);
     CB200_CHECK_LAUNCH();
 }
 
@@ -253,15 +253,15 @@ void gemm_simt<float>(const float* a, const float* b, bool b_is_nk, float* c, in
     if (!b_is_nk && aligned16 && k % 16 == 0) {
         const long long sms = device_info().num_sms;
         if (m % 128 == 0 && n % 128 == 0 && big_tiles >= sms) {
-            launch_aligned<128, 128, 16, 8, 8>(a, b, c, m, n, k, bias, bias_per_row, act, stream);
+            launch_aligned<128, 128, 8, 8, 3>(a, b, c, m, n, k, bias, bias_per_row, act, stream);
             return;
         }
         if (m % 64 == 0 && n % 64 == 0 && static_cast<long long>(m / 64) * (n / 64) >= sms) {
-            launch_aligned<64, 64, 16, 4, 4>(a, b, c, m, n, k, bias, bias_per_row, act, stream);
+            launch_aligned<64, 64, 4, 4, 4>(a, b, c, m, n, k, bias, bias_per_row, act, stream);
             return;
         }
         if (m % 32 == 0 && n % 64 == 0) {
-            launch_aligned<32, 64, 16, 4, 4>(a, b, c, m, n, k, bias, bias_per_row, act, stream);
+            launch_aligned<32, 64, 4, 4, 4>(a, b, c, m, n, k, bias, bias_per_row, act, stream);
             return;
         }
     }
