@@ -235,7 +235,10 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0 && is_leader) {
+        if (is_leader) {
+            // All 32 lanes walk the loops together (a converged warp keeps descriptors and
+            // addresses in the uniform datapath the tensor-core instructions read from); one
+            // elected lane issues the MMAs and commits.
             const uint32_t idesc =
                 ptx::idesc_tf32(UMMA_BM * CTAS, sched.umma_n, /*a_mn=*/A_MN_MAJOR ? 1 : 0,
                                 /*b_mn=*/B_MN_MAJOR ? 1 : 0);
@@ -264,8 +267,8 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 const int k_stages = (decode_unit(u).kb_count + KATOMS - 1) / KATOMS;
                 const uint32_t acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
-                if (!ptx::mbar_wait(ptx::smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, wctx,
-                                    UMMA_TIMEOUT_MMA_ACC))
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u,
+                                                            wctx, UMMA_TIMEOUT_MMA_ACC)))
                     goto mma_done;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
@@ -274,17 +277,20 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 // MMAs shows up as an idle tensor pipe.  So the barrier of the NEXT stage
                 // is probed before this stage's MMAs are issued, and only waited on if
                 // that early look found it incomplete.
-                bool ready = free_run || ptx::mbar_test(ptx::smem_u32(&bar_full[stage]), phase);
+                bool ready = free_run ||
+                             __all_sync(0xffffffffu, ptx::mbar_test(ptx::smem_u32(&bar_full[stage]), phase));
                 for (int ks = 0; ks < k_stages; ++ks) {
                     if (!ready) {
-                        if (!ptx::mbar_wait(ptx::smem_u32(&bar_full[stage]), phase, wctx,
-                                            UMMA_TIMEOUT_MMA_FULL))
+                        if (!__all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&bar_full[stage]), phase, wctx,
+                                                                    UMMA_TIMEOUT_MMA_FULL)))
                             goto mma_done;
                     }
                     uint32_t next_stage = stage + 1, next_phase = phase;
                     if (next_stage == uint32_t(sched.stages)) { next_stage = 0; next_phase ^= 1u; }
-                    ready = free_run || ptx::mbar_test(ptx::smem_u32(&bar_full[next_stage]), next_phase);
-                    if (!(sched.debug & 2u)) {
+                    ready = free_run || __all_sync(0xffffffffu, ptx::mbar_test(ptx::smem_u32(&bar_full[next_stage]),
+                                                                               next_phase));
+                    const bool issuer = ptx::elect_one();
+                    if (issuer && !(sched.debug & 2u)) {
                         // Descriptors differ only in the start-address field (address >> 4),
                         // so each one is the stage's first descriptor plus a constant.
                         const uint64_t a_stage = a_desc0 + ((stage * Cfg::STAGE_BYTES) >> 4);
@@ -300,17 +306,21 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                         }
                     }
                     // Free the stage once these MMAs have read it (in both CTAs of a pair).
-                    if (!free_run) {
+                    if (issuer && !free_run) {
                         const uint32_t empty_local = ptx::smem_u32(&bar_empty[stage]);
                         ptx::umma_commit<CTAS>(empty_local);
                         if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(empty_local, 1));
                     }
+                    __syncwarp();
                     stage = next_stage;
                     phase = next_phase;
                 }
-                const uint32_t accf_local = ptx::smem_u32(&bar_acc_full[acc]);
-                ptx::umma_commit<CTAS>(accf_local);
-                if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(accf_local, 1));
+                if (ptx::elect_one()) {
+                    const uint32_t accf_local = ptx::smem_u32(&bar_acc_full[acc]);
+                    ptx::umma_commit<CTAS>(accf_local);
+                    if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(accf_local, 1));
+                }
+                __syncwarp();
             }
         }
     mma_done:
