@@ -5,6 +5,8 @@
 
 Objects go to build/ (not tracked); the shared library is written next to this
 file as cudeep_b200/libcudeep_b200.so.  nvcc cross-compiles, so no GPU is needed.
+The pybind11 module _cudeep_core (csrc/bindings/module.cpp) is built against that
+library into the same directory when pybind11 is importable.
 """
 from __future__ import annotations
 
@@ -80,6 +82,35 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+def bindings_path() -> Path:
+    import sysconfig
+    return PKG_DIR / ("_cudeep_core" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_bindings(force: bool = False, verbose: bool = False) -> Path:
+    """Compile the pybind11 module against libcudeep_b200.so (which must exist)."""
+    import sysconfig
+    import pybind11
+    src = CSRC / "bindings" / "module.cpp"
+    out = bindings_path()
+    newest = max(src.stat().st_mtime, _newest_header_mtime(), LIB_PATH.stat().st_mtime)
+    if not force and out.exists() and out.stat().st_mtime >= newest:
+        return out
+    cuda_include = Path(find_nvcc()).resolve().parent.parent / "include"
+    cxx = "/usr/bin/g++" if Path("/usr/bin/g++").exists() else (shutil.which("g++") or "g++")
+    cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden",
+           f"-I{INCLUDE}", f"-I{cuda_include}", f"-I{pybind11.get_include()}",
+           f"-I{sysconfig.get_paths()['include']}", str(src), "-o", str(out),
+           f"-L{PKG_DIR}", "-lcudeep_b200", "-Wl,-rpath,$ORIGIN"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or proc.returncode != 0:
+        sys.stderr.write(proc.stdout + proc.stderr)
+    if proc.returncode != 0:
+        raise RuntimeError("building _cudeep_core failed")
+    return out
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)
+    print(build_bindings(force="--force" in sys.argv, verbose="-v" in sys.argv))
