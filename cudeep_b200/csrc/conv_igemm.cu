@@ -96,6 +96,8 @@ __global__ void pack_filters_kernel(const float* __restrict__ w, float* __restri
 
 template <int CTAS>
 struct ConvProblem {
+    static constexpr bool kTmaStore = false;   // results are scattered to NCHW rows: register stores
+    static constexpr bool kClusterSplit = false;
     CUtensorMap map_w;     // packed filters: dims {KH*KW*Cp, OC}, box {32, 128}
     CUtensorMap map_x;     // NHWC input: dims {Cx, W, H, N}, box {32, box_w, box_h / CTAS, 1}
     float* out;
@@ -276,6 +278,9 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     sched.n_whole = sched.tiles_m * sched.tiles_n;
     sched.split = 1;
     sched.kb_per_split = sched.k_blocks;
+    sched.cluster_split = 1;
+    sched.exchange_bytes = 0;
+    sched.tma_store = 0;
     sched.debug = 0;
 
     const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;

@@ -22,12 +22,16 @@ template <int CTAS, int BN, bool B_MN_MAJOR, bool A_MN_MAJOR = false>
 struct GemmProblem {
     CUtensorMap map_a;     // K-major: dims {K, M}, box {32, 128};  MN-major (A stored [K, M]): as map_b
     CUtensorMap map_b;     // K-major: dims {K, N}, box {32, BN/CTAS};  MN-major: dims {N, K}, box {32, 32}
+    CUtensorMap map_c;     // output for bulk tensor stores: dims {N, M}, box {32, 32}, 128-byte swizzle
     float* c;
     long long ldc;
     int m, n;
     int vec_ok;            // rows of C are 16-byte aligned
     int b_chunked;         // MN-major B described as {32, K, N/32}: one load brings every column chunk
     int a_chunked;         // the same for an MN-major A
+
+    static constexpr bool kTmaStore = true;
+    static constexpr bool kClusterSplit = true;
 
     struct Tile {
         int m0;            // first C row of this CTA
@@ -38,6 +42,46 @@ struct GemmProblem {
     __device__ __forceinline__ void prefetch_maps() const {
         ptx::prefetch_tensormap(&map_a);
         ptx::prefetch_tensormap(&map_b);
+        ptx::prefetch_tensormap(&map_c);
+    }
+    __device__ __forceinline__ const CUtensorMap* out_map() const { return &map_c; }
+    __device__ __forceinline__ void out_coords(const Tile& t, int row_in_cta, int c0, int& x, int& y) const {
+        x = t.n0 + c0;
+        y = t.m0 + row_in_cta;
+    }
+    // Bias and activation of 32 columns of one row, in registers (the store clips what lies
+    // outside C, so only the bias reads are bounded here).
+    __device__ __forceinline__ void finish(const Tile& t, int row_in_cta, int c0, float (&v)[32],
+                                           const UmmaEpilogueArgs& epi) const {
+        const int row = t.m0 + row_in_cta;
+        const int col = t.n0 + c0;
+        if (epi.bias != nullptr && row < m && col < n) {
+            if (epi.bias_per_row) {
+                const float b = __ldg(epi.bias + row);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += b;
+            } else if (col + 32 <= n) {
+                const float4* b4 = reinterpret_cast<const float4*>(epi.bias + col);
+                if ((reinterpret_cast<uintptr_t>(b4) & 15u) == 0) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 b = __ldg(b4 + j);
+                        v[4 * j] += b.x;
+                        v[4 * j + 1] += b.y;
+                        v[4 * j + 2] += b.z;
+                        v[4 * j + 3] += b.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += __ldg(epi.bias + col + j);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col + j < n) v[j] += __ldg(epi.bias + col + j);
+            }
+        }
+        apply_activation(v, epi.act);
     }
     __device__ __forceinline__ Tile decode(int tm, int tn, uint32_t cta_rank) const {
         Tile t;
@@ -223,6 +267,16 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     prob.m = m;
     prob.n = n;
     prob.vec_ok = ((n % 4) == 0) && ((reinterpret_cast<uintptr_t>(c) & 15u) == 0);
+    const bool tma_store = prob.vec_ok && tune.tma_store >= 0;
+    {
+        // Rows of C must be 16-byte multiples for a tensor map; otherwise the map describes a
+        // dummy 32 x 32 view and is never used.
+        const uint64_t dims[2] = {uint64_t(tma_store ? n : 32), uint64_t(tma_store ? m : 32)};
+        const uint64_t strides[1] = {uint64_t(tma_store ? n : 32) * 4};
+        const uint32_t box[2] = {32, 32};
+        if (tma_store) encode_tensor_map(&prob.map_c, c, 2, dims, strides, box, TmaSwizzle::B128);
+        else prob.map_c = prob.map_a;
+    }
 
     UmmaSchedule sched;
     sched.tiles_m = (m + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS);
@@ -236,6 +290,8 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     sched.umma_n = BN;
     sched.tx_bytes = Cfg::TX_BYTES;
     sched.stages = (tune.stages > 0 && tune.stages < Cfg::STAGES) ? tune.stages : Cfg::STAGES;
+    sched.tma_store = tma_store ? 1 : 0;
+    const uint32_t staging_bytes = tma_store ? UMMA_STORE_STAGING_BYTES : 0u;
     sched.debug = tune.debug;
 
     const int num_tiles = sched.tiles_m * sched.tiles_n;
@@ -274,22 +330,141 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     const int num_units = sched.n_whole + (num_tiles - sched.n_whole) * sched.split;
     if (groups > num_units) groups = num_units;
 
+    // Split-K inside a cluster, for problems with far fewer tiles than SMs: one cluster of
+    // CTAS * ksplit CTAs per tile, partial sums exchanged through distributed shared memory.
+    int ksplit = (sched.split == 1) ? tune.cluster_split : 1;
+    int per = sched.k_blocks;
+    uint32_t exchange_bytes = 0;
+    while (ksplit > 1) {
+        per = (sched.k_blocks + ksplit - 1) / ksplit;
+        per = (per + KATOMS - 1) / KATOMS * KATOMS;
+        exchange_bytes = uint32_t(ksplit - 1) * UMMA_BM * (BN / ksplit) * 4u;
+        const bool fits = exchange_bytes + staging_bytes + 2 * Cfg::STAGE_BYTES <= Cfg::SMEM_BUDGET;
+        if (CTAS * ksplit <= 8 && BN % (32 * ksplit) == 0 && (sched.k_blocks + per - 1) / per == ksplit && fits)
+            break;
+        ksplit /= 2;
+    }
+    sched.cluster_split = 1;
+    if (ksplit > 1) {
+        sched.cluster_split = ksplit;
+        sched.kb_per_split = per;
+        groups = num_tiles * ksplit;
+    } else {
+        exchange_bytes = 0;
+    }
+    sched.exchange_bytes = exchange_bytes;
+    // Dynamic shared memory: [stages][exchange buffer][store staging], after up to 1 KB of alignment.
+    const int fit_stages = int((Cfg::SMEM_BUDGET - exchange_bytes - staging_bytes) / Cfg::STAGE_BYTES);
+    if (sched.stages > fit_stages) sched.stages = fit_stages;
+    const uint32_t smem_bytes = uint32_t(sched.stages) * Cfg::STAGE_BYTES + exchange_bytes + staging_bytes + 1024;
+
     auto kernel = umma_tf32_kernel<CTAS, BN, B_MN_MAJOR, KATOMS, Prob, A_MN_MAJOR>;
-    ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), Cfg::SMEM_BYTES);
+    ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), Cfg::SMEM_MAX);
 
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(groups * CTAS), 1, 1);
     cfg.blockDim = dim3(UMMA_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.x = unsigned(CTAS * sched.cluster_split);
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     CB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, prob, sched, epi));
+}
+
+// One tile shape with what it costs, measured on B200 at 1.9 GHz with cold operands (launches
+// back to back in a CUDA graph):
+//   step_ns   one K = 8 step of a CTA in the steady state.  The MMA reads both operands from
+//             shared memory at about 96 B/clk and an SM takes in about 60 B/clk from L2, so narrow
+//             tiles pay per step for bytes, not for flops; a CTA pair halves the B bytes per CTA.
+//   base_us   launch, set-up, first loads and teardown (clusters cost more);
+//   epi_us    reading one accumulator out of TMEM and storing the CTA's part of the tile.
+struct TileCost { int ctas, bn; double step_ns, base_us, epi_us; };
+constexpr TileCost kTileCosts[] = {
+    {2, 256, 80.0, 4.9, 4.0}, {1, 256, 97.0, 3.9, 4.0}, {2, 128, 53.0, 4.9, 2.5},
+    {1, 128, 68.0, 3.9, 2.5}, {1, 64, 54.0, 3.9, 1.7}};
+
+struct TilePick { int ctas, bn, cluster_split, katoms; };
+
+// Pipeline stages left for a configuration once the exchange buffer and the store staging are
+// taken from the CTA's shared memory.
+inline int stages_for(int ctas, int bn, int katoms, int cluster_split) {
+    const int stage = katoms * (int(UMMA_BM) * UMMA_BK * 4 + bn / ctas * UMMA_BK * 4);
+    const int exchange = cluster_split > 1 ? (cluster_split - 1) * UMMA_BM * (bn / cluster_split) * 4 : 0;
+    const int budget = 232448 - 1024 - 512 - exchange - int(UMMA_STORE_STAGING_BYTES);
+    const int stages = budget / stage;
+    return stages > 8 ? 8 : stages;
+}
+
+inline int default_katoms(int ctas, int bn, int cluster_split) {
+    // Two K blocks per stage halve the barrier traffic of the MMA issuer; taken wherever at
+    // least three such stages fit.
+    if (ctas == 1 && bn == 256) return 1;
+    return stages_for(ctas, bn, 2, cluster_split) >= 3 ? 2 : 1;
+}
+
+// Estimated time of one configuration in microseconds (0 when it cannot run).
+inline double estimate_us(const TileCost& t, int cluster_split, int m, int n, int k, bool allow_tail_split,
+                          int num_sms) {
+    const long long tiles = static_cast<long long>((m + 128 * t.ctas - 1) / (128 * t.ctas)) * ((n + t.bn - 1) / t.bn);
+    const int k_blocks = (k + UMMA_BK - 1) / UMMA_BK;
+    // Operands cross HBM at least once.
+    const double dram_us = (double(m) * k + double(n) * k + double(m) * n) * 4.0 / 6.5e6;
+    if (cluster_split == 1) {
+        const long long slots = num_sms / t.ctas;
+        const long long tail = tiles % slots;
+        double waves = double(tiles / slots) + (tail > 0 ? 1.0 : 0.0);
+        double extra = 0.0;
+        if (allow_tail_split && tail > 0 && tiles > slots && slots / tail >= 2 && k_blocks >= 16) {
+            waves -= 0.5;            // the ragged last wave is cut in two K ranges
+            extra = 1.5;             // zeroing C, adding partial sums
+        }
+        const double loop_us = waves * 4.0 * k_blocks * t.step_ns * 1e-3;
+        return t.base_us + (loop_us > dram_us ? loop_us : dram_us) + t.epi_us + extra;
+    }
+    // Split-K inside a cluster: one cluster of ctas * cluster_split CTAs per tile.  Clusters of
+    // more than two CTAs live inside one GPC and do not pack the SMs completely.
+    const int cluster = cluster_split * t.ctas;
+    const long long cluster_slots = cluster <= 2 ? num_sms / cluster : static_cast<long long>(num_sms * 0.875 / cluster + 0.5);
+    const int per = (k_blocks + cluster_split - 1) / cluster_split;
+    if (cluster > 8 || tiles > cluster_slots || t.bn % (32 * cluster_split) != 0 || per < 2 ||
+        (k_blocks + per - 1) / per != cluster_split)
+        return 0.0;
+    const int katoms = default_katoms(t.ctas, t.bn, cluster_split);
+    if (stages_for(t.ctas, t.bn, katoms, cluster_split) < 2) return 0.0;
+    double exchange_us = 3.5;
+    for (int s = cluster_split; s > 2; s /= 2) exchange_us += 0.75;
+    const double loop_us = 4.0 * per * t.step_ns * 1e-3;
+    return t.base_us + (loop_us > dram_us ? loop_us : dram_us) + t.epi_us / cluster_split + exchange_us;
+}
+
+template <bool A_MN_MAJOR>
+TilePick pick_tile(int m, int n, int k, const UmmaEpilogueArgs& epi, const GemmTuning& tune, int num_sms) {
+    TilePick pick{1, 64, 1, 0};
+    double best = 0.0;
+    for (const TileCost& t : kTileCosts) {
+        if (tune.ctas != 0 && t.ctas != tune.ctas) continue;
+        if (tune.bn != 0 && t.bn != tune.bn) continue;
+        if (A_MN_MAJOR && t.bn != 256) continue;          // the transposed-A kernels are built 256 wide only
+        for (int ks = 1; ks <= 8; ks *= 2) {
+            if (ks > 1 && (A_MN_MAJOR || tune.cluster_split == 1)) break;
+            // 256-wide tiles keep too few pipeline stages beside their exchange buffer to gain
+            // from a split (measured), so only narrower ones are split unless the caller insists.
+            if (ks > 1 && t.bn == 256 && tune.cluster_split == 0) break;
+            if (tune.cluster_split > 1 && ks != tune.cluster_split) continue;
+            const bool tail_split = epi.act == EPI_NONE && tune.split_k != 1;
+            const double us = estimate_us(t, ks, m, n, k, tail_split, num_sms);
+            if (us > 0.0 && (best == 0.0 || us < best)) {
+                best = us;
+                pick = TilePick{t.ctas, t.bn, ks, 0};
+            }
+        }
+    }
+    return pick;
 }
 
 template <bool B_MN_MAJOR, bool A_MN_MAJOR = false>
@@ -298,48 +473,20 @@ void dispatch(const float* a, const float* b, float* c, int m, int n, int k,
     const DeviceInfo& dev = device_info();
     int ctas = tune.ctas;
     int bn = tune.bn;
+    int cluster_split = tune.cluster_split > 1 ? tune.cluster_split : 1;
     if (ctas == 0 || bn == 0) {
-        // Pick the tile by a small cost model.  An MMA costs the issuing thread about the
-        // same time whatever its N (measured on B200: ~150 clk for a CTA pair at N = 256,
-        // ~185 / 143 / 121 clk for one CTA at N = 256 / 128 / 64), so the time of a launch
-        // is waves x MMAs per tile x that cost, plus a fixed start-up that is larger for
-        // clusters.  Wide tiles win as soon as they fill the machine; narrow ones only
-        // help problems too small to give every SM a wide tile.
-        struct Candidate { int ctas, bn; double mma_clk, fixed_clk; };
-        const Candidate candidates[] = {
-            {2, 256, 150.0, 9000.0}, {1, 256, 185.0, 4000.0}, {1, 128, 143.0, 4000.0}, {1, 64, 121.0, 4000.0}};
-        const double k_mmas = 4.0 * ((k + UMMA_BK - 1) / UMMA_BK);
-        double best = 0.0;
-        int pick_ctas = 1, pick_bn = 64;
-        for (const Candidate& cand : candidates) {
-            if (ctas != 0 && cand.ctas != ctas) continue;
-            if (bn != 0 && cand.bn != bn) continue;
-            const long long tiles = static_cast<long long>((m + 128 * cand.ctas - 1) / (128 * cand.ctas)) *
-                                    ((n + cand.bn - 1) / cand.bn);
-            const long long slots = dev.num_sms / cand.ctas;
-            const long long tail = tiles % slots;
-            double waves = static_cast<double>(tiles / slots) + (tail > 0 ? 1.0 : 0.0);
-            double extra = 0.0;
-            if (tail > 0 && tiles > slots && slots / tail >= 2 && epi.act == EPI_NONE && tune.split_k != 1 &&
-                k >= 16 * UMMA_BK) {
-                waves -= 0.5;            // the last wave is split in two K ranges
-                extra = 3000.0;          // zeroing C and adding partial sums
-            }
-            const double cost = waves * k_mmas * cand.mma_clk + cand.fixed_clk + extra;
-            if (best == 0.0 || cost < best) {
-                best = cost;
-                pick_ctas = cand.ctas;
-                pick_bn = cand.bn;
-            }
-        }
-        if (ctas == 0) ctas = pick_ctas;
-        if (bn == 0) bn = pick_bn;
+        const TilePick pick = pick_tile<A_MN_MAJOR>(m, n, k, epi, tune, dev.num_sms);
+        ctas = pick.ctas;
+        bn = pick.bn;
+        cluster_split = pick.cluster_split;
     }
     int katoms = tune.katoms;
-    if (katoms == 0) katoms = (ctas == 2 || bn <= 128) ? 2 : 1;
+    if (katoms == 0) katoms = default_katoms(ctas, bn, cluster_split);
+    GemmTuning chosen = tune;
+    chosen.cluster_split = cluster_split;
 #define CB200_CASE(C, N, KA)                                                              \
     if (ctas == C && bn == N && katoms == KA) {                                           \
-        launch_variant<C, N, B_MN_MAJOR, KA, A_MN_MAJOR>(a, b, c, m, n, k, epi, tune, stream); \
+        launch_variant<C, N, B_MN_MAJOR, KA, A_MN_MAJOR>(a, b, c, m, n, k, epi, chosen, stream); \
         return;                                                                           \
     }
     CB200_CASE(1, 256, 1)

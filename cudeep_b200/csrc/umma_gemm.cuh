@@ -29,6 +29,7 @@ enum UmmaStatus : uint32_t {
     UMMA_TIMEOUT_MMA_FULL = 2,   // MMA issuer waited for operand data
     UMMA_TIMEOUT_MMA_ACC = 3,    // MMA issuer waited for a free accumulator
     UMMA_TIMEOUT_EPILOGUE = 4,   // epilogue waited for a finished accumulator
+    UMMA_TIMEOUT_EXCHANGE = 5,   // epilogue waited for the partial sums of the other K ranges
 };
 
 constexpr int UMMA_BM = 128;        // accumulator rows per CTA
@@ -60,6 +61,20 @@ struct UmmaSchedule {
     int n_whole;
     int split;
     int kb_per_split;
+    // Split-K inside a thread-block cluster (cluster_split > 1; then split == 1): a cluster of
+    // CTAS * cluster_split CTAs owns one tile, CTA group g of it accumulates K blocks
+    // [g * kb_per_split, (g + 1) * kb_per_split), and the groups exchange partial sums through
+    // distributed shared memory: group g receives columns [g, g + 1) * umma_n / cluster_split of
+    // every other group's accumulator, adds them to its own in a fixed order and stores that
+    // slice with bias and activation.  The grid holds one cluster per tile, the exchange buffer
+    // starts `stages` stages into the dynamic shared memory, and every group has a non-empty
+    // K range.
+    int cluster_split;
+    uint32_t exchange_bytes;   // size of that exchange buffer (0 without cluster split)
+    // Problems with a tensor map of the output (Problem::kTmaStore, and the launch says so here)
+    // stage each 32 x 32 block of results in shared memory, behind the stages and the exchange
+    // buffer, and write it with one bulk tensor store: 8 KB (two blocks) per epilogue warp.
+    int tma_store;
     // Diagnostics for performance bring-up (results are then meaningless):
     //   bit 0: after the ring has been filled once the producer stops loading and only
     //          signals the stages, so the MMA side runs without memory traffic;
@@ -107,6 +122,7 @@ struct UmmaConfig {
     static constexpr uint32_t SMEM_BUDGET = 232448 - 1024 - 512;
     static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES > 8 ? 8 : SMEM_BUDGET / STAGE_BYTES;
     static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + alignment slack
+    static constexpr uint32_t SMEM_MAX = SMEM_BUDGET + 1024;              // most a launch may ask for
     static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;      // 128 / 256 / 512
     static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
     static_assert(CTAS == 1 || CTAS == 2, "CTAS must be 1 or 2");
@@ -118,6 +134,12 @@ struct UmmaConfig {
 //   __device__ void load(tile, kb, a_smem, b_smem, bar) const;     one lane, issues all TMA loads of a stage
 //   __device__ void store(tile, row_in_cta, col0, float (&v)[32], epi, mode) const;   32 consecutive
 //       columns of one row; mode as WorkUnit::mode (1, 2: add the partial sum into C)
+//   static constexpr bool kClusterSplit;   the launcher may set UmmaSchedule::cluster_split > 1
+//   static constexpr bool kTmaStore;   if true, also:
+//   __device__ void finish(tile, row_in_cta, col0, float (&v)[32], epi) const;   bias + activation only
+//   __device__ const CUtensorMap* out_map() const;      C as {N, M}, box {32, 32}, 128-byte swizzle
+//   __device__ void out_coords(tile, row_in_cta, col0, int& x, int& y) const;
+constexpr uint32_t UMMA_STORE_STAGING_BYTES = 4 * 2 * 4096;     // 4 epilogue warps x 2 blocks of 32 x 32 floats
 template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, class Problem, bool A_MN_MAJOR = false>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
 umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
@@ -132,12 +154,19 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
     __shared__ __align__(8) uint64_t bar_empty[STAGES];
     __shared__ __align__(8) uint64_t bar_acc_full[2];
     __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ __align__(8) uint64_t bar_exchange;
     __shared__ uint32_t tmem_base_holder;
     __shared__ uint32_t abort_flag;
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
-    const uint32_t cta_rank = (CTAS == 2) ? ptx::cluster_ctarank() : 0u;
+    // K ranges per tile (>= 1); problems that never split compile the exchange away.
+    const uint32_t ksplit = Problem::kClusterSplit ? uint32_t(sched.cluster_split) : 1u;
+    const bool clustered = (CTAS == 2) || ksplit > 1;
+    const uint32_t cluster_rank = clustered ? ptx::cluster_ctarank() : 0u;
+    const uint32_t cta_rank = (CTAS == 2) ? (cluster_rank & 1u) : 0u;       // place in the CTA pair
+    const uint32_t kgroup = cluster_rank / CTAS;                            // which K range
+    const uint32_t leader_rank = cluster_rank - cta_rank;                   // cluster rank of the pair's leader
     const bool is_leader = (cta_rank == 0);
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
 
@@ -154,6 +183,8 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
             ptx::mbar_init(ptx::smem_u32(&bar_acc_full[a]), 1);
             ptx::mbar_init(ptx::smem_u32(&bar_acc_empty[a]), 4 * CTAS);
         }
+        // One arrival per epilogue thread of every other K range.
+        ptx::mbar_init(ptx::smem_u32(&bar_exchange), ksplit > 1 ? (ksplit - 1) * UMMA_BM : 1);
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
@@ -162,7 +193,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
     }
     ptx::tc_fence_before();
     __syncthreads();
-    if constexpr (CTAS == 2) {   // the peer's barriers must exist before anything signals them
+    if (clustered) {             // the peers' barriers must exist before anything signals them
         ptx::cluster_arrive();
         ptx::cluster_wait();
     }
@@ -171,15 +202,20 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
 
     const int num_tiles = sched.tiles_m * sched.tiles_n;
     const int num_units = sched.n_whole + (num_tiles - sched.n_whole) * sched.split;
-    const int unit_stride = gridDim.x / CTAS;
-    const int first_unit = blockIdx.x / CTAS;
+    const int unit_stride = gridDim.x / (CTAS * ksplit);
+    const int first_unit = blockIdx.x / (CTAS * ksplit);
 
     auto tile_coords = [&](int t, int& tm, int& tn) {
         raster_coords(t, sched.tiles_m, sched.tiles_n, sched.raster_group, tm, tn);
     };
     auto decode_unit = [&](int u) {
         WorkUnit w;
-        if (u < sched.n_whole) {
+        if (ksplit > 1) {
+            w.tile = u;
+            w.kb0 = int(kgroup) * sched.kb_per_split;
+            w.kb_count = min(sched.kb_per_split, sched.k_blocks - w.kb0);
+            w.mode = 0;
+        } else if (u < sched.n_whole) {
             w.tile = u;
             w.kb0 = 0;
             w.kb_count = sched.k_blocks;
@@ -214,7 +250,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                         if (is_leader) ptx::mbar_arrive(full_local);
                     } else {
                         if (is_leader) ptx::mbar_arrive_expect_tx(full_local, sched.tx_bytes);
-                        const uint32_t full_bar = (CTAS == 2) ? ptx::mapa(full_local, 0) : full_local;
+                        const uint32_t full_bar = (CTAS == 2) ? ptx::mapa(full_local, leader_rank) : full_local;
                         // Atoms past the end of K are loaded too; their coordinates are out
                         // of range, so they arrive as zeros and add nothing.  (A split unit
                         // that is not the last holds a whole number of stages, so it never
@@ -309,7 +345,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                     if (issuer && !free_run) {
                         const uint32_t empty_local = ptx::smem_u32(&bar_empty[stage]);
                         ptx::umma_commit<CTAS>(empty_local);
-                        if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(empty_local, 1));
+                        if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(empty_local, leader_rank + 1));
                     }
                     __syncwarp();
                     stage = next_stage;
@@ -318,7 +354,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 if (ptx::elect_one()) {
                     const uint32_t accf_local = ptx::smem_u32(&bar_acc_full[acc]);
                     ptx::umma_commit<CTAS>(accf_local);
-                    if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(accf_local, 1));
+                    if constexpr (CTAS == 2) ptx::umma_commit<CTAS>(ptx::mapa(accf_local, leader_rank + 1));
                 }
                 __syncwarp();
             }
@@ -331,6 +367,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
         const int row_in_cta = quarter * 32 + lane;
         int it = 0;
         bool ok = true;
+        uint32_t store_count = 0;      // bulk tensor stores issued by this warp
         for (int u = first_unit; u < num_units && ok; u += unit_stride, ++it) {
             const WorkUnit w = decode_unit(u);
             int tm, tn;
@@ -348,34 +385,114 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
             // current 32 are converted and stored.
             const int n_cols = (sched.debug & 8u) ? 0 : sched.umma_n;
             uint32_t r0[32], r1[32];
-            if (n_cols > 0) ptx::tmem_ld_32x32(t_row, r0);
+            // Writes 32 finished columns of this thread's row: through the staging block and a
+            // bulk tensor store where the problem has an output map, else straight from registers.
+            bool use_tma = false;
+            if constexpr (Problem::kTmaStore) use_tma = sched.tma_store != 0 && w.mode == 0;
+            const uint32_t staging = smem_base + uint32_t(sched.stages) * Cfg::STAGE_BYTES + sched.exchange_bytes +
+                                     quarter * 8192u;
+            auto emit = [&](int c, const uint32_t (&r)[32]) {
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                if constexpr (Problem::kTmaStore) {
+                    if (use_tma) {
+                        prob.finish(tile, row_in_cta, c, v, epi);
+                        // The block written two stores ago must have been read out.
+                        if (lane == 0) ptx::bulk_wait_group_read<1>();
+                        __syncwarp();
+                        const uint32_t block = staging + (store_count & 1u) * 4096u;
+                        ++store_count;
+                        const uint32_t row_smem = block + lane * 128u;
+#pragma unroll
+                        for (uint32_t q = 0; q < 8; ++q)      // 128-byte swizzle: unit q of row r at q ^ (r & 7)
+                            ptx::st_shared_v4(row_smem + ((q ^ (lane & 7u)) << 4), v[4 * q], v[4 * q + 1],
+                                              v[4 * q + 2], v[4 * q + 3]);
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            int x, y;
+                            prob.out_coords(tile, int(quarter) * 32, c, x, y);
+                            ptx::tma_store_2d(prob.out_map(), block, x, y);
+                            ptx::bulk_commit_group();
+                        }
+                        return;
+                    }
+                }
+                prob.store(tile, row_in_cta, c, v, epi, w.mode);
+            };
+            if (ksplit > 1) {
+                // ---- split-K inside the cluster: exchange partial sums, then reduce one slice
+                // Exchange buffer: [source group (own one skipped)][32-column chunk of the slice]
+                // [16-byte unit of the row (8)][row (128)][16 B]: one store instruction of a warp
+                // covers 512 contiguous bytes of the peer's shared memory, and the thread that
+                // reduces a row reads back exactly what its counterpart wrote.
+                const uint32_t xbuf = smem_base + uint32_t(sched.stages) * Cfg::STAGE_BYTES;
+                const int slice = sched.umma_n / int(ksplit);          // columns this group reduces
+                const int slice_chunks = slice / 32;
+                const uint32_t row_off = uint32_t(row_in_cta) * 16u;
 #pragma unroll 1
-            for (int c = 0; c < n_cols; c += 64) {
+                for (int c = 0; c < n_cols; c += 32) {
+                    const uint32_t owner = uint32_t(c / slice);
+                    if (owner == kgroup) continue;
+                    ptx::tmem_ld_32x32(t_row + c, r0);
+                    ptx::tmem_ld_wait();
+                    const uint32_t slot = kgroup > owner ? kgroup - 1 : kgroup;
+                    const uint32_t chunk = slot * slice_chunks + uint32_t(c - int(owner) * slice) / 32u;
+                    const uint32_t dst = ptx::mapa(xbuf + chunk * (UMMA_BM * 128u) + row_off, owner * CTAS + cta_rank);
+#pragma unroll
+                    for (uint32_t q = 0; q < 8; ++q)
+                        ptx::st_cluster_v4(dst + q * (UMMA_BM * 16u), r0[4 * q], r0[4 * q + 1], r0[4 * q + 2],
+                                           r0[4 * q + 3]);
+                }
+                for (uint32_t g = 0; g < ksplit; ++g)
+                    if (g != kgroup)
+                        ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bar_exchange), g * CTAS + cta_rank));
+                ok = ptx::mbar_wait<true>(ptx::smem_u32(&bar_exchange), 0, wctx, UMMA_TIMEOUT_EXCHANGE);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+#pragma unroll 1
+                for (int cc = 0; cc < slice_chunks && n_cols > 0; ++cc) {
+                    const int c = int(kgroup) * slice + cc * 32;
+                    ptx::tmem_ld_32x32(t_row + c, r0);
+                    ptx::tmem_ld_wait();
+                    for (uint32_t slot = 0; slot + 1 < ksplit; ++slot) {      // fixed order: reproducible
+                        const uint32_t src = xbuf + (slot * slice_chunks + cc) * (UMMA_BM * 128u) + row_off;
+#pragma unroll
+                        for (uint32_t q = 0; q < 8; ++q) {
+                            const float4 p = ptx::ld_shared_v4(src + q * (UMMA_BM * 16u));
+                            r0[4 * q] = __float_as_uint(__uint_as_float(r0[4 * q]) + p.x);
+                            r0[4 * q + 1] = __float_as_uint(__uint_as_float(r0[4 * q + 1]) + p.y);
+                            r0[4 * q + 2] = __float_as_uint(__uint_as_float(r0[4 * q + 2]) + p.z);
+                            r0[4 * q + 3] = __float_as_uint(__uint_as_float(r0[4 * q + 3]) + p.w);
+                        }
+                    }
+                    emit(c, r0);
+                }
+            }
+            if (ksplit == 1 && n_cols > 0) ptx::tmem_ld_32x32(t_row, r0);
+#pragma unroll 1
+            for (int c = 0; ksplit == 1 && c < n_cols; c += 64) {
                 ptx::tmem_ld_wait();
                 if (c + 32 < n_cols) ptx::tmem_ld_32x32(t_row + c + 32, r1);
-                {
-                    float v[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
-                    prob.store(tile, row_in_cta, c, v, epi, w.mode);
-                }
+                emit(c, r0);
                 if (c + 32 < n_cols) {
                     ptx::tmem_ld_wait();
                     if (c + 64 < n_cols) ptx::tmem_ld_32x32(t_row + c + 64, r0);
-                    float v[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
-                    prob.store(tile, row_in_cta, c + 32, v, epi, w.mode);
+                    emit(c + 32, r1);
                 }
             }
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) {
                 const uint32_t acce_local = ptx::smem_u32(&bar_acc_empty[acc]);
-                if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(ptx::mapa(acce_local, 0));
+                if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(ptx::mapa(acce_local, leader_rank));
                 else ptx::mbar_arrive(acce_local);
             }
         }
+        // Bulk stores read shared memory asynchronously: they must be done before the CTA ends.
+        if (lane == 0) ptx::bulk_wait_group<0>();
+        __syncwarp();
     }
 
     // ---------------------------------------------------------------- teardown
@@ -388,7 +505,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
         while (ptx::globaltimer_ns() - t0 < 2000000ull) { }
         __syncthreads();
     }
-    if constexpr (CTAS == 2) {
+    if (clustered) {             // no CTA leaves while a peer may still write to or signal it
         ptx::cluster_arrive();
         ptx::cluster_wait();
     }

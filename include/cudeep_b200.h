@@ -107,8 +107,11 @@ int cudeep_b200_matmul_tn_f32(const float* A, const float* B, float* C, int M, i
  * bits 29-30 set the 32-wide K blocks per pipeline stage (1 or 2, 0 = default).
  * b_lbo / b_sbo: 0, or a byte offset that overrides the B shared-memory
  * descriptor fields (b_lbo bits 0-15); bits 16-23 of b_lbo set the split-K factor
- * of the ragged last wave of tiles (0 = choose, 1 = never split).  Fails instead of falling back when the tensor-core path
- * cannot take the problem. */
+ * of the ragged last wave of tiles (0 = choose, 1 = never split); bits 24-27 of
+ * b_lbo set the K ranges per tile that a thread-block cluster reduces through
+ * distributed shared memory (0 = choose, 1 = never, else 2, 4 or 8); bit 28 of
+ * b_lbo writes C from registers instead of through bulk tensor stores.  Fails
+ * instead of falling back when the tensor-core path cannot take the problem. */
 int cudeep_b200_gemm_tf32_tuned(const float* A, const float* B, int b_is_nk, float* C, int M, int N,
                                 int K, const float* bias, int bias_per_row, int epilogue, int ctas,
                                 int bn, int raster_group, int max_ctas, uint32_t b_lbo,

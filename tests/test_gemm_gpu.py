@@ -213,6 +213,94 @@ def test_tf32_split_k_chosen_by_the_launcher(dev, lib, oracle):
     assert np.array_equal(got, again)          # two K ranges: order-independent, bitwise reproducible
 
 
+# ---- split-K inside a thread-block cluster (partial sums exchanged through distributed shared memory)
+
+@pytest.mark.parametrize("ctas,bn,cluster_split,katoms", [
+    (1, 64, 2, 0), (1, 128, 2, 0), (1, 128, 4, 0), (1, 128, 4, 1), (2, 128, 2, 0), (2, 128, 4, 0),
+    (1, 256, 2, 0), (1, 256, 4, 0), (1, 256, 8, 0), (2, 256, 2, 0), (2, 256, 4, 0),
+])
+@pytest.mark.parametrize("b_is_nk", [False, True])
+def test_tf32_cluster_split_k(dev, oracle, ctas, bn, cluster_split, katoms, b_is_nk):
+    """Every cluster shape; ragged M and N, bias and ReLU fused after the reduction; 33 K blocks, so
+    the last K range is shorter than the others and ends in a partial block."""
+    rng = np.random.default_rng(ctas * 1000 + bn + cluster_split)
+    m, n, k = 300, 520, 1044
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((n, k) if b_is_nk else (k, n), dtype=np.float32)
+    bias = rng.standard_normal(n, dtype=np.float32)
+    got = dev.gemm_tuned(a, b, b_is_nk, bias=bias, act=1, ctas=ctas, bn=bn, katoms=katoms,
+                         cluster_split=cluster_split)
+    check_tf32(oracle, got, a, b, k, b_is_nk=b_is_nk, bias=bias, act=1)
+    again = dev.gemm_tuned(a, b, b_is_nk, bias=bias, act=1, ctas=ctas, bn=bn, katoms=katoms,
+                           cluster_split=cluster_split)
+    assert np.array_equal(got, again)          # partial sums are added in a fixed order
+
+
+def test_tf32_cluster_split_k_falls_back_when_k_is_short(dev, oracle):
+    """64 floats of K are two blocks: a request for four ranges runs as two, one block each."""
+    rng = np.random.default_rng(9)
+    a = rng.standard_normal((256, 64), dtype=np.float32)
+    b = rng.standard_normal((64, 256), dtype=np.float32)
+    got = dev.gemm_tuned(a, b, False, ctas=1, bn=128, cluster_split=4)
+    check_tf32(oracle, got, a, b, 64)
+    one = rng.standard_normal((256, 32), dtype=np.float32)        # a single block cannot be split at all
+    got = dev.gemm_tuned(one, b[:32].copy(), False, ctas=1, bn=128, cluster_split=2)
+    check_tf32(oracle, got, one, b[:32].copy(), 32)
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 512, 4096), (128, 4096, 4096), (256, 1024, 8192), (1024, 1024, 4096)])
+def test_tf32_cluster_split_k_chosen_by_the_launcher(dev, lib, oracle, m, n, k):
+    """Few tiles and a long K: the plain entry points spread each tile's K over a cluster.  The result
+    must not depend on what the caller left in C."""
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    ta, tb = dev.to_dev(a), dev.to_dev(b)
+    tc = dev.torch.full((m, n), 1.0e6, device=dev.dev)
+    dev.check(lib.cudeep_b200_matmul_f32(dev.ptr(ta), dev.ptr(tb), dev.ptr(tc), m, n, k, None))
+    assert dev.sync_status() == 0
+    got = tc.cpu().numpy()
+    check_tf32(oracle, got, a, b, k)
+    w = np.ascontiguousarray(b.T)
+    bias = rng.standard_normal(n, dtype=np.float32)
+    y = dev.linear(a, w, bias, act=2)
+    check_tf32(oracle, y, a, w, k, b_is_nk=True, bias=bias, act=2)
+
+
+# ---- the two ways of writing C ------------------------------------------------------------------
+
+@pytest.mark.parametrize("m,n,k", [(640, 768, 416), (300, 520, 100), (129, 132, 64), (2048, 2048, 64)])
+@pytest.mark.parametrize("b_is_nk", [False, True])
+def test_tf32_bulk_store_matches_register_store(dev, oracle, m, n, k, b_is_nk):
+    """C goes out through shared memory and bulk tensor stores when its rows are 16-byte multiples,
+    else straight from registers; both must give the same bits (edge tiles are clipped by the store)."""
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((n, k) if b_is_nk else (k, n), dtype=np.float32)
+    bias = rng.standard_normal(n, dtype=np.float32)
+    for ctas, bn in [(2, 256), (1, 256), (1, 64), (2, 128)]:
+        bulk = dev.gemm_tuned(a, b, b_is_nk, bias=bias, act=3, ctas=ctas, bn=bn)
+        regs = dev.gemm_tuned(a, b, b_is_nk, bias=bias, act=3, ctas=ctas, bn=bn, register_store=True)
+        assert np.array_equal(bulk, regs)
+    check_tf32(oracle, bulk, a, b, k, b_is_nk=b_is_nk, bias=bias, act=3)
+
+
+def test_tf32_store_does_not_touch_memory_behind_c(dev, lib, oracle):
+    """Tiles hang over the edge of C (M = 130, N = 36): rows behind the last one stay as they were."""
+    rng = np.random.default_rng(2)
+    m, n, k = 130, 36, 64
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    ta, tb = dev.to_dev(a), dev.to_dev(b)
+    tc = dev.torch.full((m + 4, n), 7.0, device=dev.dev)
+    dev.check(lib.cudeep_b200_gemm_tf32_tuned(dev.ptr(ta), dev.ptr(tb), 0, dev.ptr(tc), m, n, k, None, 0, 0,
+                                              0, 0, 0, 0, 0, 0, None))
+    assert dev.sync_status() == 0
+    got = tc.cpu().numpy()
+    assert np.all(got[m:] == 7.0)
+    check_tf32(oracle, got[:m], a, b, k)
+
+
 def test_tf32_is_deterministic(dev):
     a, b = workloads.c2_gemm(1024)
     assert np.array_equal(dev.matmul(a, b), dev.matmul(a, b))
