@@ -490,8 +490,9 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 else ptx::mbar_arrive(acce_local);
             }
         }
-        // Bulk stores read shared memory asynchronously: they must be done before the CTA ends.
-        if (lane == 0) ptx::bulk_wait_group<0>();
+        // Bulk stores read shared memory asynchronously: the reads must be over before the CTA
+        // gives its shared memory back (the writes themselves complete with the kernel).
+        if (lane == 0) ptx::bulk_wait_group_read<0>();
         __syncwarp();
     }
 
