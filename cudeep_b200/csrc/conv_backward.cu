@@ -8,8 +8,9 @@
 // GEMM into a [C*KH*KW, N*OH*OW] temporary and scatters it back with col2im.  Strided
 // convolutions, FP64 and shapes the tensor-core path does not take use a direct gather kernel.
 //
-// grad_weight: a direct strict-precision kernel (one thread per filter element, summing over
-// images and output pixels in a fixed order).
+// grad_weight: for stride 1 an implicit GEMM over output pixels on the tensor cores
+// (conv_wgrad.cu); otherwise a direct strict-precision kernel (one thread per filter element,
+// summing over images and output pixels in a fixed order).
 #include "cudeep/kernels/conv.cuh"
 
 #include "conv_igemm.h"
@@ -140,8 +141,7 @@ void launch_conv2d_backward_data_kernel<float>(const float* grad_output, const f
     const bool stride_one = stride_h == 1 && stride_w == 1 && pad_h <= kernel_h - 1 && pad_w <= kernel_w - 1;
     if (stride_one && cudeep_b200::conv2d_igemm_supported(as_forward)) {
         const size_t bytes = static_cast<size_t>(out_channels) * in_channels * kernel_h * kernel_w * sizeof(float);
-        float* flipped = nullptr;
-        CB200_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&flipped), bytes, stream));
+        float* flipped = static_cast<float*>(cudeep_b200::scratch_alloc(bytes, stream));
         try {
             const long long total = static_cast<long long>(out_channels) * in_channels * kernel_h * kernel_w;
             long long blocks = (total + 255) / 256;
@@ -152,10 +152,10 @@ void launch_conv2d_backward_data_kernel<float>(const float* grad_output, const f
             cudeep_b200::conv2d_igemm(grad_output, flipped, nullptr, grad_input, as_forward,
                                       cudeep_b200::EPI_NONE, stream);
         } catch (...) {
-            cudaFreeAsync(flipped, stream);
+            cudeep_b200::scratch_free(flipped, stream);
             throw;
         }
-        CB200_CUDA(cudaFreeAsync(flipped, stream));
+        cudeep_b200::scratch_free(flipped, stream);
     } else {
         cudeep_b200::backward_data_direct<float>(grad_output, weight, grad_input, s, stream);
     }
@@ -194,9 +194,17 @@ void launch_conv2d_backward_weight_kernel<float>(const float* grad_output, const
                                                  int out_channels, int in_h, int in_w, int kernel_h,
                                                  int kernel_w, int stride_h, int stride_w, int pad_h,
                                                  int pad_w, cudaStream_t stream) {
-    backward_weight<float>(grad_output, input, grad_weight,
-                           ConvShape{batch, in_channels, out_channels, in_h, in_w, kernel_h, kernel_w,
-                                     stride_h, stride_w, pad_h, pad_w}, stream);
+    const ConvShape s{batch, in_channels, out_channels, in_h, in_w, kernel_h, kernel_w,
+                      stride_h, stride_w, pad_h, pad_w};
+    CB200_REQUIRE(grad_output != nullptr && input != nullptr && grad_weight != nullptr,
+                  "conv2d backward: null tensor pointer");
+    cudeep_b200::check_conv_shape(s);
+    // Stride-1 shapes with enough channels and pixels: tensor cores (TF32, like the reference's GEMM);
+    // everything else: the direct strict-FP32 kernel.
+    if (cudeep_b200::conv2d_wgrad_igemm_supported(s) && (reinterpret_cast<uintptr_t>(grad_output) & 15u) == 0)
+        cudeep_b200::conv2d_wgrad_igemm(grad_output, input, grad_weight, s, stream);
+    else
+        backward_weight<float>(grad_output, input, grad_weight, s, stream);
 }
 
 template <>

@@ -312,6 +312,15 @@ int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 }  // namespace
 
+void nchw_to_nhwc(const float* input, float* xt, int batch, int c, int hw, int cx, cudaStream_t stream) {
+    dim3 grid((hw + 63) / 64, (cx + 31) / 32, batch);
+    CB200_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "conv2d: too many channels or images");
+    const bool vec = (hw % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
+    if (vec) nchw_to_nhwc_kernel<true><<<grid, 256, 0, stream>>>(input, xt, c, hw, cx);
+    else nchw_to_nhwc_kernel<false><<<grid, 256, 0, stream>>>(input, xt, c, hw, cx);
+    CB200_CHECK_LAUNCH();
+}
+
 bool conv2d_igemm_supported(const ConvShape& s) {
     if (device_info().cc_major != 10) return false;
     if (s.s_h != 1 || s.s_w != 1) return false;
@@ -353,14 +362,7 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
     float* xt = static_cast<float*>(scratch);
     float* wp = reinterpret_cast<float*>(static_cast<char*>(scratch) + nhwc_bytes);
 
-    {
-        dim3 grid((hw + 63) / 64, (cx + 31) / 32, s.batch);
-        CB200_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "conv2d: too many channels or images");
-        const bool vec = (hw % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
-        if (vec) nchw_to_nhwc_kernel<true><<<grid, 256, 0, stream>>>(input, xt, s.in_c, hw, cx);
-        else nchw_to_nhwc_kernel<false><<<grid, 256, 0, stream>>>(input, xt, s.in_c, hw, cx);
-        CB200_CHECK_LAUNCH();
-    }
+    nchw_to_nhwc(input, xt, s.batch, s.in_c, hw, cx, stream);
     {
         const long long total = static_cast<long long>(s.out_c) * taps * cp;
         long long blocks = (total + 255) / 256;
@@ -390,24 +392,14 @@ void conv2d_igemm(const float* input, const float* weight, const float* bias, fl
     const size_t bytes = conv2d_igemm_scratch_bytes(s, nullptr, nullptr);
     // Stream-ordered scratch, as the reference does for its temporaries
     // (conv_kernel.cu:282,314,748-754): safe when calls on several streams overlap.
-    static thread_local int pool_ready_device = -1;
-    const int dev = device_info().device;
-    if (pool_ready_device != dev) {
-        cudaMemPool_t pool;
-        CB200_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
-        uint64_t keep = UINT64_MAX;   // keep freed scratch cached instead of returning it at every sync
-        CB200_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
-        pool_ready_device = dev;
-    }
-    void* scratch = nullptr;
-    CB200_CUDA(cudaMallocAsync(&scratch, bytes, stream));
+    void* scratch = scratch_alloc(bytes, stream);
     try {
         conv2d_igemm_with_scratch(input, weight, bias, output, s, act, scratch, 0, stream);
     } catch (...) {
-        cudaFreeAsync(scratch, stream);
+        scratch_free(scratch, stream);
         throw;
     }
-    CB200_CUDA(cudaFreeAsync(scratch, stream));
+    scratch_free(scratch, stream);
 }
 
 }  // namespace cudeep_b200

@@ -24,4 +24,12 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
 void conv2d_igemm(const float* input, const float* weight, const float* bias, float* output,
                   const ConvShape& s, int act, cudaStream_t stream);
 
+// x[N][C][HW] -> xt[N][HW][cx] with cx >= C a multiple of 4 (channels past C are zero).
+void nchw_to_nhwc(const float* input, float* xt, int batch, int c, int hw, int cx, cudaStream_t stream);
+
+// grad_weight of a stride-1 convolution as an implicit GEMM over output pixels (conv_wgrad.cu).
+bool conv2d_wgrad_igemm_supported(const ConvShape& s);
+void conv2d_wgrad_igemm(const float* grad_output, const float* input, float* grad_weight, const ConvShape& s,
+                        cudaStream_t stream);
+
 }  // namespace cudeep_b200

@@ -1,0 +1,302 @@
+// grad_weight of a stride-1 Conv2d as an implicit GEMM on tcgen05
+// (reference include/cudeep/kernels/conv.cuh:28-36, src/kernels/conv_kernel.cu:460-545, which
+// forms im2col(x) per image in global memory and multiplies it with grad_output).
+//
+//   dw[oc, c, kh, kw] = sum_{n, oh, ow} dy[n, oc, oh, ow] * x[n, c, oh+kh-ph, ow+kw-pw]
+//
+// For one filter tap this is D[OC, C] = dY[OC, pixels] * X_tap[pixels, C]: the reduction runs over
+// output pixels.  A K block is 32 consecutive pixels of one output row (box_w x box_h = 32 x 1):
+//   * A (K-major): grad_output read in place as a 4-D tensor {OW, OH, OC, N}; the box
+//     {32, 1, 128, 1} lands as one 128-byte row per output channel;
+//   * B (MN-major, channels contiguous): the NHWC copy of the input (channels padded to 32) seen
+//     as a 5-D tensor {32, W, H, N, Cp/32}; the box {32, box_w, box_h, 1, chunks}, started at the
+//     tap's offset, lands as 32-channel chunks of 32 pixel rows - the layout the tensor core takes
+//     for an MN-major 32-bit operand.  Padding is the out-of-range zero fill of either side.
+// Nothing of size pixels x C*KH*KW is written.  There are only taps * ceil(C / 256) output tiles
+// per 256 output channels but a very long K, so K is cut into ranges, one tile-sized partial
+// result per range goes to scratch (bulk tensor stores), and a small kernel adds the ranges in a
+// fixed order and writes the [OC][C][KH][KW] layout - bitwise reproducible, no atomics.
+#include "conv_igemm.h"
+#include "umma_gemm.cuh"
+
+namespace cudeep_b200 {
+
+namespace {
+
+template <int CTAS>
+struct WgradProblem {
+    static constexpr bool kTmaStore = true;
+    static constexpr bool kClusterSplit = false;
+    CUtensorMap map_dy;     // {OW, OH, OC, N}, box {box_w, box_h, 128, 1}
+    CUtensorMap map_x;      // {32, W, H, N, Cp/32}, box {32, box_w, box_h, 1, chunks per CTA}
+    CUtensorMap map_part;   // partial results [ranges * OCp][taps * Cp], box {32, 32}
+    int tiles_w, tiles_h;   // pixel boxes per image
+    int box_w, box_h;
+    int c_tiles;            // channel tiles (of umma_n channels) per tap
+    int taps, k_w, p_h, p_w;
+    int n_cols;             // channels per tile (umma_n)
+    int cp;                 // padded channels
+    int ocp;                // padded output channels: rows of one K range in the scratch
+    int kb_per_range;       // K blocks (pixel boxes) of one range
+    int total_kb;           // batch * tiles_h * tiles_w
+    int batch;
+
+    struct Tile {
+        int oc0;            // first output channel of this CTA
+        int tap, c0;        // filter tap and first channel of the tile
+        int cb0;            // first channel this CTA stages
+        int range;          // which K range
+    };
+
+    __device__ __forceinline__ void prefetch_maps() const {
+        ptx::prefetch_tensormap(&map_dy);
+        ptx::prefetch_tensormap(&map_x);
+        ptx::prefetch_tensormap(&map_part);
+    }
+    // tn enumerates (range, tap, channel tile), the channel tile fastest.
+    __device__ __forceinline__ Tile decode(int tm, int tn, uint32_t cta_rank) const {
+        Tile t;
+        t.oc0 = (tm * CTAS + int(cta_rank)) * UMMA_BM;
+        const int per_range = taps * c_tiles;
+        t.range = tn / per_range;
+        const int r = tn - t.range * per_range;
+        t.tap = r / c_tiles;
+        t.c0 = (r - t.tap * c_tiles) * n_cols;
+        t.cb0 = t.c0 + int(cta_rank) * (n_cols / CTAS);
+        return t;
+    }
+    template <int C>
+    __device__ __forceinline__ void load(const Tile& t, int kb, uint32_t a_smem, uint32_t b_smem,
+                                         uint32_t bar) const {
+        const int g = t.range * kb_per_range + kb;      // pixel box over the whole batch
+        const int per_image = tiles_h * tiles_w;
+        // Blocks past the end of this range or of the batch read zeros on both sides: the
+        // image index is pushed out of range.
+        int n = g / per_image;
+        const int r = g - n * per_image;
+        if (kb >= kb_per_range || g >= total_kb) n = batch;
+        const int th = r / tiles_w;
+        const int oh0 = th * box_h;
+        const int ow0 = (r - th * tiles_w) * box_w;
+        const int kh = t.tap / k_w;
+        const int kw = t.tap - kh * k_w;
+        if constexpr (C == 1) {
+            ptx::tma_load_4d(a_smem, &map_dy, bar, ow0, oh0, t.oc0, n);
+            ptx::tma_load_5d(b_smem, &map_x, bar, 0, ow0 + kw - p_w, oh0 + kh - p_h, n, t.cb0 / 32);
+        } else {
+            ptx::tma_load_4d_pair(a_smem, &map_dy, bar, ow0, oh0, t.oc0, n);
+            ptx::tma_load_5d_pair(b_smem, &map_x, bar, 0, ow0 + kw - p_w, oh0 + kh - p_h, n, t.cb0 / 32);
+        }
+    }
+    __device__ __forceinline__ const CUtensorMap* out_map() const { return &map_part; }
+    __device__ __forceinline__ void out_coords(const Tile& t, int row_in_cta, int c0, int& x, int& y) const {
+        x = t.tap * cp + t.c0 + c0;
+        y = t.range * ocp + t.oc0 + row_in_cta;
+    }
+    __device__ __forceinline__ void finish(const Tile&, int, int, float (&)[32], const UmmaEpilogueArgs&) const {}
+    // Every tile goes out through the bulk-store path.
+    __device__ __forceinline__ void store(const Tile&, int, int, float (&)[32], const UmmaEpilogueArgs&, int) const {}
+};
+
+// dw[oc][c][tap] = sum over ranges of part[range][oc][tap * cp + c], ranges in ascending order.
+__global__ void wgrad_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, int ranges, int oc_n,
+                                    int ocp, int c_n, int cp, int taps) {
+    const long long total = static_cast<long long>(oc_n) * c_n * taps;
+    const long long row_len = static_cast<long long>(taps) * cp;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int tap = static_cast<int>(i % taps);
+        const long long r = i / taps;
+        const int c = static_cast<int>(r % c_n);
+        const long long oc = r / c_n;
+        const float* src = part + oc * row_len + static_cast<long long>(tap) * cp + c;
+        float acc = 0.0f;
+        for (int s = 0; s < ranges; ++s) acc += src[static_cast<long long>(s) * ocp * row_len];
+        dw[i] = acc;
+    }
+}
+
+struct WgradPlan {
+    int ctas, box_w, box_h, n_cols, c_tiles, ranges, kb_per_range, tiles_w, tiles_h, cp, ocp;
+    size_t nhwc_bytes, part_bytes;
+};
+
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+WgradPlan plan_wgrad(const ConvShape& s, int num_sms) {
+    WgradPlan p{};
+    const int oh = s.out_h(), ow = s.out_w();
+    p.ctas = s.out_c > UMMA_BM ? 2 : 1;
+    p.cp = round_up(s.in_c, UMMA_BK);
+    // Channels per tile: the widest multiple of one 32-channel chunk per CTA, at most 256, that
+    // divides the padded channel count (a tile never reaches into the next tap's columns).
+    auto widest = [&](int step) {
+        for (int n = 256; n >= step; n -= step)
+            if (n % step == 0 && p.cp % n == 0) return n;
+        return 0;
+    };
+    p.n_cols = widest(32 * p.ctas);
+    if (p.ctas == 2 && p.n_cols < 128) {
+        p.ctas = 1;
+        p.n_cols = widest(32);
+    }
+    p.c_tiles = p.cp / p.n_cols;
+    // A K block is 32 consecutive pixels of one output row.  (Boxes of 16 x 2 or 8 x 4 pixels would
+    // waste fewer pixels of narrow images, but a swizzled TMA box whose inner extent is under 128
+    // bytes is not packed densely in shared memory, so grad_output could not be read in place.)
+    p.box_w = 32;
+    p.box_h = 1;
+    p.tiles_w = (ow + p.box_w - 1) / p.box_w;
+    p.tiles_h = (oh + p.box_h - 1) / p.box_h;
+    const long long total_kb = static_cast<long long>(s.batch) * p.tiles_h * p.tiles_w;
+    const int tiles_m = (s.out_c + UMMA_BM * p.ctas - 1) / (UMMA_BM * p.ctas);
+    p.ocp = tiles_m * UMMA_BM * p.ctas;
+    const long long base_tiles = static_cast<long long>(tiles_m) * s.k_h * s.k_w * p.c_tiles;
+    // Enough K ranges to give every CTA (pair) a unit, each at least 16 K blocks long.
+    const long long slots = num_sms / p.ctas;
+    long long ranges = slots / base_tiles;
+    if (ranges > total_kb / 16) ranges = total_kb / 16;
+    if (ranges < 1) ranges = 1;
+    if (ranges > 64) ranges = 64;
+    long long per = (total_kb + ranges - 1) / ranges;
+    per = (per + 1) / 2 * 2;                              // whole pipeline stages of two K blocks
+    p.kb_per_range = static_cast<int>(per);
+    p.ranges = static_cast<int>((total_kb + per - 1) / per);
+    p.nhwc_bytes = (static_cast<size_t>(s.batch) * s.in_h * s.in_w * p.cp * sizeof(float) + 1023) / 1024 * 1024;
+    p.part_bytes = static_cast<size_t>(p.ranges) * p.ocp * s.k_h * s.k_w * p.cp * sizeof(float);
+    return p;
+}
+
+template <int CTAS, int KATOMS>
+void launch_wgrad(const float* dy, const float* xt, float* part, const ConvShape& s, const WgradPlan& p,
+                  cudaStream_t stream) {
+    using Cfg = UmmaConfig<CTAS, 256, true, KATOMS>;
+    using Prob = WgradProblem<CTAS>;
+    const DeviceInfo& dev = device_info();
+    const int oh = s.out_h(), ow = s.out_w();
+    const int taps = s.k_h * s.k_w;
+
+    Prob prob;
+    {
+        const uint64_t dims[4] = {uint64_t(ow), uint64_t(oh), uint64_t(s.out_c), uint64_t(s.batch)};
+        const uint64_t strides[3] = {uint64_t(ow) * 4, uint64_t(oh) * ow * 4, uint64_t(s.out_c) * oh * ow * 4};
+        const uint32_t box[4] = {uint32_t(p.box_w), uint32_t(p.box_h), UMMA_BM, 1};
+        encode_tensor_map(&prob.map_dy, dy, 4, dims, strides, box, TmaSwizzle::B128);
+    }
+    {
+        const uint64_t dims[5] = {32, uint64_t(s.in_w), uint64_t(s.in_h), uint64_t(s.batch), uint64_t(p.cp / 32)};
+        const uint64_t strides[4] = {uint64_t(p.cp) * 4, uint64_t(s.in_w) * p.cp * 4,
+                                     uint64_t(s.in_h) * s.in_w * p.cp * 4, 128};
+        const uint32_t box[5] = {32, uint32_t(p.box_w), uint32_t(p.box_h), 1, uint32_t(p.n_cols / CTAS / 32)};
+        encode_tensor_map(&prob.map_x, xt, 5, dims, strides, box, TmaSwizzle::B128Atom32);
+    }
+    {
+        const uint64_t dims[2] = {uint64_t(taps) * p.cp, uint64_t(p.ranges) * p.ocp};
+        const uint64_t strides[1] = {uint64_t(taps) * p.cp * 4};
+        const uint32_t box[2] = {32, 32};
+        encode_tensor_map(&prob.map_part, part, 2, dims, strides, box, TmaSwizzle::B128);
+    }
+    prob.tiles_w = p.tiles_w;
+    prob.tiles_h = p.tiles_h;
+    prob.box_w = p.box_w;
+    prob.box_h = p.box_h;
+    prob.c_tiles = p.c_tiles;
+    prob.taps = taps;
+    prob.k_w = s.k_w;
+    prob.p_h = s.p_h;
+    prob.p_w = s.p_w;
+    prob.n_cols = p.n_cols;
+    prob.cp = p.cp;
+    prob.ocp = p.ocp;
+    prob.kb_per_range = p.kb_per_range;
+    prob.total_kb = s.batch * p.tiles_h * p.tiles_w;
+    prob.batch = s.batch;
+
+    UmmaSchedule sched;
+    sched.tiles_m = p.ocp / (UMMA_BM * CTAS);
+    sched.tiles_n = p.ranges * taps * p.c_tiles;
+    sched.k_blocks = p.kb_per_range;
+    sched.raster_group = sched.tiles_m;
+    sched.status = dev.status_word;
+    sched.wait_limit_ns = 2000000000ull;
+    sched.b_lbo = 0;
+    sched.b_sbo = 0;
+    sched.umma_n = p.n_cols;
+    sched.tx_bytes = (Cfg::A_BYTES + uint32_t(p.n_cols / CTAS) * UMMA_BK * 4) * CTAS * KATOMS;
+    sched.n_whole = sched.tiles_m * sched.tiles_n;
+    sched.split = 1;
+    sched.kb_per_split = sched.k_blocks;
+    sched.cluster_split = 1;
+    sched.exchange_bytes = 0;
+    sched.tma_store = 1;
+    sched.debug = 0;
+    const int fit_stages = int((Cfg::SMEM_BUDGET - UMMA_STORE_STAGING_BYTES) / Cfg::STAGE_BYTES);
+    sched.stages = fit_stages < Cfg::STAGES ? fit_stages : Cfg::STAGES;
+    const uint32_t smem_bytes = uint32_t(sched.stages) * Cfg::STAGE_BYTES + UMMA_STORE_STAGING_BYTES + 1024;
+
+    const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;
+    long long groups = dev.num_sms / CTAS;
+    if (groups < 1) groups = 1;
+    if (groups > num_tiles) groups = num_tiles;
+
+    auto kernel = umma_tf32_kernel<CTAS, 256, true, KATOMS, Prob>;
+    ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), Cfg::SMEM_MAX);
+
+    UmmaEpilogueArgs epi{nullptr, 0, EPI_NONE};
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(groups * CTAS), 1, 1);
+    cfg.blockDim = dim3(UMMA_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, prob, sched, epi));
+}
+
+}  // namespace
+
+bool conv2d_wgrad_igemm_supported(const ConvShape& s) {
+    if (device_info().cc_major != 10) return false;
+    if (s.s_h != 1 || s.s_w != 1) return false;
+    if (s.p_h >= s.k_h || s.p_w >= s.k_w) return false;     // keeps every box start within TMA's signed range
+    const int oh = s.out_h(), ow = s.out_w();
+    if (oh < 1 || ow < 1) return false;
+    if (ow % 4 != 0) return false;                          // rows of grad_output must be 16-byte multiples
+    if (s.out_c < 32) return false;
+    if (static_cast<long long>(s.batch) * oh * ow < 256) return false;
+    return true;
+}
+
+void conv2d_wgrad_igemm(const float* grad_output, const float* input, float* grad_weight, const ConvShape& s,
+                        cudaStream_t stream) {
+    check_conv_shape(s);
+    CB200_REQUIRE(conv2d_wgrad_igemm_supported(s), "conv2d backward: shape not supported by the tensor-core path");
+    CB200_REQUIRE((reinterpret_cast<uintptr_t>(grad_output) & 15u) == 0,
+                  "conv2d backward: grad_output must be 16-byte aligned");
+    const WgradPlan p = plan_wgrad(s, device_info().num_sms);
+    char* scratch = static_cast<char*>(scratch_alloc(p.nhwc_bytes + p.part_bytes, stream));
+    try {
+        float* xt = reinterpret_cast<float*>(scratch);
+        float* part = reinterpret_cast<float*>(scratch + p.nhwc_bytes);
+        nchw_to_nhwc(input, xt, s.batch, s.in_c, s.in_h * s.in_w, p.cp, stream);
+        if (p.ctas == 2) launch_wgrad<2, 2>(grad_output, xt, part, s, p, stream);
+        else launch_wgrad<1, 1>(grad_output, xt, part, s, p, stream);
+        const long long total = static_cast<long long>(s.out_c) * s.in_c * s.k_h * s.k_w;
+        long long blocks = (total + 255) / 256;
+        if (blocks > 4096) blocks = 4096;
+        wgrad_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+            part, grad_weight, p.ranges, s.out_c, p.ocp, s.in_c, p.cp, s.k_h * s.k_w);
+        CB200_CHECK_LAUNCH();
+    } catch (...) {
+        scratch_free(scratch, stream);
+        throw;
+    }
+    scratch_free(scratch, stream);
+}
+
+}  // namespace cudeep_b200

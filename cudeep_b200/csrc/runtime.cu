@@ -92,6 +92,25 @@ void ensure_dynamic_smem(const void* func, size_t bytes) {
     st.smem_done.insert(func);
 }
 
+void* scratch_alloc(size_t bytes, cudaStream_t stream) {
+    static thread_local int pool_ready_device = -1;
+    const int dev = device_info().device;
+    if (pool_ready_device != dev) {
+        cudaMemPool_t pool;
+        CB200_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+        uint64_t keep = UINT64_MAX;
+        CB200_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+        pool_ready_device = dev;
+    }
+    void* ptr = nullptr;
+    CB200_CUDA(cudaMallocAsync(&ptr, bytes, stream));
+    return ptr;
+}
+
+void scratch_free(void* ptr, cudaStream_t stream) noexcept {
+    if (ptr != nullptr) cudaFreeAsync(ptr, stream);
+}
+
 uint32_t read_device_status(bool clear) {
     const DeviceInfo& info = device_info();
     CB200_CUDA(cudaDeviceSynchronize());
@@ -103,12 +122,12 @@ uint32_t read_device_status(bool clear) {
 
 void encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint64_t* dims,
                        const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle) {
-    CB200_REQUIRE(rank >= 1 && rank <= 4, "tensor map rank must be 1..4");
+    CB200_REQUIRE(rank >= 1 && rank <= 5, "tensor map rank must be 1..5");
     CB200_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15u) == 0, "TMA base address must be 16-byte aligned");
-    cuuint64_t gdim[4];
-    cuuint64_t gstride[3];
-    cuuint32_t gbox[4];
-    cuuint32_t estride[4];
+    cuuint64_t gdim[5];
+    cuuint64_t gstride[4];
+    cuuint32_t gbox[5];
+    cuuint32_t estride[5];
     for (int i = 0; i < rank; ++i) {
         gdim[i] = dims[i];
         gbox[i] = box[i];

@@ -44,6 +44,12 @@ const DeviceInfo& device_info();
 // Raise the dynamic shared-memory limit of `func` on the current device once.
 void ensure_dynamic_smem(const void* func, size_t bytes);
 
+// Stream-ordered scratch (cudaMallocAsync / cudaFreeAsync on `stream`) from the device's default
+// memory pool, whose release threshold is raised once so that freed scratch stays cached instead
+// of going back to the driver at every synchronisation.
+void* scratch_alloc(size_t bytes, cudaStream_t stream);
+void scratch_free(void* ptr, cudaStream_t stream) noexcept;
+
 // Read-and-clear the current device's kernel status word (synchronises the device).
 uint32_t read_device_status(bool clear);
 
@@ -53,10 +59,11 @@ enum class TmaSwizzle {
     B128Atom32,    // 32-byte chunks XOR-ed within each 128-byte row, period 4 rows
 };
 
-// 64-byte aligned TMA descriptor for a row-major fp32 tensor of rank <= 4.
+// 64-byte aligned TMA descriptor for an fp32 tensor of rank <= 5.
 // dims[0] is the contiguous dimension; strides_bytes[i] is the stride of
 // dims[i+1].  Out-of-range elements read as zero.  With a swizzle the inner
-// box must span exactly 128 bytes.
+// box must span exactly 128 bytes (narrower boxes are not packed densely in
+// shared memory: measured, a {8, 4, 128} box did not land as 128-byte rows).
 void encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint64_t* dims,
                        const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle);
 

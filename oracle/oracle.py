@@ -199,9 +199,12 @@ def conv2d_backward_data_np(dy, w, in_hw, stride=(1, 1), padding=(0, 0), input_m
     return dxp[:, :, ph:ph + h, pw:pw + wd]
 
 
-def conv2d_backward_weight_np(dy, x, k_hw, stride=(1, 1), padding=(0, 0)) -> np.ndarray:
+def conv2d_backward_weight_np(dy, x, k_hw, stride=(1, 1), padding=(0, 0), input_mode: int = INPUT_EXACT) -> np.ndarray:
     """float64 gradient of conv2d w.r.t. its filters: dw[oc,c,kh,kw] = sum over images and output
-    pixels of dy[n,oc,oh,ow] * x[n,c,oh*s-p+kh,ow*s-p+kw] (src/kernels/conv_kernel.cu:486-545)."""
+    pixels of dy[n,oc,oh,ow] * x[n,c,oh*s-p+kh,ow*s-p+kw] (src/kernels/conv_kernel.cu:486-545).
+    input_mode INPUT_TF32_TRUNC first drops both operands to TF32 the way the tensor core does."""
+    if input_mode == INPUT_TF32_TRUNC:
+        dy, x = tf32_truncate(dy), tf32_truncate(x)
     dy64 = np.asarray(dy, dtype=np.float64)
     x64 = np.asarray(x, dtype=np.float64)
     n, oc, oh, ow = dy64.shape

@@ -175,6 +175,36 @@ def test_backward_against_oracle(dev, lib, oracle, shape, oc, k, stride, padding
         assert oracle.rel_frobenius(dx, dx_ref) <= FP32_TOL
 
 
+@pytest.mark.parametrize("shape,oc,k,padding", [
+    ((4, 64, 28, 28), 64, (3, 3), (1, 1)),      # one CTA per tile; 28 of the 32 pixels of a K block are real
+    ((2, 256, 56, 56), 256, (3, 3), (1, 1)),    # the C4 layer: CTA pairs, two K blocks per row, 256-channel tiles
+    ((3, 48, 16, 24), 160, (3, 5), (1, 2)),     # 160 output channels: the second 128-row tile is partly empty
+    ((2, 320, 12, 16), 256, (3, 3), (1, 1)),    # 320 channels: two tiles of 160 columns
+    ((1, 16, 20, 20), 32, (1, 1), (0, 0)),      # 1 x 1 filter, channels padded 16 -> 32
+    ((5, 32, 9, 12), 40, (3, 3), (0, 0)),       # no padding: 7 x 10 outputs... OW = 10 is not a multiple of 4
+])
+def test_backward_weight_tensor_core_path(dev, lib, oracle, shape, oc, k, padding):
+    """grad_weight as an implicit GEMM over output pixels (stride 1, OW % 4 == 0, >= 256 pixels): TF32
+    bars, and FP32-accumulation agreement with the float64 sum of the TF32-truncated operands."""
+    rng = np.random.default_rng(sum(shape) + oc)
+    x = rng.standard_normal(shape, dtype=np.float32)
+    w = np.zeros((oc, shape[1], *k), dtype=np.float32)
+    oh = shape[2] + 2 * padding[0] - k[0] + 1
+    ow = shape[3] + 2 * padding[1] - k[1] + 1
+    dy = rng.standard_normal((shape[0], oc, oh, ow), dtype=np.float32)
+    _, dw = conv_backward(dev, lib, dy, w, x, (1, 1), padding)
+    _, again = conv_backward(dev, lib, dy, w, x, (1, 1), padding)
+    assert np.array_equal(dw, again)                      # K ranges are added in a fixed order
+    dw_ref = oracle.conv2d_backward_weight_np(dy, x, k, (1, 1), padding)
+    if ow % 4 == 0:
+        assert oracle.rel_frobenius(dw, dw_ref) <= TF32_TOL
+        model = oracle.conv2d_backward_weight_np(dy, x, k, (1, 1), padding, input_mode=oracle.INPUT_TF32_TRUNC)
+        pixels = shape[0] * oh * ow
+        assert oracle.rel_frobenius(dw, model) <= TF32_MODEL_TOL * max(1.0, pixels / 4096.0)
+    else:
+        assert oracle.rel_frobenius(dw, dw_ref) <= FP32_TOL
+
+
 def test_conv_host_buffers(lib, cuda, oracle):
     import ctypes
     from cudeep_b200 import _lib

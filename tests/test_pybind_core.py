@@ -165,7 +165,7 @@ def test_conv2d_forward_and_backward(core, cuda, oracle, shape):
     want_gi = oracle.conv2d_backward_data_np(dy.astype(np.float64), w.astype(np.float64), (ih, iw), (s, s), (p, p))
     want_gw = oracle.conv2d_backward_weight_np(dy.astype(np.float64), x.astype(np.float64), (ks, ks), (s, s), (p, p))
     assert _rel(gi, want_gi) <= 5e-3
-    assert _rel(gw, want_gw) <= 1e-4
+    assert _rel(gw, want_gw) <= 5e-3      # tensor cores (TF32) where the shape allows, else strict FP32
 
 
 @pytest.mark.gpu
