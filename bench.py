@@ -42,7 +42,7 @@ NOMINAL_TF32_TFLOPS = 1125.0        # half the nominal dense bf16 rate of a B200
 
 # DRAM bytes one 8192^3 launch moves (dram__bytes_read.sum + dram__bytes_write.sum from the
 # ncu capture summarised in profiles/); None until a capture exists.
-NCU_DRAM_BYTES_PER_LAUNCH = 2.84e9
+NCU_DRAM_BYTES_PER_LAUNCH = 2.54e9
 
 
 def parse_args():
@@ -60,7 +60,8 @@ def parse_args():
                     help="instead of the headline line, time every benchmark configuration next to "
                          "cuBLAS / cuDNN (through torch) and the reference's kernels; one JSON line each")
     ap.add_argument("--only", default="", help="with --suite: run only the configurations whose name starts "
-                                               "with one of these comma-separated tags (C1, C2, C3, C4)")
+                                               "with one of these comma-separated tags (C1, C2, C3, C4; "
+                                               "B1 matmul backward, B2 conv backward, S1 small-batch Linear)")
     ap.add_argument("--no-comparators", action="store_true",
                     help="with --suite: time only this library (short runs for profiling)")
     return ap.parse_args()
@@ -459,6 +460,12 @@ def run_suite(args):
         run_c3(lib, ref, timed, emit, ok, P, stream, trim)
     if want("C4"):
         run_c4(lib, ref, timed, emit, ok, P, stream, trim)
+    if want("B1"):
+        run_b1(lib, ref, timed, emit, ok, P, stream, trim)
+    if want("B2"):
+        run_b2(lib, ref, timed, emit, ok, P, stream, trim)
+    if want("S1"):
+        run_s1(lib, ref, timed, emit, ok, P, stream, trim)
     status = _lib.device_status(True)
     if status != 0:
         raise RuntimeError(f"kernel status word {status}")
@@ -549,6 +556,61 @@ def run_c4(lib, ref, timed, emit, ok, P, stream, trim):
             P(xc), P(wc), P(bc), P(yc), nb, ch, oc, size, size, 3, 3, 1, 1, 1, 1, stream), 5, cmp=True)
     emit("C4 conv 3x3 64x256x56x56 -> 256, bias + ReLU", workloads.conv_flops(nb, ch, oc, size, size, 3, 3),
          trim(rows))
+
+
+def run_b1(lib, ref, timed, emit, ok, P, stream, trim):
+    """The two products of matmul's backward pass at 4096^3, operands consumed as stored:
+    dA = dC B^T (NT) and dB = A^T dC (TN)."""
+    import torch
+    torch.backends.cuda.matmul.allow_tf32 = True
+    n = 4096
+    a = torch.randn((n, n), device="cuda")
+    b = torch.randn((n, n), device="cuda")
+    dc = torch.randn((n, n), device="cuda")
+    out = torch.empty((n, n), device="cuda")
+    rows = {"ours": timed(lambda: ok(lib.cudeep_b200_matmul_nt_f32(P(dc), P(b), P(out), n, n, n, stream)), 20),
+            "cublas_tf32": timed(lambda: torch.matmul(dc, b.t(), out=out), 20, cmp=True)}
+    emit(f"B1 matmul backward dA = dC B^T {n}^3", 2.0 * n ** 3, trim(rows))
+    rows = {"ours": timed(lambda: ok(lib.cudeep_b200_matmul_tn_f32(P(a), P(dc), P(out), n, n, n, stream)), 20),
+            "cublas_tf32": timed(lambda: torch.matmul(a.t(), dc, out=out), 20, cmp=True)}
+    emit(f"B1 matmul backward dB = A^T dC {n}^3", 2.0 * n ** 3, trim(rows))
+
+
+def run_b2(lib, ref, timed, emit, ok, P, stream, trim):
+    """Backward of the C4 layer: grad_input and grad_weight."""
+    import torch
+    from cudeep_b200 import workloads
+    nb, ch, size, oc = 64, 256, 56, 256
+    x = torch.randn((nb, ch, size, size), device="cuda")
+    w = torch.randn((oc, ch, 3, 3), device="cuda") * (2.0 / (ch * 9)) ** 0.5
+    dy = torch.randn((nb, oc, size, size), device="cuda")
+    dx = torch.empty_like(x)
+    dw = torch.empty_like(w)
+    torch.backends.cudnn.allow_tf32 = True
+    torch.backends.cudnn.benchmark = True
+    flops = workloads.conv_flops(nb, ch, oc, size, size, 3, 3)
+    geom = (nb, ch, oc, size, size, 3, 3, 1, 1, 1, 1)
+    rows = {"ours": timed(lambda: ok(lib.cudeep_b200_conv2d_backward_data_f32(P(dy), P(w), P(dx), *geom, stream)), 15),
+            "cudnn_tf32_torch": timed(lambda: torch.nn.grad.conv2d_input(x.shape, w, dy, padding=1), 15, cmp=True)}
+    emit("B2 conv backward grad_input, C4 layer", flops, trim(rows))
+    rows = {"ours": timed(lambda: ok(lib.cudeep_b200_conv2d_backward_weight_f32(P(dy), P(x), P(dw), *geom, stream)), 15),
+            "cudnn_tf32_torch": timed(lambda: torch.nn.grad.conv2d_weight(x, w.shape, dy, padding=1), 15, cmp=True)}
+    emit("B2 conv backward grad_weight, C4 layer", flops, trim(rows))
+
+
+def run_s1(lib, ref, timed, emit, ok, P, stream, trim):
+    """Linear layers with a small batch (few output tiles, long K): bias + GELU fused, W as stored."""
+    import torch
+    import torch.nn.functional as F
+    torch.backends.cuda.matmul.allow_tf32 = True
+    for m, n, k in [(128, 4096, 4096), (256, 1024, 8192), (512, 512, 4096), (1024, 1024, 4096)]:
+        x = torch.randn((m, k), device="cuda")
+        w = torch.randn((n, k), device="cuda") * (1.0 / k) ** 0.5
+        bias = torch.randn(n, device="cuda") * 0.01
+        y = torch.empty((m, n), device="cuda")
+        rows = {"ours": timed(lambda: ok(lib.cudeep_b200_linear_forward_f32(P(x), P(w), P(bias), P(y), m, n, k, 2, stream)), 30),
+                "cublas_tf32_torch": timed(lambda: F.gelu(F.linear(x, w, bias), approximate="tanh"), 30, cmp=True)}
+        emit(f"S1 Linear + GELU, batch {m}: {k} -> {n}", 2.0 * m * n * k, trim(rows))
 
 
 def main():
