@@ -61,7 +61,8 @@ def parse_args():
                          "cuBLAS / cuDNN (through torch) and the reference's kernels; one JSON line each")
     ap.add_argument("--only", default="", help="with --suite: run only the configurations whose name starts "
                                                "with one of these comma-separated tags (C1, C2, C3, C4; "
-                                               "B1 matmul backward, B2 conv backward, S1 small-batch Linear)")
+                                               "B1 matmul backward, B2 conv backward, S1 small-batch Linear; "
+                                               "G1, only when named: small GEMMs timed inside a CUDA graph)")
     ap.add_argument("--no-comparators", action="store_true",
                     help="with --suite: time only this library (short runs for profiling)")
     return ap.parse_args()
@@ -466,6 +467,8 @@ def run_suite(args):
         run_b2(lib, ref, timed, emit, ok, P, stream, trim)
     if want("S1"):
         run_s1(lib, ref, timed, emit, ok, P, stream, trim)
+    if "G1" in only:            # only on request: a different timing protocol
+        run_g1(lib, emit, ok, P)
     status = _lib.device_status(True)
     if status != 0:
         raise RuntimeError(f"kernel status word {status}")
@@ -611,6 +614,51 @@ def run_s1(lib, ref, timed, emit, ok, P, stream, trim):
         rows = {"ours": timed(lambda: ok(lib.cudeep_b200_linear_forward_f32(P(x), P(w), P(bias), P(y), m, n, k, 2, stream)), 30),
                 "cublas_tf32_torch": timed(lambda: F.gelu(F.linear(x, w, bias), approximate="tanh"), 30, cmp=True)}
         emit(f"S1 Linear + GELU, batch {m}: {k} -> {n}", 2.0 * m * n * k, trim(rows))
+
+
+def run_g1(lib, emit, ok, P):
+    """Small and skinny GEMMs, timed as launches back to back inside a CUDA graph over rotating
+    operand sets that together exceed L2: cold operands, no host gaps between launches and none
+    of the ~2 us granularity of per-launch events."""
+    import torch
+    torch.backends.cuda.matmul.allow_tf32 = True
+    shapes = [(256, 256, 256), (512, 512, 512), (1024, 1024, 1024), (1536, 1536, 1536), (2048, 2048, 2048),
+              (3072, 3072, 3072), (4096, 4096, 4096), (1024, 1024, 4096), (128, 4096, 4096), (512, 512, 4096),
+              (256, 1024, 8192), (128, 128, 8192), (8192, 1024, 1024), (4096, 1024, 4096), (5000, 3000, 520)]
+    side = torch.cuda.Stream()
+    sp = ctypes.c_void_p(side.cuda_stream)
+
+    def graph_ms(launch, sets):
+        with torch.cuda.stream(side):
+            for i in range(sets):
+                launch(i)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(sets):
+                    launch(i)
+            graph.replay()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(5):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(side)
+                graph.replay()
+                e1.record(side)
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) / sets)
+        return float(np.median(ts)), float(np.min(ts))
+
+    for m, n, k in shapes:
+        per_set = (m * k + k * n + m * n) * 4
+        sets = max(3, min(40, (400 << 20) // per_set + 1))
+        a = [torch.randn((m, k), device="cuda") for _ in range(sets)]
+        b = [torch.randn((k, n), device="cuda") for _ in range(sets)]
+        c = [torch.empty((m, n), device="cuda") for _ in range(sets)]
+        rows = {"ours": graph_ms(lambda i: ok(lib.cudeep_b200_matmul_f32(P(a[i]), P(b[i]), P(c[i]), m, n, k, sp)), sets),
+                "cublas_tf32": graph_ms(lambda i: torch.matmul(a[i], b[i], out=c[i]), sets)}
+        emit(f"G1 TF32 GEMM {m} x {n} x {k}, graph-timed over {sets} operand sets", 2.0 * m * n * k, rows)
+        del a, b, c
 
 
 def main():

@@ -62,6 +62,8 @@ PROTOTYPES = {
                                         POINTER(c_size_t)]),
     "cudeep_b200_pool_alloc": (c_int, [c_size_t, POINTER(c_void_p)]),
     "cudeep_b200_pool_free": (c_int, [c_void_p]),
+    "cudeep_b200_pool_alloc_on_stream": (c_int, [c_size_t, c_void_p, POINTER(c_void_p)]),
+    "cudeep_b200_pool_free_on_stream": (c_int, [c_void_p, c_void_p]),
     "cudeep_b200_pool_release_cached": (c_int, []),
     "cudeep_b200_pool_stats": (c_int, [POINTER(c_size_t), POINTER(c_size_t)]),
 }

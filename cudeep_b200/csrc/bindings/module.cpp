@@ -98,6 +98,9 @@ PYBIND11_MODULE(_cudeep_core, m) {
         .def("fill_", &Tensor::fill_)
         .def("zero_", &Tensor::zero_)
         .def("matmul", &Tensor::matmul)
+        // Addition: queue this tensor's work on a Stream (the reference has set_stream in C++ only).
+        .def("set_stream", [](Tensor& t, const Stream& s) { t.set_stream(s.get()); }, py::arg("stream"),
+             py::keep_alive<1, 2>())
         .def("__add__", &Tensor::operator+)
         .def("__sub__", &Tensor::operator-)
         .def("__mul__", &Tensor::operator*)

@@ -477,6 +477,17 @@ int cudeep_b200_pool_free(void* ptr) {
     return guarded([&] { cudeep::device_free(ptr); });
 }
 
+int cudeep_b200_pool_alloc_on_stream(size_t nbytes, cudeep_b200_stream_t stream, void** ptr) {
+    return guarded([&] {
+        CB200_REQUIRE(ptr != nullptr, "pool_alloc: null result pointer");
+        *ptr = cudeep::MemoryPool::instance().allocate(nbytes, as_stream(stream));
+    });
+}
+
+int cudeep_b200_pool_free_on_stream(void* ptr, cudeep_b200_stream_t stream) {
+    return guarded([&] { cudeep::device_free(ptr, as_stream(stream)); });
+}
+
 int cudeep_b200_pool_release_cached(void) {
     return guarded([&] { cudeep::MemoryPool::instance().release_cached(); });
 }

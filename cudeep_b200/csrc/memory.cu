@@ -29,36 +29,70 @@ MemoryPool& MemoryPool::instance() {
     return *g_pools[dev];
 }
 
+namespace {
+// Makes `device` current for the lifetime of the guard.
+struct DeviceGuard {
+    int prev = 0;
+    bool switched = false;
+    explicit DeviceGuard(int device) {
+        CB200_CUDA(cudaGetDevice(&prev));
+        if (prev != device) {
+            CB200_CUDA(cudaSetDevice(device));
+            switched = true;
+        }
+    }
+    ~DeviceGuard() {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+}  // namespace
+
 MemoryPool::~MemoryPool() {
     // The CUDA context may already be gone at process exit; ignore errors.
     for (auto& kv : free_blocks_)
-        for (void* p : kv.second) cudaFree(p);
+        for (FreeBlock& b : kv.second) {
+            cudaFree(b.ptr);
+            cudaEventDestroy(b.ready);
+        }
+    for (cudaEvent_t e : spare_events_) cudaEventDestroy(e);
     for (auto& kv : live_blocks_) cudaFree(kv.first);
 }
 
-void* MemoryPool::allocate(size_t nbytes) {
+void* MemoryPool::allocate(size_t nbytes) { return allocate(nbytes, nullptr); }
+void MemoryPool::deallocate(void* ptr) { deallocate(ptr, nullptr); }
+
+void* MemoryPool::allocate(size_t nbytes, cudaStream_t stream) {
     const size_t bin = size_class(nbytes);
     void* ptr = nullptr;
     {
         std::lock_guard<std::mutex> lock(mutex_);
         auto it = free_blocks_.find(bin);
-        if (it != free_blocks_.end() && !it->second.empty()) {
-            ptr = it->second.back();
-            it->second.pop_back();
-            cached_bytes_ -= bin;
+        if (it != free_blocks_.end()) {
+            std::vector<FreeBlock>& blocks = it->second;
+            int pick = -1;
+            // A block last used on the same stream is ordered behind that use by the stream
+            // itself; any other block only once the work queued before its release has drained.
+            for (int i = static_cast<int>(blocks.size()) - 1; i >= 0 && pick < 0; --i)
+                if (blocks[i].stream == stream) pick = i;
+            for (int i = static_cast<int>(blocks.size()) - 1; i >= 0 && pick < 0; --i)
+                if (cudaEventQuery(blocks[i].ready) == cudaSuccess) pick = i;
+            cudaGetLastError();      // cudaErrorNotReady from the queries is not an error
+            if (pick >= 0) {
+                ptr = blocks[pick].ptr;
+                spare_events_.push_back(blocks[pick].ready);
+                blocks.erase(blocks.begin() + pick);
+                cached_bytes_ -= bin;
+            }
         }
     }
     if (ptr == nullptr) {
-        int prev = 0;
-        CB200_CUDA(cudaGetDevice(&prev));
-        if (prev != device_) CB200_CUDA(cudaSetDevice(device_));
+        DeviceGuard guard(device_);
         cudaError_t err = cudaMalloc(&ptr, bin);
         if (err == cudaErrorMemoryAllocation) {
             cudaGetLastError();
             release_cached();                 // give cached blocks back and retry once
             err = cudaMalloc(&ptr, bin);
         }
-        if (prev != device_) cudaSetDevice(prev);
         if (err != cudaSuccess) cudeep_b200::throw_cuda(err, "cudaMalloc", __FILE__, __LINE__);
     }
     {
@@ -73,37 +107,60 @@ void* MemoryPool::allocate(size_t nbytes) {
     return ptr;
 }
 
-void MemoryPool::deallocate(void* ptr) {
+void MemoryPool::deallocate(void* ptr, cudaStream_t stream) {
     if (ptr == nullptr) return;
     std::lock_guard<std::mutex> lock(mutex_);
     auto it = live_blocks_.find(ptr);
     if (it == live_blocks_.end()) return;     // not ours: ignore, as the reference does
     const size_t bin = it->second;
+    cudaEvent_t ready = nullptr;
+    {
+        DeviceGuard guard(device_);
+        if (!spare_events_.empty()) {
+            ready = spare_events_.back();
+            spare_events_.pop_back();
+        } else {
+            CB200_CUDA(cudaEventCreateWithFlags(&ready, cudaEventDisableTiming));
+        }
+        if (cudaEventRecord(ready, stream) != cudaSuccess) {
+            // The stream no longer exists (destroyed before the tensors that worked on it):
+            // whatever it had queued is over once the device is idle.
+            cudaGetLastError();
+            CB200_CUDA(cudaDeviceSynchronize());
+            stream = nullptr;
+            CB200_CUDA(cudaEventRecord(ready, stream));
+        }
+    }
     live_blocks_.erase(it);
     allocated_bytes_ -= bin;
-    free_blocks_[bin].push_back(ptr);
+    free_blocks_[bin].push_back(FreeBlock{ptr, stream, ready});
     cached_bytes_ += bin;
 }
 
 void MemoryPool::release_cached() {
-    std::vector<void*> doomed;
+    std::vector<FreeBlock> doomed;
     {
         std::lock_guard<std::mutex> lock(mutex_);
         for (auto& kv : free_blocks_)
-            for (void* p : kv.second) doomed.push_back(p);
+            for (FreeBlock& b : kv.second) doomed.push_back(b);
         free_blocks_.clear();
         cached_bytes_ = 0;
     }
     {
         std::lock_guard<std::mutex> lock(g_owner_mu);
-        for (void* p : doomed) g_owner.erase(p);
+        for (FreeBlock& b : doomed) g_owner.erase(b.ptr);
     }
-    for (void* p : doomed) cudaFree(p);
+    for (FreeBlock& b : doomed) {
+        cudaFree(b.ptr);                      // waits for the device, so pending uses are over
+        std::lock_guard<std::mutex> lock(mutex_);
+        spare_events_.push_back(b.ready);
+    }
 }
 
 void* device_malloc(size_t nbytes) { return MemoryPool::instance().allocate(nbytes); }
+void* device_malloc(size_t nbytes, cudaStream_t stream) { return MemoryPool::instance().allocate(nbytes, stream); }
 
-void device_free(void* ptr) {
+void device_free(void* ptr, cudaStream_t stream) {
     if (ptr == nullptr) return;
     MemoryPool* owner = nullptr;
     {
@@ -111,8 +168,9 @@ void device_free(void* ptr) {
         auto it = g_owner.find(ptr);
         if (it != g_owner.end()) owner = it->second;
     }
-    if (owner != nullptr) owner->deallocate(ptr);
+    if (owner != nullptr) owner->deallocate(ptr, stream);
 }
+void device_free(void* ptr) { device_free(ptr, nullptr); }
 
 static void copy(void* dst, const void* src, size_t nbytes, cudaMemcpyKind kind, cudaStream_t stream) {
     if (nbytes == 0) return;

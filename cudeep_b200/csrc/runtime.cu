@@ -19,6 +19,7 @@ static const char* base_name(const char* path) {
 }
 
 void throw_cuda(cudaError_t err, const char* what, const char* file, int line) {
+    cudaGetLastError();      // reported here: a later launch check must not find it again
     throw std::runtime_error(std::string("CUDA error: ") + cudaGetErrorString(err) + " in " + what +
                              " (" + base_name(file) + ":" + std::to_string(line) + ")");
 }

@@ -11,10 +11,13 @@
 
 namespace cudeep {
 
+// Device storage shared by a tensor and its views.  It remembers the stream its owner works
+// on, so that the pool hands the block to other streams only after that work has drained.
 struct Tensor::Buffer {
     void* ptr = nullptr;
-    explicit Buffer(size_t bytes) : ptr(device_malloc(bytes > 0 ? bytes : 1)) {}
-    ~Buffer() { device_free(ptr); }
+    cudaStream_t stream = nullptr;
+    Buffer(size_t bytes, cudaStream_t s) : ptr(device_malloc(bytes > 0 ? bytes : 1, s)), stream(s) {}
+    ~Buffer() { device_free(ptr, stream); }
     Buffer(const Buffer&) = delete;
     Buffer& operator=(const Buffer&) = delete;
 };
@@ -38,17 +41,25 @@ std::atomic<uint64_t> g_randn_counter{0x9e3779b97f4a7c15ull};
 
 Tensor::Tensor() = default;
 
-Tensor::Tensor(const std::vector<int64_t>& shape, DType dtype) : shape_(shape), dtype_(dtype) {
+Tensor::Tensor(const std::vector<int64_t>& shape, DType dtype) : Tensor(shape, dtype, nullptr) {}
+
+Tensor::Tensor(const std::vector<int64_t>& shape, DType dtype, cudaStream_t stream)
+    : shape_(shape), dtype_(dtype), stream_(stream) {
     for (int64_t s : shape_) CB200_REQUIRE(s >= 0, "Tensor: negative extent");
     compute_strides();
-    buffer_ = std::make_shared<Buffer>(nbytes());
+    buffer_ = std::make_shared<Buffer>(nbytes(), stream);
+}
+
+void Tensor::set_stream(cudaStream_t stream) {
+    stream_ = stream;
+    if (buffer_) buffer_->stream = stream;
 }
 
 Tensor::Tensor(const Tensor& other)
     : shape_(other.shape_), dtype_(other.dtype_), stream_(other.stream_) {
     compute_strides();
     if (other.buffer_) {
-        buffer_ = std::make_shared<Buffer>(nbytes());
+        buffer_ = std::make_shared<Buffer>(nbytes(), stream_);
         const Tensor src = other.is_contiguous() ? Tensor() : other.contiguous();
         const void* from = other.is_contiguous() ? other.data() : src.data();
         memcpy_d2d(buffer_->ptr, from, nbytes(), stream_);
@@ -195,8 +206,7 @@ Tensor Tensor::contiguous() const {
         return out;
     }
     CB200_REQUIRE(dtype_ != DType::Float16, "contiguous: float16 views are not supported");
-    Tensor out(shape_, dtype_);
-    out.stream_ = stream_;
+    Tensor out(shape_, dtype_, stream_);
     cudeep_b200::StridedView view{};
     CB200_REQUIRE(ndim() <= cudeep_b200::StridedView::kMaxDims, "contiguous: rank above 8");
     view.ndim = static_cast<int>(ndim());
@@ -219,8 +229,7 @@ Tensor Tensor::binary(const Tensor& other, int op) const {
     CB200_REQUIRE(shape_ == other.shape_, "elementwise op: shape mismatch");
     CB200_REQUIRE(dtype_ == other.dtype_ && dtype_ != DType::Float16, "elementwise op: dtype mismatch");
     const Tensor a = contiguous(), b = other.contiguous();
-    Tensor out(shape_, dtype_);
-    out.stream_ = stream_;
+    Tensor out(shape_, dtype_, stream_);
     const long long n = numel();
     if (n > 0) {
         long long blocks = (n + 255) / 256;
@@ -249,8 +258,7 @@ Tensor Tensor::matmul(const Tensor& other) const {
     CB200_REQUIRE(is_contiguous() && other.is_contiguous(), "matmul requires contiguous tensors");
     const int m = static_cast<int>(shape_[0]), k = static_cast<int>(shape_[1]);
     const int n = static_cast<int>(other.shape_[1]);
-    Tensor out({shape_[0], other.shape_[1]}, dtype_);
-    out.stream_ = stream_;
+    Tensor out({shape_[0], other.shape_[1]}, dtype_, stream_);
     if (dtype_ == DType::Float32)
         kernels::launch_matmul_kernel<float>(static_cast<const float*>(data()),
                                              static_cast<const float*>(other.data()),

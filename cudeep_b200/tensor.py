@@ -52,16 +52,20 @@ def _contiguous_strides(shape: Sequence[int]) -> list[int]:
 
 
 class _Storage:
-    """A pool block, returned to the pool when the last view of it goes away."""
+    """A pool block, returned to the pool when the last view of it goes away.  `stream` is the
+    stream its tensor last worked on: the pool lets other streams have the block only after
+    that stream has drained."""
 
-    def __init__(self, nbytes: int):
+    def __init__(self, nbytes: int, stream=None):
         self.ptr = ctypes.c_void_p()
-        _lib.check(_lib.load().cudeep_b200_pool_alloc(max(int(nbytes), 1), ctypes.byref(self.ptr)))
+        self.stream = stream
+        _lib.check(_lib.load().cudeep_b200_pool_alloc_on_stream(max(int(nbytes), 1), stream,
+                                                                ctypes.byref(self.ptr)))
 
     def __del__(self):
         try:
             if self.ptr:
-                _lib.load().cudeep_b200_pool_free(self.ptr)
+                _lib.load().cudeep_b200_pool_free_on_stream(self.ptr, self.stream)
         except Exception:
             pass
 
@@ -76,7 +80,23 @@ class Tensor:
         self._dtype = dtype
         self._strides = list(_strides) if _strides is not None else _contiguous_strides(self._shape)
         self._storage = _storage if _storage is not None else _Storage(self.nbytes())
-        self.stream = None          # cudaStream_t as int / c_void_p; None = legacy default stream
+        self._stream = getattr(self._storage, "stream", None)
+
+    @property
+    def stream(self):
+        """cudaStream_t (int / c_void_p) this tensor's operations are queued on; None = legacy default."""
+        return self._stream
+
+    @stream.setter
+    def stream(self, value):
+        self._stream = value
+        self._storage.stream = value
+
+    def set_stream(self, stream) -> None:
+        """Accepts a Stream object or a raw handle (Tensor::set_stream, include/cudeep/tensor.cuh).
+        A Stream object is kept alive for as long as the storage that was used on it."""
+        self.stream = getattr(stream, "handle", stream)
+        self._storage.stream_owner = stream
 
     # ---- metadata ------------------------------------------------------------------------
     def shape(self) -> list[int]:

@@ -252,6 +252,10 @@ int cudeep_b200_device_info(int* device, int* sm_count, int* cc_major, int* cc_m
 
 int cudeep_b200_pool_alloc(size_t nbytes, void** ptr);     /* MemoryPool::allocate   */
 int cudeep_b200_pool_free(void* ptr);                      /* MemoryPool::deallocate */
+/* Stream-aware forms (additions): a block freed on a stream serves that stream again at once, any
+ * other stream only after the work queued before the free has drained. */
+int cudeep_b200_pool_alloc_on_stream(size_t nbytes, cudeep_b200_stream_t stream, void** ptr);
+int cudeep_b200_pool_free_on_stream(void* ptr, cudeep_b200_stream_t stream);
 int cudeep_b200_pool_release_cached(void);                 /* MemoryPool::release_cached */
 int cudeep_b200_pool_stats(size_t* allocated_bytes, size_t* cached_bytes);
 

@@ -267,3 +267,48 @@ class TestConv2dLayer:
         y64 = cd.conv2d(cd.Tensor.from_numpy(x.astype(np.float64)), cd.Tensor.from_numpy(w.astype(np.float64)),
                         cd.Tensor.from_numpy(b.astype(np.float64)), padding=1).numpy()
         assert oracle.rel_frobenius(y64, oracle.conv2d(x, w, b, (1, 1), (1, 1))) <= 1e-12
+
+
+def test_pool_is_stream_aware(lib, cuda):
+    """A block freed on a stream serves that stream again at once, but another stream only after
+    the work queued before the free has drained (include/cudeep/memory.cuh)."""
+    import ctypes
+    from cudeep_b200 import _lib
+    torch = cuda
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    p1, p2 = ctypes.c_void_p(s1.cuda_stream), ctypes.c_void_p(s2.cuda_stream)
+    nbytes = (8 << 20) + 4096          # a size class of its own
+
+    def alloc(stream):
+        out = ctypes.c_void_p()
+        _lib.check(lib.cudeep_b200_pool_alloc_on_stream(nbytes, stream, ctypes.byref(out)))
+        return out.value
+
+    def free(ptr, stream):
+        _lib.check(lib.cudeep_b200_pool_free_on_stream(ctypes.c_void_p(ptr), stream))
+
+    _lib.check(lib.cudeep_b200_pool_release_cached())
+    block = alloc(p1)
+    # About 10 ms of work on stream 1, then the block is released behind it.
+    n = 8192
+    a = torch.randn((n, n), device="cuda")
+    c = torch.empty((n, n), device="cuda")
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    torch.cuda.synchronize()
+    for _ in range(8):
+        _lib.check(lib.cudeep_b200_matmul_f32(ptr(a), ptr(a), ptr(c), n, n, n, p1))
+    free(block, p1)
+    same_stream = alloc(p1)
+    assert same_stream == block                      # ordered behind the pending work by the stream itself
+    free(same_stream, p1)
+    other_stream = alloc(p2)
+    still_busy = not s1.query()
+    if still_busy:
+        assert other_stream != block                 # stream 1 has not drained: a fresh block instead
+    torch.cuda.synchronize()
+    free(other_stream, p2)
+    later = alloc(p2)
+    assert later in (block, other_stream)            # everything has drained: cached blocks serve any stream
+    free(later, p2)
+    assert _lib.device_status() == 0
+    _lib.check(lib.cudeep_b200_pool_release_cached())

@@ -190,7 +190,11 @@ def test_stream_event_pool_device_info(core, cuda):
     s = core.Stream()
     e0, e1 = core.Event(), core.Event()
     e0.record(s)
+    a = core.Tensor.from_numpy(np.eye(96, dtype=np.float32))
+    a.set_stream(s)                      # addition: the product and its storage belong to stream s
+    prod = a.matmul(a)
     e1.record(s)
     s.synchronize()
+    np.testing.assert_array_equal(prod.numpy(), np.eye(96, dtype=np.float32))
     e1.synchronize()
     assert e1.elapsed_ms(e0) >= 0.0
