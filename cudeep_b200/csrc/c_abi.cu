@@ -148,6 +148,7 @@ int cudeep_b200_gemm_tf32_tuned(const float* A, const float* B, int b_is_nk, flo
         tune.split_k = static_cast<int>(b_lbo >> 16) & 0xff;      // packed: see cudeep_b200.h
         tune.cluster_split = static_cast<int>(b_lbo >> 24) & 0xf;
         tune.tma_store = ((b_lbo >> 28) & 1u) ? -1 : 0;
+        tune.debug |= ((b_lbo >> 29) & 7u) << 4;
         tune.b_lbo = b_lbo & 0xffffu;
         tune.b_sbo = b_sbo;
         cudeep_b200::gemm_tf32(A, B, b_is_nk != 0, C, M, N, K, bias, bias_per_row != 0, epilogue, tune,
@@ -417,13 +418,12 @@ int cudeep_b200_activation_f32(const float* x, float* y, long long count, int ep
 int cudeep_b200_stream_create(cudeep_b200_stream_t* stream) {
     return guarded([&] {
         CB200_REQUIRE(stream != nullptr, "stream_create: null result pointer");
-        cudaStream_t s = nullptr;
-        CB200_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
-        *stream = s;
+        cudeep::Stream s;
+        *stream = s.release();
     });
 }
 int cudeep_b200_stream_destroy(cudeep_b200_stream_t stream) {
-    return guarded([&] { CB200_CUDA(cudaStreamDestroy(as_stream(stream))); });
+    return guarded([&] { cudeep::Stream::destroy_handle(as_stream(stream)); });
 }
 int cudeep_b200_event_create(void** event) {
     return guarded([&] {

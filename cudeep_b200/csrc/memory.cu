@@ -3,10 +3,41 @@
 #include "runtime.h"
 
 #include <memory>
+#include <unordered_set>
 
 namespace cudeep {
 
 namespace {
+// Streams created and destroyed through this library.  A tensor may outlive the stream it worked
+// on; the pool must then not hand that stream to the CUDA runtime again.  Streams are drained
+// before they are destroyed, so storage last used on a destroyed stream has no work pending.
+std::mutex g_streams_mu;
+std::unordered_set<cudaStream_t> g_dead_streams;
+
+cudaStream_t create_tracked_stream() {
+    cudaStream_t s = nullptr;
+    CB200_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    std::lock_guard<std::mutex> lock(g_streams_mu);
+    g_dead_streams.erase(s);           // the driver may reuse a handle value
+    return s;
+}
+
+void destroy_tracked_stream(cudaStream_t s) noexcept {
+    if (s == nullptr) return;
+    cudaStreamSynchronize(s);
+    {
+        std::lock_guard<std::mutex> lock(g_streams_mu);
+        g_dead_streams.insert(s);
+    }
+    cudaStreamDestroy(s);
+}
+
+bool stream_is_dead(cudaStream_t s) {
+    if (s == nullptr) return false;
+    std::lock_guard<std::mutex> lock(g_streams_mu);
+    return g_dead_streams.count(s) != 0;
+}
+
 std::mutex g_pools_mu;
 std::vector<std::unique_ptr<MemoryPool>> g_pools;
 // Which pool owns a live block (blocks may be freed while another device is current).
@@ -122,14 +153,10 @@ void MemoryPool::deallocate(void* ptr, cudaStream_t stream) {
         } else {
             CB200_CUDA(cudaEventCreateWithFlags(&ready, cudaEventDisableTiming));
         }
-        if (cudaEventRecord(ready, stream) != cudaSuccess) {
-            // The stream no longer exists (destroyed before the tensors that worked on it):
-            // whatever it had queued is over once the device is idle.
-            cudaGetLastError();
-            CB200_CUDA(cudaDeviceSynchronize());
-            stream = nullptr;
-            CB200_CUDA(cudaEventRecord(ready, stream));
-        }
+        // A stream of this library that is gone was drained when it was destroyed: nothing is
+        // pending on the block.  (Streams created elsewhere must outlive the storage used on them.)
+        if (stream_is_dead(stream)) stream = nullptr;
+        CB200_CUDA(cudaEventRecord(ready, stream));
     }
     live_blocks_.erase(it);
     allocated_bytes_ -= bin;
@@ -188,18 +215,24 @@ void memcpy_d2d(void* dst, const void* src, size_t nbytes, cudaStream_t stream) 
 }
 
 // ------------------------------------------------------------------ Stream / Event
-Stream::Stream() { CB200_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking)); }
-Stream::~Stream() { if (stream_) cudaStreamDestroy(stream_); }
+Stream::Stream() : stream_(create_tracked_stream()) {}
+Stream::~Stream() { destroy_tracked_stream(stream_); }
 Stream::Stream(Stream&& other) noexcept : stream_(other.stream_) { other.stream_ = nullptr; }
 Stream& Stream::operator=(Stream&& other) noexcept {
     if (this != &other) {
-        if (stream_) cudaStreamDestroy(stream_);
+        destroy_tracked_stream(stream_);
         stream_ = other.stream_;
         other.stream_ = nullptr;
     }
     return *this;
 }
 void Stream::synchronize() const { CB200_CUDA(cudaStreamSynchronize(stream_)); }
+cudaStream_t Stream::release() noexcept {
+    cudaStream_t s = stream_;
+    stream_ = nullptr;
+    return s;
+}
+void Stream::destroy_handle(cudaStream_t stream) noexcept { destroy_tracked_stream(stream); }
 
 Event::Event() { CB200_CUDA(cudaEventCreate(&event_)); }
 Event::~Event() { if (event_) cudaEventDestroy(event_); }

@@ -82,7 +82,9 @@ struct UmmaSchedule {
     //          runs alone;
     //   bit 2: the MMA issuer ignores the stage ring (no waits, no stage commits) and the
     //          producer does nothing: raw MMA issue rate;
-    //   bit 3: the epilogue neither reads TMEM nor stores.
+    //   bit 3: the epilogue neither reads TMEM nor stores;
+    //   bit 4: the bulk-store epilogue stages its results but issues no store;
+    //   bit 5: the bulk-store epilogue skips the accumulator loads.
     uint32_t debug;
 };
 
@@ -470,16 +472,63 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                     emit(c, r0);
                 }
             }
-            if (ksplit == 1 && n_cols > 0) ptx::tmem_ld_32x32(t_row, r0);
+            if (ksplit == 1 && use_tma) {
+                // Two 32-column chunks per round: both staging blocks are filled, one proxy fence
+                // covers them, two bulk stores go out as one group, and the accumulator loads of
+                // the next round are in flight while this round is fenced and stored.
+                if constexpr (Problem::kTmaStore) {
+                    const bool dbg_nold = (sched.debug & 0x20u) != 0, dbg_nost = (sched.debug & 0x10u) != 0;
+                    if (n_cols > 0 && !dbg_nold) ptx::tmem_ld_32x32(t_row, r0);
+                    if (n_cols > 32 && !dbg_nold) ptx::tmem_ld_32x32(t_row + 32, r1);
 #pragma unroll 1
-            for (int c = 0; ksplit == 1 && c < n_cols; c += 64) {
-                ptx::tmem_ld_wait();
-                if (c + 32 < n_cols) ptx::tmem_ld_32x32(t_row + c + 32, r1);
-                emit(c, r0);
-                if (c + 32 < n_cols) {
+                    for (int c = 0; c < n_cols; c += 64) {
+                        const bool two = c + 32 < n_cols;
+                        ptx::tmem_ld_wait();
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
+                        prob.finish(tile, row_in_cta, c, v, epi);
+                        if (lane == 0) ptx::bulk_wait_group_read<0>();      // last round's stores have read their blocks
+                        __syncwarp();
+                        const uint32_t row_smem = staging + lane * 128u;
+#pragma unroll
+                        for (uint32_t q = 0; q < 8; ++q)      // 128-byte swizzle: unit q of row r at q ^ (r & 7)
+                            ptx::st_shared_v4(row_smem + ((q ^ (lane & 7u)) << 4), v[4 * q], v[4 * q + 1],
+                                              v[4 * q + 2], v[4 * q + 3]);
+                        if (two) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
+                            prob.finish(tile, row_in_cta, c + 32, v, epi);
+#pragma unroll
+                            for (uint32_t q = 0; q < 8; ++q)
+                                ptx::st_shared_v4(row_smem + 4096u + ((q ^ (lane & 7u)) << 4), v[4 * q], v[4 * q + 1],
+                                                  v[4 * q + 2], v[4 * q + 3]);
+                        }
+                        if (c + 64 < n_cols && !dbg_nold) ptx::tmem_ld_32x32(t_row + c + 64, r0);
+                        if (c + 96 < n_cols && !dbg_nold) ptx::tmem_ld_32x32(t_row + c + 96, r1);
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0 && !dbg_nost) {
+                            int x, y;
+                            prob.out_coords(tile, int(quarter) * 32, c, x, y);
+                            ptx::tma_store_2d(prob.out_map(), staging, x, y);
+                            if (two) ptx::tma_store_2d(prob.out_map(), staging + 4096u, x + 32, y);
+                            ptx::bulk_commit_group();
+                        }
+                    }
+                }
+            } else if (ksplit == 1) {
+                if (n_cols > 0) ptx::tmem_ld_32x32(t_row, r0);
+#pragma unroll 1
+                for (int c = 0; c < n_cols; c += 64) {
                     ptx::tmem_ld_wait();
-                    if (c + 64 < n_cols) ptx::tmem_ld_32x32(t_row + c + 64, r0);
-                    emit(c + 32, r1);
+                    if (c + 32 < n_cols) ptx::tmem_ld_32x32(t_row + c + 32, r1);
+                    emit(c, r0);
+                    if (c + 32 < n_cols) {
+                        ptx::tmem_ld_wait();
+                        if (c + 64 < n_cols) ptx::tmem_ld_32x32(t_row + c + 64, r0);
+                        emit(c + 32, r1);
+                    }
                 }
             }
             ptx::tc_fence_before();

@@ -1,7 +1,9 @@
 // RAII stream and event wrappers; public surface of the reference's
 // include/cudeep/stream.cuh:8-44 (Stream: get/synchronize, Event:
 // record/synchronize/elapsed_ms).  Streams here are created non-blocking so
-// work on them overlaps the legacy default stream.
+// work on them overlaps the legacy default stream.  A Stream is drained before it is
+// destroyed, and the memory pool knows which of these streams are gone, so tensors may
+// outlive the stream they worked on.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -19,6 +21,10 @@ public:
 
     cudaStream_t get() const { return stream_; }
     void synchronize() const;
+    // Additions for callers that hold raw handles (the C ABI): give up ownership of the handle /
+    // drain and destroy a handle obtained that way.
+    cudaStream_t release() noexcept;
+    static void destroy_handle(cudaStream_t stream) noexcept;
 
 private:
     cudaStream_t stream_ = nullptr;
