@@ -61,7 +61,7 @@ def parse_args():
                          "cuBLAS / cuDNN (through torch) and the reference's kernels; one JSON line each")
     ap.add_argument("--only", default="", help="with --suite: run only the configurations whose name starts "
                                                "with one of these comma-separated tags (C1, C2, C3, C4; "
-                                               "B1 matmul backward, B2 conv backward, S1 small-batch Linear; "
+                                               "B1 matmul backward, B2 conv backward, S1 small-batch Linear, H1 FP16 GEMM; "
                                                "G1, only when named: small GEMMs timed inside a CUDA graph)")
     ap.add_argument("--no-comparators", action="store_true",
                     help="with --suite: time only this library (short runs for profiling)")
@@ -467,6 +467,8 @@ def run_suite(args):
         run_b2(lib, ref, timed, emit, ok, P, stream, trim)
     if want("S1"):
         run_s1(lib, ref, timed, emit, ok, P, stream, trim)
+    if want("H1"):
+        run_h1(lib, timed, emit, ok, P, stream, trim)
     if "G1" in only:            # only on request: a different timing protocol
         run_g1(lib, emit, ok, P)
     status = _lib.device_status(True)
@@ -525,7 +527,12 @@ def run_c3(lib, ref, timed, emit, ok, P, stream, trim):
     def torch_c3():
         F.linear(F.gelu(F.linear(x, w1, b1), approximate="tanh"), w2, b2)
 
+    def lt_c3():        # cuBLASLt with the bias + GELU epilogue fused into the first GEMM
+        torch.addmm(b2, torch._addmm_activation(b1, x, w1.t(), use_gelu=True), w2.t())
+
     rows = {"ours": timed(ours_c3, 8), "cublas_tf32_torch": timed(torch_c3, 8, cmp=True)}
+    if hasattr(torch, "_addmm_activation"):
+        rows["cublaslt_fused_epilogue_torch"] = timed(lt_c3, 8, cmp=True)
     if ref is not None:
         w1t, w2t = w1.t().contiguous(), w2.t().contiguous()
 
@@ -613,7 +620,24 @@ def run_s1(lib, ref, timed, emit, ok, P, stream, trim):
         y = torch.empty((m, n), device="cuda")
         rows = {"ours": timed(lambda: ok(lib.cudeep_b200_linear_forward_f32(P(x), P(w), P(bias), P(y), m, n, k, 2, stream)), 30),
                 "cublas_tf32_torch": timed(lambda: F.gelu(F.linear(x, w, bias), approximate="tanh"), 30, cmp=True)}
+        if hasattr(torch, "_addmm_activation"):
+            rows["cublaslt_fused_epilogue_torch"] = timed(
+                lambda: torch._addmm_activation(bias, x, w.t(), use_gelu=True), 30, cmp=True)
         emit(f"S1 Linear + GELU, batch {m}: {k} -> {n}", 2.0 * m * n * k, trim(rows))
+
+
+def run_h1(lib, timed, emit, ok, P, stream, trim):
+    """FP16 operands, FP32 accumulate and FP32 result (launch_matmul_kernel_fp16).  cuBLAS through torch
+    writes an FP16 result (half the output bytes); it is the nearest library comparator at hand."""
+    import torch
+    for n in (4096, 8192):
+        a = torch.randn((n, n), device="cuda").half()
+        b = torch.randn((n, n), device="cuda").half()
+        c = torch.empty((n, n), device="cuda")
+        ch = torch.empty((n, n), device="cuda", dtype=torch.half)
+        rows = {"ours": timed(lambda: ok(lib.cudeep_b200_matmul_f16(P(a), P(b), P(c), n, n, n, stream)), 15),
+                "cublas_f16_result_torch": timed(lambda: torch.matmul(a, b, out=ch), 15, cmp=True)}
+        emit(f"H1 FP16 GEMM {n}^3, FP32 result", 2.0 * n ** 3, trim(rows))
 
 
 def run_g1(lib, emit, ok, P):

@@ -7,6 +7,7 @@
 #include "cudeep/kernels/matmul.cuh"
 #include "cudeep/memory.cuh"
 #include "conv_igemm.h"
+#include "gemm_f16.h"
 #include "gemm_tf32.h"
 #include "abi_error.h"
 #include "tensor_ops.h"
@@ -153,6 +154,23 @@ int cudeep_b200_gemm_tf32_tuned(const float* A, const float* B, int b_is_nk, flo
         tune.b_sbo = b_sbo;
         cudeep_b200::gemm_tf32(A, B, b_is_nk != 0, C, M, N, K, bias, bias_per_row != 0, epilogue, tune,
                                as_stream(stream));
+    });
+}
+
+int cudeep_b200_matmul_f16(const void* A, const void* B, float* C, int M, int N, int K,
+                           cudeep_b200_stream_t stream) {
+    return guarded([&] {
+        cudeep::kernels::launch_matmul_kernel_fp16(static_cast<const __half*>(A), static_cast<const __half*>(B), C,
+                                                   M, N, K, as_stream(stream));
+    });
+}
+
+int cudeep_b200_matmul_f16_tuned(const void* A, const void* B, float* C, int M, int N, int K, int ctas,
+                                 uint32_t b_lbo, uint32_t b_sbo, cudeep_b200_stream_t stream) {
+    return guarded([&] {
+        CB200_REQUIRE(A != nullptr && B != nullptr && C != nullptr, "gemm: null operand pointer");
+        cudeep_b200::gemm_f16(static_cast<const __half*>(A), static_cast<const __half*>(B), C, M, N, K, ctas,
+                              b_lbo, b_sbo, as_stream(stream));
     });
 }
 

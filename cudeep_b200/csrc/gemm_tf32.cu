@@ -12,6 +12,7 @@
 // mantissa bits, the same truncation the reference's mma.sync path applies
 // (matmul_kernel.cu:186-201).
 #include "gemm_tf32.h"
+#include "gemm_output.cuh"
 #include "umma_gemm.cuh"
 
 namespace cudeep_b200 {
@@ -19,14 +20,9 @@ namespace cudeep_b200 {
 namespace {
 
 template <int CTAS, int BN, bool B_MN_MAJOR, bool A_MN_MAJOR = false>
-struct GemmProblem {
+struct GemmProblem : GemmOutput {
     CUtensorMap map_a;     // K-major: dims {K, M}, box {32, 128};  MN-major (A stored [K, M]): as map_b
     CUtensorMap map_b;     // K-major: dims {K, N}, box {32, BN/CTAS};  MN-major: dims {N, K}, box {32, 32}
-    CUtensorMap map_c;     // output for bulk tensor stores: dims {N, M}, box {32, 32}, 128-byte swizzle
-    float* c;
-    long long ldc;
-    int m, n;
-    int vec_ok;            // rows of C are 16-byte aligned
     int b_chunked;         // MN-major B described as {32, K, N/32}: one load brings every column chunk
     int a_chunked;         // the same for an MN-major A
 
@@ -43,45 +39,6 @@ struct GemmProblem {
         ptx::prefetch_tensormap(&map_a);
         ptx::prefetch_tensormap(&map_b);
         ptx::prefetch_tensormap(&map_c);
-    }
-    __device__ __forceinline__ const CUtensorMap* out_map() const { return &map_c; }
-    __device__ __forceinline__ void out_coords(const Tile& t, int row_in_cta, int c0, int& x, int& y) const {
-        x = t.n0 + c0;
-        y = t.m0 + row_in_cta;
-    }
-    // Bias and activation of 32 columns of one row, in registers (the store clips what lies
-    // outside C, so only the bias reads are bounded here).
-    __device__ __forceinline__ void finish(const Tile& t, int row_in_cta, int c0, float (&v)[32],
-                                           const UmmaEpilogueArgs& epi) const {
-        const int row = t.m0 + row_in_cta;
-        const int col = t.n0 + c0;
-        if (epi.bias != nullptr && row < m && col < n) {
-            if (epi.bias_per_row) {
-                const float b = __ldg(epi.bias + row);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] += b;
-            } else if (col + 32 <= n) {
-                const float4* b4 = reinterpret_cast<const float4*>(epi.bias + col);
-                if ((reinterpret_cast<uintptr_t>(b4) & 15u) == 0) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float4 b = __ldg(b4 + j);
-                        v[4 * j] += b.x;
-                        v[4 * j + 1] += b.y;
-                        v[4 * j + 2] += b.z;
-                        v[4 * j + 3] += b.w;
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] += __ldg(epi.bias + col + j);
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (col + j < n) v[j] += __ldg(epi.bias + col + j);
-            }
-        }
-        apply_activation(v, epi.act);
     }
     __device__ __forceinline__ Tile decode(int tm, int tn, uint32_t cta_rank) const {
         Tile t;
@@ -140,52 +97,6 @@ struct GemmProblem {
             } else {
                 ptx::tma_load_2d_pair(b_smem, &map_b, bar, k0, t.nb0);
             }
-        }
-    }
-    __device__ __forceinline__ void store(const Tile& t, int row_in_cta, int c0, float (&v)[32],
-                                          const UmmaEpilogueArgs& epi, int mode) const {
-        const int row = t.m0 + row_in_cta;
-        const int col = t.n0 + c0;
-        if (row >= m || col >= n) return;
-        if (epi.bias != nullptr && mode != 2) {      // a split tile gets its bias once
-            if (epi.bias_per_row) {
-                const float b = __ldg(epi.bias + row);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] += b;
-            } else if (col + 32 <= n) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] += __ldg(epi.bias + col + j);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (col + j < n) v[j] += __ldg(epi.bias + col + j);
-            }
-        }
-        float* dst = c + static_cast<long long>(row) * ldc + col;
-        if (mode != 0) {
-            // Partial sum of a split tile: C was zeroed before the launch and every K range
-            // adds its share.  With two ranges the result does not depend on their order
-            // (0 + p + q == 0 + q + p exactly); more ranges are summed in arrival order.
-            if (vec_ok && col + 32 <= n) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                    atomicAdd(reinterpret_cast<float4*>(dst + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (col + j < n) atomicAdd(dst + j, v[j]);
-            }
-            return;
-        }
-        apply_activation(v, epi.act);
-        if (vec_ok && col + 32 <= n) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                if (col + j < n) dst[j] = v[j];
         }
     }
 };
@@ -262,21 +173,7 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
         const uint32_t box[2] = {UMMA_BK, uint32_t(Cfg::BN_CTA)};
         encode_tensor_map(&prob.map_b, b, 2, dims, strides, box, TmaSwizzle::B128);
     }
-    prob.c = c;
-    prob.ldc = n;
-    prob.m = m;
-    prob.n = n;
-    prob.vec_ok = ((n % 4) == 0) && ((reinterpret_cast<uintptr_t>(c) & 15u) == 0);
-    const bool tma_store = prob.vec_ok && tune.tma_store >= 0;
-    {
-        // Rows of C must be 16-byte multiples for a tensor map; otherwise the map describes a
-        // dummy 32 x 32 view and is never used.
-        const uint64_t dims[2] = {uint64_t(tma_store ? n : 32), uint64_t(tma_store ? m : 32)};
-        const uint64_t strides[1] = {uint64_t(tma_store ? n : 32) * 4};
-        const uint32_t box[2] = {32, 32};
-        if (tma_store) encode_tensor_map(&prob.map_c, c, 2, dims, strides, box, TmaSwizzle::B128);
-        else prob.map_c = prob.map_a;
-    }
+    const bool tma_store = prob.set_output(c, m, n, tune.tma_store >= 0);
 
     UmmaSchedule sched;
     sched.tiles_m = (m + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS);

@@ -2,6 +2,7 @@
 // tcgen05 TF32 GEMM and the strict SIMT GEMMs.
 #include "cudeep/kernels/matmul.cuh"
 
+#include "gemm_f16.h"
 #include "gemm_simt.h"
 #include "gemm_tf32.h"
 #include "epilogue_math.cuh"
@@ -71,7 +72,12 @@ template void launch_matmul_tiled_kernel<double>(const double*, const double*, d
 void launch_matmul_kernel_fp16(const __half* A, const __half* B, float* C, int M, int N, int K,
                                cudaStream_t stream) {
     check_dims(A, B, C, M, N, K);
-    cudeep_b200::gemm_simt_half(A, B, C, M, N, K, stream);
+    // Tensor cores (FP16 products are exact, FP32 accumulation) for aligned shapes of at least a
+    // tile; the SIMT kernel otherwise.
+    if (cudeep_b200::gemm_f16_supported(A, B, M, N, K))
+        cudeep_b200::gemm_f16(A, B, C, M, N, K, 0, 0, 0, stream);
+    else
+        cudeep_b200::gemm_simt_half(A, B, C, M, N, K, stream);
 }
 
 void launch_matmul_fused_act(const float* A, const float* B, float* C, int M, int N, int K,

@@ -121,8 +121,9 @@ uint32_t read_device_status(bool clear) {
     return v;
 }
 
-void encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint64_t* dims,
-                       const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle) {
+namespace {
+void encode_map(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, uint32_t elem_bytes, int rank,
+                const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle) {
     CB200_REQUIRE(rank >= 1 && rank <= 5, "tensor map rank must be 1..5");
     CB200_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15u) == 0, "TMA base address must be 16-byte aligned");
     cuuint64_t gdim[5];
@@ -140,15 +141,25 @@ void encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint
         CB200_REQUIRE((strides_bytes[i] & 15u) == 0, "TMA strides must be multiples of 16 bytes");
     }
     if (swizzle != TmaSwizzle::None)
-        CB200_REQUIRE(box[0] * 4 == 128, "128-byte swizzle needs a 128-byte inner box");
+        CB200_REQUIRE(box[0] * elem_bytes == 128, "128-byte swizzle needs a 128-byte inner box");
     const CUtensorMapSwizzle sw = swizzle == TmaSwizzle::B128         ? CU_TENSOR_MAP_SWIZZLE_128B
                                   : swizzle == TmaSwizzle::B128Atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
                                                                       : CU_TENSOR_MAP_SWIZZLE_NONE;
-    CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, static_cast<cuuint32_t>(rank),
-                             const_cast<float*>(base), gdim, gstride, gbox, estride,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+    CUresult r = encode_fn()(map, dtype, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim, gstride,
+                             gbox, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     CB200_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+}
+}  // namespace
+
+void encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint64_t* dims,
+                       const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle) {
+    encode_map(map, base, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, rank, dims, strides_bytes, box, swizzle);
+}
+
+void encode_tensor_map_f16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle) {
+    encode_map(map, base, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, rank, dims, strides_bytes, box, swizzle);
 }
 
 }  // namespace cudeep_b200

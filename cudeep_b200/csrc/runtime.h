@@ -64,6 +64,9 @@ enum class TmaSwizzle {
 // dims[i+1].  Out-of-range elements read as zero.  With a swizzle the inner
 // box must span exactly 128 bytes (narrower boxes are not packed densely in
 // shared memory: measured, a {8, 4, 128} box did not land as 128-byte rows).
+// The same for 2-byte (FP16) elements: dims, boxes and coordinates count elements.
+void encode_tensor_map_f16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle);
 void encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint64_t* dims,
                        const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle);
 

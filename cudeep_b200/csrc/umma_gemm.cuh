@@ -142,7 +142,14 @@ struct UmmaConfig {
 //   __device__ const CUtensorMap* out_map() const;      C as {N, M}, box {32, 32}, 128-byte swizzle
 //   __device__ void out_coords(tile, row_in_cta, col0, int& x, int& y) const;
 constexpr uint32_t UMMA_STORE_STAGING_BYTES = 4 * 2 * 4096;     // 4 epilogue warps x 2 blocks of 32 x 32 floats
-template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, class Problem, bool A_MN_MAJOR = false>
+// KIND: 0 = FP32 operands multiplied as TF32 (K block of 32 elements), 1 = FP16 operands (K block of
+// 64 elements); a K block is 128 bytes per operand row either way, so stages, barriers and the
+// epilogue do not change.
+constexpr int UMMA_KIND_TF32 = 0;
+constexpr int UMMA_KIND_F16 = 1;
+
+template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, class Problem, bool A_MN_MAJOR = false,
+          int KIND = UMMA_KIND_TF32>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
 umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                  const UmmaEpilogueArgs epi) {
@@ -278,8 +285,10 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
             // addresses in the uniform datapath the tensor-core instructions read from); one
             // elected lane issues the MMAs and commits.
             const uint32_t idesc =
-                ptx::idesc_tf32(UMMA_BM * CTAS, sched.umma_n, /*a_mn=*/A_MN_MAJOR ? 1 : 0,
-                                /*b_mn=*/B_MN_MAJOR ? 1 : 0);
+                KIND == UMMA_KIND_F16
+                    ? ptx::idesc_f16(UMMA_BM * CTAS, sched.umma_n, A_MN_MAJOR ? 1 : 0, B_MN_MAJOR ? 1 : 0)
+                    : ptx::idesc_tf32(UMMA_BM * CTAS, sched.umma_n, /*a_mn=*/A_MN_MAJOR ? 1 : 0,
+                                      /*b_mn=*/B_MN_MAJOR ? 1 : 0);
             // K-major operand: rows are 128 B, 8-row swizzle atoms 1024 B apart.
             // An MN-major A (a transposed left operand, stored [K, M]) uses the same layout as
             // an MN-major B: 32-row chunks 4096 B apart, 4-row K groups 512 B apart.
@@ -291,11 +300,15 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
             // K rows.  Each TMA box is 32 columns x 32 K rows (4096 B): column chunks
             // are 4096 B apart (LBO), 4-row K groups 512 B apart (SBO), and one MMA
             // (K = 8) advances the start address by 8 rows = 1024 B.
-            const uint32_t b_lbo = sched.b_lbo ? sched.b_lbo : (B_MN_MAJOR ? 4096u : 16u);
-            const uint32_t b_sbo = sched.b_sbo ? sched.b_sbo : (B_MN_MAJOR ? 512u : 1024u);
+            // MN-major 16-bit B: the plain 128-byte swizzle; TMA boxes of 64 columns x 64 K rows
+            // (8192 B): column chunks 8192 B apart, 8-row K groups 1024 B apart, and one MMA
+            // (K = 16) advances by 16 rows = 2048 B.
+            constexpr bool b_mn16 = B_MN_MAJOR && KIND == UMMA_KIND_F16;
+            const uint32_t b_lbo = sched.b_lbo ? sched.b_lbo : (b_mn16 ? 8192u : B_MN_MAJOR ? 4096u : 16u);
+            const uint32_t b_sbo = sched.b_sbo ? sched.b_sbo : (b_mn16 ? 1024u : B_MN_MAJOR ? 512u : 1024u);
             const uint64_t b_base = ptx::smem_desc(
-                b_lbo, b_sbo, B_MN_MAJOR ? ptx::SMEM_LAYOUT_SW128_ATOM32 : ptx::SMEM_LAYOUT_SW128);
-            constexpr uint32_t b_kstep = B_MN_MAJOR ? 1024u : UMMA_K * 4u;
+                b_lbo, b_sbo, (B_MN_MAJOR && !b_mn16) ? ptx::SMEM_LAYOUT_SW128_ATOM32 : ptx::SMEM_LAYOUT_SW128);
+            constexpr uint32_t b_kstep = b_mn16 ? 2048u : B_MN_MAJOR ? 1024u : UMMA_K * 4u;
             const uint64_t a_desc0 = ptx::smem_desc_at(a_base, smem_base);
             const uint64_t b_desc0 = ptx::smem_desc_at(b_base, smem_base + Cfg::A_BYTES);
 
@@ -339,7 +352,10 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                             for (int kk = 0; kk < UMMA_BK / UMMA_K; ++kk) {
                                 const uint64_t a_desc = a_stage + ((j * Cfg::ATOM_BYTES + kk * a_kstep) >> 4);
                                 const uint64_t b_desc = b_stage + ((j * Cfg::ATOM_BYTES + kk * b_kstep) >> 4);
-                                ptx::umma_tf32<CTAS>(d_tmem, a_desc, b_desc, idesc, (ks | j | kk) != 0);
+                                if constexpr (KIND == UMMA_KIND_F16)
+                                    ptx::umma_f16<CTAS>(d_tmem, a_desc, b_desc, idesc, (ks | j | kk) != 0);
+                                else
+                                    ptx::umma_tf32<CTAS>(d_tmem, a_desc, b_desc, idesc, (ks | j | kk) != 0);
                             }
                         }
                     }

@@ -95,6 +95,16 @@ int cudeep_b200_matmul_nt_f32(const float* A, const float* B, float* C, int M, i
 int cudeep_b200_matmul_tn_f32(const float* A, const float* B, float* C, int M, int N, int K,
                               cudeep_b200_stream_t stream);
 
+/* C[M,N] (float) = A[M,K] * B[K,N] with IEEE half operands (passed as const void*) and FP32
+ * accumulation: launch_matmul_kernel_fp16 (matmul.cuh:27-30).  Tensor cores (kind::f16) when A and
+ * B are 16-byte aligned, K and N are multiples of 8 and M, N, K >= 64; a SIMT kernel otherwise. */
+int cudeep_b200_matmul_f16(const void* A, const void* B, float* C, int M, int N, int K,
+                           cudeep_b200_stream_t stream);
+/* The same on the tensor-core path only (fails instead of falling back), for benchmarks and
+ * bring-up: ctas 0 | 1 | 2; b_lbo / b_sbo as in cudeep_b200_gemm_tf32_tuned (bits 0-15 only). */
+int cudeep_b200_matmul_f16_tuned(const void* A, const void* B, float* C, int M, int N, int K, int ctas,
+                                 uint32_t b_lbo, uint32_t b_sbo, cudeep_b200_stream_t stream);
+
 /* The TF32 tensor-core GEMM with explicit tile choices, for benchmarks and
  * bring-up.  b_is_nk: 0 = B is [K,N], 1 = B is [N,K].  bias: NULL, N values, or
  * M values when bias_per_row != 0.  ctas (1|2), bn (64|128|256), raster_group,

@@ -97,6 +97,20 @@ class DeviceOps:
         assert self.sync_status() == 0
         return tc.cpu().numpy()
 
+    def matmul_f16(self, a, b, ctas=None):
+        """a, b: float16 arrays; returns float32.  ctas None: the launcher's own choice of path."""
+        ta, tb = self.to_dev(a), self.to_dev(b)
+        m, k = a.shape
+        n = b.shape[1]
+        tc = self.empty((m, n))
+        if ctas is None:
+            self.check(self.lib.cudeep_b200_matmul_f16(self.ptr(ta), self.ptr(tb), self.ptr(tc), m, n, k, None))
+        else:
+            self.check(self.lib.cudeep_b200_matmul_f16_tuned(self.ptr(ta), self.ptr(tb), self.ptr(tc), m, n, k,
+                                                             ctas, 0, 0, None))
+        assert self.sync_status() == 0
+        return tc.cpu().numpy()
+
     def linear(self, x, w, bias=None, act=0):
         tx, tw = self.to_dev(x), self.to_dev(w)
         tb = self.to_dev(bias) if bias is not None else None

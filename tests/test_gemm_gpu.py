@@ -312,6 +312,38 @@ def test_tf32_linearity(dev, oracle):
     assert np.array_equal(dev.matmul(2 * a, b), 2 * dev.matmul(a, b))
 
 
+# ---- FP16 operands, FP32 result (launch_matmul_kernel_fp16, matmul.cuh:27-30) -----------------------
+
+@pytest.mark.parametrize("m,n,k,ctas", [
+    (256, 256, 64, 1), (256, 256, 64, 2),          # one K block
+    (640, 768, 416, 1), (640, 768, 416, 2),        # several tiles, 6.5 K blocks
+    (300, 520, 1000, 2),                           # ragged M, N a multiple of 8 but not of 64: B loaded chunk by chunk
+    (130, 72, 64, 1),                              # barely more than one tile row
+    (2048, 2048, 2048, 2),
+])
+def test_fp16_tensor_core_gemm(dev, oracle, m, n, k, ctas):
+    """FP16 x FP16 products are exact in FP32, so only the FP32 accumulation separates the result from
+    the float64 product: the strict-FP32 bar applies, scaled like the accumulation error with K."""
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k)).astype(np.float16)
+    b = rng.standard_normal((k, n)).astype(np.float16)
+    got = dev.matmul_f16(a, b, ctas=ctas)
+    want = oracle.gemm(a.astype(np.float32), b.astype(np.float32))
+    assert not np.isnan(got).any()
+    assert oracle.rel_frobenius(got, want) <= FP32_TOL * max(1.0, k / 4096.0)
+
+
+@pytest.mark.parametrize("m,n,k", [(2, 2, 3), (33, 17, 20), (64, 64, 60), (100, 260, 36), (512, 512, 512)])
+def test_fp16_launcher_any_shape(dev, oracle, m, n, k):
+    """The launcher takes every shape: tensor cores where aligned and large enough, SIMT otherwise."""
+    rng = np.random.default_rng(m * 3 + n * 5 + k)
+    a = rng.standard_normal((m, k)).astype(np.float16)
+    b = rng.standard_normal((k, n)).astype(np.float16)
+    got = dev.matmul_f16(a, b)
+    want = oracle.gemm(a.astype(np.float32), b.astype(np.float32))
+    assert oracle.rel_frobenius(got, want) <= FP32_TOL
+
+
 # ---- transposed operands (the products of matmul's backward pass) ---------------------------------
 
 @pytest.mark.parametrize("m,n,k", [
