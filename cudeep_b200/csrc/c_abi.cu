@@ -149,7 +149,8 @@ int cudeep_b200_gemm_tf32_tuned(const float* A, const float* B, int b_is_nk, flo
         tune.split_k = static_cast<int>(b_lbo >> 16) & 0xff;      // packed: see cudeep_b200.h
         tune.cluster_split = static_cast<int>(b_lbo >> 24) & 0xf;
         tune.tma_store = ((b_lbo >> 28) & 1u) ? -1 : 0;
-        tune.debug |= ((b_lbo >> 29) & 7u) << 4;
+        tune.debug |= ((b_lbo >> 29) & 3u) << 4;
+        tune.ring_staging = ((b_lbo >> 31) & 1u) ? -1 : 0;
         tune.b_lbo = b_lbo & 0xffffu;
         tune.b_sbo = b_sbo;
         cudeep_b200::gemm_tf32(A, B, b_is_nk != 0, C, M, N, K, bias, bias_per_row != 0, epilogue, tune,

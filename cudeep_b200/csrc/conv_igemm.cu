@@ -281,6 +281,7 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     sched.cluster_split = 1;
     sched.exchange_bytes = 0;
     sched.tma_store = 0;
+    sched.ring_staging = 0;
     sched.debug = 0;
 
     const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;

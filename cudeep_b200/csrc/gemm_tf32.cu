@@ -125,6 +125,9 @@ __global__ void zero_tiles_kernel(float* __restrict__ c, long long ldc, int m, i
     }
 }
 
+// Whether a CTA's last tile stages its results in the idle stage ring (see umma_gemm.cuh).
+constexpr bool kRingStagingDefault = false;
+
 template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, bool A_MN_MAJOR = false>
 void launch_variant(const float* a, const float* b, float* c, int m, int n, int k,
                     const UmmaEpilogueArgs& epi, const GemmTuning& tune, cudaStream_t stream) {
@@ -188,6 +191,7 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     sched.tx_bytes = Cfg::TX_BYTES;
     sched.stages = (tune.stages > 0 && tune.stages < Cfg::STAGES) ? tune.stages : Cfg::STAGES;
     sched.tma_store = tma_store ? 1 : 0;
+    sched.ring_staging = 0;      // set below, once the number of stages is known
     const uint32_t staging_bytes = tma_store ? UMMA_STORE_STAGING_BYTES : 0u;
     sched.debug = tune.debug;
 
@@ -253,6 +257,8 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     // Dynamic shared memory: [stages][exchange buffer][store staging], after up to 1 KB of alignment.
     const int fit_stages = int((Cfg::SMEM_BUDGET - exchange_bytes - staging_bytes) / Cfg::STAGE_BYTES);
     if (sched.stages > fit_stages) sched.stages = fit_stages;
+    const bool ring_wanted = kRingStagingDefault != (tune.ring_staging < 0);      // the tuning flag flips the default
+    sched.ring_staging = (uint32_t(sched.stages) * Cfg::STAGE_BYTES >= 131072u && ring_wanted) ? 1 : 0;
     const uint32_t smem_bytes = uint32_t(sched.stages) * Cfg::STAGE_BYTES + exchange_bytes + staging_bytes + 1024;
 
     auto kernel = umma_tf32_kernel<CTAS, BN, B_MN_MAJOR, KATOMS, Prob, A_MN_MAJOR>;

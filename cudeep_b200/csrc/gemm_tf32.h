@@ -18,6 +18,7 @@ struct GemmTuning {
     int katoms = 0;          // 32-wide K blocks per pipeline stage: 1 or 2
     int cluster_split = 0;   // K ranges per tile reduced inside a thread-block cluster (2, 4, 8):
                              // 0 = choose, 1 = never
+    int ring_staging = 0;    // -1: flip the default of staging a CTA's last tile in the idle stage ring
     int tma_store = 0;       // -1: write C from registers even where bulk tensor stores are possible
     int b_chunked = 0;       // -1: load B[K,N] as separate 32-column boxes even when N % 32 == 0
     uint32_t debug = 0;      // diagnostics, see UmmaSchedule::debug

@@ -75,6 +75,7 @@ struct UmmaSchedule {
     // stage each 32 x 32 block of results in shared memory, behind the stages and the exchange
     // buffer, and write it with one bulk tensor store: 8 KB (two blocks) per epilogue warp.
     int tma_store;
+    int ring_staging;      // the stages in use span at least 128 KB: the last tile's epilogue may stage in them
     // Diagnostics for performance bring-up (results are then meaningless):
     //   bit 0: after the ring has been filled once the producer stops loading and only
     //          signals the stages, so the MMA side runs without memory traffic;
@@ -492,8 +493,16 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 // Two 32-column chunks per round: both staging blocks are filled, one proxy fence
                 // covers them, two bulk stores go out as one group, and the accumulator loads of
                 // the next round are in flight while this round is fenced and stored.
+                //
+                // The CTA's last tile is the one whose epilogue nothing hides.  By then the stage
+                // ring is idle (every load was consumed by an MMA that has completed, and the
+                // producer has nothing left to issue), so each warp stages all its chunks in a
+                // 32 KB slice of the ring, a block per chunk, and never waits for a store to
+                // release a block.
                 if constexpr (Problem::kTmaStore) {
                     const bool dbg_nold = (sched.debug & 0x20u) != 0, dbg_nost = (sched.debug & 0x10u) != 0;
+                    const bool in_ring = sched.ring_staging != 0 && (u + unit_stride >= num_units);
+                    uint32_t block0 = in_ring ? smem_base + quarter * 32768u : staging;
                     if (n_cols > 0 && !dbg_nold) ptx::tmem_ld_32x32(t_row, r0);
                     if (n_cols > 32 && !dbg_nold) ptx::tmem_ld_32x32(t_row + 32, r1);
 #pragma unroll 1
@@ -504,9 +513,11 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
                         prob.finish(tile, row_in_cta, c, v, epi);
-                        if (lane == 0) ptx::bulk_wait_group_read<0>();      // last round's stores have read their blocks
-                        __syncwarp();
-                        const uint32_t row_smem = staging + lane * 128u;
+                        if (!in_ring) {
+                            if (lane == 0) ptx::bulk_wait_group_read<0>();  // last round's stores have read their blocks
+                            __syncwarp();
+                        }
+                        const uint32_t row_smem = block0 + lane * 128u;
 #pragma unroll
                         for (uint32_t q = 0; q < 8; ++q)      // 128-byte swizzle: unit q of row r at q ^ (r & 7)
                             ptx::st_shared_v4(row_smem + ((q ^ (lane & 7u)) << 4), v[4 * q], v[4 * q + 1],
@@ -527,10 +538,11 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                         if (lane == 0 && !dbg_nost) {
                             int x, y;
                             prob.out_coords(tile, int(quarter) * 32, c, x, y);
-                            ptx::tma_store_2d(prob.out_map(), staging, x, y);
-                            if (two) ptx::tma_store_2d(prob.out_map(), staging + 4096u, x + 32, y);
+                            ptx::tma_store_2d(prob.out_map(), block0, x, y);
+                            if (two) ptx::tma_store_2d(prob.out_map(), block0 + 4096u, x + 32, y);
                             ptx::bulk_commit_group();
                         }
+                        if (in_ring) block0 += 8192u;
                     }
                 }
             } else if (ksplit == 1) {

@@ -122,7 +122,8 @@ int cudeep_b200_matmul_f16_tuned(const void* A, const void* B, float* C, int M, 
  * distributed shared memory (0 = choose, 1 = never, else 2, 4 or 8); bit 28 of
  * b_lbo writes C from registers instead of through bulk tensor stores; bits
  * 29-30 of b_lbo are two more diagnostics (29: stage the results but issue no
- * bulk store, 30: skip the accumulator loads).  Fails
+ * bulk store, 30: skip the accumulator loads); bit 31 of b_lbo flips whether a
+ * CTA's last tile stages its results in the idle stage ring.  Fails
  * instead of falling back when the tensor-core path cannot take the problem. */
 int cudeep_b200_gemm_tf32_tuned(const float* A, const float* B, int b_is_nk, float* C, int M, int N,
                                 int K, const float* bias, int bias_per_row, int epilogue, int ctas,

@@ -83,7 +83,8 @@ class DeviceOps:
         return tc.cpu().numpy()
 
     def gemm_tuned(self, a, b, b_is_nk, bias=None, bias_per_row=False, act=0, ctas=0, bn=0, raster=0,
-                   max_ctas=0, katoms=0, unchunked=False, split_k=0, cluster_split=0, register_store=False):
+                   max_ctas=0, katoms=0, unchunked=False, split_k=0, cluster_split=0, register_store=False,
+                   flip_ring_staging=False):
         ta, tb = self.to_dev(a), self.to_dev(b)
         m, k = a.shape
         n = b.shape[0] if b_is_nk else b.shape[1]
@@ -93,7 +94,8 @@ class DeviceOps:
             self.ptr(ta), self.ptr(tb), int(b_is_nk), self.ptr(tc), m, n, k, self.ptr(tbias),
             int(bias_per_row), act, ctas, bn, raster,
             max_ctas | (int(unchunked) << 28) | (katoms << 29),
-            (split_k << 16) | (cluster_split << 24) | (int(register_store) << 28), 0, None))
+            (split_k << 16) | (cluster_split << 24) | (int(register_store) << 28) | (int(flip_ring_staging) << 31),
+            0, None))
         assert self.sync_status() == 0
         return tc.cpu().numpy()
 

@@ -9,6 +9,8 @@
 #include "cudeep/stream.cuh"
 #include "cudeep/tensor.cuh"
 
+#include <cuda_fp16.h>
+
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -167,6 +169,66 @@ static void test_pool_and_events() {
     std::printf("[PASS] pool, stream, event\n");
 }
 
+static void test_stream_aware_pool() {
+    MemoryPool& pool = MemoryPool::instance();
+    pool.release_cached();
+    Stream s1, s2;
+    const size_t bytes = (4u << 20) + 512;                      // a size class of its own
+    void* p = pool.allocate(bytes, s1.get());
+    // A few milliseconds of work on s1, then the block is released behind it.
+    Tensor a = Tensor::randn({4096, 4096}, DType::Float32, 3);
+    a.set_stream(s1.get());
+    Tensor c1 = a.matmul(a), c2 = a.matmul(a), c3 = a.matmul(a), c4 = a.matmul(a);
+    pool.deallocate(p, s1.get());
+    void* same = pool.allocate(bytes, s1.get());
+    CHECK(same == p);                                           // same stream: reused at once
+    pool.deallocate(same, s1.get());
+    void* other = pool.allocate(bytes, s2.get());
+    if (cudaStreamQuery(s1.get()) == cudaErrorNotReady) CHECK(other != p);   // s1 still busy: a fresh block
+    cudaGetLastError();
+    s1.synchronize();
+    pool.deallocate(other, s2.get());
+    // A tensor may outlive the stream it worked on.
+    Tensor survivor;
+    {
+        Stream inner;
+        Tensor t = Tensor::ones({256, 256});
+        t.set_stream(inner.get());
+        survivor = t.matmul(t);
+    }
+    CHECK(std::fabs(host_of(survivor)[0] - 256.0f) < 1e-2f);
+    survivor = Tensor();                                        // storage released after its stream is gone
+    pool.release_cached();
+    std::printf("[PASS] stream-aware pool\n");
+}
+
+static void test_fp16_launcher() {
+    const int m = 256, n = 192, k = 128;
+    std::vector<__half> ha(m * k), hb(k * n);
+    std::vector<float> fa(m * k), fb(k * n);
+    for (int i = 0; i < m * k; ++i) { fa[i] = float((i * 7) % 13 - 6) / 8.0f; ha[i] = __float2half(fa[i]); }
+    for (int i = 0; i < k * n; ++i) { fb[i] = float((i * 5) % 11 - 5) / 4.0f; hb[i] = __float2half(fb[i]); }
+    __half* da = static_cast<__half*>(device_malloc(ha.size() * 2));
+    __half* db = static_cast<__half*>(device_malloc(hb.size() * 2));
+    float* dc = static_cast<float*>(device_malloc(size_t(m) * n * 4));
+    memcpy_h2d(da, ha.data(), ha.size() * 2);
+    memcpy_h2d(db, hb.data(), hb.size() * 2);
+    kernels::launch_matmul_kernel_fp16(da, db, dc, m, n, k);
+    std::vector<float> hc(size_t(m) * n);
+    memcpy_d2h(hc.data(), dc, hc.size() * 4);
+    for (int i : {0, 17, 255}) {
+        for (int j : {0, 63, 191}) {
+            double want = 0.0;
+            for (int q = 0; q < k; ++q) want += double(fa[i * k + q]) * double(fb[q * n + j]);
+            CHECK(std::fabs(hc[size_t(i) * n + j] - want) <= 1e-4 * (1.0 + std::fabs(want)));   // the inputs are exact in FP16
+        }
+    }
+    device_free(da);
+    device_free(db);
+    device_free(dc);
+    std::printf("[PASS] fp16 launcher\n");
+}
+
 int main() {
     try {
         test_tensor_basics();
@@ -174,6 +236,8 @@ int main() {
         test_tf32_product_against_host();
         test_conv_launcher();
         test_pool_and_events();
+        test_stream_aware_pool();
+        test_fp16_launcher();
     } catch (const std::exception& e) {
         std::printf("FAILED with exception: %s\n", e.what());
         return 1;

@@ -285,6 +285,22 @@ def test_tf32_bulk_store_matches_register_store(dev, oracle, m, n, k, b_is_nk):
     check_tf32(oracle, bulk, a, b, k, b_is_nk=b_is_nk, bias=bias, act=3)
 
 
+@pytest.mark.parametrize("ctas,bn,max_ctas", [(2, 256, 0), (1, 256, 0), (1, 64, 0), (2, 256, 4), (1, 128, 6)])
+def test_tf32_last_tile_staged_in_the_stage_ring(dev, oracle, ctas, bn, max_ctas):
+    """A CTA's last tile may stage its results in the idle operand ring instead of the two small
+    staging blocks; with few CTAs (max_ctas) the earlier tiles of each CTA take the normal path.
+    Both ways must give the same bits."""
+    rng = np.random.default_rng(ctas * 10 + bn + max_ctas)
+    m, n, k = 900, 1100, 288
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    bias = rng.standard_normal(n, dtype=np.float32)
+    ring = dev.gemm_tuned(a, b, False, bias=bias, act=1, ctas=ctas, bn=bn, max_ctas=max_ctas)
+    plain = dev.gemm_tuned(a, b, False, bias=bias, act=1, ctas=ctas, bn=bn, max_ctas=max_ctas, flip_ring_staging=True)
+    assert np.array_equal(ring, plain)
+    check_tf32(oracle, ring, a, b, k, bias=bias, act=1)
+
+
 def test_tf32_store_does_not_touch_memory_behind_c(dev, lib, oracle):
     """Tiles hang over the edge of C (M = 130, N = 36): rows behind the last one stay as they were."""
     rng = np.random.default_rng(2)
