@@ -232,7 +232,7 @@ void launch_wgrad(const float* dy, const float* xt, float* part, const ConvShape
     sched.debug = 0;
     const int fit_stages = int((Cfg::SMEM_BUDGET - UMMA_STORE_STAGING_BYTES) / Cfg::STAGE_BYTES);
     sched.stages = fit_stages < Cfg::STAGES ? fit_stages : Cfg::STAGES;
-    sched.ring_staging = 0;
+    sched.ring_staging = uint32_t(sched.stages) * Cfg::STAGE_BYTES >= 131072u ? 1 : 0;
     const uint32_t smem_bytes = uint32_t(sched.stages) * Cfg::STAGE_BYTES + UMMA_STORE_STAGING_BYTES + 1024;
 
     const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;

@@ -117,7 +117,7 @@ void launch_f16(const __half* a, const __half* b, float* c, int m, int n, int k,
     const uint32_t staging_bytes = tma_store ? UMMA_STORE_STAGING_BYTES : 0u;
     const int fit_stages = int((Cfg::SMEM_BUDGET - staging_bytes) / Cfg::STAGE_BYTES);
     sched.stages = fit_stages < Cfg::STAGES ? fit_stages : Cfg::STAGES;
-    sched.ring_staging = 0;
+    sched.ring_staging = uint32_t(sched.stages) * Cfg::STAGE_BYTES >= 131072u ? 1 : 0;
     const uint32_t smem_bytes = uint32_t(sched.stages) * Cfg::STAGE_BYTES + staging_bytes + 1024;
 
     const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;

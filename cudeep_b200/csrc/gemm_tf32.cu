@@ -126,7 +126,7 @@ __global__ void zero_tiles_kernel(float* __restrict__ c, long long ldc, int m, i
 }
 
 // Whether a CTA's last tile stages its results in the idle stage ring (see umma_gemm.cuh).
-constexpr bool kRingStagingDefault = false;
+constexpr bool kRingStagingDefault = true;
 
 template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, bool A_MN_MAJOR = false>
 void launch_variant(const float* a, const float* b, float* c, int m, int n, int k,

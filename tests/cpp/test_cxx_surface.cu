@@ -196,8 +196,17 @@ static void test_stream_aware_pool() {
         t.set_stream(inner.get());
         survivor = t.matmul(t);
     }
+    survivor.set_stream(nullptr);                               // its stream is gone: further work goes elsewhere
     CHECK(std::fabs(host_of(survivor)[0] - 256.0f) < 1e-2f);
-    survivor = Tensor();                                        // storage released after its stream is gone
+    survivor = Tensor();
+    Tensor orphan;
+    {
+        Stream inner;
+        Tensor t = Tensor::ones({128, 128});
+        t.set_stream(inner.get());
+        orphan = t.matmul(t);
+    }
+    orphan = Tensor();                                          // storage released on a stream that no longer exists
     pool.release_cached();
     std::printf("[PASS] stream-aware pool\n");
 }
@@ -230,6 +239,7 @@ static void test_fp16_launcher() {
 }
 
 int main() {
+    std::setvbuf(stdout, nullptr, _IONBF, 0);
     try {
         test_tensor_basics();
         test_tensor_matmul();
