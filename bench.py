@@ -38,6 +38,9 @@ sys.path.insert(0, str(ROOT))
 SIZE = 8192
 METRIC = "TF32 GEMM TFLOP/s at 8192^3"
 FALLBACK_BF16_TFLOPS = 1590.0       # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+FALLBACK_BF16_SUSTAINED_TFLOPS = 1400.0
+# A timed region longer than this runs under the power cap: its roofline uses the sustained peak.
+SUSTAINED_REGION_MS = 100.0
 NOMINAL_TF32_TFLOPS = 1125.0        # half the nominal dense bf16 rate of a B200
 
 # DRAM bytes one 8192^3 launch moves (dram__bytes_read.sum + dram__bytes_write.sum from the
@@ -133,10 +136,10 @@ def measured_peaks():
     if path.exists():
         try:
             d = json.loads(path.read_text())
-            return float(d["bf16_tflops"]), "measured"
+            return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
         except Exception:
             pass
-    return FALLBACK_BF16_TFLOPS, "fallback"
+    return FALLBACK_BF16_TFLOPS, FALLBACK_BF16_SUSTAINED_TFLOPS, "fallback"
 
 
 def dist_setup(n_gpus: int):
@@ -298,9 +301,11 @@ def run_ours(args):
         dist.destroy_process_group()
     if rank != 0:
         return
-    bf16_peak, peak_kind = measured_peaks()
+    bf16_burst, bf16_sustained, peak_kind = measured_peaks()
     kernel_ms = float(np.mean(per_launch))
     achieved = 2.0 * SIZE ** 3 / (kernel_ms * 1e-3) / 1e12
+    long_region = seconds * 1e3 >= SUSTAINED_REGION_MS
+    bf16_peak = bf16_sustained if long_region else bf16_burst
     peak = bf16_peak / 2.0
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -319,8 +324,10 @@ def run_ours(args):
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak,
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
-                     "peak_source": f"{peak_kind} dense bf16 cuBLAS burst ({bf16_peak} TFLOP/s) / 2: "
-                                    "TF32 issues at half the bf16 rate",
+                     "peak_source": f"{peak_kind} dense bf16 cuBLAS {'sustained' if long_region else 'burst'} "
+                                    f"({bf16_peak} TFLOP/s) / 2: TF32 issues at half the bf16 rate; the timed "
+                                    f"region lasted {seconds * 1e3:.0f} ms (sustained figure from {SUSTAINED_REGION_MS:.0f} ms on)",
+                     "frac_of_burst_peak": achieved / (bf16_burst / 2.0),
                      "kernel": "umma_tf32_kernel", "kernel_ms": kernel_ms},
     }
     if gather_info is not None:
