@@ -60,6 +60,8 @@ PROTOTYPES = {
     "cudeep_b200_event_elapsed_ms": (c_int, [c_void_p, c_void_p, POINTER(c_float)]),
     "cudeep_b200_device_info": (c_int, [POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int),
                                         POINTER(c_size_t)]),
+    "cudeep_b200_gemm_tf32_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int),
+                                           POINTER(c_int), POINTER(c_int), POINTER(c_double)]),
     "cudeep_b200_matmul_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "cudeep_b200_matmul_f16_tuned": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                              ctypes.c_uint32, ctypes.c_uint32, c_void_p]),

@@ -158,6 +158,18 @@ int cudeep_b200_gemm_tf32_tuned(const float* A, const float* B, int b_is_nk, flo
     });
 }
 
+int cudeep_b200_gemm_tf32_plan(int M, int N, int K, int epilogue, int num_sms, int* ctas, int* bn,
+                               int* cluster_split, int* katoms, double* estimate_us) {
+    return guarded([&] {
+        const cudeep_b200::GemmPlan plan = cudeep_b200::gemm_tf32_plan(M, N, K, epilogue, num_sms);
+        if (ctas) *ctas = plan.ctas;
+        if (bn) *bn = plan.bn;
+        if (cluster_split) *cluster_split = plan.cluster_split;
+        if (katoms) *katoms = plan.katoms;
+        if (estimate_us) *estimate_us = plan.estimate_us;
+    });
+}
+
 int cudeep_b200_matmul_f16(const void* A, const void* B, float* C, int M, int N, int K,
                            cudeep_b200_stream_t stream) {
     return guarded([&] {

@@ -409,6 +409,18 @@ void dispatch(const float* a, const float* b, float* c, int m, int n, int k,
 
 }  // namespace
 
+GemmPlan gemm_tf32_plan(int m, int n, int k, int act, int num_sms) {
+    CB200_REQUIRE(m > 0 && n > 0 && k > 0 && num_sms > 0, "gemm plan: extents and SM count must be positive");
+    const UmmaEpilogueArgs epi{nullptr, 0, act};
+    const GemmTuning tune;
+    const TilePick pick = pick_tile<false>(m, n, k, epi, tune, num_sms);
+    GemmPlan plan{pick.ctas, pick.bn, pick.cluster_split, default_katoms(pick.ctas, pick.bn, pick.cluster_split), 0.0};
+    for (const TileCost& t : kTileCosts)
+        if (t.ctas == pick.ctas && t.bn == pick.bn)
+            plan.estimate_us = estimate_us(t, pick.cluster_split, m, n, k, act == EPI_NONE, num_sms);
+    return plan;
+}
+
 bool gemm_tf32_supported(const float* a, const float* b, const float* c, int m, int n, int k,
                          bool b_is_nk) {
     if (m < 1 || n < 1 || k < 1) return false;

@@ -37,6 +37,15 @@ void gemm_tf32(const float* a, const float* b, bool b_is_nk, float* c, int m, in
                const float* bias, bool bias_per_row, int act, const GemmTuning& tune,
                cudaStream_t stream);
 
+// The tile shape the launcher would pick for a problem on a device with `num_sms` SMs (host
+// arithmetic only: no device is touched): CTAs per MMA, tile columns, K ranges per cluster,
+// K blocks per stage, and the estimated time in microseconds.
+struct GemmPlan {
+    int ctas, bn, cluster_split, katoms;
+    double estimate_us;
+};
+GemmPlan gemm_tf32_plan(int m, int n, int k, int act, int num_sms);
+
 // C[M,N] = A^T * B with A stored [K,M] and B stored [K,N] (both row-major): the weight-gradient
 // product dW = X^T dY of a Linear layer, and a^T @ grad of matmul's backward, without a transposed
 // copy of the left operand (reference python/cuDeep/tensor.py:430-443 makes that copy).

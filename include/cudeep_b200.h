@@ -95,6 +95,13 @@ int cudeep_b200_matmul_nt_f32(const float* A, const float* B, float* C, int M, i
 int cudeep_b200_matmul_tn_f32(const float* A, const float* B, float* C, int M, int N, int K,
                               cudeep_b200_stream_t stream);
 
+/* What the launcher would choose for C[M,N] = A[M,K] * B on a device with num_sms SMs: CTAs per
+ * MMA (1 | 2), tile columns, K ranges reduced inside a cluster (1 = none), K blocks per pipeline
+ * stage, and its time estimate in microseconds.  Host arithmetic only: works without a GPU.  No
+ * reference counterpart (the reference dispatches on cc and size thresholds, matmul_kernel.cu:1785-1841). */
+int cudeep_b200_gemm_tf32_plan(int M, int N, int K, int epilogue, int num_sms, int* ctas, int* bn,
+                               int* cluster_split, int* katoms, double* estimate_us);
+
 /* C[M,N] (float) = A[M,K] * B[K,N] with IEEE half operands (passed as const void*) and FP32
  * accumulation: launch_matmul_kernel_fp16 (matmul.cuh:27-30).  Tensor cores (kind::f16) when A and
  * B are 16-byte aligned, K and N are multiples of 8 and M, N, K >= 64; a SIMT kernel otherwise. */

@@ -104,3 +104,49 @@ def test_workload_generators_are_seeded_and_shaped():
     rows = w.c5_a_rows(2 * w.C5_BAND_ROWS, 2 * w.C5_BAND_ROWS, 64)
     assert np.array_equal(rows[w.C5_BAND_ROWS:], band)
     assert w.gemm_flops(2, 3, 4) == 48 and w.conv_flops(64, 256, 256, 56, 56, 3, 3) == pytest.approx(236.76e9, rel=1e-4)
+
+
+# ---- the launcher's tile choice (host arithmetic of cudeep_b200/csrc/gemm_tf32.cu) -----------------
+
+def _plan(lib, m, n, k, act=0, sms=148):
+    import ctypes
+    from cudeep_b200 import _lib
+    ctas, bn, split, katoms = (ctypes.c_int() for _ in range(4))
+    est = ctypes.c_double()
+    _lib.check(lib.cudeep_b200_gemm_tf32_plan(m, n, k, act, sms, ctypes.byref(ctas), ctypes.byref(bn),
+                                              ctypes.byref(split), ctypes.byref(katoms), ctypes.byref(est)))
+    return ctas.value, bn.value, split.value, katoms.value, est.value
+
+
+def test_plan_fills_the_machine_with_wide_pair_tiles(lib):
+    for shape in [(8192, 8192, 8192), (4096, 4096, 4096), (2048, 2048, 2048), (8192, 16384, 4096)]:
+        ctas, bn, split, katoms, est = _plan(lib, *shape)
+        assert (ctas, bn, split, katoms) == (2, 256, 1, 2), shape
+        assert est > 0.0
+
+
+def test_plan_narrows_tiles_for_small_problems(lib):
+    assert _plan(lib, 1024, 1024, 1024)[:3] == (1, 64, 1)       # 128 tiles of 128 x 64 on 148 SMs
+    assert _plan(lib, 256, 256, 256)[:3] == (1, 64, 1)
+    ctas, bn, split, _, _ = _plan(lib, 1536, 1536, 1536)
+    assert (ctas, bn, split) == (2, 128, 1)                     # 72 CTA pairs of 256 x 128
+
+
+def test_plan_splits_k_inside_a_cluster_for_few_tiles_and_long_k(lib):
+    for shape in [(512, 512, 4096), (128, 4096, 4096), (256, 1024, 8192), (1024, 1024, 4096)]:
+        ctas, bn, split, katoms, _ = _plan(lib, *shape)
+        assert split in (2, 4) and bn <= 128 and ctas * split <= 8, (shape, ctas, bn, split)
+    # the clusters of one launch must fit the machine at once
+    ctas, bn, split, _, _ = _plan(lib, 1024, 1024, 4096)
+    tiles = -(-1024 // (128 * ctas)) * -(-1024 // bn)
+    assert tiles * split * ctas <= 148
+
+
+def test_plan_follows_the_sm_count_and_rejects_nonsense(lib):
+    from cudeep_b200 import _lib
+    few = _plan(lib, 1024, 1024, 1024, sms=16)
+    many = _plan(lib, 1024, 1024, 1024, sms=148)
+    assert few[1] > many[1]                                     # 16 SMs are full with wide tiles already
+    assert lib.cudeep_b200_gemm_tf32_plan(0, 8, 8, 0, 148, None, None, None, None, None) != 0
+    assert "positive" in lib.cudeep_b200_last_error().decode()
+    assert _plan(lib, 4096, 4096, 4096, act=2)[:2] == (2, 256)  # an activation rules out the split last wave only
