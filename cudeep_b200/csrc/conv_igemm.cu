@@ -261,28 +261,14 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     prob.vec_ok = (prob.contig && ((plan.box_h * ow) % 4 == 0) && ((oh * ow) % 4 == 0) &&
                    ((reinterpret_cast<uintptr_t>(out) & 15u) == 0)) ? 1 : 0;
 
-    UmmaSchedule sched;
-    sched.tiles_m = (s.out_c + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS);
-    sched.tiles_n = s.batch * prob.tiles_h * prob.tiles_w;
-    sched.k_blocks = taps * prob.c_blocks;
+    const int umma_n = plan.box_w * plan.box_h;
+    UmmaSchedule sched = whole_tile_schedule(
+        (s.out_c + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS), s.batch * prob.tiles_h * prob.tiles_w,
+        taps * prob.c_blocks, umma_n, (Cfg::A_BYTES + uint32_t(umma_n / CTAS) * UMMA_BK * 4) * CTAS * KATOMS,
+        Cfg::STAGES, dev.status_word);
     // Consecutive tiles walk the output-channel tiles of one pixel block, so
     // concurrent CTAs read the same input pixels from L2.
     sched.raster_group = sched.tiles_m;
-    sched.status = dev.status_word;
-    sched.wait_limit_ns = 2000000000ull;
-    sched.b_lbo = 0;
-    sched.b_sbo = 0;
-    sched.umma_n = plan.box_w * plan.box_h;
-    sched.tx_bytes = (Cfg::A_BYTES + uint32_t(sched.umma_n / CTAS) * UMMA_BK * 4) * CTAS * KATOMS;
-    sched.stages = Cfg::STAGES;
-    sched.n_whole = sched.tiles_m * sched.tiles_n;
-    sched.split = 1;
-    sched.kb_per_split = sched.k_blocks;
-    sched.cluster_split = 1;
-    sched.exchange_bytes = 0;
-    sched.tma_store = 0;
-    sched.ring_staging = 0;
-    sched.debug = 0;
 
     const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;
     CB200_REQUIRE(num_tiles < (1LL << 30), "conv2d: too many tiles");
@@ -291,22 +277,8 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     if (groups > num_tiles) groups = num_tiles;
 
     auto kernel = umma_tf32_kernel<CTAS, 256, false, KATOMS, Prob>;
-    ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), Cfg::SMEM_BYTES);
-
     UmmaEpilogueArgs epi{bias, 1, act};
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(unsigned(groups * CTAS), 1, 1);
-    cfg.blockDim = dim3(UMMA_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CTAS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    CB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, prob, sched, epi));
+    launch_umma(kernel, prob, sched, epi, groups, CTAS, Cfg::SMEM_BYTES, Cfg::SMEM_BYTES, stream);
 }
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }

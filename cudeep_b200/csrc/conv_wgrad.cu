@@ -212,26 +212,13 @@ void launch_wgrad(const float* dy, const float* xt, float* part, const ConvShape
     prob.total_kb = s.batch * p.tiles_h * p.tiles_w;
     prob.batch = s.batch;
 
-    UmmaSchedule sched;
-    sched.tiles_m = p.ocp / (UMMA_BM * CTAS);
-    sched.tiles_n = p.ranges * taps * p.c_tiles;
-    sched.k_blocks = p.kb_per_range;
-    sched.raster_group = sched.tiles_m;
-    sched.status = dev.status_word;
-    sched.wait_limit_ns = 2000000000ull;
-    sched.b_lbo = 0;
-    sched.b_sbo = 0;
-    sched.umma_n = p.n_cols;
-    sched.tx_bytes = (Cfg::A_BYTES + uint32_t(p.n_cols / CTAS) * UMMA_BK * 4) * CTAS * KATOMS;
-    sched.n_whole = sched.tiles_m * sched.tiles_n;
-    sched.split = 1;
-    sched.kb_per_split = sched.k_blocks;
-    sched.cluster_split = 1;
-    sched.exchange_bytes = 0;
-    sched.tma_store = 1;
-    sched.debug = 0;
     const int fit_stages = int((Cfg::SMEM_BUDGET - UMMA_STORE_STAGING_BYTES) / Cfg::STAGE_BYTES);
-    sched.stages = fit_stages < Cfg::STAGES ? fit_stages : Cfg::STAGES;
+    UmmaSchedule sched = whole_tile_schedule(
+        p.ocp / (UMMA_BM * CTAS), p.ranges * taps * p.c_tiles, p.kb_per_range, p.n_cols,
+        (Cfg::A_BYTES + uint32_t(p.n_cols / CTAS) * UMMA_BK * 4) * CTAS * KATOMS,
+        fit_stages < Cfg::STAGES ? fit_stages : Cfg::STAGES, dev.status_word);
+    sched.raster_group = sched.tiles_m;
+    sched.tma_store = 1;
     sched.ring_staging = uint32_t(sched.stages) * Cfg::STAGE_BYTES >= 131072u ? 1 : 0;
     const uint32_t smem_bytes = uint32_t(sched.stages) * Cfg::STAGE_BYTES + UMMA_STORE_STAGING_BYTES + 1024;
 
@@ -241,22 +228,8 @@ void launch_wgrad(const float* dy, const float* xt, float* part, const ConvShape
     if (groups > num_tiles) groups = num_tiles;
 
     auto kernel = umma_tf32_kernel<CTAS, 256, true, KATOMS, Prob>;
-    ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), Cfg::SMEM_MAX);
-
     UmmaEpilogueArgs epi{nullptr, 0, EPI_NONE};
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(unsigned(groups * CTAS), 1, 1);
-    cfg.blockDim = dim3(UMMA_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = smem_bytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CTAS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    CB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, prob, sched, epi));
+    launch_umma(kernel, prob, sched, epi, groups, CTAS, smem_bytes, Cfg::SMEM_MAX, stream);
 }
 
 }  // namespace

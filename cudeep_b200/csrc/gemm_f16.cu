@@ -95,28 +95,14 @@ void launch_f16(const __half* a, const __half* b, float* c, int m, int n, int k,
     }
     const bool tma_store = prob.set_output(c, m, n, true);
 
-    UmmaSchedule sched;
-    sched.tiles_m = (m + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS);
-    sched.tiles_n = (n + BN - 1) / BN;
-    sched.k_blocks = (k + F16_BK - 1) / F16_BK;
-    sched.raster_group = 8;
-    sched.status = dev.status_word;
-    sched.wait_limit_ns = 2000000000ull;
-    sched.b_lbo = b_lbo;
-    sched.b_sbo = b_sbo;
-    sched.umma_n = BN;
-    sched.tx_bytes = Cfg::TX_BYTES;
-    sched.n_whole = sched.tiles_m * sched.tiles_n;
-    sched.split = 1;
-    sched.kb_per_split = sched.k_blocks;
-    sched.cluster_split = 1;
-    sched.exchange_bytes = 0;
-    sched.tma_store = tma_store ? 1 : 0;
-    sched.ring_staging = 0;      // set below, once the number of stages is known
-    sched.debug = 0;
     const uint32_t staging_bytes = tma_store ? UMMA_STORE_STAGING_BYTES : 0u;
     const int fit_stages = int((Cfg::SMEM_BUDGET - staging_bytes) / Cfg::STAGE_BYTES);
-    sched.stages = fit_stages < Cfg::STAGES ? fit_stages : Cfg::STAGES;
+    UmmaSchedule sched = whole_tile_schedule((m + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS), (n + BN - 1) / BN,
+                                             (k + F16_BK - 1) / F16_BK, BN, Cfg::TX_BYTES,
+                                             fit_stages < Cfg::STAGES ? fit_stages : Cfg::STAGES, dev.status_word);
+    sched.b_lbo = b_lbo;
+    sched.b_sbo = b_sbo;
+    sched.tma_store = tma_store ? 1 : 0;
     sched.ring_staging = uint32_t(sched.stages) * Cfg::STAGE_BYTES >= 131072u ? 1 : 0;
     const uint32_t smem_bytes = uint32_t(sched.stages) * Cfg::STAGE_BYTES + staging_bytes + 1024;
 
@@ -126,22 +112,8 @@ void launch_f16(const __half* a, const __half* b, float* c, int m, int n, int k,
     if (groups > num_tiles) groups = num_tiles;
 
     auto kernel = umma_tf32_kernel<CTAS, BN, true, KATOMS, Prob, false, UMMA_KIND_F16>;
-    ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), Cfg::SMEM_MAX);
-
     UmmaEpilogueArgs epi{nullptr, 0, EPI_NONE};
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(unsigned(groups * CTAS), 1, 1);
-    cfg.blockDim = dim3(UMMA_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = smem_bytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CTAS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    CB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, prob, sched, epi));
+    launch_umma(kernel, prob, sched, epi, groups, CTAS, smem_bytes, Cfg::SMEM_MAX, stream);
 }
 
 }  // namespace

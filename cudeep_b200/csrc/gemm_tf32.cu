@@ -178,22 +178,15 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     }
     const bool tma_store = prob.set_output(c, m, n, tune.tma_store >= 0);
 
-    UmmaSchedule sched;
-    sched.tiles_m = (m + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS);
-    sched.tiles_n = (n + BN - 1) / BN;
-    sched.k_blocks = (k + UMMA_BK - 1) / UMMA_BK;
-    sched.raster_group = tune.raster_group > 0 ? tune.raster_group : 8;
-    sched.status = dev.status_word;
-    sched.wait_limit_ns = 2000000000ull;
+    UmmaSchedule sched = whole_tile_schedule(
+        (m + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS), (n + BN - 1) / BN, (k + UMMA_BK - 1) / UMMA_BK, BN,
+        Cfg::TX_BYTES, (tune.stages > 0 && tune.stages < Cfg::STAGES) ? tune.stages : Cfg::STAGES, dev.status_word);
+    if (tune.raster_group > 0) sched.raster_group = tune.raster_group;
     sched.b_lbo = tune.b_lbo;
     sched.b_sbo = tune.b_sbo;
-    sched.umma_n = BN;
-    sched.tx_bytes = Cfg::TX_BYTES;
-    sched.stages = (tune.stages > 0 && tune.stages < Cfg::STAGES) ? tune.stages : Cfg::STAGES;
     sched.tma_store = tma_store ? 1 : 0;
-    sched.ring_staging = 0;      // set below, once the number of stages is known
-    const uint32_t staging_bytes = tma_store ? UMMA_STORE_STAGING_BYTES : 0u;
     sched.debug = tune.debug;
+    const uint32_t staging_bytes = tma_store ? UMMA_STORE_STAGING_BYTES : 0u;
 
     const int num_tiles = sched.tiles_m * sched.tiles_n;
     int max_ctas = tune.max_ctas > 0 ? tune.max_ctas : dev.num_sms;
@@ -262,21 +255,9 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     const uint32_t smem_bytes = uint32_t(sched.stages) * Cfg::STAGE_BYTES + exchange_bytes + staging_bytes + 1024;
 
     auto kernel = umma_tf32_kernel<CTAS, BN, B_MN_MAJOR, KATOMS, Prob, A_MN_MAJOR>;
-    ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), Cfg::SMEM_MAX);
-
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(unsigned(groups * CTAS), 1, 1);
-    cfg.blockDim = dim3(UMMA_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = smem_bytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = unsigned(CTAS * sched.cluster_split);
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    CB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, prob, sched, epi));
+    // `groups` counts CTA groups (a CTA or a pair); a cluster holds cluster_split of them.
+    launch_umma(kernel, prob, sched, epi, groups / sched.cluster_split, CTAS * sched.cluster_split, smem_bytes,
+                Cfg::SMEM_MAX, stream);
 }
 
 // One tile shape with what it costs, measured on B200 at 1.9 GHz with cold operands (launches

@@ -17,6 +17,7 @@
 // decode, the TMA loads of one K block and the output store.
 #pragma once
 
+#include "runtime.h"
 #include "sm100_ptx.cuh"
 #include "epilogue_math.cuh"
 
@@ -595,6 +596,51 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
     // Compiled for an architecture without tcgen05: report instead of running.
     if (threadIdx.x == 0 && blockIdx.x == 0) atomicCAS(sched.status, 0u, 0xdeadu);
 #endif
+}
+
+// ---------------------------------------------------------------- host helpers
+
+// A schedule of whole tiles (no K split of either kind, register-store epilogue, no diagnostics)
+// for `k_blocks` K blocks per tile; launchers change what they need.
+inline UmmaSchedule whole_tile_schedule(int tiles_m, int tiles_n, int k_blocks, int umma_n, uint32_t tx_bytes,
+                                        int stages, uint32_t* status_word) {
+    UmmaSchedule sched{};
+    sched.tiles_m = tiles_m;
+    sched.tiles_n = tiles_n;
+    sched.k_blocks = k_blocks;
+    sched.raster_group = 8;
+    sched.status = status_word;
+    sched.wait_limit_ns = 2000000000ull;
+    sched.umma_n = umma_n;
+    sched.tx_bytes = tx_bytes;
+    sched.stages = stages;
+    sched.n_whole = tiles_m * tiles_n;
+    sched.split = 1;
+    sched.kb_per_split = k_blocks;
+    sched.cluster_split = 1;
+    return sched;
+}
+
+// Launches `kernel` on `clusters` clusters of `cluster_size` CTAs with `smem_bytes` of dynamic
+// shared memory (the kernel's opt-in limit is raised to `smem_limit` on first use).
+template <class Kernel, class Problem>
+void launch_umma(Kernel kernel, const Problem& prob, const UmmaSchedule& sched, const UmmaEpilogueArgs& epi,
+                 long long clusters, int cluster_size, uint32_t smem_bytes, uint32_t smem_limit,
+                 cudaStream_t stream) {
+    ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem_limit);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(clusters * cluster_size), 1, 1);
+    cfg.blockDim = dim3(UMMA_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = unsigned(cluster_size);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, prob, sched, epi));
 }
 
 }  // namespace cudeep_b200
