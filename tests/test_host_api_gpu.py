@@ -312,3 +312,56 @@ def test_pool_is_stream_aware(lib, cuda):
     free(later, p2)
     assert _lib.device_status() == 0
     _lib.check(lib.cudeep_b200_pool_release_cached())
+
+
+def test_entry_points_can_be_captured_in_a_cuda_graph(lib, cuda, oracle):
+    """Launch-bound chains are meant to be replayed from CUDA graphs: GEMM, fused Linear, conv forward
+    (with its stream-ordered scratch) and conv grad_weight are captured once on a side stream and
+    replayed on new inputs."""
+    import ctypes
+    from cudeep_b200 import _lib
+    torch = cuda
+    rng = np.random.default_rng(31)
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    x = torch.zeros((128, 256), device="cuda")
+    w = torch.from_numpy(rng.standard_normal((512, 256), dtype=np.float32) * np.float32(0.1)).cuda()
+    b = torch.from_numpy(rng.standard_normal(512, dtype=np.float32)).cuda()
+    h = torch.empty((128, 512), device="cuda")
+    w2 = torch.from_numpy(rng.standard_normal((512, 64), dtype=np.float32) * np.float32(0.1)).cuda()
+    y = torch.empty((128, 64), device="cuda")
+    img = torch.zeros((2, 32, 16, 16), device="cuda")
+    filt = torch.from_numpy(rng.standard_normal((64, 32, 3, 3), dtype=np.float32) * np.float32(0.1)).cuda()
+    out = torch.empty((2, 64, 16, 16), device="cuda")
+    dw = torch.empty_like(filt)
+    side = torch.cuda.Stream()
+    sp = ctypes.c_void_p(side.cuda_stream)
+
+    def chain():
+        _lib.check(lib.cudeep_b200_linear_forward_f32(ptr(x), ptr(w), ptr(b), ptr(h), 128, 512, 256, 1, sp))
+        _lib.check(lib.cudeep_b200_matmul_f32(ptr(h), ptr(w2), ptr(y), 128, 64, 512, sp))
+        _lib.check(lib.cudeep_b200_conv2d_forward_f32(ptr(img), ptr(filt), None, ptr(out), 2, 32, 64, 16, 16, 3, 3,
+                                                      1, 1, 1, 1, sp))
+        _lib.check(lib.cudeep_b200_conv2d_backward_weight_f32(ptr(out), ptr(img), ptr(dw), 2, 32, 64, 16, 16, 3, 3,
+                                                              1, 1, 1, 1, sp))
+
+    with torch.cuda.stream(side):
+        chain()                                    # first use outside the capture (attributes, pools)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            chain()
+        for seed in (1, 2):
+            xr = np.random.default_rng(seed).standard_normal((128, 256), dtype=np.float32)
+            ir = np.random.default_rng(seed + 10).standard_normal((2, 32, 16, 16), dtype=np.float32)
+            x.copy_(torch.from_numpy(xr))
+            img.copy_(torch.from_numpy(ir))
+            graph.replay()
+            torch.cuda.synchronize()
+            hidden = oracle.linear(xr, w.cpu().numpy(), b.cpu().numpy(), act=oracle.EPI_RELU)
+            assert oracle.rel_frobenius(h.cpu().numpy(), hidden) <= 5e-3
+            assert oracle.rel_frobenius(y.cpu().numpy(), oracle.gemm(h.cpu().numpy(), w2.cpu().numpy())) <= 5e-3
+            conv = oracle.conv2d_np(ir, filt.cpu().numpy(), None, (1, 1), (1, 1))
+            assert oracle.rel_frobenius(out.cpu().numpy(), conv) <= 5e-3
+            grad = oracle.conv2d_backward_weight_np(out.cpu().numpy(), ir, (3, 3), (1, 1), (1, 1))
+            assert oracle.rel_frobenius(dw.cpu().numpy(), grad) <= 5e-3
+    assert _lib.device_status() == 0
