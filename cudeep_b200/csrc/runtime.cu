@@ -1,5 +1,6 @@
 #include "runtime.h"
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_set>
 #include <vector>
@@ -91,6 +92,14 @@ void ensure_dynamic_smem(const void* func, size_t bytes) {
     CB200_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     static_cast<int>(bytes)));
     st.smem_done.insert(func);
+}
+
+bool programmatic_launch_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("CUDEEP_B200_PDL");
+        return !(v != nullptr && v[0] == '0');
+    }();
+    return on;
 }
 
 void* scratch_alloc(size_t bytes, cudaStream_t stream) {

@@ -35,6 +35,18 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with programmatic stream serialization may start while the kernel before it
+// in the stream is still running.  grid_dependency_wait() blocks until every such predecessor
+// has completed and its memory is visible (a no-op without one); grid_launch_dependents() lets
+// the next kernel in the stream start being scheduled once every CTA of this grid has called it.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- cluster
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;

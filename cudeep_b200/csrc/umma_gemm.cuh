@@ -210,6 +210,10 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
     }
     ptx::tc_fence_after();
     const uint32_t tmem_base = tmem_base_holder;
+    // Everything above touched only this launch's parameters and on-chip state, so it may overlap
+    // the tail of the previous kernel in the stream; operands, bias and C are touched from here on.
+    ptx::grid_dependency_wait();
+    ptx::grid_launch_dependents();
 
     const int num_tiles = sched.tiles_m * sched.tiles_n;
     const int num_units = sched.n_whole + (num_tiles - sched.n_whole) * sched.split;
@@ -621,6 +625,9 @@ inline UmmaSchedule whole_tile_schedule(int tiles_m, int tiles_n, int k_blocks, 
     return sched;
 }
 
+// Off when the environment variable CUDEEP_B200_PDL is "0" (read once).
+bool programmatic_launch_enabled();
+
 // Launches `kernel` on `clusters` clusters of `cluster_size` CTAs with `smem_bytes` of dynamic
 // shared memory (the kernel's opt-in limit is raised to `smem_limit` on first use).
 template <class Kernel, class Problem>
@@ -633,13 +640,17 @@ void launch_umma(Kernel kernel, const Problem& prob, const UmmaSchedule& sched, 
     cfg.blockDim = dim3(UMMA_THREADS, 1, 1);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = unsigned(cluster_size);
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // The kernel waits for its predecessors itself (grid_dependency_wait), so its set-up may
+    // overlap their tail.
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = programmatic_launch_enabled() ? 2 : 1;
     CB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, prob, sched, epi));
 }
 
