@@ -99,20 +99,22 @@ struct WgradProblem {
 };
 
 // dw[oc][c][tap] = sum over ranges of part[range][oc][tap * cp + c], ranges in ascending order.
+// Threads walk (oc, tap, c) with c fastest, so the reads of the partial tiles (ranges times the
+// size of dw) coalesce; the writes are strided by the tap count.
 __global__ void wgrad_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, int ranges, int oc_n,
                                     int ocp, int c_n, int cp, int taps) {
-    const long long total = static_cast<long long>(oc_n) * c_n * taps;
+    const long long total = static_cast<long long>(oc_n) * taps * c_n;
     const long long row_len = static_cast<long long>(taps) * cp;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int tap = static_cast<int>(i % taps);
-        const long long r = i / taps;
-        const int c = static_cast<int>(r % c_n);
-        const long long oc = r / c_n;
+        const int c = static_cast<int>(i % c_n);
+        const long long r = i / c_n;
+        const int tap = static_cast<int>(r % taps);
+        const long long oc = r / taps;
         const float* src = part + oc * row_len + static_cast<long long>(tap) * cp + c;
         float acc = 0.0f;
         for (int s = 0; s < ranges; ++s) acc += src[static_cast<long long>(s) * ocp * row_len];
-        dw[i] = acc;
+        dw[(oc * c_n + c) * taps + tap] = acc;
     }
 }
 
