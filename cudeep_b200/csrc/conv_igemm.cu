@@ -96,10 +96,13 @@ __global__ void pack_filters_kernel(const float* __restrict__ w, float* __restri
 
 template <int CTAS>
 struct ConvProblem {
-    static constexpr bool kTmaStore = false;   // results are scattered to NCHW rows: register stores
+    // When a tile's pixels are contiguous in the output plane (box_w == OW) the output is the 2-D
+    // tensor {OH*OW, N*OC} and goes out by bulk tensor stores like a GEMM's C; otherwise registers.
+    static constexpr bool kTmaStore = true;
     static constexpr bool kClusterSplit = false;
     CUtensorMap map_w;     // packed filters: dims {KH*KW*Cp, OC}, box {32, 128}
     CUtensorMap map_x;     // NHWC input: dims {Cx, W, H, N}, box {32, box_w, box_h / CTAS, 1}
+    CUtensorMap map_out;   // output planes: dims {OH*OW, N*OC}, box {32, 32}
     float* out;
     int oc_n, oh_n, ow_n;
     int box_w, box_h;      // output pixels per tile: box_h rows of box_w
@@ -121,6 +124,26 @@ struct ConvProblem {
     __device__ __forceinline__ void prefetch_maps() const {
         ptx::prefetch_tensormap(&map_w);
         ptx::prefetch_tensormap(&map_x);
+        ptx::prefetch_tensormap(&map_out);
+    }
+    __device__ __forceinline__ const CUtensorMap* out_map() const { return &map_out; }
+    // Columns of a tile whose rows reach past OH map past the end of the plane and are clipped.
+    // Rows past OC would land in the next image's planes: OC is a multiple of 32 on this path, so
+    // a 32-row block is either whole or entirely past OC, and the latter is sent out of range.
+    __device__ __forceinline__ void out_coords(const Tile& t, int row_in_cta, int c0, int& x, int& y) const {
+        x = t.oh0 * ow_n + c0;
+        y = t.n * oc_n + t.oc0 + row_in_cta;
+        if (t.oc0 + row_in_cta >= oc_n) y = batch * oc_n;      // a block of rows past OC: clipped as a whole
+    }
+    __device__ __forceinline__ void finish(const Tile& t, int row_in_cta, int /*c0*/, float (&v)[32],
+                                           const UmmaEpilogueArgs& epi) const {
+        const int oc = t.oc0 + row_in_cta;
+        if (epi.bias != nullptr && oc < oc_n) {
+            const float b = __ldg(epi.bias + oc);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += b;
+        }
+        apply_activation(v, epi.act);
     }
     __device__ __forceinline__ Tile decode(int tm, int tn, uint32_t cta_rank) const {
         Tile t;
@@ -260,6 +283,17 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     prob.contig = (plan.box_w == ow) ? 1 : 0;
     prob.vec_ok = (prob.contig && ((plan.box_h * ow) % 4 == 0) && ((oh * ow) % 4 == 0) &&
                    ((reinterpret_cast<uintptr_t>(out) & 15u) == 0)) ? 1 : 0;
+    // Bulk stores: contiguous tiles, plane rows of 16-byte multiples, chunk starts on 16-byte
+    // boundaries (oh0 * OW is a multiple of box_h * OW), whole 32-row blocks of output channels.
+    const bool bulk_store = prob.vec_ok && s.out_c % 32 == 0;
+    if (bulk_store) {
+        const uint64_t dims[2] = {uint64_t(oh) * ow, uint64_t(s.batch) * s.out_c};
+        const uint64_t strides[1] = {uint64_t(oh) * ow * 4};
+        const uint32_t box[2] = {32, 32};
+        encode_tensor_map(&prob.map_out, out, 2, dims, strides, box, TmaSwizzle::B128);
+    } else {
+        prob.map_out = prob.map_w;
+    }
 
     const int umma_n = plan.box_w * plan.box_h;
     UmmaSchedule sched = whole_tile_schedule(
@@ -269,6 +303,12 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     // Consecutive tiles walk the output-channel tiles of one pixel block, so
     // concurrent CTAs read the same input pixels from L2.
     sched.raster_group = sched.tiles_m;
+    const uint32_t staging_bytes = bulk_store ? UMMA_STORE_STAGING_BYTES : 0u;
+    const int fit_stages = int((Cfg::SMEM_BUDGET - staging_bytes) / Cfg::STAGE_BYTES);
+    if (sched.stages > fit_stages) sched.stages = fit_stages;
+    sched.tma_store = bulk_store ? 1 : 0;
+    sched.ring_staging = (bulk_store && uint32_t(sched.stages) * Cfg::STAGE_BYTES >= 131072u) ? 1 : 0;
+    const uint32_t smem_bytes = uint32_t(sched.stages) * Cfg::STAGE_BYTES + staging_bytes + 1024;
 
     const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;
     CB200_REQUIRE(num_tiles < (1LL << 30), "conv2d: too many tiles");
@@ -278,7 +318,7 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
 
     auto kernel = umma_tf32_kernel<CTAS, 256, false, KATOMS, Prob>;
     UmmaEpilogueArgs epi{bias, 1, act};
-    launch_umma(kernel, prob, sched, epi, groups, CTAS, Cfg::SMEM_BYTES, Cfg::SMEM_BYTES, stream);
+    launch_umma(kernel, prob, sched, epi, groups, CTAS, smem_bytes, Cfg::SMEM_MAX, stream);
 }
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }

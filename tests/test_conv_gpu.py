@@ -74,6 +74,8 @@ def test_direct_path_shapes(dev, oracle, shape, oc, k, stride, padding):
     ((1, 36, 20, 20), 160, (3, 3), (0, 0)),      # no padding: output smaller than input
     ((3, 6, 16, 16), 64, (3, 3), (1, 1)),        # few input channels (C*KH*KW >= 32 still holds)
     ((1, 32, 6, 300), 64, (3, 3), (1, 1)),       # rows wider than one tile
+    ((2, 32, 12, 16), 160, (3, 3), (1, 1)),      # bulk-store tiles whose rows past OC = 160 must not reach image 1
+    ((3, 32, 10, 8), 96, (3, 3), (1, 1)),        # bulk-store tiles taller than the image (rows past OH clipped)
 ])
 @pytest.mark.parametrize("act", [0, 1])
 def test_tensor_core_path_shapes(dev, oracle, shape, oc, k, padding, act):
