@@ -3,8 +3,8 @@
 //
 // grad_input: for stride 1 it is itself a convolution - of grad_output with the filters
 // flipped in both spatial directions and with their channel axes swapped, padded by
-// (KH-1-pad_h, KW-1-pad_w) - so it runs on the forward implicit-GEMM path after a small
-// filter re-arrangement.  The reference instead forms weight^T x grad_output as one big
+// (KH-1-pad_h, KW-1-pad_w) - so it runs on the forward implicit-GEMM path, whose filter
+// packing reads the filters in that order.  The reference instead forms weight^T x grad_output as one big
 // GEMM into a [C*KH*KW, N*OH*OW] temporary and scatters it back with col2im.  Strided
 // convolutions, FP64 and shapes the tensor-core path does not take use a direct gather kernel.
 //
@@ -18,22 +18,6 @@
 
 namespace cudeep_b200 {
 namespace {
-
-// w[OC][C][KH][KW] -> wf[C][OC][KH][KW] with both spatial axes reversed.
-__global__ void flip_filters_kernel(const float* __restrict__ w, float* __restrict__ wf, int oc_n, int c_n,
-                                    int kh_n, int kw_n) {
-    const long long total = static_cast<long long>(oc_n) * c_n * kh_n * kw_n;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int kw = static_cast<int>(i % kw_n);
-        long long r = i / kw_n;
-        const int kh = static_cast<int>(r % kh_n);
-        r /= kh_n;
-        const int oc = static_cast<int>(r % oc_n);
-        const int c = static_cast<int>(r / oc_n);
-        wf[i] = w[((static_cast<long long>(oc) * c_n + c) * kh_n + (kh_n - 1 - kh)) * kw_n + (kw_n - 1 - kw)];
-    }
-}
 
 template <typename T>
 __global__ void conv2d_backward_data_direct_kernel(const T* __restrict__ dy, const T* __restrict__ w,
@@ -140,22 +124,10 @@ void launch_conv2d_backward_data_kernel<float>(const float* grad_output, const f
                                1, 1, kernel_h - 1 - pad_h, kernel_w - 1 - pad_w};
     const bool stride_one = stride_h == 1 && stride_w == 1 && pad_h <= kernel_h - 1 && pad_w <= kernel_w - 1;
     if (stride_one && cudeep_b200::conv2d_igemm_supported(as_forward)) {
-        const size_t bytes = static_cast<size_t>(out_channels) * in_channels * kernel_h * kernel_w * sizeof(float);
-        float* flipped = static_cast<float*>(cudeep_b200::scratch_alloc(bytes, stream));
-        try {
-            const long long total = static_cast<long long>(out_channels) * in_channels * kernel_h * kernel_w;
-            long long blocks = (total + 255) / 256;
-            if (blocks > 4096) blocks = 4096;
-            cudeep_b200::flip_filters_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-                weight, flipped, out_channels, in_channels, kernel_h, kernel_w);
-            CB200_CHECK_LAUNCH();
-            cudeep_b200::conv2d_igemm(grad_output, flipped, nullptr, grad_input, as_forward,
-                                      cudeep_b200::EPI_NONE, stream);
-        } catch (...) {
-            cudeep_b200::scratch_free(flipped, stream);
-            throw;
-        }
-        cudeep_b200::scratch_free(flipped, stream);
+        // The filter packing of the forward path reads the filters flipped and with their
+        // channel axes swapped: no re-arranged copy is made.
+        cudeep_b200::conv2d_igemm(grad_output, weight, nullptr, grad_input, as_forward, cudeep_b200::EPI_NONE,
+                                  stream, /*flipped_filters=*/true);
     } else {
         cudeep_b200::backward_data_direct<float>(grad_output, weight, grad_input, s, stream);
     }

@@ -28,14 +28,57 @@ namespace {
 
 // ------------------------------------------------------------------ layout transforms
 
+// Filters -> wp[OC][KH*KW][Cp], the K-major A operand (zero for c >= C); OC and C are the output and
+// input channel counts of the convolution being launched.
+//   plain:   w is [OC][C][KH][KW]:  wp[oc][kh*KW + kw][c] = w[oc][c][kh][kw];
+//   flipped: the launch computes a grad_input, whose filters are the forward ones with both
+//            spatial axes reversed and the channel axes swapped; w is the forward tensor, which
+//            in this launch's terms is [C][OC][KH][KW]:
+//            wp[oc][kh*KW + kw][c] = w[c][oc][KH-1-kh][KW-1-kw].
+struct FilterPack {
+    const float* w;
+    float* wp;
+    int oc_n, c, k_h, k_w, cp, flipped;
+};
+
+__device__ __forceinline__ void pack_filters(const FilterPack& f, long long block, long long blocks, int threads) {
+    const int taps = f.k_h * f.k_w;
+    const long long total = static_cast<long long>(f.oc_n) * taps * f.cp;
+    for (long long i = block * threads + threadIdx.x; i < total; i += blocks * threads) {
+        const int ch = static_cast<int>(i % f.cp);
+        const long long r = i / f.cp;
+        const int tap = static_cast<int>(r % taps);
+        const long long oc = r / taps;
+        float v = 0.0f;
+        if (ch < f.c) {
+            if (f.flipped) {
+                const int kh = tap / f.k_w, kw = tap - kh * f.k_w;
+                v = f.w[((static_cast<long long>(ch) * f.oc_n + oc) * f.k_h + (f.k_h - 1 - kh)) * f.k_w +
+                        (f.k_w - 1 - kw)];
+            } else {
+                v = f.w[(oc * f.c + ch) * taps + tap];
+            }
+        }
+        f.wp[i] = v;
+    }
+}
+
 // x[N][C][HW] -> xt[N][HW][Cx], Cx >= C (extra channels written as zero).
 // 32-channel x 64-pixel tiles through shared memory: reads coalesce along HW, writes along C.
 // With HW a multiple of 4 both sides move 128 bits per thread (a warp reads 512 contiguous
 // bytes of one channel and writes four pixels' 128-byte channel runs); otherwise scalars.
+// With `with_filters`, the blocks of one extra z slice pack the filters instead (one launch for
+// both preparations of a convolution).
 template <bool VEC>
 __global__ void __launch_bounds__(256)
-nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, int hw, int cx) {
+nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, int hw, int cx, int batch,
+                    FilterPack filters, int with_filters) {
     __shared__ float tile[32][65];
+    if (with_filters && int(blockIdx.z) == batch) {
+        pack_filters(filters, static_cast<long long>(blockIdx.y) * gridDim.x + blockIdx.x,
+                     static_cast<long long>(gridDim.x) * gridDim.y, 256);
+        return;
+    }
     const int n = blockIdx.z;
     const int p0 = blockIdx.x * 64;
     const int c0 = blockIdx.y * 32;
@@ -75,20 +118,6 @@ nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, 
             const int p = p0 + p_l, ch = c0 + ch_l;
             if (p < hw && ch < cx) xtn[static_cast<long long>(p) * cx + ch] = tile[ch_l][p_l];
         }
-    }
-}
-
-// w[OC][C][KH*KW] -> wp[OC][KH*KW][Cp], zero for c >= C.
-__global__ void pack_filters_kernel(const float* __restrict__ w, float* __restrict__ wp, int oc_n,
-                                    int c, int taps, int cp) {
-    const long long total = static_cast<long long>(oc_n) * taps * cp;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int ch = static_cast<int>(i % cp);
-        const long long r = i / cp;
-        const int tap = static_cast<int>(r % taps);
-        const long long oc = r / taps;
-        wp[i] = ch < c ? w[(oc * c + ch) * taps + tap] : 0.0f;
     }
 }
 
@@ -325,13 +354,23 @@ int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 }  // namespace
 
-void nchw_to_nhwc(const float* input, float* xt, int batch, int c, int hw, int cx, cudaStream_t stream) {
-    dim3 grid((hw + 63) / 64, (cx + 31) / 32, batch);
+namespace {
+// One launch: the input re-layout and, in an extra z slice of blocks, the filter packing.
+void prepare_operands(const float* input, float* xt, int batch, int c, int hw, int cx, const FilterPack* filters,
+                      cudaStream_t stream) {
+    dim3 grid((hw + 63) / 64, (cx + 31) / 32, batch + (filters ? 1 : 0));
     CB200_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "conv2d: too many channels or images");
     const bool vec = (hw % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
-    if (vec) nchw_to_nhwc_kernel<true><<<grid, 256, 0, stream>>>(input, xt, c, hw, cx);
-    else nchw_to_nhwc_kernel<false><<<grid, 256, 0, stream>>>(input, xt, c, hw, cx);
+    const FilterPack f = filters ? *filters : FilterPack{};
+    const int with = filters ? 1 : 0;
+    if (vec) nchw_to_nhwc_kernel<true><<<grid, 256, 0, stream>>>(input, xt, c, hw, cx, batch, f, with);
+    else nchw_to_nhwc_kernel<false><<<grid, 256, 0, stream>>>(input, xt, c, hw, cx, batch, f, with);
     CB200_CHECK_LAUNCH();
+}
+}  // namespace
+
+void nchw_to_nhwc(const float* input, float* xt, int batch, int c, int hw, int cx, cudaStream_t stream) {
+    prepare_operands(input, xt, batch, c, hw, cx, nullptr, stream);
 }
 
 bool conv2d_igemm_supported(const ConvShape& s) {
@@ -361,7 +400,7 @@ size_t conv2d_igemm_scratch_bytes(const ConvShape& s, size_t* nhwc_bytes, size_t
 
 void conv2d_igemm_with_scratch(const float* input, const float* weight, const float* bias,
                                float* output, const ConvShape& s, int act, void* scratch,
-                               int force_ctas, cudaStream_t stream) {
+                               int force_ctas, cudaStream_t stream, bool flipped_filters) {
     check_conv_shape(s);
     CB200_REQUIRE(conv2d_igemm_supported(s), "conv2d: shape not supported by the tensor-core path");
     CB200_REQUIRE(scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0,
@@ -375,15 +414,8 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
     float* xt = static_cast<float*>(scratch);
     float* wp = reinterpret_cast<float*>(static_cast<char*>(scratch) + nhwc_bytes);
 
-    nchw_to_nhwc(input, xt, s.batch, s.in_c, hw, cx, stream);
-    {
-        const long long total = static_cast<long long>(s.out_c) * taps * cp;
-        long long blocks = (total + 255) / 256;
-        if (blocks > 4096) blocks = 4096;
-        pack_filters_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(weight, wp, s.out_c,
-                                                                               s.in_c, taps, cp);
-        CB200_CHECK_LAUNCH();
-    }
+    const FilterPack filters{weight, wp, s.out_c, s.in_c, s.k_h, s.k_w, cp, flipped_filters ? 1 : 0};
+    prepare_operands(input, xt, s.batch, s.in_c, hw, cx, &filters, stream);
 
     const int oh = s.out_h(), ow = s.out_w();
     int ctas = force_ctas;
@@ -401,13 +433,13 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
 }
 
 void conv2d_igemm(const float* input, const float* weight, const float* bias, float* output,
-                  const ConvShape& s, int act, cudaStream_t stream) {
+                  const ConvShape& s, int act, cudaStream_t stream, bool flipped_filters) {
     const size_t bytes = conv2d_igemm_scratch_bytes(s, nullptr, nullptr);
     // Stream-ordered scratch, as the reference does for its temporaries
     // (conv_kernel.cu:282,314,748-754): safe when calls on several streams overlap.
     void* scratch = scratch_alloc(bytes, stream);
     try {
-        conv2d_igemm_with_scratch(input, weight, bias, output, s, act, scratch, 0, stream);
+        conv2d_igemm_with_scratch(input, weight, bias, output, s, act, scratch, 0, stream, flipped_filters);
     } catch (...) {
         scratch_free(scratch, stream);
         throw;

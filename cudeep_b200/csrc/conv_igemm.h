@@ -16,13 +16,16 @@ size_t conv2d_igemm_scratch_bytes(const ConvShape& s, size_t* nhwc_bytes, size_t
 
 // Convolution with caller-provided scratch (256-byte aligned, at least
 // conv2d_igemm_scratch_bytes).  force_ctas: 0 = choose, 1 or 2 = CTAs per MMA.
+// flipped_filters: `weight` is [C][OC][KH][KW] as seen from `s` (the forward filters of the
+// convolution whose grad_input this call computes) and is used with both spatial axes reversed
+// and the channel axes swapped.
 void conv2d_igemm_with_scratch(const float* input, const float* weight, const float* bias,
                                float* output, const ConvShape& s, int act, void* scratch,
-                               int force_ctas, cudaStream_t stream);
+                               int force_ctas, cudaStream_t stream, bool flipped_filters = false);
 
 // Convolution with stream-ordered scratch (cudaMallocAsync / cudaFreeAsync on `stream`).
 void conv2d_igemm(const float* input, const float* weight, const float* bias, float* output,
-                  const ConvShape& s, int act, cudaStream_t stream);
+                  const ConvShape& s, int act, cudaStream_t stream, bool flipped_filters = false);
 
 // x[N][C][HW] -> xt[N][HW][cx] with cx >= C a multiple of 4 (channels past C are zero).
 void nchw_to_nhwc(const float* input, float* xt, int batch, int c, int hw, int cx, cudaStream_t stream);
