@@ -328,6 +328,36 @@ def test_tf32_linearity(dev, oracle):
     assert np.array_equal(dev.matmul(2 * a, b), 2 * dev.matmul(a, b))
 
 
+# ---- seeded random shapes through the plain entry points (whatever path the launcher picks) ----------
+
+def test_random_shapes_through_the_launchers(dev, oracle):
+    """60 seeded shapes, extents 1..900 with a bias towards multiples of 4 and long K: every dispatch
+    outcome (SIMT, each tile shape, cluster split, bulk and register stores, ragged edges) must stay
+    within the TF32 bar, and within the FP32 bar when the shape cannot take the tensor cores."""
+    rng = np.random.default_rng(2024)
+    for case in range(60):
+        m, n = (int(rng.integers(1, 900)) for _ in range(2))
+        k = int(rng.integers(1, 900)) if case % 3 else int(rng.integers(900, 5000))
+        if rng.random() < 0.7:
+            n, k = max(4, n // 4 * 4), max(4, k // 4 * 4)
+        a = rng.standard_normal((m, k), dtype=np.float32)
+        if case % 2 == 0:
+            b = rng.standard_normal((k, n), dtype=np.float32)
+            got = dev.matmul(a, b)
+            want = oracle.gemm(a, b)
+            tensor_core = m >= 64 and n >= 64 and k >= 32 and k % 4 == 0 and n % 4 == 0
+        else:
+            w = rng.standard_normal((n, k), dtype=np.float32)
+            bias = rng.standard_normal(n, dtype=np.float32)
+            act = int(rng.integers(0, 5))
+            got = dev.linear(a, w, bias, act=act)
+            want = oracle.linear(a, w, bias, act=act)
+            tensor_core = m >= 64 and n >= 64 and k >= 32 and k % 4 == 0
+        assert got.shape == want.shape and not np.isnan(got).any(), (case, m, n, k)
+        err = oracle.rel_frobenius(got, want)
+        assert err <= (TF32_TOL if tensor_core else 2e-5), (case, m, n, k, err)
+
+
 # ---- FP16 operands, FP32 result (launch_matmul_kernel_fp16, matmul.cuh:27-30) -----------------------
 
 @pytest.mark.parametrize("m,n,k,ctas", [
