@@ -207,6 +207,32 @@ def test_backward_weight_tensor_core_path(dev, lib, oracle, shape, oc, k, paddin
         assert oracle.rel_frobenius(dw, dw_ref) <= FP32_TOL
 
 
+def test_random_conv_shapes_forward_and_backward(dev, lib, oracle):
+    """24 seeded layer shapes (1..3 images, 1..80 channels, 5..40 pixels a side, 1x1..5x5 filters, strides
+    1..2, any valid padding): whatever path each of the three launchers picks must stay within the TF32 bar."""
+    rng = np.random.default_rng(77)
+    for case in range(24):
+        nb = int(rng.integers(1, 4))
+        c, oc = int(rng.integers(1, 81)), int(rng.integers(1, 161))
+        h, wd = int(rng.integers(5, 41)), int(rng.integers(5, 41))
+        kh, kw = int(rng.integers(1, 6)), int(rng.integers(1, 6))
+        stride = (1, 1) if rng.random() < 0.75 else (int(rng.integers(1, 3)), int(rng.integers(1, 3)))
+        ph, pw = int(rng.integers(0, kh)), int(rng.integers(0, kw))
+        if h + 2 * ph < kh or wd + 2 * pw < kw:
+            continue
+        x = rng.standard_normal((nb, c, h, wd), dtype=np.float32)
+        w = rng.standard_normal((oc, c, kh, kw), dtype=np.float32) * np.float32(0.2)
+        bias = rng.standard_normal(oc, dtype=np.float32)
+        y = dev.conv2d(x, w, bias, stride, (ph, pw), act=1)
+        want = oracle.conv2d_np(x, w, bias, stride, (ph, pw), act=1)
+        assert y.shape == want.shape, (case, x.shape, w.shape, stride, (ph, pw))
+        assert oracle.rel_frobenius(y, want) <= TF32_TOL, (case, x.shape, w.shape, stride, (ph, pw))
+        dy = rng.standard_normal(want.shape, dtype=np.float32)
+        dx, dw = conv_backward(dev, lib, dy, w, x, stride, (ph, pw))
+        assert oracle.rel_frobenius(dx, oracle.conv2d_backward_data_np(dy, w, (h, wd), stride, (ph, pw))) <= TF32_TOL, case
+        assert oracle.rel_frobenius(dw, oracle.conv2d_backward_weight_np(dy, x, (kh, kw), stride, (ph, pw))) <= TF32_TOL, case
+
+
 def test_conv_host_buffers(lib, cuda, oracle):
     import ctypes
     from cudeep_b200 import _lib
