@@ -152,7 +152,9 @@ int cudeep_b200_gemm_tf32_tuned(const float* A, const float* B, int b_is_nk, flo
         tune.debug |= ((b_lbo >> 29) & 3u) << 4;
         tune.ring_staging = ((b_lbo >> 31) & 1u) ? -1 : 0;
         tune.b_lbo = b_lbo & 0xffffu;
-        tune.b_sbo = b_sbo;
+        tune.b_sbo = b_sbo & 0xffffu;
+        tune.wait_limit_ms = (b_sbo >> 16) & 0x7fffu;
+        if (b_sbo >> 31) tune.debug |= 0x80u;
         cudeep_b200::gemm_tf32(A, B, b_is_nk != 0, C, M, N, K, bias, bias_per_row != 0, epilogue, tune,
                                as_stream(stream));
     });

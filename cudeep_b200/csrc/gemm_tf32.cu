@@ -186,6 +186,7 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     sched.b_sbo = tune.b_sbo;
     sched.tma_store = tma_store ? 1 : 0;
     sched.debug = tune.debug;
+    if (tune.wait_limit_ms > 0) sched.wait_limit_ns = static_cast<unsigned long long>(tune.wait_limit_ms) * 1000000ull;
     const uint32_t staging_bytes = tma_store ? UMMA_STORE_STAGING_BYTES : 0u;
 
     const int num_tiles = sched.tiles_m * sched.tiles_n;

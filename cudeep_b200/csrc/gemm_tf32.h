@@ -22,6 +22,7 @@ struct GemmTuning {
     int tma_store = 0;       // -1: write C from registers even where bulk tensor stores are possible
     int b_chunked = 0;       // -1: load B[K,N] as separate 32-column boxes even when N % 32 == 0
     uint32_t debug = 0;      // diagnostics, see UmmaSchedule::debug
+    uint32_t wait_limit_ms = 0;   // limit of every in-kernel wait (0 = the default of 2000 ms)
 };
 
 // True when the tensor-core path can take this problem (sm_100 device,

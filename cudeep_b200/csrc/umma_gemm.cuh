@@ -86,7 +86,10 @@ struct UmmaSchedule {
     //          producer does nothing: raw MMA issue rate;
     //   bit 3: the epilogue neither reads TMEM nor stores;
     //   bit 4: the bulk-store epilogue stages its results but issues no store;
-    //   bit 5: the bulk-store epilogue skips the accumulator loads.
+    //   bit 5: the bulk-store epilogue skips the accumulator loads;
+    //   bit 7: the producer issues nothing at all, so the MMA issuer's bounded wait for operands
+    //          runs out: the kernel must then record its status code, unwind every role, free
+    //          its TMEM and return (the way to test that path without a fault).
     uint32_t debug;
 };
 
@@ -248,7 +251,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0 && !(sched.debug & 4u)) {
+        if (lane == 0 && !(sched.debug & (4u | 0x80u))) {
             uint32_t stage = 0, phase = 0, issued = 0;
             for (int u = first_unit; u < num_units; u += unit_stride) {
                 const WorkUnit w = decode_unit(u);

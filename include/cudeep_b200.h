@@ -130,7 +130,11 @@ int cudeep_b200_matmul_f16_tuned(const void* A, const void* B, float* C, int M, 
  * b_lbo writes C from registers instead of through bulk tensor stores; bits
  * 29-30 of b_lbo are two more diagnostics (29: stage the results but issue no
  * bulk store, 30: skip the accumulator loads); bit 31 of b_lbo flips whether a
- * CTA's last tile stages its results in the idle stage ring.  Fails
+ * CTA's last tile stages its results in the idle stage ring.  b_sbo: bits 0-15
+ * the descriptor override, bits 16-30 a limit in milliseconds for every wait
+ * inside the kernel (0 = 2000 ms), bit 31 a diagnostic in which no operand is
+ * ever loaded, so that the wait for operands runs out and the kernel returns with
+ * cudeep_b200_device_status() = 2 (the bounded-wait path, testable without a fault).  Fails
  * instead of falling back when the tensor-core path cannot take the problem. */
 int cudeep_b200_gemm_tf32_tuned(const float* A, const float* B, int b_is_nk, float* C, int M, int N,
                                 int K, const float* bias, int bias_per_row, int epilogue, int ctas,

@@ -513,3 +513,31 @@ def test_matmul_host_buffers(lib, cuda, oracle):
     c2 = np.empty_like(c)
     _lib.check(lib.cudeep_b200_matmul_host_f32(p(a), p(b), p(c2), 1024, 1024, 1024, 1))
     assert oracle.rel_frobenius(c2, oracle.gemm(a, b)) <= FP32_TOL
+
+
+# ---- bounded waits: a wait that cannot complete ends the kernel with a status, not a hang -----------
+
+@pytest.mark.parametrize("ctas,bn", [(1, 64), (1, 256), (2, 256)])
+def test_a_wait_that_runs_out_reports_a_status_and_leaves_the_device_usable(dev, lib, oracle, ctas, bn):
+    """Diagnostic mode: the producer loads nothing, so the MMA issuer's wait for operands reaches its
+    limit (set to 40 ms here).  The kernel must return, the status word must name the role that gave
+    up (2 = MMA issuer waiting for operands, or 4 = an epilogue of the pair's second CTA waiting for
+    the accumulator), and the next launch must work."""
+    import time
+    from cudeep_b200 import _lib
+    rng = np.random.default_rng(8)
+    a = rng.standard_normal((256, 128), dtype=np.float32)
+    b = rng.standard_normal((128, 512), dtype=np.float32)
+    ta, tb = dev.to_dev(a), dev.to_dev(b)
+    tc = dev.empty((256, 512))
+    starve, limit_ms = 1 << 31, 40
+    t0 = time.time()
+    dev.check(lib.cudeep_b200_gemm_tf32_tuned(dev.ptr(ta), dev.ptr(tb), 0, dev.ptr(tc), 256, 512, 128, None, 0, 0,
+                                              ctas, bn, 0, 0, 0, starve | (limit_ms << 16), None))
+    status = dev.sync_status()                 # synchronises, reads and clears the status word
+    elapsed = time.time() - t0
+    assert status in (2, 4), status
+    assert 0.03 <= elapsed < 5.0               # it waited for the limit, and only about that long
+    assert _lib.device_status() == 0           # cleared
+    got = dev.gemm_tuned(a, b, False, ctas=ctas, bn=bn)     # the device and the library still work
+    check_tf32(oracle, got, a, b, 128)
