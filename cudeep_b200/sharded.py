@@ -48,6 +48,55 @@ def _device_matmul(a, b, c, stream) -> None:
                                                   ctypes.c_void_p(c.data_ptr()), m, n, k, stream))
 
 
+class PeerFailure(RuntimeError):
+    """Another rank of the sharded product reported an error, or did not report in time."""
+
+
+class StepGuard:
+    """Host-side liveness check, so that a rank that failed is noticed before the others enter a
+    collective they would hang in.
+
+    Every rank calls report(step) when its kernels for that step are queued (or report(step,
+    ok=False, message=...) from its exception handler), then wait_all(step) before the collective.
+    Reports go through a torch.distributed store (the TCP store of the process group, or any other
+    `Store`); nothing here touches a GPU.  A rank that leaves does so between steps, with none of
+    its kernels or collectives in flight."""
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 30.0, prefix: str = "cudeep_b200/step"):
+        self.store, self.rank, self.world = store, rank, world
+        self.timeout_s = timeout_s
+        self.prefix = prefix
+
+    def _key(self, step: int, rank: int) -> str:
+        return f"{self.prefix}/{step}/{rank}"
+
+    def report(self, step: int, ok: bool = True, message: str = "") -> None:
+        self.store.set(self._key(step, self.rank), "ok" if ok else "error: " + message)
+
+    def wait_all(self, step: int) -> None:
+        """Returns when every rank has reported success for `step`; raises PeerFailure naming the
+        ranks that reported an error or did not report within the timeout."""
+        import datetime
+        import time
+        deadline = time.monotonic() + self.timeout_s
+        failed, missing = {}, []
+        for r in range(self.world):
+            key = self._key(step, r)
+            left = max(deadline - time.monotonic(), 0.001)
+            try:
+                self.store.wait([key], datetime.timedelta(seconds=left))
+            except Exception:
+                missing.append(r)
+                continue
+            value = self.store.get(key).decode("utf-8", "replace")
+            if value != "ok":
+                failed[r] = value
+        if failed or missing:
+            parts = [f"rank {r} {v}" for r, v in sorted(failed.items())]
+            parts += [f"rank {r} did not report within {self.timeout_s:g} s" for r in missing]
+            raise PeerFailure(f"step {step}: " + "; ".join(parts))
+
+
 class ShardedGemm:
     """This rank's share of a row-sharded product.
 
@@ -75,10 +124,15 @@ class ShardedGemm:
             _device_matmul(self.a, self.b, self.c, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
         return self.c
 
-    def gather(self, shards: list[RowShard], group=None):
-        """All-gather the row shards into the full C on every rank (shards may differ in size)."""
+    def gather(self, shards: list[RowShard], group=None, guard: Optional[StepGuard] = None, step: int = 0):
+        """All-gather the row shards into the full C on every rank (shards may differ in size).
+        With a guard, every rank first confirms that all ranks reached this step: a failed or
+        absent peer raises PeerFailure here instead of leaving the collective to hang."""
         import torch
         import torch.distributed as dist
+        if guard is not None:
+            guard.report(step)
+            guard.wait_all(step)
         n = self.b.shape[1]
         if all(s.rows == shards[0].rows for s in shards):
             full = torch.empty((sum(s.rows for s in shards), n), dtype=self.c.dtype, device=self.c.device)
