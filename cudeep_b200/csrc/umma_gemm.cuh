@@ -644,16 +644,23 @@ void launch_umma(Kernel kernel, const Problem& prob, const UmmaSchedule& sched, 
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = unsigned(cluster_size);
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    // The kernel waits for its predecessors itself (grid_dependency_wait), so its set-up may
-    // overlap their tail.
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    int count = 0;
+    if (cluster_size > 1) {          // a lone CTA is launched as a plain grid
+        attr[count].id = cudaLaunchAttributeClusterDimension;
+        attr[count].val.clusterDim.x = unsigned(cluster_size);
+        attr[count].val.clusterDim.y = 1;
+        attr[count].val.clusterDim.z = 1;
+        ++count;
+    }
+    if (programmatic_launch_enabled()) {
+        // The kernel waits for its predecessors itself (grid_dependency_wait), so its set-up may
+        // overlap their tail.
+        attr[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[count].val.programmaticStreamSerializationAllowed = 1;
+        ++count;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = programmatic_launch_enabled() ? 2 : 1;
+    cfg.numAttrs = unsigned(count);
     CB200_CUDA(cudaLaunchKernelEx(&cfg, kernel, prob, sched, epi));
 }
 
