@@ -6,8 +6,8 @@
 namespace cudeep_b200 {
 
 // True when the tensor-core path takes this shape: sm_100 device, stride 1,
-// padding smaller than the filter, at least 32 output channels, C*KH*KW >= 32
-// and at least 64 output pixels.
+// padding smaller than the filter, at least 32 output channels, at least 3
+// input channels and at least 64 output pixels.
 bool conv2d_igemm_supported(const ConvShape& s);
 
 // Bytes of scratch one call needs: the NHWC copy of the input followed by the

@@ -72,7 +72,9 @@ def test_direct_path_shapes(dev, oracle, shape, oc, k, stride, padding):
     ((1, 64, 56, 56), 256, (3, 3), (1, 1)),      # C4's image size and filter, one image
     ((2, 40, 10, 12), 200, (5, 5), (2, 2)),      # 5x5, ragged channels on both sides
     ((1, 36, 20, 20), 160, (3, 3), (0, 0)),      # no padding: output smaller than input
-    ((3, 6, 16, 16), 64, (3, 3), (1, 1)),        # few input channels (C*KH*KW >= 32 still holds)
+    ((3, 6, 16, 16), 64, (3, 3), (1, 1)),        # few input channels: each tap's K block is mostly zero padding
+    ((2, 3, 32, 32), 64, (3, 3), (1, 1)),        # a first layer: three channels, the fewest this path takes
+    ((1, 4, 20, 20), 32, (5, 5), (2, 2)),        # four channels, 5 x 5
     ((1, 32, 6, 300), 64, (3, 3), (1, 1)),       # rows wider than one tile
     ((2, 32, 12, 16), 160, (3, 3), (1, 1)),      # bulk-store tiles whose rows past OC = 160 must not reach image 1
     ((3, 32, 10, 8), 96, (3, 3), (1, 1)),        # bulk-store tiles taller than the image (rows past OH clipped)
