@@ -8,7 +8,7 @@
 // GEMM into a [C*KH*KW, N*OH*OW] temporary and scatters it back with col2im.  Strided
 // convolutions, FP64 and shapes the tensor-core path does not take use a direct gather kernel.
 //
-// grad_weight: for stride 1 an implicit GEMM over output pixels on the tensor cores
+// grad_weight: an implicit GEMM over output pixels on the tensor cores (any stride up to 8)
 // (conv_wgrad.cu); otherwise a direct strict-precision kernel (one thread per filter element,
 // summing over images and output pixels in a fixed order).
 #include "cudeep/kernels/conv.cuh"

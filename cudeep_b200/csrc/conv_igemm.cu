@@ -1,6 +1,6 @@
-// Conv2d forward as an implicit GEMM on tcgen05 (stride 1).
+// Conv2d forward as an implicit GEMM on tcgen05.
 //
-//   out[n, oc, oh, ow] = act( sum_{kh,kw,c} w[oc, c, kh, kw] * x[n, c, oh+kh-ph, ow+kw-pw] + bias[oc] )
+//   out[n, oc, oh, ow] = act( sum_{kh,kw,c} w[oc, c, kh, kw] * x[n, c, oh*sh+kh-ph, ow*sw+kw-pw] + bias[oc] )
 //
 // is computed as D[OC, pixels] = Wp[OC, K] * X[K, pixels] with K ordered
 // (kh, kw, c).  Nothing of size K x pixels is ever written to memory:
@@ -10,8 +10,9 @@
 //     multiple of 4).  A K block is then "32 channels of one filter tap", and
 //     the B tile of a block of output pixels is a 4-D TMA box
 //     {32 channels, box_w, box_h, 1 image} whose start coordinate carries the
-//     tap offset (ow0+kw-pw, oh0+kh-ph); padding is TMA's out-of-range zero
-//     fill.  The box lands in shared memory as one 128-byte row per pixel,
+//     tap offset (ow0*sw+kw-pw, oh0*sh+kh-ph); padding is TMA's out-of-range zero
+//     fill, and a strided convolution's every s-th pixel is the TMA box's element
+//     stride.  The box lands in shared memory as one 128-byte row per pixel,
 //     which is a K-major B operand as is.
 // Accumulator rows are output channels and columns are output pixels, so the
 // epilogue writes NCHW directly with bias and activation fused.
@@ -139,6 +140,7 @@ struct ConvProblem {
     int c_blocks;          // Cp / 32
     int k_w;
     int p_h, p_w;
+    int s_h, s_w;          // convolution strides: the box walks the input in these steps
     int total_kb;          // K blocks of the reduction: KH * KW * c_blocks
     int batch;
     int contig;            // box_w == OW: the tile's pixels are contiguous in the output plane
@@ -199,10 +201,10 @@ struct ConvProblem {
         const int n = kb < total_kb ? t.n : batch;
         if constexpr (C == 1) {
             ptx::tma_load_2d(a_smem, &map_w, bar, kb * UMMA_BK, t.oc0);
-            ptx::tma_load_4d(b_smem, &map_x, bar, c0, t.ow0 + kw - p_w, t.hb0 + kh - p_h, n);
+            ptx::tma_load_4d(b_smem, &map_x, bar, c0, t.ow0 * s_w + kw - p_w, t.hb0 * s_h + kh - p_h, n);
         } else {
             ptx::tma_load_2d_pair(a_smem, &map_w, bar, kb * UMMA_BK, t.oc0);
-            ptx::tma_load_4d_pair(b_smem, &map_x, bar, c0, t.ow0 + kw - p_w, t.hb0 + kh - p_h, n);
+            ptx::tma_load_4d_pair(b_smem, &map_x, bar, c0, t.ow0 * s_w + kw - p_w, t.hb0 * s_h + kh - p_h, n);
         }
     }
     __device__ __forceinline__ void store(const Tile& t, int row_in_cta, int c0, float (&v)[32],
@@ -249,15 +251,17 @@ struct TilePlan {
 // Output-pixel box of one tile: box_h rows of box_w pixels, box_w * box_h a
 // multiple of 32 and at most 256, box_h a multiple of the CTAs that split it;
 // picked to waste the fewest accumulator columns, then to be as large as possible.
-TilePlan plan_tile(int oh, int ow, int ctas) {
+// With strides the TMA box spans box * stride input pixels, which must stay within 256 per dimension.
+TilePlan plan_tile(int oh, int ow, int ctas, int s_h, int s_w) {
     TilePlan best;
     double best_eff = -1.0;
-    const int w_lo = ow < 256 ? ow : 256;
-    const int w_hi = (w_lo + 31 < 256) ? w_lo + 31 : 256;
+    const int max_w = 256 / s_w, max_h = 256 / s_h * ctas;
+    const int w_lo = ow < max_w ? ow : max_w;
+    const int w_hi = (w_lo + 31 < max_w) ? w_lo + 31 : max_w;
     for (int bw = w_lo; bw <= w_hi; ++bw) {
         for (int bh = ctas; bh * bw <= 256; bh += ctas) {
             if ((bh * bw) % 32 != 0) continue;
-            if (bh > 256 || bw > 256) continue;
+            if (bh > max_h || bw > max_w) continue;
             const int tiles_w = (ow + bw - 1) / bw;
             const int tiles_h = (oh + bh - 1) / bh;
             const double eff = double(oh) * ow / (double(tiles_w) * tiles_h * bw * bh);
@@ -292,8 +296,11 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
         const uint64_t dims[4] = {uint64_t(cx), uint64_t(s.in_w), uint64_t(s.in_h), uint64_t(s.batch)};
         const uint64_t strides[3] = {uint64_t(cx) * 4, uint64_t(s.in_w) * cx * 4,
                                      uint64_t(s.in_h) * s.in_w * cx * 4};
-        const uint32_t box[4] = {UMMA_BK, uint32_t(plan.box_w), uint32_t(plan.box_h / CTAS), 1};
-        encode_tensor_map(&prob.map_x, xt, 4, dims, strides, box, TmaSwizzle::B128);
+        // A strided convolution reads every s-th input pixel: the box spans box * s input pixels
+        // and the TMA unit walks it in steps of s (element strides), so box_w x box_h pixels land.
+        const uint32_t box[4] = {UMMA_BK, uint32_t(plan.box_w * s.s_w), uint32_t(plan.box_h / CTAS * s.s_h), 1};
+        const uint32_t steps[4] = {1, uint32_t(s.s_w), uint32_t(s.s_h), 1};
+        encode_tensor_map(&prob.map_x, xt, 4, dims, strides, box, TmaSwizzle::B128, steps);
     }
     prob.out = out;
     prob.oc_n = s.out_c;
@@ -307,6 +314,8 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     prob.k_w = s.k_w;
     prob.p_h = s.p_h;
     prob.p_w = s.p_w;
+    prob.s_h = s.s_h;
+    prob.s_w = s.s_w;
     prob.total_kb = taps * prob.c_blocks;
     prob.batch = s.batch;
     prob.contig = (plan.box_w == ow) ? 1 : 0;
@@ -375,7 +384,7 @@ void nchw_to_nhwc(const float* input, float* xt, int batch, int c, int hw, int c
 
 bool conv2d_igemm_supported(const ConvShape& s) {
     if (device_info().cc_major != 10) return false;
-    if (s.s_h != 1 || s.s_w != 1) return false;
+    if (s.s_h < 1 || s.s_w < 1 || s.s_h > 8 || s.s_w > 8) return false;     // TMA element strides go up to 8
     if (s.p_h >= s.k_h || s.p_w >= s.k_w) return false;     // keeps every box start within TMA's signed range
     const int oh = s.out_h(), ow = s.out_w();
     if (oh < 1 || ow < 1) return false;
@@ -424,10 +433,10 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
     const int oh = s.out_h(), ow = s.out_w();
     int ctas = force_ctas;
     if (ctas == 0) ctas = (s.out_c > UMMA_BM) ? 2 : 1;
-    TilePlan plan = plan_tile(oh, ow, ctas);
+    TilePlan plan = plan_tile(oh, ow, ctas, s.s_h, s.s_w);
     if (plan.box_w == 0 && ctas == 2) {
         ctas = 1;
-        plan = plan_tile(oh, ow, 1);
+        plan = plan_tile(oh, ow, 1, s.s_h, s.s_w);
     }
     CB200_REQUIRE(plan.box_w > 0, "conv2d: no tile shape fits this output size");
     // A CTA pair stages at most 32 KB per K block, so two blocks share a pipeline

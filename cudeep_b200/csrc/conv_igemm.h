@@ -5,7 +5,7 @@
 
 namespace cudeep_b200 {
 
-// True when the tensor-core path takes this shape: sm_100 device, stride 1,
+// True when the tensor-core path takes this shape: sm_100 device, strides 1..8,
 // padding smaller than the filter, at least 32 output channels, at least 3
 // input channels and at least 64 output pixels.
 bool conv2d_igemm_supported(const ConvShape& s);
@@ -30,7 +30,7 @@ void conv2d_igemm(const float* input, const float* weight, const float* bias, fl
 // x[N][C][HW] -> xt[N][HW][cx] with cx >= C a multiple of 4 (channels past C are zero).
 void nchw_to_nhwc(const float* input, float* xt, int batch, int c, int hw, int cx, cudaStream_t stream);
 
-// grad_weight of a stride-1 convolution as an implicit GEMM over output pixels (conv_wgrad.cu).
+// grad_weight as an implicit GEMM over output pixels (conv_wgrad.cu): strides 1..8, OW % 4 == 0.
 bool conv2d_wgrad_igemm_supported(const ConvShape& s);
 void conv2d_wgrad_igemm(const float* grad_output, const float* input, float* grad_weight, const ConvShape& s,
                         cudaStream_t stream);

@@ -1,8 +1,8 @@
-// grad_weight of a stride-1 Conv2d as an implicit GEMM on tcgen05
+// grad_weight of a Conv2d as an implicit GEMM on tcgen05
 // (reference include/cudeep/kernels/conv.cuh:28-36, src/kernels/conv_kernel.cu:460-545, which
 // forms im2col(x) per image in global memory and multiplies it with grad_output).
 //
-//   dw[oc, c, kh, kw] = sum_{n, oh, ow} dy[n, oc, oh, ow] * x[n, c, oh+kh-ph, ow+kw-pw]
+//   dw[oc, c, kh, kw] = sum_{n, oh, ow} dy[n, oc, oh, ow] * x[n, c, oh*sh+kh-ph, ow*sw+kw-pw]
 //
 // For one filter tap this is D[OC, C] = dY[OC, pixels] * X_tap[pixels, C]: the reduction runs over
 // output pixels.  A K block is 32 consecutive pixels of one output row (box_w x box_h = 32 x 1):
@@ -34,6 +34,7 @@ struct WgradProblem {
     int box_w, box_h;
     int c_tiles;            // channel tiles (of umma_n channels) per tap
     int taps, k_w, p_h, p_w;
+    int s_h, s_w;           // convolution strides
     int n_cols;             // channels per tile (umma_n)
     int cp;                 // padded channels
     int ocp;                // padded output channels: rows of one K range in the scratch
@@ -82,10 +83,10 @@ struct WgradProblem {
         const int kw = t.tap - kh * k_w;
         if constexpr (C == 1) {
             ptx::tma_load_4d(a_smem, &map_dy, bar, ow0, oh0, t.oc0, n);
-            ptx::tma_load_5d(b_smem, &map_x, bar, 0, ow0 + kw - p_w, oh0 + kh - p_h, n, t.cb0 / 32);
+            ptx::tma_load_5d(b_smem, &map_x, bar, 0, ow0 * s_w + kw - p_w, oh0 * s_h + kh - p_h, n, t.cb0 / 32);
         } else {
             ptx::tma_load_4d_pair(a_smem, &map_dy, bar, ow0, oh0, t.oc0, n);
-            ptx::tma_load_5d_pair(b_smem, &map_x, bar, 0, ow0 + kw - p_w, oh0 + kh - p_h, n, t.cb0 / 32);
+            ptx::tma_load_5d_pair(b_smem, &map_x, bar, 0, ow0 * s_w + kw - p_w, oh0 * s_h + kh - p_h, n, t.cb0 / 32);
         }
     }
     __device__ __forceinline__ const CUtensorMap* out_map() const { return &map_part; }
@@ -189,8 +190,11 @@ void launch_wgrad(const float* dy, const float* xt, float* part, const ConvShape
         const uint64_t dims[5] = {32, uint64_t(s.in_w), uint64_t(s.in_h), uint64_t(s.batch), uint64_t(p.cp / 32)};
         const uint64_t strides[4] = {uint64_t(p.cp) * 4, uint64_t(s.in_w) * p.cp * 4,
                                      uint64_t(s.in_h) * s.in_w * p.cp * 4, 128};
-        const uint32_t box[5] = {32, uint32_t(p.box_w), uint32_t(p.box_h), 1, uint32_t(p.n_cols / CTAS / 32)};
-        encode_tensor_map(&prob.map_x, xt, 5, dims, strides, box, TmaSwizzle::B128Atom32);
+        // With strides the box spans box * stride input pixels walked in steps of the stride.
+        const uint32_t box[5] = {32, uint32_t(p.box_w * s.s_w), uint32_t(p.box_h * s.s_h), 1,
+                                 uint32_t(p.n_cols / CTAS / 32)};
+        const uint32_t steps[5] = {1, uint32_t(s.s_w), uint32_t(s.s_h), 1, 1};
+        encode_tensor_map(&prob.map_x, xt, 5, dims, strides, box, TmaSwizzle::B128Atom32, steps);
     }
     {
         const uint64_t dims[2] = {uint64_t(taps) * p.cp, uint64_t(p.ranges) * p.ocp};
@@ -207,6 +211,8 @@ void launch_wgrad(const float* dy, const float* xt, float* part, const ConvShape
     prob.k_w = s.k_w;
     prob.p_h = s.p_h;
     prob.p_w = s.p_w;
+    prob.s_h = s.s_h;
+    prob.s_w = s.s_w;
     prob.n_cols = p.n_cols;
     prob.cp = p.cp;
     prob.ocp = p.ocp;
@@ -238,7 +244,7 @@ void launch_wgrad(const float* dy, const float* xt, float* part, const ConvShape
 
 bool conv2d_wgrad_igemm_supported(const ConvShape& s) {
     if (device_info().cc_major != 10) return false;
-    if (s.s_h != 1 || s.s_w != 1) return false;
+    if (s.s_h < 1 || s.s_w < 1 || s.s_h > 8 || s.s_w > 8) return false;     // 32 pixels x stride <= 256, TMA steps <= 8
     if (s.p_h >= s.k_h || s.p_w >= s.k_w) return false;     // keeps every box start within TMA's signed range
     const int oh = s.out_h(), ow = s.out_w();
     if (oh < 1 || ow < 1) return false;

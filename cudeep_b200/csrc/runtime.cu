@@ -132,7 +132,8 @@ uint32_t read_device_status(bool clear) {
 
 namespace {
 void encode_map(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, uint32_t elem_bytes, int rank,
-                const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle) {
+                const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle,
+                const uint32_t* element_strides) {
     CB200_REQUIRE(rank >= 1 && rank <= 5, "tensor map rank must be 1..5");
     CB200_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15u) == 0, "TMA base address must be 16-byte aligned");
     cuuint64_t gdim[5];
@@ -142,8 +143,10 @@ void encode_map(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, u
     for (int i = 0; i < rank; ++i) {
         gdim[i] = dims[i];
         gbox[i] = box[i];
-        estride[i] = 1;
+        estride[i] = element_strides ? element_strides[i] : 1;
         CB200_REQUIRE(box[i] >= 1 && box[i] <= 256, "TMA box extent must be 1..256");
+        CB200_REQUIRE(estride[i] >= 1 && estride[i] <= 8 && box[i] % estride[i] == 0,
+                      "TMA element stride must be 1..8 and divide the box extent");
     }
     for (int i = 0; i + 1 < rank; ++i) {
         gstride[i] = strides_bytes[i];
@@ -162,13 +165,15 @@ void encode_map(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, u
 }  // namespace
 
 void encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint64_t* dims,
-                       const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle) {
-    encode_map(map, base, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, rank, dims, strides_bytes, box, swizzle);
+                       const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle,
+                       const uint32_t* element_strides) {
+    encode_map(map, base, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, rank, dims, strides_bytes, box, swizzle,
+               element_strides);
 }
 
 void encode_tensor_map_f16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
                            const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle) {
-    encode_map(map, base, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, rank, dims, strides_bytes, box, swizzle);
+    encode_map(map, base, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, rank, dims, strides_bytes, box, swizzle, nullptr);
 }
 
 }  // namespace cudeep_b200

@@ -67,7 +67,11 @@ enum class TmaSwizzle {
 // The same for 2-byte (FP16) elements: dims, boxes and coordinates count elements.
 void encode_tensor_map_f16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
                            const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle);
+// element_strides (optional, one per dimension): traverse dimension i in steps of that many
+// elements; box[i] then is the extent traversed (a multiple of the step) and box[i] / step
+// elements are loaded.
 void encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint64_t* dims,
-                       const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle);
+                       const uint64_t* strides_bytes, const uint32_t* box, TmaSwizzle swizzle,
+                       const uint32_t* element_strides = nullptr);
 
 }  // namespace cudeep_b200

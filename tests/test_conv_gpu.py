@@ -51,7 +51,8 @@ def test_golden_fixtures(dev, oracle):
     ((1, 1, 5, 5), 1, (3, 3), (1, 1), (0, 0)),
     ((2, 3, 9, 11), 8, (3, 3), (2, 2), (1, 1)),
     ((1, 16, 12, 12), 8, (5, 3), (1, 2), (2, 0)),
-    ((2, 64, 14, 14), 64, (3, 3), (2, 2), (1, 1)),      # strided: direct path even with many channels
+    ((2, 64, 14, 14), 16, (3, 3), (2, 2), (1, 1)),      # fewer than 32 output channels: direct even with many inputs
+    ((2, 64, 14, 14), 64, (3, 3), (2, 2), (3, 1)),      # padding as large as the filter: direct
 ])
 def test_direct_path_shapes(dev, oracle, shape, oc, k, stride, padding):
     rng = np.random.default_rng(sum(shape) + oc)
@@ -92,6 +93,35 @@ def test_tensor_core_path_shapes(dev, oracle, shape, oc, k, padding, act):
     assert got.shape == exact.shape
     assert oracle.rel_frobenius(got, exact) <= TF32_TOL
     assert oracle.rel_frobenius(got, model) <= TF32_MODEL_TOL
+
+
+@pytest.mark.parametrize("shape,oc,k,stride,padding", [
+    ((2, 64, 14, 14), 64, (3, 3), (2, 2), (1, 1)),       # 7 x 7 outputs, every second pixel in both directions
+    ((2, 32, 28, 28), 128, (3, 3), (2, 2), (1, 1)),      # a ResNet down-sampling layer
+    ((1, 3, 64, 64), 64, (7, 7), (2, 2), (3, 3)),        # a ResNet stem: 7 x 7, stride 2, three channels
+    ((2, 64, 16, 16), 256, (1, 1), (2, 2), (0, 0)),      # 1 x 1 stride 2 projection, CTA pair
+    ((1, 32, 20, 33), 64, (3, 3), (1, 3), (1, 1)),       # different strides per direction, width not a multiple
+    ((2, 40, 39, 39), 96, (5, 5), (4, 4), (2, 2)),       # stride 4
+])
+@pytest.mark.parametrize("act", [0, 1])
+def test_strided_tensor_core_path_shapes(dev, lib, oracle, shape, oc, k, stride, padding, act):
+    """Strided convolutions: the TMA box walks the NHWC input in steps of the stride."""
+    rng = np.random.default_rng(sum(shape) + oc + act)
+    x = rng.standard_normal(shape, dtype=np.float32)
+    w = rng.standard_normal((oc, shape[1], *k), dtype=np.float32) * np.float32(0.1)
+    bias = rng.standard_normal(oc, dtype=np.float32)
+    got = dev.conv2d(x, w, bias, stride, padding, act=act)
+    assert not np.isnan(got).any()
+    exact = oracle.conv2d(x, w, bias, stride, padding, act=act)
+    model = oracle.conv2d(x, w, bias, stride, padding, act=act, input_mode=oracle.INPUT_TF32_TRUNC)
+    assert got.shape == exact.shape
+    assert oracle.rel_frobenius(got, exact) <= TF32_TOL
+    assert oracle.rel_frobenius(got, model) <= TF32_MODEL_TOL        # so the tensor cores did run
+    if act == 0:
+        dy = rng.standard_normal(exact.shape, dtype=np.float32)
+        _, dw = conv_backward(dev, lib, dy, w, x, stride, padding)
+        dw_ref = oracle.conv2d_backward_weight_np(dy, x, k, stride, padding)
+        assert oracle.rel_frobenius(dw, dw_ref) <= TF32_TOL
 
 
 def test_no_bias_and_bias_differ_by_bias(dev):
