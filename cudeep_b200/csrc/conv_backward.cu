@@ -5,8 +5,9 @@
 // flipped in both spatial directions and with their channel axes swapped, padded by
 // (KH-1-pad_h, KW-1-pad_w) - so it runs on the forward implicit-GEMM path, whose filter
 // packing reads the filters in that order.  The reference instead forms weight^T x grad_output as one big
-// GEMM into a [C*KH*KW, N*OH*OW] temporary and scatters it back with col2im.  Strided
-// convolutions, FP64 and shapes the tensor-core path does not take use a direct gather kernel.
+// GEMM into a [C*KH*KW, N*OH*OW] temporary and scatters it back with col2im.  A strided
+// convolution takes the same path with zeros inserted between the pixels of grad_output.
+// FP64 and shapes the tensor-core path does not take use a direct gather kernel.
 //
 // grad_weight: an implicit GEMM over output pixels on the tensor cores (any stride up to 8)
 // (conv_wgrad.cu); otherwise a direct strict-precision kernel (one thread per filter element,
@@ -122,12 +123,25 @@ void launch_conv2d_backward_data_kernel<float>(const float* grad_output, const f
     // output = grad_input [N, C, H, W].
     const ConvShape as_forward{batch, out_channels, in_channels, s.out_h(), s.out_w(), kernel_h, kernel_w,
                                1, 1, kernel_h - 1 - pad_h, kernel_w - 1 - pad_w};
-    const bool stride_one = stride_h == 1 && stride_w == 1 && pad_h <= kernel_h - 1 && pad_w <= kernel_w - 1;
-    if (stride_one && cudeep_b200::conv2d_igemm_supported(as_forward)) {
+    const bool pad_fits = pad_h <= kernel_h - 1 && pad_w <= kernel_w - 1;
+    const bool stride_one = stride_h == 1 && stride_w == 1;
+    // A strided convolution: grad_output with (stride - 1) zeros put between its pixels, and as
+    // many zero rows and columns behind it as the forward pass left unread, is the input of the
+    // same stride-1 convolution.  The tensor cores then multiply stride_h * stride_w times more
+    // zeros than data, which still beats the gather kernel by far up to that factor 16.
+    ConvShape dilated = as_forward;
+    dilated.in_h = (s.out_h() - 1) * stride_h + 1 + (in_h + 2 * pad_h - kernel_h) % stride_h;
+    dilated.in_w = (s.out_w() - 1) * stride_w + 1 + (in_w + 2 * pad_w - kernel_w) % stride_w;
+    if (pad_fits && stride_one && cudeep_b200::conv2d_igemm_supported(as_forward)) {
         // The filter packing of the forward path reads the filters flipped and with their
         // channel axes swapped: no re-arranged copy is made.
         cudeep_b200::conv2d_igemm(grad_output, weight, nullptr, grad_input, as_forward, cudeep_b200::EPI_NONE,
                                   stream, /*flipped_filters=*/true);
+    } else if (pad_fits && !stride_one && stride_h * stride_w <= 16 &&
+               cudeep_b200::conv2d_igemm_supported(dilated)) {
+        const cudeep_b200::InputDilation dilation{s.out_h(), s.out_w(), stride_h, stride_w};
+        cudeep_b200::conv2d_igemm(grad_output, weight, nullptr, grad_input, dilated, cudeep_b200::EPI_NONE,
+                                  stream, /*flipped_filters=*/true, &dilation);
     } else {
         cudeep_b200::backward_data_direct<float>(grad_output, weight, grad_input, s, stream);
     }
@@ -173,7 +187,7 @@ void launch_conv2d_backward_weight_kernel<float>(const float* grad_output, const
     cudeep_b200::check_conv_shape(s);
     // Stride-1 shapes with enough channels and pixels: tensor cores (TF32, like the reference's GEMM);
     // everything else: the direct strict-FP32 kernel.
-    if (cudeep_b200::conv2d_wgrad_igemm_supported(s) && (reinterpret_cast<uintptr_t>(grad_output) & 15u) == 0)
+    if (cudeep_b200::conv2d_wgrad_igemm_supported(s))
         cudeep_b200::conv2d_wgrad_igemm(grad_output, input, grad_weight, s, stream);
     else
         backward_weight<float>(grad_output, input, grad_weight, s, stream);

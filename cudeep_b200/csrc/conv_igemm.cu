@@ -36,13 +36,27 @@ namespace {
 //            spatial axes reversed and the channel axes swapped; w is the forward tensor, which
 //            in this launch's terms is [C][OC][KH][KW]:
 //            wp[oc][kh*KW + kw][c] = w[c][oc][KH-1-kh][KW-1-kw].
+//   row-packed (row_cx > 0, few input channels): one 32-wide K block per filter row holds its
+//            KW taps of row_cx channels each, wp[oc][kh][kw * row_cx + c] = w[oc][c][kh][kw].
 struct FilterPack {
     const float* w;
     float* wp;
-    int oc_n, c, k_h, k_w, cp, flipped;
+    int oc_n, c, k_h, k_w, cp, flipped, row_cx;
 };
 
 __device__ __forceinline__ void pack_filters(const FilterPack& f, long long block, long long blocks, int threads) {
+    if (f.row_cx > 0) {
+        const long long total = static_cast<long long>(f.oc_n) * f.k_h * UMMA_BK;
+        for (long long i = block * threads + threadIdx.x; i < total; i += blocks * threads) {
+            const int slot = static_cast<int>(i % UMMA_BK);
+            const long long r = i / UMMA_BK;
+            const int kh = static_cast<int>(r % f.k_h);
+            const long long oc = r / f.k_h;
+            const int kw = slot / f.row_cx, ch = slot - kw * f.row_cx;
+            f.wp[i] = (kw < f.k_w && ch < f.c) ? f.w[((oc * f.c + ch) * f.k_h + kh) * f.k_w + kw] : 0.0f;
+        }
+        return;
+    }
     const int taps = f.k_h * f.k_w;
     const long long total = static_cast<long long>(f.oc_n) * taps * f.cp;
     for (long long i = block * threads + threadIdx.x; i < total; i += blocks * threads) {
@@ -70,10 +84,20 @@ __device__ __forceinline__ void pack_filters(const FilterPack& f, long long bloc
 // bytes of one channel and writes four pixels' 128-byte channel runs); otherwise scalars.
 // With `with_filters`, the blocks of one extra z slice pack the filters instead (one launch for
 // both preparations of a convolution).
-template <bool VEC>
+// With SCATTER, source pixel (r, q) of a src_w-wide plane lands at (r * d_h, q * d_w) of a
+// dst_w-wide plane of dst_hw pixels per image (zeroed by the caller beforehand).
+struct PixelScatter {
+    int src_w, dst_w, dst_hw, d_h, d_w, first;      // `first`: destination pixel of source pixel 0
+    __device__ __forceinline__ long long operator()(int p) const {
+        const int r = p / src_w;
+        return first + static_cast<long long>(r) * d_h * dst_w + static_cast<long long>(p - r * src_w) * d_w;
+    }
+};
+
+template <bool VEC, bool SCATTER = false>
 __global__ void __launch_bounds__(256)
 nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, int hw, int cx, int batch,
-                    FilterPack filters, int with_filters) {
+                    FilterPack filters, int with_filters, PixelScatter scatter = PixelScatter{}) {
     __shared__ float tile[32][65];
     if (with_filters && int(blockIdx.z) == batch) {
         pack_filters(filters, static_cast<long long>(blockIdx.y) * gridDim.x + blockIdx.x,
@@ -84,7 +108,7 @@ nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, 
     const int p0 = blockIdx.x * 64;
     const int c0 = blockIdx.y * 32;
     const float* xn = x + static_cast<long long>(n) * c * hw;
-    float* xtn = xt + static_cast<long long>(n) * hw * cx;
+    float* xtn = xt + static_cast<long long>(n) * (SCATTER ? scatter.dst_hw : hw) * cx;
     const int tid = threadIdx.x;
     if constexpr (VEC) {
 #pragma unroll
@@ -104,7 +128,7 @@ nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, 
             const int p_l = pass * 32 + tid / 8, ch_l = (tid % 8) * 4;
             const int p = p0 + p_l, ch = c0 + ch_l;
             if (p < hw && ch < cx)
-                *reinterpret_cast<float4*>(xtn + static_cast<long long>(p) * cx + ch) =
+                *reinterpret_cast<float4*>(xtn + (SCATTER ? scatter(p) : static_cast<long long>(p)) * cx + ch) =
                     make_float4(tile[ch_l][p_l], tile[ch_l + 1][p_l], tile[ch_l + 2][p_l], tile[ch_l + 3][p_l]);
         }
     } else {
@@ -117,7 +141,8 @@ nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, 
         for (int i = tid; i < 32 * 64; i += 256) {
             const int p_l = i / 32, ch_l = i % 32;
             const int p = p0 + p_l, ch = c0 + ch_l;
-            if (p < hw && ch < cx) xtn[static_cast<long long>(p) * cx + ch] = tile[ch_l][p_l];
+            if (p < hw && ch < cx)
+                xtn[(SCATTER ? scatter(p) : static_cast<long long>(p)) * cx + ch] = tile[ch_l][p_l];
         }
     }
 }
@@ -143,6 +168,7 @@ struct ConvProblem {
     int s_h, s_w;          // convolution strides: the box walks the input in these steps
     int total_kb;          // K blocks of the reduction: KH * KW * c_blocks
     int batch;
+    int row_packed;        // one K block per filter row (see launch_conv): map_x is the window view
     int contig;            // box_w == OW: the tile's pixels are contiguous in the output plane
     int vec_ok;            // 128-bit stores are aligned for every tile
 
@@ -193,18 +219,20 @@ struct ConvProblem {
                                          uint32_t bar) const {
         const int tap = kb / c_blocks;
         const int c0 = (kb - tap * c_blocks) * UMMA_BK;
-        const int kh = tap / k_w;
-        const int kw = tap - kh * k_w;
+        // Row-packed: K block kb is filter row kb, and coordinate 1 counts output columns (each
+        // the start of a window of KW pixels in the width-padded copy).
+        const int kh = row_packed ? kb : tap / k_w;
+        const int x1 = row_packed ? t.ow0 : t.ow0 * s_w + (tap - kh * k_w) - p_w;
         // A K block past the end of the reduction (a stage's padding) must read zeros on
         // both sides: the filter coordinate is out of range by itself, the image index is
         // pushed out of range here.
         const int n = kb < total_kb ? t.n : batch;
         if constexpr (C == 1) {
             ptx::tma_load_2d(a_smem, &map_w, bar, kb * UMMA_BK, t.oc0);
-            ptx::tma_load_4d(b_smem, &map_x, bar, c0, t.ow0 * s_w + kw - p_w, t.hb0 * s_h + kh - p_h, n);
+            ptx::tma_load_4d(b_smem, &map_x, bar, c0, x1, t.hb0 * s_h + kh - p_h, n);
         } else {
             ptx::tma_load_2d_pair(a_smem, &map_w, bar, kb * UMMA_BK, t.oc0);
-            ptx::tma_load_4d_pair(b_smem, &map_x, bar, c0, t.ow0 * s_w + kw - p_w, t.hb0 * s_h + kh - p_h, n);
+            ptx::tma_load_4d_pair(b_smem, &map_x, bar, c0, x1, t.hb0 * s_h + kh - p_h, n);
         }
     }
     __device__ __forceinline__ void store(const Tile& t, int row_in_cta, int c0, float (&v)[32],
@@ -278,12 +306,13 @@ TilePlan plan_tile(int oh, int ow, int ctas, int s_h, int s_w) {
 
 template <int CTAS, int KATOMS>
 void launch_conv(const float* xt, const float* wp, const float* bias, float* out, const ConvShape& s,
-                 int cx, int cp, const TilePlan& plan, int act, cudaStream_t stream) {
+                 int cx, int cp, const TilePlan& plan, int act, cudaStream_t stream, bool row_packed) {
     using Cfg = UmmaConfig<CTAS, 256, false, KATOMS>;
     using Prob = ConvProblem<CTAS>;
     const DeviceInfo& dev = device_info();
     const int oh = s.out_h(), ow = s.out_w();
-    const int taps = s.k_h * s.k_w;
+    // Row-packed: the K blocks are the KH filter rows, each one 32-wide block.
+    const int taps = row_packed ? s.k_h : s.k_h * s.k_w;
 
     Prob prob;
     {
@@ -292,7 +321,19 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
         const uint32_t box[2] = {UMMA_BK, UMMA_BM};
         encode_tensor_map(&prob.map_w, wp, 2, dims, strides, box, TmaSwizzle::B128);
     }
-    {
+    if (row_packed) {
+        // The input copy is [N][H][W + 2 * pad_w][cx] with the padding columns zero.  Seen as
+        // {KW * cx, OW, H, N} with a step of stride_w pixels between output columns, row (q, h, n)
+        // is the window of KW pixels x cx channels that output column q reads from input row h:
+        // contiguous in memory, overlapping its neighbours'.  A 32-wide box reads zeros past KW * cx.
+        const int wp_pixels = s.in_w + 2 * s.p_w;
+        const uint64_t dims[4] = {uint64_t(s.k_w) * cx, uint64_t(ow), uint64_t(s.in_h), uint64_t(s.batch)};
+        const uint64_t strides[3] = {uint64_t(s.s_w) * cx * 4, uint64_t(wp_pixels) * cx * 4,
+                                     uint64_t(s.in_h) * wp_pixels * cx * 4};
+        const uint32_t box[4] = {UMMA_BK, uint32_t(plan.box_w), uint32_t(plan.box_h / CTAS * s.s_h), 1};
+        const uint32_t steps[4] = {1, 1, uint32_t(s.s_h), 1};
+        encode_tensor_map(&prob.map_x, xt, 4, dims, strides, box, TmaSwizzle::B128, steps);
+    } else {
         const uint64_t dims[4] = {uint64_t(cx), uint64_t(s.in_w), uint64_t(s.in_h), uint64_t(s.batch)};
         const uint64_t strides[3] = {uint64_t(cx) * 4, uint64_t(s.in_w) * cx * 4,
                                      uint64_t(s.in_h) * s.in_w * cx * 4};
@@ -317,6 +358,7 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     prob.s_h = s.s_h;
     prob.s_w = s.s_w;
     prob.total_kb = taps * prob.c_blocks;
+    prob.row_packed = row_packed ? 1 : 0;
     prob.batch = s.batch;
     prob.contig = (plan.box_w == ow) ? 1 : 0;
     prob.vec_ok = (prob.contig && ((plan.box_h * ow) % 4 == 0) && ((oh * ow) % 4 == 0) &&
@@ -366,13 +408,16 @@ int round_up(int v, int m) { return (v + m - 1) / m * m; }
 namespace {
 // One launch: the input re-layout and, in an extra z slice of blocks, the filter packing.
 void prepare_operands(const float* input, float* xt, int batch, int c, int hw, int cx, const FilterPack* filters,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, const PixelScatter* scatter = nullptr) {
     dim3 grid((hw + 63) / 64, (cx + 31) / 32, batch + (filters ? 1 : 0));
     CB200_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "conv2d: too many channels or images");
     const bool vec = (hw % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
     const FilterPack f = filters ? *filters : FilterPack{};
     const int with = filters ? 1 : 0;
-    if (vec) nchw_to_nhwc_kernel<true><<<grid, 256, 0, stream>>>(input, xt, c, hw, cx, batch, f, with);
+    if (scatter) {
+        if (vec) nchw_to_nhwc_kernel<true, true><<<grid, 256, 0, stream>>>(input, xt, c, hw, cx, batch, f, with, *scatter);
+        else nchw_to_nhwc_kernel<false, true><<<grid, 256, 0, stream>>>(input, xt, c, hw, cx, batch, f, with, *scatter);
+    } else if (vec) nchw_to_nhwc_kernel<true><<<grid, 256, 0, stream>>>(input, xt, c, hw, cx, batch, f, with);
     else nchw_to_nhwc_kernel<false><<<grid, 256, 0, stream>>>(input, xt, c, hw, cx, batch, f, with);
     CB200_CHECK_LAUNCH();
 }
@@ -398,10 +443,18 @@ bool conv2d_igemm_supported(const ConvShape& s) {
     return true;
 }
 
+// Few input channels: a filter row's KW taps of cx channels fit one 32-wide K block, so the
+// reduction takes KH blocks instead of KH * KW (a 7 x 7 filter over 3 channels: 7 blocks of which
+// 21 / 32 are real, against 49 blocks of which 3 / 32 are).
+bool conv2d_igemm_row_packed(const ConvShape& s) {
+    return s.k_w > 1 && round_up(s.in_c, 4) * s.k_w <= UMMA_BK;
+}
+
 size_t conv2d_igemm_scratch_bytes(const ConvShape& s, size_t* nhwc_bytes, size_t* filter_bytes) {
     const int cx = round_up(s.in_c, 4);
     const int cp = round_up(s.in_c, UMMA_BK);
-    const size_t a = static_cast<size_t>(s.batch) * s.in_h * s.in_w * cx * sizeof(float);
+    // The larger of the two layouts (a call with flipped filters never packs rows).
+    const size_t a = static_cast<size_t>(s.batch) * s.in_h * (s.in_w + 2 * s.p_w) * cx * sizeof(float);
     const size_t b = static_cast<size_t>(s.out_c) * s.k_h * s.k_w * cp * sizeof(float);
     // Both regions start on 1 KiB boundaries.
     const size_t a_pad = (a + 1023) / 1024 * 1024;
@@ -413,7 +466,8 @@ size_t conv2d_igemm_scratch_bytes(const ConvShape& s, size_t* nhwc_bytes, size_t
 
 void conv2d_igemm_with_scratch(const float* input, const float* weight, const float* bias,
                                float* output, const ConvShape& s, int act, void* scratch,
-                               int force_ctas, cudaStream_t stream, bool flipped_filters) {
+                               int force_ctas, cudaStream_t stream, bool flipped_filters,
+                               const InputDilation* dilation) {
     check_conv_shape(s);
     CB200_REQUIRE(conv2d_igemm_supported(s), "conv2d: shape not supported by the tensor-core path");
     CB200_REQUIRE(scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0,
@@ -427,8 +481,28 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
     float* xt = static_cast<float*>(scratch);
     float* wp = reinterpret_cast<float*>(static_cast<char*>(scratch) + nhwc_bytes);
 
-    const FilterPack filters{weight, wp, s.out_c, s.in_c, s.k_h, s.k_w, cp, flipped_filters ? 1 : 0};
-    prepare_operands(input, xt, s.batch, s.in_c, hw, cx, &filters, stream);
+    const bool row_packed = !flipped_filters && dilation == nullptr && conv2d_igemm_row_packed(s);
+    const FilterPack filters{weight, wp, s.out_c, s.in_c, s.k_h, s.k_w, cp, flipped_filters ? 1 : 0,
+                             row_packed ? cx : 0};
+    if (row_packed) {
+        // The copy gets pad_w zero pixels on either side of every row, so that each output
+        // column's window of KW pixels is contiguous in it.
+        const int wp_pixels = s.in_w + 2 * s.p_w;
+        CB200_CUDA(cudaMemsetAsync(xt, 0, static_cast<size_t>(s.batch) * s.in_h * wp_pixels * cx * sizeof(float),
+                                   stream));
+        const PixelScatter scatter{s.in_w, wp_pixels, s.in_h * wp_pixels, 1, 1, s.p_w};
+        prepare_operands(input, xt, s.batch, s.in_c, hw, cx, &filters, stream, &scatter);
+    } else if (dilation) {
+        const InputDilation& d = *dilation;
+        CB200_REQUIRE(d.d_h >= 1 && d.d_w >= 1 && d.src_h >= 1 && d.src_w >= 1 &&
+                          (d.src_h - 1) * d.d_h < s.in_h && (d.src_w - 1) * d.d_w < s.in_w,
+                      "conv2d: the dilated input does not fit the plane");
+        CB200_CUDA(cudaMemsetAsync(xt, 0, static_cast<size_t>(s.batch) * hw * cx * sizeof(float), stream));
+        const PixelScatter scatter{d.src_w, s.in_w, hw, d.d_h, d.d_w, 0};
+        prepare_operands(input, xt, s.batch, s.in_c, d.src_h * d.src_w, cx, &filters, stream, &scatter);
+    } else {
+        prepare_operands(input, xt, s.batch, s.in_c, hw, cx, &filters, stream);
+    }
 
     const int oh = s.out_h(), ow = s.out_w();
     int ctas = force_ctas;
@@ -441,18 +515,20 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
     CB200_REQUIRE(plan.box_w > 0, "conv2d: no tile shape fits this output size");
     // A CTA pair stages at most 32 KB per K block, so two blocks share a pipeline
     // stage and the barrier handshake is paid half as often.
-    if (ctas == 2) launch_conv<2, 2>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
-    else launch_conv<1, 1>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+    if (ctas == 2) launch_conv<2, 2>(xt, wp, bias, output, s, cx, cp, plan, act, stream, row_packed);
+    else launch_conv<1, 1>(xt, wp, bias, output, s, cx, cp, plan, act, stream, row_packed);
 }
 
 void conv2d_igemm(const float* input, const float* weight, const float* bias, float* output,
-                  const ConvShape& s, int act, cudaStream_t stream, bool flipped_filters) {
+                  const ConvShape& s, int act, cudaStream_t stream, bool flipped_filters,
+                  const InputDilation* dilation) {
     const size_t bytes = conv2d_igemm_scratch_bytes(s, nullptr, nullptr);
     // Stream-ordered scratch, as the reference does for its temporaries
     // (conv_kernel.cu:282,314,748-754): safe when calls on several streams overlap.
     void* scratch = scratch_alloc(bytes, stream);
     try {
-        conv2d_igemm_with_scratch(input, weight, bias, output, s, act, scratch, 0, stream, flipped_filters);
+        conv2d_igemm_with_scratch(input, weight, bias, output, s, act, scratch, 0, stream, flipped_filters,
+                                  dilation);
     } catch (...) {
         scratch_free(scratch, stream);
         throw;

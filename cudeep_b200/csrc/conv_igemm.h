@@ -14,6 +14,14 @@ bool conv2d_igemm_supported(const ConvShape& s);
 // packed filters.  The two optional outputs receive the size of each part.
 size_t conv2d_igemm_scratch_bytes(const ConvShape& s, size_t* nhwc_bytes, size_t* filter_bytes);
 
+// The input of a launch given in compact form: `input` holds src_h x src_w pixels per channel and
+// pixel (r, q) of it stands at (r * d_h, q * d_w) of the in_h x in_w plane the shape describes;
+// every other pixel of that plane is zero.  This is how the grad_output of a strided convolution
+// enters the stride-1 convolution that yields its grad_input.
+struct InputDilation {
+    int src_h, src_w, d_h, d_w;
+};
+
 // Convolution with caller-provided scratch (256-byte aligned, at least
 // conv2d_igemm_scratch_bytes).  force_ctas: 0 = choose, 1 or 2 = CTAs per MMA.
 // flipped_filters: `weight` is [C][OC][KH][KW] as seen from `s` (the forward filters of the
@@ -21,16 +29,19 @@ size_t conv2d_igemm_scratch_bytes(const ConvShape& s, size_t* nhwc_bytes, size_t
 // and the channel axes swapped.
 void conv2d_igemm_with_scratch(const float* input, const float* weight, const float* bias,
                                float* output, const ConvShape& s, int act, void* scratch,
-                               int force_ctas, cudaStream_t stream, bool flipped_filters = false);
+                               int force_ctas, cudaStream_t stream, bool flipped_filters = false,
+                               const InputDilation* dilation = nullptr);
 
 // Convolution with stream-ordered scratch (cudaMallocAsync / cudaFreeAsync on `stream`).
 void conv2d_igemm(const float* input, const float* weight, const float* bias, float* output,
-                  const ConvShape& s, int act, cudaStream_t stream, bool flipped_filters = false);
+                  const ConvShape& s, int act, cudaStream_t stream, bool flipped_filters = false,
+                  const InputDilation* dilation = nullptr);
 
 // x[N][C][HW] -> xt[N][HW][cx] with cx >= C a multiple of 4 (channels past C are zero).
 void nchw_to_nhwc(const float* input, float* xt, int batch, int c, int hw, int cx, cudaStream_t stream);
 
-// grad_weight as an implicit GEMM over output pixels (conv_wgrad.cu): strides 1..8, OW % 4 == 0.
+// grad_weight as an implicit GEMM over output pixels (conv_wgrad.cu): strides 1..8, at least 32
+// output channels and 256 output pixels.
 bool conv2d_wgrad_igemm_supported(const ConvShape& s);
 void conv2d_wgrad_igemm(const float* grad_output, const float* input, float* grad_weight, const ConvShape& s,
                         cudaStream_t stream);

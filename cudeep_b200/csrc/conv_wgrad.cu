@@ -99,6 +99,19 @@ struct WgradProblem {
     __device__ __forceinline__ void store(const Tile&, int, int, float (&)[32], const UmmaEpilogueArgs&, int) const {}
 };
 
+// Copies rows of `ow` floats to rows of `pitch` floats (pitch >= ow, a multiple of 4), zero in
+// the tail: grad_output with 16-byte-aligned rows for the tensor map.
+__global__ void pad_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, long long rows, int ow,
+                                int pitch) {
+    const long long total = rows * pitch;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = i / pitch;
+        const int q = static_cast<int>(i - r * pitch);
+        dst[i] = q < ow ? src[r * ow + q] : 0.0f;
+    }
+}
+
 // dw[oc][c][tap] = sum over ranges of part[range][oc][tap * cp + c], ranges in ascending order.
 // Threads walk (oc, tap, c) with c fastest, so the reads of the partial tiles (ranges times the
 // size of dw) coalesce; the writes are strided by the tap count.
@@ -170,9 +183,11 @@ WgradPlan plan_wgrad(const ConvShape& s, int num_sms) {
     return p;
 }
 
+// dy_pitch: floats between consecutive rows of grad_output as passed here (OW, or OW rounded up to
+// a multiple of 4 when a padded copy had to be made).
 template <int CTAS, int KATOMS>
-void launch_wgrad(const float* dy, const float* xt, float* part, const ConvShape& s, const WgradPlan& p,
-                  cudaStream_t stream) {
+void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, const ConvShape& s,
+                  const WgradPlan& p, cudaStream_t stream) {
     using Cfg = UmmaConfig<CTAS, 256, true, KATOMS>;
     using Prob = WgradProblem<CTAS>;
     const DeviceInfo& dev = device_info();
@@ -182,7 +197,8 @@ void launch_wgrad(const float* dy, const float* xt, float* part, const ConvShape
     Prob prob;
     {
         const uint64_t dims[4] = {uint64_t(ow), uint64_t(oh), uint64_t(s.out_c), uint64_t(s.batch)};
-        const uint64_t strides[3] = {uint64_t(ow) * 4, uint64_t(oh) * ow * 4, uint64_t(s.out_c) * oh * ow * 4};
+        const uint64_t strides[3] = {uint64_t(dy_pitch) * 4, uint64_t(oh) * dy_pitch * 4,
+                                     uint64_t(s.out_c) * oh * dy_pitch * 4};
         const uint32_t box[4] = {uint32_t(p.box_w), uint32_t(p.box_h), UMMA_BM, 1};
         encode_tensor_map(&prob.map_dy, dy, 4, dims, strides, box, TmaSwizzle::B128);
     }
@@ -248,7 +264,6 @@ bool conv2d_wgrad_igemm_supported(const ConvShape& s) {
     if (s.p_h >= s.k_h || s.p_w >= s.k_w) return false;     // keeps every box start within TMA's signed range
     const int oh = s.out_h(), ow = s.out_w();
     if (oh < 1 || ow < 1) return false;
-    if (ow % 4 != 0) return false;                          // rows of grad_output must be 16-byte multiples
     if (s.out_c < 32) return false;
     if (static_cast<long long>(s.batch) * oh * ow < 256) return false;
     return true;
@@ -258,16 +273,31 @@ void conv2d_wgrad_igemm(const float* grad_output, const float* input, float* gra
                         cudaStream_t stream) {
     check_conv_shape(s);
     CB200_REQUIRE(conv2d_wgrad_igemm_supported(s), "conv2d backward: shape not supported by the tensor-core path");
-    CB200_REQUIRE((reinterpret_cast<uintptr_t>(grad_output) & 15u) == 0,
-                  "conv2d backward: grad_output must be 16-byte aligned");
     const WgradPlan p = plan_wgrad(s, device_info().num_sms);
-    char* scratch = static_cast<char*>(scratch_alloc(p.nhwc_bytes + p.part_bytes, stream));
+    // The tensor map of grad_output needs 16-byte-aligned rows: when OW is not a multiple of 4 (14 x 14
+    // and 7 x 7 feature maps) or the pointer is unaligned, a padded copy is read instead.
+    const int oh = s.out_h(), ow = s.out_w();
+    const bool copy_dy = (ow % 4 != 0) || (reinterpret_cast<uintptr_t>(grad_output) & 15u) != 0;
+    const int dy_pitch = (ow + 3) / 4 * 4;
+    const size_t part_bytes = (p.part_bytes + 1023) / 1024 * 1024;
+    const size_t dy_bytes = copy_dy ? static_cast<size_t>(s.batch) * s.out_c * oh * dy_pitch * sizeof(float) : 0;
+    char* scratch = static_cast<char*>(scratch_alloc(p.nhwc_bytes + part_bytes + dy_bytes, stream));
     try {
         float* xt = reinterpret_cast<float*>(scratch);
         float* part = reinterpret_cast<float*>(scratch + p.nhwc_bytes);
+        const float* dy = grad_output;
+        if (copy_dy) {
+            float* padded = reinterpret_cast<float*>(scratch + p.nhwc_bytes + part_bytes);
+            const long long rows = static_cast<long long>(s.batch) * s.out_c * oh;
+            long long blocks = (rows * dy_pitch + 255) / 256;
+            if (blocks > 148 * 16) blocks = 148 * 16;
+            pad_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(grad_output, padded, rows, ow, dy_pitch);
+            CB200_CHECK_LAUNCH();
+            dy = padded;
+        }
         nchw_to_nhwc(input, xt, s.batch, s.in_c, s.in_h * s.in_w, p.cp, stream);
-        if (p.ctas == 2) launch_wgrad<2, 2>(grad_output, xt, part, s, p, stream);
-        else launch_wgrad<1, 1>(grad_output, xt, part, s, p, stream);
+        if (p.ctas == 2) launch_wgrad<2, 2>(dy, copy_dy ? dy_pitch : ow, xt, part, s, p, stream);
+        else launch_wgrad<1, 1>(dy, copy_dy ? dy_pitch : ow, xt, part, s, p, stream);
         const long long total = static_cast<long long>(s.out_c) * s.in_c * s.k_h * s.k_w;
         long long blocks = (total + 255) / 256;
         if (blocks > 4096) blocks = 4096;

@@ -76,6 +76,11 @@ def test_direct_path_shapes(dev, oracle, shape, oc, k, stride, padding):
     ((3, 6, 16, 16), 64, (3, 3), (1, 1)),        # few input channels: each tap's K block is mostly zero padding
     ((2, 3, 32, 32), 64, (3, 3), (1, 1)),        # a first layer: three channels, the fewest this path takes
     ((1, 4, 20, 20), 32, (5, 5), (2, 2)),        # four channels, 5 x 5
+    ((2, 3, 17, 33), 64, (3, 8), (1, 3)),        # row-packed K blocks: 8 taps x 4 channel slots fill a block exactly
+    ((2, 8, 16, 16), 64, (3, 4), (1, 2)),        # row-packed, eight channels per tap, even filter width
+    ((1, 5, 14, 18), 256, (5, 3), (2, 1)),       # row-packed, five channels in eight slots, CTA pair, odd row count
+    ((1, 16, 12, 12), 32, (2, 2), (0, 0)),       # row-packed, two taps of sixteen channels
+    ((2, 3, 9, 300), 64, (1, 7), (0, 3)),        # row-packed, a single filter row, rows wider than one tile
     ((1, 32, 6, 300), 64, (3, 3), (1, 1)),       # rows wider than one tile
     ((2, 32, 12, 16), 160, (3, 3), (1, 1)),      # bulk-store tiles whose rows past OC = 160 must not reach image 1
     ((3, 32, 10, 8), 96, (3, 3), (1, 1)),        # bulk-store tiles taller than the image (rows past OH clipped)
@@ -99,6 +104,8 @@ def test_tensor_core_path_shapes(dev, oracle, shape, oc, k, padding, act):
     ((2, 64, 14, 14), 64, (3, 3), (2, 2), (1, 1)),       # 7 x 7 outputs, every second pixel in both directions
     ((2, 32, 28, 28), 128, (3, 3), (2, 2), (1, 1)),      # a ResNet down-sampling layer
     ((1, 3, 64, 64), 64, (7, 7), (2, 2), (3, 3)),        # a ResNet stem: 7 x 7, stride 2, three channels
+    ((2, 3, 35, 37), 96, (7, 7), (2, 3), (3, 2)),        # the same with odd sizes and different strides
+    ((2, 4, 30, 30), 64, (5, 5), (3, 3), (0, 0)),        # row-packed, stride 3, no padding
     ((2, 64, 16, 16), 256, (1, 1), (2, 2), (0, 0)),      # 1 x 1 stride 2 projection, CTA pair
     ((1, 32, 20, 33), 64, (3, 3), (1, 3), (1, 1)),       # different strides per direction, width not a multiple
     ((2, 40, 39, 39), 96, (5, 5), (4, 4), (2, 2)),       # stride 4
@@ -119,9 +126,18 @@ def test_strided_tensor_core_path_shapes(dev, lib, oracle, shape, oc, k, stride,
     assert oracle.rel_frobenius(got, model) <= TF32_MODEL_TOL        # so the tensor cores did run
     if act == 0:
         dy = rng.standard_normal(exact.shape, dtype=np.float32)
-        _, dw = conv_backward(dev, lib, dy, w, x, stride, padding)
+        dx, dw = conv_backward(dev, lib, dy, w, x, stride, padding)
         dw_ref = oracle.conv2d_backward_weight_np(dy, x, k, stride, padding)
         assert oracle.rel_frobenius(dw, dw_ref) <= TF32_TOL
+        # grad_input: grad_output with zeros between its pixels through the stride-1 implicit GEMM
+        # (32 or more input channels), else the direct kernel.
+        dx_ref = oracle.conv2d_backward_data_np(dy, w, shape[2:], stride, padding)
+        assert dx.shape == x.shape and not np.isnan(dx).any()
+        assert oracle.rel_frobenius(dx, dx_ref) <= TF32_TOL
+        if shape[1] >= 32:
+            model = oracle.conv2d_backward_data_np(dy, w, shape[2:], stride, padding,
+                                                   input_mode=oracle.INPUT_TF32_TRUNC)
+            assert oracle.rel_frobenius(dx, model) <= TF32_MODEL_TOL
 
 
 def test_no_bias_and_bias_differ_by_bias(dev):
@@ -200,7 +216,8 @@ def test_backward_against_oracle(dev, lib, oracle, shape, oc, k, stride, padding
     dx, dw = conv_backward(dev, lib, dy, w, x, stride, padding)
     dx_ref = oracle.conv2d_backward_data_np(dy, w, shape[2:], stride, padding)
     dw_ref = oracle.conv2d_backward_weight_np(dy, x, k, stride, padding)
-    assert oracle.rel_frobenius(dw, dw_ref) <= FP32_TOL
+    wgrad_on_tensor_cores = oc >= 32 and shape[0] * oh * ow >= 256       # the launcher's rule (any row length)
+    assert oracle.rel_frobenius(dw, dw_ref) <= (TF32_TOL if wgrad_on_tensor_cores else FP32_TOL)
     if tensor_core:
         assert oracle.rel_frobenius(dx, dx_ref) <= TF32_TOL
         model = oracle.conv2d_backward_data_np(dy, w, shape[2:], stride, padding, input_mode=oracle.INPUT_TF32_TRUNC)
@@ -215,10 +232,13 @@ def test_backward_against_oracle(dev, lib, oracle, shape, oc, k, stride, padding
     ((3, 48, 16, 24), 160, (3, 5), (1, 2)),     # 160 output channels: the second 128-row tile is partly empty
     ((2, 320, 12, 16), 256, (3, 3), (1, 1)),    # 320 channels: two tiles of 160 columns
     ((1, 16, 20, 20), 32, (1, 1), (0, 0)),      # 1 x 1 filter, channels padded 16 -> 32
-    ((5, 32, 9, 12), 40, (3, 3), (0, 0)),       # no padding: 7 x 10 outputs... OW = 10 is not a multiple of 4
+    ((5, 32, 9, 12), 40, (3, 3), (0, 0)),       # 7 x 10 outputs: rows of 10 floats, read through a padded copy
+    ((4, 48, 14, 14), 64, (3, 3), (1, 1)),      # 14 x 14 feature maps
+    ((8, 64, 7, 7), 128, (3, 3), (1, 1)),       # 7 x 7 feature maps
+    ((2, 16, 6, 6), 32, (3, 3), (1, 1)),        # 72 output pixels: too few, the direct kernel
 ])
 def test_backward_weight_tensor_core_path(dev, lib, oracle, shape, oc, k, padding):
-    """grad_weight as an implicit GEMM over output pixels (stride 1, OW % 4 == 0, >= 256 pixels): TF32
+    """grad_weight as an implicit GEMM over output pixels (>= 32 output channels, >= 256 pixels): TF32
     bars, and FP32-accumulation agreement with the float64 sum of the TF32-truncated operands."""
     rng = np.random.default_rng(sum(shape) + oc)
     x = rng.standard_normal(shape, dtype=np.float32)
@@ -230,7 +250,7 @@ def test_backward_weight_tensor_core_path(dev, lib, oracle, shape, oc, k, paddin
     _, again = conv_backward(dev, lib, dy, w, x, (1, 1), padding)
     assert np.array_equal(dw, again)                      # K ranges are added in a fixed order
     dw_ref = oracle.conv2d_backward_weight_np(dy, x, k, (1, 1), padding)
-    if ow % 4 == 0:
+    if shape[0] * oh * ow >= 256:
         assert oracle.rel_frobenius(dw, dw_ref) <= TF32_TOL
         model = oracle.conv2d_backward_weight_np(dy, x, k, (1, 1), padding, input_mode=oracle.INPUT_TF32_TRUNC)
         pixels = shape[0] * oh * ow
