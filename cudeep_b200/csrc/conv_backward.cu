@@ -123,7 +123,9 @@ void launch_conv2d_backward_data_kernel<float>(const float* grad_output, const f
     // output = grad_input [N, C, H, W].
     const ConvShape as_forward{batch, out_channels, in_channels, s.out_h(), s.out_w(), kernel_h, kernel_w,
                                1, 1, kernel_h - 1 - pad_h, kernel_w - 1 - pad_w};
-    const bool pad_fits = pad_h <= kernel_h - 1 && pad_w <= kernel_w - 1;
+    // (As a forward convolution its input channels are this one's output channels; with one or two
+    // of them the forward path would need its row-packed form, which flipped filters do not have.)
+    const bool pad_fits = pad_h <= kernel_h - 1 && pad_w <= kernel_w - 1 && out_channels >= 3;
     const bool stride_one = stride_h == 1 && stride_w == 1;
     // A strided convolution: grad_output with (stride - 1) zeros put between its pixels, and as
     // many zero rows and columns behind it as the forward pass left unread, is the input of the

@@ -438,7 +438,8 @@ bool conv2d_igemm_supported(const ConvShape& s) {
     // to one 32-wide K block, which the tensor cores absorb far better than the direct kernel does
     // the gather (3 x 3 x 3 -> 64 on 224 x 224 images: 6.4 ms direct).
     // One or two channels waste too much of it (128 x 1 x 28 x 28, 5 x 5: 111 us against 74 us direct).
-    if (s.out_c < 32 || s.in_c < 3) return false;
+    // One or two channels are taken only when a filter row's taps share a K block.
+    if (s.out_c < 32 || (s.in_c < 3 && !conv2d_igemm_row_packed(s))) return false;
     if (static_cast<long long>(s.batch) * oh * ow < 64) return false;
     return true;
 }

@@ -7,8 +7,12 @@ namespace cudeep_b200 {
 
 // True when the tensor-core path takes this shape: sm_100 device, strides 1..8,
 // padding smaller than the filter, at least 32 output channels, at least 3
-// input channels and at least 64 output pixels.
+// input channels (any number when conv2d_igemm_row_packed) and at least 64 output pixels.
 bool conv2d_igemm_supported(const ConvShape& s);
+
+// True when a filter row's taps share one 32-wide K block (KW x the channel count rounded up to a
+// multiple of 4 is at most 32, KW > 1): only for calls without flipped filters or dilation.
+bool conv2d_igemm_row_packed(const ConvShape& s);
 
 // Bytes of scratch one call needs: the NHWC copy of the input followed by the
 // packed filters.  The two optional outputs receive the size of each part.

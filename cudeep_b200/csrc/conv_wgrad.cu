@@ -8,6 +8,10 @@
 // output pixels.  A K block is 32 consecutive pixels of one output row (box_w x box_h = 32 x 1):
 //   * A (K-major): grad_output read in place as a 4-D tensor {OW, OH, OC, N}; the box
 //     {32, 1, 128, 1} lands as one 128-byte row per output channel;
+//     (rows of at most 16 pixels: a copy of grad_output with rows padded to 4, 8 or 16 pixels, whose
+//     planes are then contiguous runs of OH * pitch floats, so that 32 consecutive floats of a plane
+//     are 32 / pitch whole rows - box_w x box_h = pitch x 32 / pitch - and a 7 x 7 feature map fills
+//     28 of a block's 32 pixels instead of 7);
 //   * B (MN-major, channels contiguous): the NHWC copy of the input (channels padded to 32) seen
 //     as a 5-D tensor {32, W, H, N, Cp/32}; the box {32, box_w, box_h, 1, chunks}, started at the
 //     tap's offset, lands as 32-channel chunks of 32 pixel rows - the layout the tensor core takes
@@ -38,6 +42,7 @@ struct WgradProblem {
     int n_cols;             // channels per tile (umma_n)
     int cp;                 // padded channels
     int ocp;                // padded output channels: rows of one K range in the scratch
+    int dy_row_pitch;       // > 0: map_dy is {OH * pitch, 1, OC, N} over a copy with rows padded to `pitch`
     int kb_per_range;       // K blocks (pixel boxes) of one range
     int total_kb;           // batch * tiles_h * tiles_w
     int batch;
@@ -81,11 +86,13 @@ struct WgradProblem {
         const int ow0 = (r - th * tiles_w) * box_w;
         const int kh = t.tap / k_w;
         const int kw = t.tap - kh * k_w;
+        const int dy_x = dy_row_pitch > 0 ? oh0 * dy_row_pitch : ow0;
+        const int dy_y = dy_row_pitch > 0 ? 0 : oh0;
         if constexpr (C == 1) {
-            ptx::tma_load_4d(a_smem, &map_dy, bar, ow0, oh0, t.oc0, n);
+            ptx::tma_load_4d(a_smem, &map_dy, bar, dy_x, dy_y, t.oc0, n);
             ptx::tma_load_5d(b_smem, &map_x, bar, 0, ow0 * s_w + kw - p_w, oh0 * s_h + kh - p_h, n, t.cb0 / 32);
         } else {
-            ptx::tma_load_4d_pair(a_smem, &map_dy, bar, ow0, oh0, t.oc0, n);
+            ptx::tma_load_4d_pair(a_smem, &map_dy, bar, dy_x, dy_y, t.oc0, n);
             ptx::tma_load_5d_pair(b_smem, &map_x, bar, 0, ow0 * s_w + kw - p_w, oh0 * s_h + kh - p_h, n, t.cb0 / 32);
         }
     }
@@ -133,6 +140,8 @@ __global__ void wgrad_reduce_kernel(const float* __restrict__ part, float* __res
 }
 
 struct WgradPlan {
+    int dy_pitch;       // floats per row of the grad_output the kernel reads
+    bool narrow;        // rows of at most 16 pixels: several rows per K block, always from a padded copy
     int ctas, box_w, box_h, n_cols, c_tiles, ranges, kb_per_range, tiles_w, tiles_h, cp, ocp;
     size_t nhwc_bytes, part_bytes;
 };
@@ -157,11 +166,19 @@ WgradPlan plan_wgrad(const ConvShape& s, int num_sms) {
         p.n_cols = widest(32);
     }
     p.c_tiles = p.cp / p.n_cols;
-    // A K block is 32 consecutive pixels of one output row.  (Boxes of 16 x 2 or 8 x 4 pixels would
-    // waste fewer pixels of narrow images, but a swizzled TMA box whose inner extent is under 128
-    // bytes is not packed densely in shared memory, so grad_output could not be read in place.)
+    // A K block is 32 consecutive pixels of one output row.  A swizzled TMA box whose inner extent
+    // is under 128 bytes is not packed densely in shared memory, so boxes of 16 x 2 or 8 x 4 pixels
+    // cannot be read from grad_output in place; for rows of at most 16 pixels they are read from
+    // a copy whose rows are padded to 4, 8 or 16, as 32 consecutive floats of a plane.
+    p.narrow = ow <= 16;
+    p.dy_pitch = round_up(ow, 4);
     p.box_w = 32;
     p.box_h = 1;
+    if (p.narrow) {
+        p.dy_pitch = ow <= 4 ? 4 : ow <= 8 ? 8 : 16;
+        p.box_w = p.dy_pitch;
+        p.box_h = 32 / p.dy_pitch;
+    }
     p.tiles_w = (ow + p.box_w - 1) / p.box_w;
     p.tiles_h = (oh + p.box_h - 1) / p.box_h;
     const long long total_kb = static_cast<long long>(s.batch) * p.tiles_h * p.tiles_w;
@@ -183,8 +200,8 @@ WgradPlan plan_wgrad(const ConvShape& s, int num_sms) {
     return p;
 }
 
-// dy_pitch: floats between consecutive rows of grad_output as passed here (OW, or OW rounded up to
-// a multiple of 4 when a padded copy had to be made).
+// dy_pitch: floats between consecutive rows of grad_output as passed here (OW, or the plan's
+// pitch when a padded copy had to be made).
 template <int CTAS, int KATOMS>
 void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, const ConvShape& s,
                   const WgradPlan& p, cudaStream_t stream) {
@@ -195,7 +212,13 @@ void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, c
     const int taps = s.k_h * s.k_w;
 
     Prob prob;
-    {
+    if (p.narrow) {
+        const uint64_t plane = uint64_t(oh) * dy_pitch;
+        const uint64_t dims[4] = {plane, 1, uint64_t(s.out_c), uint64_t(s.batch)};
+        const uint64_t strides[3] = {plane * 4, plane * 4, uint64_t(s.out_c) * plane * 4};
+        const uint32_t box[4] = {32, 1, UMMA_BM, 1};
+        encode_tensor_map(&prob.map_dy, dy, 4, dims, strides, box, TmaSwizzle::B128);
+    } else {
         const uint64_t dims[4] = {uint64_t(ow), uint64_t(oh), uint64_t(s.out_c), uint64_t(s.batch)};
         const uint64_t strides[3] = {uint64_t(dy_pitch) * 4, uint64_t(oh) * dy_pitch * 4,
                                      uint64_t(s.out_c) * oh * dy_pitch * 4};
@@ -232,6 +255,7 @@ void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, c
     prob.n_cols = p.n_cols;
     prob.cp = p.cp;
     prob.ocp = p.ocp;
+    prob.dy_row_pitch = p.narrow ? dy_pitch : 0;
     prob.kb_per_range = p.kb_per_range;
     prob.total_kb = s.batch * p.tiles_h * p.tiles_w;
     prob.batch = s.batch;
@@ -277,8 +301,8 @@ void conv2d_wgrad_igemm(const float* grad_output, const float* input, float* gra
     // The tensor map of grad_output needs 16-byte-aligned rows: when OW is not a multiple of 4 (14 x 14
     // and 7 x 7 feature maps) or the pointer is unaligned, a padded copy is read instead.
     const int oh = s.out_h(), ow = s.out_w();
-    const bool copy_dy = (ow % 4 != 0) || (reinterpret_cast<uintptr_t>(grad_output) & 15u) != 0;
-    const int dy_pitch = (ow + 3) / 4 * 4;
+    const int dy_pitch = p.dy_pitch;
+    const bool copy_dy = ow != dy_pitch || (reinterpret_cast<uintptr_t>(grad_output) & 15u) != 0;
     const size_t part_bytes = (p.part_bytes + 1023) / 1024 * 1024;
     const size_t dy_bytes = copy_dy ? static_cast<size_t>(s.batch) * s.out_c * oh * dy_pitch * sizeof(float) : 0;
     char* scratch = static_cast<char*>(scratch_alloc(p.nhwc_bytes + part_bytes + dy_bytes, stream));

@@ -80,6 +80,8 @@ def test_direct_path_shapes(dev, oracle, shape, oc, k, stride, padding):
     ((2, 8, 16, 16), 64, (3, 4), (1, 2)),        # row-packed, eight channels per tap, even filter width
     ((1, 5, 14, 18), 256, (5, 3), (2, 1)),       # row-packed, five channels in eight slots, CTA pair, odd row count
     ((1, 16, 12, 12), 32, (2, 2), (0, 0)),       # row-packed, two taps of sixteen channels
+    ((4, 1, 28, 28), 32, (5, 5), (2, 2)),        # row-packed, a single input channel
+    ((2, 2, 20, 24), 64, (3, 3), (1, 1)),        # row-packed, two input channels
     ((2, 3, 9, 300), 64, (1, 7), (0, 3)),        # row-packed, a single filter row, rows wider than one tile
     ((1, 32, 6, 300), 64, (3, 3), (1, 1)),       # rows wider than one tile
     ((2, 32, 12, 16), 160, (3, 3), (1, 1)),      # bulk-store tiles whose rows past OC = 160 must not reach image 1
@@ -109,6 +111,7 @@ def test_tensor_core_path_shapes(dev, oracle, shape, oc, k, padding, act):
     ((2, 64, 16, 16), 256, (1, 1), (2, 2), (0, 0)),      # 1 x 1 stride 2 projection, CTA pair
     ((1, 32, 20, 33), 64, (3, 3), (1, 3), (1, 1)),       # different strides per direction, width not a multiple
     ((2, 40, 39, 39), 96, (5, 5), (4, 4), (2, 2)),       # stride 4
+    ((6, 32, 27, 27), 64, (3, 3), (2, 2), (1, 1)),       # 14 x 14 outputs: grad_weight reads two padded rows per K block
 ])
 @pytest.mark.parametrize("act", [0, 1])
 def test_strided_tensor_core_path_shapes(dev, lib, oracle, shape, oc, k, stride, padding, act):
@@ -234,7 +237,11 @@ def test_backward_against_oracle(dev, lib, oracle, shape, oc, k, stride, padding
     ((1, 16, 20, 20), 32, (1, 1), (0, 0)),      # 1 x 1 filter, channels padded 16 -> 32
     ((5, 32, 9, 12), 40, (3, 3), (0, 0)),       # 7 x 10 outputs: rows of 10 floats, read through a padded copy
     ((4, 48, 14, 14), 64, (3, 3), (1, 1)),      # 14 x 14 feature maps
-    ((8, 64, 7, 7), 128, (3, 3), (1, 1)),       # 7 x 7 feature maps
+    ((8, 64, 7, 7), 128, (3, 3), (1, 1)),       # 7 x 7 feature maps: four rows padded to 8 pixels per K block
+    ((16, 32, 4, 4), 32, (3, 3), (1, 1)),       # rows of 4 pixels: eight rows per K block, the image has four
+    ((2, 32, 16, 16), 64, (3, 3), (1, 1)),      # rows of 16: two rows per K block, read without a padded copy
+    ((8, 32, 7, 5), 32, (3, 3), (1, 1)),        # 7 rows of 5 pixels: the last K block of an image is one row short
+    ((3, 40, 11, 12), 48, (3, 5), (0, 2)),      # 9 rows of 12 pixels padded to 16, no vertical padding
     ((2, 16, 6, 6), 32, (3, 3), (1, 1)),        # 72 output pixels: too few, the direct kernel
 ])
 def test_backward_weight_tensor_core_path(dev, lib, oracle, shape, oc, k, padding):
