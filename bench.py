@@ -64,7 +64,7 @@ def parse_args():
                          "cuBLAS / cuDNN (through torch) and the reference's kernels; one JSON line each")
     ap.add_argument("--only", default="", help="with --suite: run only the configurations whose name starts "
                                                "with one of these comma-separated tags (C1, C2, C3, C4; "
-                                               "B1 matmul backward, B2 conv backward, S1 small-batch Linear, H1 FP16 GEMM; "
+                                               "B1 matmul backward, B2 conv backward, V1 other conv layers, S1 small-batch Linear, H1 FP16 GEMM; "
                                                "G1, only when named: small GEMMs timed inside a CUDA graph)")
     ap.add_argument("--no-comparators", action="store_true",
                     help="with --suite: time only this library (short runs for profiling)")
@@ -472,6 +472,8 @@ def run_suite(args):
         run_b1(lib, ref, timed, emit, ok, P, stream, trim)
     if want("B2"):
         run_b2(lib, ref, timed, emit, ok, P, stream, trim)
+    if want("V1"):
+        run_v1(lib, timed, emit, ok, P, stream, trim)
     if want("S1"):
         run_s1(lib, ref, timed, emit, ok, P, stream, trim)
     if want("H1"):
@@ -613,6 +615,40 @@ def run_b2(lib, ref, timed, emit, ok, P, stream, trim):
     rows = {"ours": timed(lambda: ok(lib.cudeep_b200_conv2d_backward_weight_f32(P(dy), P(x), P(dw), *geom, stream)), 15),
             "cudnn_tf32_torch": timed(lambda: torch.nn.grad.conv2d_weight(x, w.shape, dy, padding=1), 15, cmp=True)}
     emit("B2 conv backward grad_weight, C4 layer", flops, trim(rows))
+
+
+def run_v1(lib, timed, emit, ok, P, stream, trim):
+    """Convolution layers of a ResNet-style network other than C4, batch 64: a 7 x 7 stride-2 stem over
+    three channels, a stride-2 down-sampling layer and the 14 x 14 and 7 x 7 feature maps; forward
+    (bias, no activation), grad_input and grad_weight against cuDNN (TF32) through torch."""
+    import torch
+    import torch.nn.functional as F
+    from cudeep_b200 import workloads
+    torch.backends.cudnn.allow_tf32 = True
+    torch.backends.cudnn.benchmark = True
+    nb = 64
+    for ch, size, oc, k, s, p in [(3, 224, 64, 7, 2, 3), (64, 56, 128, 3, 2, 1), (256, 14, 256, 3, 1, 1),
+                                  (512, 7, 512, 3, 1, 1)]:
+        out = (size + 2 * p - k) // s + 1
+        x = torch.randn((nb, ch, size, size), device="cuda")
+        w = torch.randn((oc, ch, k, k), device="cuda") * (2.0 / (ch * k * k)) ** 0.5
+        b = (torch.rand(oc, device="cuda") * 2 - 1) * 0.01
+        y = torch.empty((nb, oc, out, out), device="cuda")
+        dy = torch.randn((nb, oc, out, out), device="cuda")
+        dx, dw = torch.empty_like(x), torch.empty_like(w)
+        geom = (nb, ch, oc, size, size, k, k, s, s, p, p)
+        flops = workloads.conv_flops(nb, ch, oc, out, out, k, k)
+        tag = f"{nb}x{ch}x{size}x{size} -> {oc}, {k}x{k} stride {s}"
+        rows = {"ours": timed(lambda: ok(lib.cudeep_b200_conv2d_forward_f32(P(x), P(w), P(b), P(y), *geom, stream)), 15),
+                "cudnn_tf32_torch": timed(lambda: F.conv2d(x, w, b, stride=s, padding=p), 15, cmp=True)}
+        emit(f"V1 conv forward {tag}", flops, trim(rows))
+        if ch >= 32:        # a stem's input is the images: no network asks for their gradient
+            rows = {"ours": timed(lambda: ok(lib.cudeep_b200_conv2d_backward_data_f32(P(dy), P(w), P(dx), *geom, stream)), 15),
+                    "cudnn_tf32_torch": timed(lambda: torch.nn.grad.conv2d_input(x.shape, w, dy, stride=s, padding=p), 15, cmp=True)}
+            emit(f"V1 conv grad_input {tag}", flops, trim(rows))
+        rows = {"ours": timed(lambda: ok(lib.cudeep_b200_conv2d_backward_weight_f32(P(dy), P(x), P(dw), *geom, stream)), 15),
+                "cudnn_tf32_torch": timed(lambda: torch.nn.grad.conv2d_weight(x, w.shape, dy, stride=s, padding=p), 15, cmp=True)}
+        emit(f"V1 conv grad_weight {tag}", flops, trim(rows))
 
 
 def run_s1(lib, ref, timed, emit, ok, P, stream, trim):

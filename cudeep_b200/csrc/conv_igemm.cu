@@ -82,8 +82,8 @@ __device__ __forceinline__ void pack_filters(const FilterPack& f, long long bloc
 // 32-channel x 64-pixel tiles through shared memory: reads coalesce along HW, writes along C.
 // With HW a multiple of 4 both sides move 128 bits per thread (a warp reads 512 contiguous
 // bytes of one channel and writes four pixels' 128-byte channel runs); otherwise scalars.
-// With `with_filters`, the blocks of one extra z slice pack the filters instead (one launch for
-// both preparations of a convolution).
+// With `with_filters`, the blocks of the z slices past the batch pack the filters instead (one
+// launch for both preparations of a convolution).
 // With SCATTER, source pixel (r, q) of a src_w-wide plane lands at (r * d_h, q * d_w) of a
 // dst_w-wide plane of dst_hw pixels per image (zeroed by the caller beforehand).
 struct PixelScatter {
@@ -99,9 +99,10 @@ __global__ void __launch_bounds__(256)
 nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, int hw, int cx, int batch,
                     FilterPack filters, int with_filters, PixelScatter scatter = PixelScatter{}) {
     __shared__ float tile[32][65];
-    if (with_filters && int(blockIdx.z) == batch) {
-        pack_filters(filters, static_cast<long long>(blockIdx.y) * gridDim.x + blockIdx.x,
-                     static_cast<long long>(gridDim.x) * gridDim.y, 256);
+    if (with_filters && int(blockIdx.z) >= batch) {
+        const long long per_slice = static_cast<long long>(gridDim.x) * gridDim.y;
+        pack_filters(filters, (int(blockIdx.z) - batch) * per_slice + blockIdx.y * gridDim.x + blockIdx.x,
+                     per_slice * (int(gridDim.z) - batch), 256);
         return;
     }
     const int n = blockIdx.z;
@@ -149,7 +150,7 @@ nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, 
 
 // ------------------------------------------------------------------ problem policy
 
-template <int CTAS>
+template <int CTAS, bool ROW_PACKED = false>
 struct ConvProblem {
     // When a tile's pixels are contiguous in the output plane (box_w == OW) the output is the 2-D
     // tensor {OH*OW, N*OC} and goes out by bulk tensor stores like a GEMM's C; otherwise registers.
@@ -168,7 +169,7 @@ struct ConvProblem {
     int s_h, s_w;          // convolution strides: the box walks the input in these steps
     int total_kb;          // K blocks of the reduction: KH * KW * c_blocks
     int batch;
-    int row_packed;        // one K block per filter row (see launch_conv): map_x is the window view
+    // ROW_PACKED: one K block per filter row (see launch_conv), map_x is the window view.
     int contig;            // box_w == OW: the tile's pixels are contiguous in the output plane
     int vec_ok;            // 128-bit stores are aligned for every tile
 
@@ -221,8 +222,8 @@ struct ConvProblem {
         const int c0 = (kb - tap * c_blocks) * UMMA_BK;
         // Row-packed: K block kb is filter row kb, and coordinate 1 counts output columns (each
         // the start of a window of KW pixels in the width-padded copy).
-        const int kh = row_packed ? kb : tap / k_w;
-        const int x1 = row_packed ? t.ow0 : t.ow0 * s_w + (tap - kh * k_w) - p_w;
+        const int kh = ROW_PACKED ? kb : tap / k_w;
+        const int x1 = ROW_PACKED ? t.ow0 : t.ow0 * s_w + (tap - kh * k_w) - p_w;
         // A K block past the end of the reduction (a stage's padding) must read zeros on
         // both sides: the filter coordinate is out of range by itself, the image index is
         // pushed out of range here.
@@ -304,11 +305,12 @@ TilePlan plan_tile(int oh, int ow, int ctas, int s_h, int s_w) {
     return best;
 }
 
-template <int CTAS, int KATOMS>
+template <int CTAS, int KATOMS, bool ROW_PACKED>
 void launch_conv(const float* xt, const float* wp, const float* bias, float* out, const ConvShape& s,
-                 int cx, int cp, const TilePlan& plan, int act, cudaStream_t stream, bool row_packed) {
+                 int cx, int cp, const TilePlan& plan, int act, cudaStream_t stream) {
     using Cfg = UmmaConfig<CTAS, 256, false, KATOMS>;
-    using Prob = ConvProblem<CTAS>;
+    using Prob = ConvProblem<CTAS, ROW_PACKED>;
+    constexpr bool row_packed = ROW_PACKED;
     const DeviceInfo& dev = device_info();
     const int oh = s.out_h(), ow = s.out_w();
     // Row-packed: the K blocks are the KH filter rows, each one 32-wide block.
@@ -358,7 +360,6 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     prob.s_h = s.s_h;
     prob.s_w = s.s_w;
     prob.total_kb = taps * prob.c_blocks;
-    prob.row_packed = row_packed ? 1 : 0;
     prob.batch = s.batch;
     prob.contig = (plan.box_w == ow) ? 1 : 0;
     prob.vec_ok = (prob.contig && ((plan.box_h * ow) % 4 == 0) && ((oh * ow) % 4 == 0) &&
@@ -409,7 +410,20 @@ namespace {
 // One launch: the input re-layout and, in an extra z slice of blocks, the filter packing.
 void prepare_operands(const float* input, float* xt, int batch, int c, int hw, int cx, const FilterPack* filters,
                       cudaStream_t stream, const PixelScatter* scatter = nullptr) {
-    dim3 grid((hw + 63) / 64, (cx + 31) / 32, batch + (filters ? 1 : 0));
+    // Filter packing takes as many extra z slices as give it about one block per 2048 elements
+    // (small feature maps have few blocks per slice, and their filters are the large ones).
+    int filter_slices = 0;
+    if (filters) {
+        const long long elems = static_cast<long long>(filters->oc_n) * filters->k_h *
+                                (filters->row_cx > 0 ? UMMA_BK : filters->k_w * filters->cp);
+        const long long per_slice = static_cast<long long>((hw + 63) / 64) * ((cx + 31) / 32);
+        long long want = (elems + 2047) / 2048;
+        if (want > 148 * 8) want = 148 * 8;
+        filter_slices = static_cast<int>((want + per_slice - 1) / per_slice);
+        if (filter_slices < 1) filter_slices = 1;
+        if (filter_slices > 1024) filter_slices = 1024;
+    }
+    dim3 grid((hw + 63) / 64, (cx + 31) / 32, batch + filter_slices);
     CB200_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "conv2d: too many channels or images");
     const bool vec = (hw % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
     const FilterPack f = filters ? *filters : FilterPack{};
@@ -516,8 +530,13 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
     CB200_REQUIRE(plan.box_w > 0, "conv2d: no tile shape fits this output size");
     // A CTA pair stages at most 32 KB per K block, so two blocks share a pipeline
     // stage and the barrier handshake is paid half as often.
-    if (ctas == 2) launch_conv<2, 2>(xt, wp, bias, output, s, cx, cp, plan, act, stream, row_packed);
-    else launch_conv<1, 1>(xt, wp, bias, output, s, cx, cp, plan, act, stream, row_packed);
+    if (row_packed) {
+        if (ctas == 2) launch_conv<2, 2, true>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+        else launch_conv<1, 1, true>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+    } else {
+        if (ctas == 2) launch_conv<2, 2, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+        else launch_conv<1, 1, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+    }
 }
 
 void conv2d_igemm(const float* input, const float* weight, const float* bias, float* output,
