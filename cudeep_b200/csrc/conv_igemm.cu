@@ -150,7 +150,7 @@ nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, 
 
 // ------------------------------------------------------------------ problem policy
 
-template <int CTAS, bool ROW_PACKED = false>
+template <int CTAS, bool ROW_PACKED = false, bool MULTI_IMAGE = false>
 struct ConvProblem {
     // When a tile's pixels are contiguous in the output plane (box_w == OW) the output is the 2-D
     // tensor {OH*OW, N*OC} and goes out by bulk tensor stores like a GEMM's C; otherwise registers.
@@ -162,6 +162,7 @@ struct ConvProblem {
     float* out;
     int oc_n, oh_n, ow_n;
     int box_w, box_h;      // output pixels per tile: box_h rows of box_w
+    int box_n;             // MULTI_IMAGE: images per tile (each one whole: box_w >= OW, box_h >= OH)
     int tiles_w, tiles_h;  // tiles per image
     int c_blocks;          // Cp / 32
     int k_w;
@@ -177,6 +178,7 @@ struct ConvProblem {
         int oc0;           // first output channel of this CTA
         int n, oh0, ow0;   // image and first output pixel of the tile
         int hb0;           // first output row whose pixels this CTA stages as B
+        int nb0;           // image whose pixels this CTA stages as B (MULTI_IMAGE: its first image)
     };
 
     __device__ __forceinline__ void prefetch_maps() const {
@@ -206,6 +208,14 @@ struct ConvProblem {
     __device__ __forceinline__ Tile decode(int tm, int tn, uint32_t cta_rank) const {
         Tile t;
         t.oc0 = (tm * CTAS + int(cta_rank)) * UMMA_BM;
+        if constexpr (MULTI_IMAGE) {
+            // The CTAs of a pair split the tile's images, not its rows, so the accumulator
+            // columns stay in (image, row, column) order.
+            t.n = tn * box_n;
+            t.oh0 = t.ow0 = t.hb0 = 0;
+            t.nb0 = t.n + int(cta_rank) * (box_n / CTAS);
+            return t;
+        }
         const int per_image = tiles_h * tiles_w;
         t.n = tn / per_image;
         const int r = tn - t.n * per_image;
@@ -213,6 +223,7 @@ struct ConvProblem {
         t.oh0 = th * box_h;
         t.ow0 = (r - th * tiles_w) * box_w;
         t.hb0 = t.oh0 + int(cta_rank) * (box_h / CTAS);
+        t.nb0 = t.n;
         return t;
     }
     template <int C>
@@ -227,7 +238,7 @@ struct ConvProblem {
         // A K block past the end of the reduction (a stage's padding) must read zeros on
         // both sides: the filter coordinate is out of range by itself, the image index is
         // pushed out of range here.
-        const int n = kb < total_kb ? t.n : batch;
+        const int n = kb < total_kb ? t.nb0 : batch;
         if constexpr (C == 1) {
             ptx::tma_load_2d(a_smem, &map_w, bar, kb * UMMA_BK, t.oc0);
             ptx::tma_load_4d(b_smem, &map_x, bar, c0, x1, t.hb0 * s_h + kh - p_h, n);
@@ -246,6 +257,19 @@ struct ConvProblem {
             for (int j = 0; j < 32; ++j) v[j] += b;
         }
         apply_activation(v, epi.act);
+        if constexpr (MULTI_IMAGE) {
+            const int per_image = box_w * box_h;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int col = c0 + j;
+                const int img = col / per_image;
+                const int rem = col - img * per_image;
+                const int oh = rem / box_w, ow = rem - oh * box_w;
+                if (t.n + img < batch && oh < oh_n && ow < ow_n)
+                    out[((static_cast<long long>(t.n + img) * oc_n + oc) * oh_n + oh) * ow_n + ow] = v[j];
+            }
+            return;
+        }
         float* plane = out + (static_cast<long long>(t.n) * oc_n + oc) * oh_n * ow_n;
         if (contig) {
             const int rows = min(box_h, oh_n - t.oh0);
@@ -275,6 +299,7 @@ struct ConvProblem {
 
 struct TilePlan {
     int box_w = 0, box_h = 0;
+    int box_n = 1;      // > 1: whole images per tile (small feature maps)
 };
 
 // Output-pixel box of one tile: box_h rows of box_w pixels, box_w * box_h a
@@ -305,11 +330,45 @@ TilePlan plan_tile(int oh, int ow, int ctas, int s_h, int s_w) {
     return best;
 }
 
-template <int CTAS, int KATOMS, bool ROW_PACKED>
+// Small feature maps: a tile of box_n whole images (box_w >= OW, box_h >= OH, box_n a multiple of
+// the CTAs that split it), so that the filter slab a CTA stages per K block is used by up to 256
+// accumulator columns instead of one image's 49 or 16.  Taken when it wastes fewer columns than
+// the best single-image box, or as few with more columns per tile.
+TilePlan plan_multi_image_tile(int oh, int ow, int batch, int ctas, int s_h, int s_w, const TilePlan& single) {
+    TilePlan best = single;
+    if (oh * ow > 128 || batch < 2) return best;
+    auto score_of = [&](int bw, int bh, int bn, int tiles) {
+        const double eff = double(oh) * ow * batch / (double(tiles) * bw * bh * bn);
+        return eff + 1e-4 * (bw * bh * bn) / 256.0;
+    };
+    double best_score = -1.0;
+    if (single.box_w > 0) {
+        const int tiles = ((ow + single.box_w - 1) / single.box_w) * ((oh + single.box_h - 1) / single.box_h) * batch;
+        best_score = score_of(single.box_w, single.box_h, 1, tiles);
+    }
+    for (int bw = ow; bw <= ow + 7 && bw * s_w <= 256; ++bw)
+        for (int bh = oh; bh <= oh + 7 && bh * s_h <= 256; ++bh)
+            for (int bn = ctas; bw * bh * bn <= 256; bn += ctas) {
+                if (bn < 2 || (bw * bh * bn) % 32 != 0) continue;
+                const double score = score_of(bw, bh, bn, (batch + bn - 1) / bn);
+                if (score > best_score + 1e-9) {
+                    best_score = score;
+                    best.box_w = bw;
+                    best.box_h = bh;
+                    best.box_n = bn;
+                }
+            }
+    return best;
+}
+
+template <int CTAS, int KATOMS, bool ROW_PACKED, bool MULTI_IMAGE>
 void launch_conv(const float* xt, const float* wp, const float* bias, float* out, const ConvShape& s,
                  int cx, int cp, const TilePlan& plan, int act, cudaStream_t stream) {
     using Cfg = UmmaConfig<CTAS, 256, false, KATOMS>;
-    using Prob = ConvProblem<CTAS, ROW_PACKED>;
+    using Prob = ConvProblem<CTAS, ROW_PACKED, MULTI_IMAGE>;
+    // Rows and images of the pixel box one CTA stages.
+    const uint32_t cta_rows = uint32_t(MULTI_IMAGE ? plan.box_h : plan.box_h / CTAS);
+    const uint32_t cta_images = uint32_t(MULTI_IMAGE ? plan.box_n / CTAS : 1);
     constexpr bool row_packed = ROW_PACKED;
     const DeviceInfo& dev = device_info();
     const int oh = s.out_h(), ow = s.out_w();
@@ -332,7 +391,7 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
         const uint64_t dims[4] = {uint64_t(s.k_w) * cx, uint64_t(ow), uint64_t(s.in_h), uint64_t(s.batch)};
         const uint64_t strides[3] = {uint64_t(s.s_w) * cx * 4, uint64_t(wp_pixels) * cx * 4,
                                      uint64_t(s.in_h) * wp_pixels * cx * 4};
-        const uint32_t box[4] = {UMMA_BK, uint32_t(plan.box_w), uint32_t(plan.box_h / CTAS * s.s_h), 1};
+        const uint32_t box[4] = {UMMA_BK, uint32_t(plan.box_w), cta_rows * s.s_h, cta_images};
         const uint32_t steps[4] = {1, 1, uint32_t(s.s_h), 1};
         encode_tensor_map(&prob.map_x, xt, 4, dims, strides, box, TmaSwizzle::B128, steps);
     } else {
@@ -341,7 +400,7 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
                                      uint64_t(s.in_h) * s.in_w * cx * 4};
         // A strided convolution reads every s-th input pixel: the box spans box * s input pixels
         // and the TMA unit walks it in steps of s (element strides), so box_w x box_h pixels land.
-        const uint32_t box[4] = {UMMA_BK, uint32_t(plan.box_w * s.s_w), uint32_t(plan.box_h / CTAS * s.s_h), 1};
+        const uint32_t box[4] = {UMMA_BK, uint32_t(plan.box_w * s.s_w), cta_rows * s.s_h, cta_images};
         const uint32_t steps[4] = {1, uint32_t(s.s_w), uint32_t(s.s_h), 1};
         encode_tensor_map(&prob.map_x, xt, 4, dims, strides, box, TmaSwizzle::B128, steps);
     }
@@ -351,6 +410,7 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     prob.ow_n = ow;
     prob.box_w = plan.box_w;
     prob.box_h = plan.box_h;
+    prob.box_n = plan.box_n;
     prob.tiles_w = (ow + plan.box_w - 1) / plan.box_w;
     prob.tiles_h = (oh + plan.box_h - 1) / plan.box_h;
     prob.c_blocks = cp / UMMA_BK;
@@ -361,7 +421,7 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     prob.s_w = s.s_w;
     prob.total_kb = taps * prob.c_blocks;
     prob.batch = s.batch;
-    prob.contig = (plan.box_w == ow) ? 1 : 0;
+    prob.contig = (plan.box_w == ow && !MULTI_IMAGE) ? 1 : 0;
     prob.vec_ok = (prob.contig && ((plan.box_h * ow) % 4 == 0) && ((oh * ow) % 4 == 0) &&
                    ((reinterpret_cast<uintptr_t>(out) & 15u) == 0)) ? 1 : 0;
     // Bulk stores: contiguous tiles, plane rows of 16-byte multiples, chunk starts on 16-byte
@@ -376,9 +436,11 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
         prob.map_out = prob.map_w;
     }
 
-    const int umma_n = plan.box_w * plan.box_h;
+    const int umma_n = plan.box_w * plan.box_h * plan.box_n;
+    const int pixel_tiles = MULTI_IMAGE ? (s.batch + plan.box_n - 1) / plan.box_n
+                                        : s.batch * prob.tiles_h * prob.tiles_w;
     UmmaSchedule sched = whole_tile_schedule(
-        (s.out_c + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS), s.batch * prob.tiles_h * prob.tiles_w,
+        (s.out_c + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS), pixel_tiles,
         taps * prob.c_blocks, umma_n, (Cfg::A_BYTES + uint32_t(umma_n / CTAS) * UMMA_BK * 4) * CTAS * KATOMS,
         Cfg::STAGES, dev.status_word);
     // Consecutive tiles walk the output-channel tiles of one pixel block, so
@@ -530,12 +592,17 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
     CB200_REQUIRE(plan.box_w > 0, "conv2d: no tile shape fits this output size");
     // A CTA pair stages at most 32 KB per K block, so two blocks share a pipeline
     // stage and the barrier handshake is paid half as often.
+    if (!row_packed) plan = plan_multi_image_tile(oh, ow, s.batch, ctas, s.s_h, s.s_w, plan);
+    CB200_REQUIRE(plan.box_w > 0, "conv2d: no tile shape fits this output size");
     if (row_packed) {
-        if (ctas == 2) launch_conv<2, 2, true>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
-        else launch_conv<1, 1, true>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+        if (ctas == 2) launch_conv<2, 2, true, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+        else launch_conv<1, 1, true, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+    } else if (plan.box_n > 1) {
+        if (ctas == 2) launch_conv<2, 2, false, true>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+        else launch_conv<1, 1, false, true>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
     } else {
-        if (ctas == 2) launch_conv<2, 2, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
-        else launch_conv<1, 1, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+        if (ctas == 2) launch_conv<2, 2, false, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
+        else launch_conv<1, 1, false, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
     }
 }
 

@@ -84,6 +84,10 @@ def test_direct_path_shapes(dev, oracle, shape, oc, k, stride, padding):
     ((2, 2, 20, 24), 64, (3, 3), (1, 1)),        # row-packed, two input channels
     ((2, 3, 9, 300), 64, (1, 7), (0, 3)),        # row-packed, a single filter row, rows wider than one tile
     ((1, 32, 6, 300), 64, (3, 3), (1, 1)),       # rows wider than one tile
+    ((5, 64, 7, 7), 512, (3, 3), (1, 1)),        # 7 x 7 maps: four whole images per tile, CTA pairs, the last tile has one image
+    ((6, 48, 4, 4), 64, (3, 3), (1, 1)),         # 4 x 4 maps: six images fill one tile
+    ((9, 32, 5, 9), 160, (3, 3), (1, 1)),        # 5 x 9 maps, ragged output channels, odd image count
+    ((7, 40, 9, 9), 64, (3, 3), (0, 0)),         # 7 x 7 outputs without padding
     ((2, 32, 12, 16), 160, (3, 3), (1, 1)),      # bulk-store tiles whose rows past OC = 160 must not reach image 1
     ((3, 32, 10, 8), 96, (3, 3), (1, 1)),        # bulk-store tiles taller than the image (rows past OH clipped)
 ])
@@ -111,6 +115,7 @@ def test_tensor_core_path_shapes(dev, oracle, shape, oc, k, padding, act):
     ((2, 64, 16, 16), 256, (1, 1), (2, 2), (0, 0)),      # 1 x 1 stride 2 projection, CTA pair
     ((1, 32, 20, 33), 64, (3, 3), (1, 3), (1, 1)),       # different strides per direction, width not a multiple
     ((2, 40, 39, 39), 96, (5, 5), (4, 4), (2, 2)),       # stride 4
+    ((4, 32, 14, 14), 64, (3, 3), (2, 2), (1, 1)),       # 7 x 7 outputs: several whole images per tile, walked in strides
     ((6, 32, 27, 27), 64, (3, 3), (2, 2), (1, 1)),       # 14 x 14 outputs: grad_weight reads two padded rows per K block
 ])
 @pytest.mark.parametrize("act", [0, 1])
@@ -208,6 +213,7 @@ def test_backward_reference_known_answers(dev, lib):
     ((2, 64, 14, 14), 96, (3, 3), (1, 1), (1, 1), True),    # grad_input on the implicit-GEMM path
     ((1, 160, 12, 20), 48, (5, 5), (1, 1), (2, 2), True),   # 5x5, more input than output channels
     ((2, 32, 10, 10), 64, (3, 3), (1, 1), (0, 0), True),    # no padding: full correlation with pad 2
+    ((6, 64, 7, 7), 96, (3, 3), (1, 1), (1, 1), True),      # 7 x 7 maps: grad_input on tiles of several images
 ])
 def test_backward_against_oracle(dev, lib, oracle, shape, oc, k, stride, padding, tensor_core):
     rng = np.random.default_rng(sum(shape) + oc)
