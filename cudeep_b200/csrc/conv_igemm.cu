@@ -503,6 +503,14 @@ void nchw_to_nhwc(const float* input, float* xt, int batch, int c, int hw, int c
     prepare_operands(input, xt, batch, c, hw, cx, nullptr, stream);
 }
 
+void nchw_to_nhwc_padded(const float* input, float* xt, int batch, int c, int h, int w, int cx, int pad_w,
+                         cudaStream_t stream) {
+    const int wp_pixels = w + 2 * pad_w;
+    CB200_CUDA(cudaMemsetAsync(xt, 0, static_cast<size_t>(batch) * h * wp_pixels * cx * sizeof(float), stream));
+    const PixelScatter scatter{w, wp_pixels, h * wp_pixels, 1, 1, pad_w};
+    prepare_operands(input, xt, batch, c, h * w, cx, nullptr, stream, &scatter);
+}
+
 bool conv2d_igemm_supported(const ConvShape& s) {
     if (device_info().cc_major != 10) return false;
     if (s.s_h < 1 || s.s_w < 1 || s.s_h > 8 || s.s_w > 8) return false;     // TMA element strides go up to 8

@@ -44,6 +44,11 @@ void conv2d_igemm(const float* input, const float* weight, const float* bias, fl
 // x[N][C][HW] -> xt[N][HW][cx] with cx >= C a multiple of 4 (channels past C are zero).
 void nchw_to_nhwc(const float* input, float* xt, int batch, int c, int hw, int cx, cudaStream_t stream);
 
+// x[N][C][H][W] -> xt[N][H][W + 2 * pad_w][cx] with pad_w zero pixels on either side of every row
+// (the input layout of the row-packed form).
+void nchw_to_nhwc_padded(const float* input, float* xt, int batch, int c, int h, int w, int cx, int pad_w,
+                         cudaStream_t stream);
+
 // grad_weight as an implicit GEMM over output pixels (conv_wgrad.cu): strides 1..8, at least 32
 // output channels and 256 output pixels.
 bool conv2d_wgrad_igemm_supported(const ConvShape& s);

@@ -27,7 +27,11 @@ namespace cudeep_b200 {
 
 namespace {
 
-template <int CTAS>
+// ROW_PACKED (few input channels): one tile per filter row instead of per tap; map_x is the view
+// {KW * Cx, OW, H, N, 1} of the width-padded input copy, whose rows are the windows of KW pixels x Cx
+// channels the output columns read (the forward path's row-packed form), so the 32 columns of a
+// tile are a filter row's (tap, channel) pairs.
+template <int CTAS, bool ROW_PACKED = false>
 struct WgradProblem {
     static constexpr bool kTmaStore = true;
     static constexpr bool kClusterSplit = false;
@@ -84,16 +88,16 @@ struct WgradProblem {
         const int th = r / tiles_w;
         const int oh0 = th * box_h;
         const int ow0 = (r - th * tiles_w) * box_w;
-        const int kh = t.tap / k_w;
-        const int kw = t.tap - kh * k_w;
+        const int kh = ROW_PACKED ? t.tap : t.tap / k_w;
+        const int x1 = ROW_PACKED ? ow0 : ow0 * s_w + (t.tap - kh * k_w) - p_w;
         const int dy_x = dy_row_pitch > 0 ? oh0 * dy_row_pitch : ow0;
         const int dy_y = dy_row_pitch > 0 ? 0 : oh0;
         if constexpr (C == 1) {
             ptx::tma_load_4d(a_smem, &map_dy, bar, dy_x, dy_y, t.oc0, n);
-            ptx::tma_load_5d(b_smem, &map_x, bar, 0, ow0 * s_w + kw - p_w, oh0 * s_h + kh - p_h, n, t.cb0 / 32);
+            ptx::tma_load_5d(b_smem, &map_x, bar, 0, x1, oh0 * s_h + kh - p_h, n, t.cb0 / 32);
         } else {
             ptx::tma_load_4d_pair(a_smem, &map_dy, bar, dy_x, dy_y, t.oc0, n);
-            ptx::tma_load_5d_pair(b_smem, &map_x, bar, 0, ow0 * s_w + kw - p_w, oh0 * s_h + kh - p_h, n, t.cb0 / 32);
+            ptx::tma_load_5d_pair(b_smem, &map_x, bar, 0, x1, oh0 * s_h + kh - p_h, n, t.cb0 / 32);
         }
     }
     __device__ __forceinline__ const CUtensorMap* out_map() const { return &map_part; }
@@ -139,7 +143,29 @@ __global__ void wgrad_reduce_kernel(const float* __restrict__ part, float* __res
     }
 }
 
+// Row-packed tiles: dw[oc][c][kh][kw] = sum over ranges of part[range][oc][kh * 32 + kw * cx + c].
+__global__ void wgrad_reduce_rows_kernel(const float* __restrict__ part, float* __restrict__ dw, int ranges,
+                                         int oc_n, int ocp, int c_n, int cx, int k_h, int k_w) {
+    const long long total = static_cast<long long>(oc_n) * c_n * k_h * k_w;
+    const long long row_len = static_cast<long long>(k_h) * UMMA_BK;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int kw = static_cast<int>(i % k_w);
+        long long r = i / k_w;
+        const int kh = static_cast<int>(r % k_h);
+        r /= k_h;
+        const int c = static_cast<int>(r % c_n);
+        const long long oc = r / c_n;
+        const float* src = part + oc * row_len + kh * UMMA_BK + kw * cx + c;
+        float acc = 0.0f;
+        for (int s = 0; s < ranges; ++s) acc += src[static_cast<long long>(s) * ocp * row_len];
+        dw[i] = acc;
+    }
+}
+
 struct WgradPlan {
+    bool row_packed;    // few input channels: one tile per filter row
+    int taps;           // tiles per channel tile: KH * KW, or KH when row-packed
     int dy_pitch;       // floats per row of the grad_output the kernel reads
     bool narrow;        // rows of at most 16 pixels: several rows per K block, always from a padded copy
     int ctas, box_w, box_h, n_cols, c_tiles, ranges, kb_per_range, tiles_w, tiles_h, cp, ocp;
@@ -153,6 +179,8 @@ WgradPlan plan_wgrad(const ConvShape& s, int num_sms) {
     const int oh = s.out_h(), ow = s.out_w();
     p.ctas = s.out_c > UMMA_BM ? 2 : 1;
     p.cp = round_up(s.in_c, UMMA_BK);
+    p.row_packed = conv2d_igemm_row_packed(s);
+    p.taps = p.row_packed ? s.k_h : s.k_h * s.k_w;
     // Channels per tile: the widest multiple of one 32-channel chunk per CTA, at most 256, that
     // divides the padded channel count (a tile never reaches into the next tap's columns).
     auto widest = [&](int step) {
@@ -184,7 +212,7 @@ WgradPlan plan_wgrad(const ConvShape& s, int num_sms) {
     const long long total_kb = static_cast<long long>(s.batch) * p.tiles_h * p.tiles_w;
     const int tiles_m = (s.out_c + UMMA_BM * p.ctas - 1) / (UMMA_BM * p.ctas);
     p.ocp = tiles_m * UMMA_BM * p.ctas;
-    const long long base_tiles = static_cast<long long>(tiles_m) * s.k_h * s.k_w * p.c_tiles;
+    const long long base_tiles = static_cast<long long>(tiles_m) * p.taps * p.c_tiles;
     // Enough K ranges to give every CTA (pair) a unit, each at least 16 K blocks long.
     const long long slots = num_sms / p.ctas;
     long long ranges = slots / base_tiles;
@@ -195,21 +223,24 @@ WgradPlan plan_wgrad(const ConvShape& s, int num_sms) {
     per = (per + 1) / 2 * 2;                              // whole pipeline stages of two K blocks
     p.kb_per_range = static_cast<int>(per);
     p.ranges = static_cast<int>((total_kb + per - 1) / per);
-    p.nhwc_bytes = (static_cast<size_t>(s.batch) * s.in_h * s.in_w * p.cp * sizeof(float) + 1023) / 1024 * 1024;
-    p.part_bytes = static_cast<size_t>(p.ranges) * p.ocp * s.k_h * s.k_w * p.cp * sizeof(float);
+    const size_t nhwc = p.row_packed
+        ? static_cast<size_t>(s.batch) * s.in_h * (s.in_w + 2 * s.p_w) * round_up(s.in_c, 4) * sizeof(float)
+        : static_cast<size_t>(s.batch) * s.in_h * s.in_w * p.cp * sizeof(float);
+    p.nhwc_bytes = (nhwc + 1023) / 1024 * 1024;
+    p.part_bytes = static_cast<size_t>(p.ranges) * p.ocp * p.taps * p.cp * sizeof(float);
     return p;
 }
 
 // dy_pitch: floats between consecutive rows of grad_output as passed here (OW, or the plan's
 // pitch when a padded copy had to be made).
-template <int CTAS, int KATOMS>
+template <int CTAS, int KATOMS, bool ROW_PACKED = false>
 void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, const ConvShape& s,
                   const WgradPlan& p, cudaStream_t stream) {
     using Cfg = UmmaConfig<CTAS, 256, true, KATOMS>;
-    using Prob = WgradProblem<CTAS>;
+    using Prob = WgradProblem<CTAS, ROW_PACKED>;
     const DeviceInfo& dev = device_info();
     const int oh = s.out_h(), ow = s.out_w();
-    const int taps = s.k_h * s.k_w;
+    const int taps = p.taps;
 
     Prob prob;
     if (p.narrow) {
@@ -225,7 +256,16 @@ void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, c
         const uint32_t box[4] = {uint32_t(p.box_w), uint32_t(p.box_h), UMMA_BM, 1};
         encode_tensor_map(&prob.map_dy, dy, 4, dims, strides, box, TmaSwizzle::B128);
     }
-    {
+    if (ROW_PACKED) {
+        const int cx = round_up(s.in_c, 4);
+        const uint64_t wp_pixels = uint64_t(s.in_w) + 2 * s.p_w;
+        const uint64_t dims[5] = {uint64_t(s.k_w) * cx, uint64_t(ow), uint64_t(s.in_h), uint64_t(s.batch), 1};
+        const uint64_t strides[4] = {uint64_t(s.s_w) * cx * 4, wp_pixels * cx * 4,
+                                     uint64_t(s.in_h) * wp_pixels * cx * 4, 128};
+        const uint32_t box[5] = {32, uint32_t(p.box_w), uint32_t(p.box_h * s.s_h), 1, 1};
+        const uint32_t steps[5] = {1, 1, uint32_t(s.s_h), 1, 1};
+        encode_tensor_map(&prob.map_x, xt, 5, dims, strides, box, TmaSwizzle::B128Atom32, steps);
+    } else {
         const uint64_t dims[5] = {32, uint64_t(s.in_w), uint64_t(s.in_h), uint64_t(s.batch), uint64_t(p.cp / 32)};
         const uint64_t strides[4] = {uint64_t(p.cp) * 4, uint64_t(s.in_w) * p.cp * 4,
                                      uint64_t(s.in_h) * s.in_w * p.cp * 4, 128};
@@ -319,14 +359,22 @@ void conv2d_wgrad_igemm(const float* grad_output, const float* input, float* gra
             CB200_CHECK_LAUNCH();
             dy = padded;
         }
-        nchw_to_nhwc(input, xt, s.batch, s.in_c, s.in_h * s.in_w, p.cp, stream);
-        if (p.ctas == 2) launch_wgrad<2, 2>(dy, copy_dy ? dy_pitch : ow, xt, part, s, p, stream);
-        else launch_wgrad<1, 1>(dy, copy_dy ? dy_pitch : ow, xt, part, s, p, stream);
         const long long total = static_cast<long long>(s.out_c) * s.in_c * s.k_h * s.k_w;
         long long blocks = (total + 255) / 256;
         if (blocks > 4096) blocks = 4096;
-        wgrad_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-            part, grad_weight, p.ranges, s.out_c, p.ocp, s.in_c, p.cp, s.k_h * s.k_w);
+        if (p.row_packed) {
+            const int cx = round_up(s.in_c, 4);
+            nchw_to_nhwc_padded(input, xt, s.batch, s.in_c, s.in_h, s.in_w, cx, s.p_w, stream);
+            launch_wgrad<1, 1, true>(dy, copy_dy ? dy_pitch : ow, xt, part, s, p, stream);
+            wgrad_reduce_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+                part, grad_weight, p.ranges, s.out_c, p.ocp, s.in_c, cx, s.k_h, s.k_w);
+        } else {
+            nchw_to_nhwc(input, xt, s.batch, s.in_c, s.in_h * s.in_w, p.cp, stream);
+            if (p.ctas == 2) launch_wgrad<2, 2>(dy, copy_dy ? dy_pitch : ow, xt, part, s, p, stream);
+            else launch_wgrad<1, 1>(dy, copy_dy ? dy_pitch : ow, xt, part, s, p, stream);
+            wgrad_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+                part, grad_weight, p.ranges, s.out_c, p.ocp, s.in_c, p.cp, s.k_h * s.k_w);
+        }
         CB200_CHECK_LAUNCH();
     } catch (...) {
         scratch_free(scratch, stream);
