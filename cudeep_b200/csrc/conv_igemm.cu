@@ -331,28 +331,36 @@ TilePlan plan_tile(int oh, int ow, int ctas, int s_h, int s_w) {
 }
 
 // Small feature maps: a tile of box_n whole images (box_w >= OW, box_h >= OH, box_n a multiple of
-// the CTAs that split it), so that the filter slab a CTA stages per K block is used by up to 256
-// accumulator columns instead of one image's 49 or 16.  Taken when it wastes fewer columns than
-// the best single-image box, or as few with more columns per tile.
-TilePlan plan_multi_image_tile(int oh, int ow, int batch, int ctas, int s_h, int s_w, const TilePlan& single) {
+// the CTAs that split it), so that the filter slab a CTA stages per K block is used by more
+// accumulator columns than one image's 49 or 16.  Candidates are ranked by an estimate of the
+// time per K block - the slower of the tensor pipe (about 1.08 ns per accumulator column) and
+// the CTA's operand ingest (about 114 bytes per ns) - times the waves of tiles over the SMs:
+// few large tiles leave SMs idle, many small ones re-read the filters.
+TilePlan plan_multi_image_tile(int oh, int ow, int batch, int ctas, int s_h, int s_w, int tiles_m, int num_sms,
+                               const TilePlan& single) {
     TilePlan best = single;
     if (oh * ow > 128 || batch < 2) return best;
-    auto score_of = [&](int bw, int bh, int bn, int tiles) {
-        const double eff = double(oh) * ow * batch / (double(tiles) * bw * bh * bn);
-        return eff + 1e-4 * (bw * bh * bn) / 256.0;
+    const int slots = num_sms / ctas > 0 ? num_sms / ctas : 1;
+    auto cost_of = [&](int bw, int bh, int bn, long long pixel_tiles) {
+        const int n = bw * bh * bn;
+        const double mma_ns = 1.08 * n;
+        const double ingest_ns = (UMMA_BM * UMMA_BK * 4 + double(n / ctas) * UMMA_BK * 4) / 114.0;
+        const long long waves = (pixel_tiles * tiles_m + slots - 1) / slots;
+        return double(waves) * (mma_ns > ingest_ns ? mma_ns : ingest_ns);
     };
-    double best_score = -1.0;
+    double best_cost = 1e30;
     if (single.box_w > 0) {
-        const int tiles = ((ow + single.box_w - 1) / single.box_w) * ((oh + single.box_h - 1) / single.box_h) * batch;
-        best_score = score_of(single.box_w, single.box_h, 1, tiles);
+        const long long tiles = static_cast<long long>((ow + single.box_w - 1) / single.box_w) *
+                                ((oh + single.box_h - 1) / single.box_h) * batch;
+        best_cost = cost_of(single.box_w, single.box_h, 1, tiles);
     }
     for (int bw = ow; bw <= ow + 7 && bw * s_w <= 256; ++bw)
         for (int bh = oh; bh <= oh + 7 && bh * s_h <= 256; ++bh)
             for (int bn = ctas; bw * bh * bn <= 256; bn += ctas) {
                 if (bn < 2 || (bw * bh * bn) % 32 != 0) continue;
-                const double score = score_of(bw, bh, bn, (batch + bn - 1) / bn);
-                if (score > best_score + 1e-9) {
-                    best_score = score;
+                const double cost = cost_of(bw, bh, bn, (batch + bn - 1) / bn);
+                if (cost < best_cost * 0.999) {
+                    best_cost = cost;
                     best.box_w = bw;
                     best.box_h = bh;
                     best.box_n = bn;
@@ -600,7 +608,9 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
     CB200_REQUIRE(plan.box_w > 0, "conv2d: no tile shape fits this output size");
     // A CTA pair stages at most 32 KB per K block, so two blocks share a pipeline
     // stage and the barrier handshake is paid half as often.
-    if (!row_packed) plan = plan_multi_image_tile(oh, ow, s.batch, ctas, s.s_h, s.s_w, plan);
+    if (!row_packed)
+        plan = plan_multi_image_tile(oh, ow, s.batch, ctas, s.s_h, s.s_w, (s.out_c + UMMA_BM * ctas - 1) / (UMMA_BM * ctas),
+                                     device_info().num_sms, plan);
     CB200_REQUIRE(plan.box_w > 0, "conv2d: no tile shape fits this output size");
     if (row_packed) {
         if (ctas == 2) launch_conv<2, 2, true, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
