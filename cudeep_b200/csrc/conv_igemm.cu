@@ -148,6 +148,35 @@ nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, 
     }
 }
 
+// The same for at most four channels (cx == 4, a network's first layer), where the tiled kernel
+// would leave most of its threads idle: a thread reads four consecutive pixels of every channel
+// (128 bits each) and writes the four pixels' 16-byte channel groups.  hw must be a multiple of 4.
+template <bool SCATTER>
+__global__ void __launch_bounds__(256)
+nchw_to_nhwc4_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, int hw, int batch,
+                     FilterPack filters, int with_filters, PixelScatter scatter) {
+    if (with_filters && int(blockIdx.z) >= batch) {
+        const long long per_slice = static_cast<long long>(gridDim.x) * gridDim.y;
+        pack_filters(filters, (int(blockIdx.z) - batch) * per_slice + blockIdx.y * gridDim.x + blockIdx.x,
+                     per_slice * (int(gridDim.z) - batch), 256);
+        return;
+    }
+    const int n = blockIdx.z;
+    const int p = (blockIdx.x * 256 + threadIdx.x) * 4;
+    if (p >= hw) return;
+    const float* xn = x + static_cast<long long>(n) * c * hw + p;
+    float4 v[4];
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch)
+        v[ch] = ch < c ? *reinterpret_cast<const float4*>(xn + static_cast<long long>(ch) * hw)
+                       : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4* dst = reinterpret_cast<float4*>(xt) + static_cast<long long>(n) * (SCATTER ? scatter.dst_hw : hw);
+    dst[SCATTER ? scatter(p + 0) : p + 0] = make_float4(v[0].x, v[1].x, v[2].x, v[3].x);
+    dst[SCATTER ? scatter(p + 1) : p + 1] = make_float4(v[0].y, v[1].y, v[2].y, v[3].y);
+    dst[SCATTER ? scatter(p + 2) : p + 2] = make_float4(v[0].z, v[1].z, v[2].z, v[3].z);
+    dst[SCATTER ? scatter(p + 3) : p + 3] = make_float4(v[0].w, v[1].w, v[2].w, v[3].w);
+}
+
 // ------------------------------------------------------------------ problem policy
 
 template <int CTAS, bool ROW_PACKED = false, bool MULTI_IMAGE = false>
@@ -498,6 +527,15 @@ void prepare_operands(const float* input, float* xt, int batch, int c, int hw, i
     const bool vec = (hw % 4 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15u) == 0);
     const FilterPack f = filters ? *filters : FilterPack{};
     const int with = filters ? 1 : 0;
+    if (vec && cx == 4) {
+        // (The filter slices were sized for 64-pixel blocks; these blocks cover 1024 pixels, so
+        // there are fewer per slice: the grid-stride loop of the packing absorbs it.)
+        dim3 grid4((hw / 4 + 255) / 256, 1, batch + filter_slices);
+        if (scatter) nchw_to_nhwc4_kernel<true><<<grid4, 256, 0, stream>>>(input, xt, c, hw, batch, f, with, *scatter);
+        else nchw_to_nhwc4_kernel<false><<<grid4, 256, 0, stream>>>(input, xt, c, hw, batch, f, with, PixelScatter{});
+        CB200_CHECK_LAUNCH();
+        return;
+    }
     if (scatter) {
         if (vec) nchw_to_nhwc_kernel<true, true><<<grid, 256, 0, stream>>>(input, xt, c, hw, cx, batch, f, with, *scatter);
         else nchw_to_nhwc_kernel<false, true><<<grid, 256, 0, stream>>>(input, xt, c, hw, cx, batch, f, with, *scatter);
