@@ -114,12 +114,19 @@ struct WgradProblem {
 // the tail: grad_output with 16-byte-aligned rows for the tensor map.
 __global__ void pad_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, long long rows, int ow,
                                 int pitch) {
-    const long long total = rows * pitch;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const long long r = i / pitch;
-        const int q = static_cast<int>(i - r * pitch);
-        dst[i] = q < ow ? src[r * ow + q] : 0.0f;
+    // One 128-bit store per thread; 32-bit index arithmetic (the launcher checks the range).
+    const unsigned quads = static_cast<unsigned>(pitch / 4);
+    const unsigned total = static_cast<unsigned>(rows) * quads;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const unsigned r = i / quads;
+        const int q = static_cast<int>(i - r * quads) * 4;
+        const float* row = src + static_cast<long long>(r) * ow;
+        float4 v;
+        v.x = q + 0 < ow ? row[q + 0] : 0.0f;
+        v.y = q + 1 < ow ? row[q + 1] : 0.0f;
+        v.z = q + 2 < ow ? row[q + 2] : 0.0f;
+        v.w = q + 3 < ow ? row[q + 3] : 0.0f;
+        reinterpret_cast<float4*>(dst)[i] = v;
     }
 }
 
@@ -353,7 +360,8 @@ void conv2d_wgrad_igemm(const float* grad_output, const float* input, float* gra
         if (copy_dy) {
             float* padded = reinterpret_cast<float*>(scratch + p.nhwc_bytes + part_bytes);
             const long long rows = static_cast<long long>(s.batch) * s.out_c * oh;
-            long long blocks = (rows * dy_pitch + 255) / 256;
+            CB200_REQUIRE(rows * (dy_pitch / 4) < (1LL << 31), "conv2d backward: grad_output too large to pad");
+            long long blocks = (rows * (dy_pitch / 4) + 255) / 256;
             if (blocks > 148 * 16) blocks = 148 * 16;
             pad_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(grad_output, padded, rows, ow, dy_pitch);
             CB200_CHECK_LAUNCH();
