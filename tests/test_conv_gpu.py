@@ -248,6 +248,8 @@ def test_backward_against_oracle(dev, lib, oracle, shape, oc, k, stride, padding
     ((2, 32, 16, 16), 64, (3, 3), (1, 1)),      # rows of 16: two rows per K block, read without a padded copy
     ((8, 32, 7, 5), 32, (3, 3), (1, 1)),        # 7 rows of 5 pixels: the last K block of an image is one row short
     ((3, 40, 11, 12), 48, (3, 5), (0, 2)),      # 9 rows of 12 pixels padded to 16, no vertical padding
+    ((2, 32, 24, 24), 32, (10, 10), (4, 4)),    # 10 x 10 filters: 100 tiles per channel tile
+    ((2, 200, 12, 16), 40, (3, 3), (1, 1)),     # 200 channels padded to 224: one tile of 224 columns
     ((4, 3, 20, 20), 64, (3, 3), (1, 1)),       # three input channels: one tile per filter row
     ((8, 8, 12, 12), 32, (3, 4), (1, 2)),       # row-packed and short rows (13 pixels padded to 16) together
     ((2, 1, 40, 40), 160, (5, 5), (2, 2)),      # a single input channel, 160 output channels
