@@ -169,9 +169,9 @@ int cudeep_b200_conv2d_forward_fused_f32(const float* input, const float* weight
  * filters) lives in a 32 MiB array built into the library, which every GPU that loads
  * the library holds until the process exits.
  *   - Shapes whose scratch exceeds cudeep_b200_conv2d_noalloc_capacity() are refused
- *     with an error that states both sizes (C*H*W*batch*4 bytes, channels rounded up
- *     to 4, plus the filters with channels rounded up to 32).  Shapes the tensor-core
- *     path does not take (stride > 1, tiny) run the direct kernel and need no scratch.
+ *     with an error that states both sizes (C*H*(W + 2*pad_w)*batch*4 bytes, channels
+ *     rounded up to 4, plus the filters with channels rounded up to 32).  Shapes the
+ *     tensor-core path does not take (tiny, stride > 8) run the direct kernel and need no scratch.
  *   - The first call on each device looks up the array's device address; make that
  *     call before starting any stream capture.
  *   - All calls on a device share the one array and it keeps the previous call's
@@ -197,8 +197,9 @@ int cudeep_b200_conv2d_forward_f64(const double* input, const double* weight, co
 /* Gradients of the convolution.  Replace launch_conv2d_backward_data_kernel<float> and
  * launch_conv2d_backward_weight_kernel<float> (include/cudeep/kernels/conv.cuh:18-36,
  * src/kernels/conv_kernel.cu:417-545).  in_h / in_w are the forward input's size.
- * grad_input runs on the forward tensor-core path for stride 1 (TF32), otherwise both are
- * strict FP32. */
+ * Both run on the tensor cores (TF32) for layers with at least 32 output channels: grad_input
+ * with at least 32 input channels and stride_h * stride_w <= 16, grad_weight with at least 256
+ * output pixels and strides up to 8; strict FP32 kernels otherwise. */
 int cudeep_b200_conv2d_backward_data_f32(const float* grad_output, const float* weight, float* grad_input,
                                          int batch, int in_channels, int out_channels, int in_h, int in_w,
                                          int kernel_h, int kernel_w, int stride_h, int stride_w, int pad_h,
