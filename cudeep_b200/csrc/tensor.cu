@@ -111,10 +111,10 @@ Tensor Tensor::ones(const std::vector<int64_t>& shape, DType dtype) {
 }
 
 Tensor Tensor::randn(const std::vector<int64_t>& shape, DType dtype) {
-    return randn(shape, dtype, g_randn_counter.fetch_add(0x632be59bd9b4e019ull));
+    return randn_seeded(shape, dtype, g_randn_counter.fetch_add(0x632be59bd9b4e019ull));
 }
 
-Tensor Tensor::randn(const std::vector<int64_t>& shape, DType dtype, uint64_t seed) {
+Tensor Tensor::randn_seeded(const std::vector<int64_t>& shape, DType dtype, uint64_t seed) {
     CB200_REQUIRE(dtype == DType::Float32 || dtype == DType::Float64, "randn: float32 or float64 only");
     Tensor t(shape, dtype);
     const int64_t n = t.numel();

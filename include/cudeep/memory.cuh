@@ -17,6 +17,9 @@
 //     without a stream mean the legacy default stream.
 #pragma once
 
+#include "common.cuh"
+#include "error.cuh"
+
 #include <cuda_runtime.h>
 #include <cstddef>
 #include <mutex>

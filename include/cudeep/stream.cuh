@@ -6,6 +6,9 @@
 // outlive the stream they worked on.
 #pragma once
 
+#include "common.cuh"
+#include "error.cuh"
+
 #include <cuda_runtime.h>
 
 namespace cudeep {

@@ -26,6 +26,7 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "_build" / "liboracle.so"
 REF_LIB_PATH = HERE / "_ref" / "libcudeep_ref.so"
+DROPIN_DIR = HERE / "_ref" / "dropin"
 
 EPI_NONE, EPI_RELU, EPI_GELU, EPI_SILU, EPI_SIGMOID = range(5)
 INPUT_EXACT, INPUT_TF32_TRUNC, INPUT_TF32_ROUND = range(3)
@@ -33,10 +34,27 @@ INPUT_EXACT, INPUT_TF32_TRUNC, INPUT_TF32_ROUND = range(3)
 _lib = None
 
 
-def build(ref: bool = False) -> None:
-    """Compile the C oracle (and, with ref=True and the reference tree present, its kernels)."""
-    targets = ["oracle"] + (["ref"] if ref else [])
-    subprocess.run(["make", "-s", "-C", str(HERE), *targets], check=True)
+def reference_dir() -> Path | None:
+    """Root of a cuDeep checkout: $CUDEEP_REFERENCE_DIR, else a directory named `reference`
+    beside this repository; None when neither holds the reference's sources."""
+    import os
+    candidates = [os.environ.get("CUDEEP_REFERENCE_DIR"), HERE.parent.parent / "reference"]
+    for c in candidates:
+        if c and (Path(c) / "src" / "kernels" / "matmul_kernel.cu").exists():
+            return Path(c)
+    return None
+
+
+def build(ref: bool = False, dropin: bool = False) -> None:
+    """Compile the C oracle.  With ref / dropin and a cuDeep checkout at hand (reference_dir()),
+    also the reference's kernels as a checker library, and the drop-in proof (the reference's
+    binding module, remaining kernels and C++ tests built on this repository's headers and
+    library; see oracle/Makefile)."""
+    subprocess.run(["make", "-s", "-C", str(HERE), "oracle"], check=True)
+    where = reference_dir()
+    targets = (["ref"] if ref else []) + (["dropin"] if dropin else [])
+    if targets and where is not None:
+        subprocess.run(["make", "-s", "-C", str(HERE), *targets, f"REFERENCE={where}"], check=True)
 
 
 def lib() -> ctypes.CDLL:

@@ -63,7 +63,7 @@ static void test_tensor_basics() {
     std::vector<float> hs = host_of(s), hd = host_of(d), hp = host_of(p);
     for (int i = 0; i < 24; ++i) CHECK(hs[i] == 2 * iota[i] && hd[i] == 0.0f && hp[i] == iota[i] * iota[i]);
     for (float v : host_of(Tensor::ones({5}))) CHECK(v == 1.0f);
-    Tensor z = Tensor::randn({1000}, DType::Float32, 7), z2 = Tensor::randn({1000}, DType::Float32, 7);
+    Tensor z = Tensor::randn_seeded({1000}, DType::Float32, 7), z2 = Tensor::randn_seeded({1000}, DType::Float32, 7);
     CHECK(host_of(z) == host_of(z2));
     std::printf("[PASS] tensor basics\n");
 }
@@ -79,7 +79,7 @@ static void test_tensor_matmul() {
     std::vector<float> c24 = host_of(Tensor::from_host(a23.data(), {2, 3}).matmul(Tensor::from_host(b34.data(), {3, 4})));
     CHECK(c24[0] == 1 && c24[1] == 2 && c24[2] == 3 && c24[3] == 0 && c24[4] == 4 && c24[6] == 6 && c24[7] == 0);
     // 8x8 times identity
-    Tensor r = Tensor::randn({8, 8}, DType::Float32, 3);
+    Tensor r = Tensor::randn_seeded({8, 8}, DType::Float32, 3);
     std::vector<float> eye(64, 0.0f);
     for (int i = 0; i < 8; ++i) eye[i * 9] = 1.0f;
     std::vector<float> hr = host_of(r), hri = host_of(r.matmul(Tensor::from_host(eye.data(), {8, 8})));
@@ -100,7 +100,7 @@ static void test_tensor_matmul() {
 
 static void test_tf32_product_against_host() {
     const int m = 384, n = 512, k = 256;
-    Tensor a = Tensor::randn({m, k}, DType::Float32, 11), b = Tensor::randn({k, n}, DType::Float32, 12);
+    Tensor a = Tensor::randn_seeded({m, k}, DType::Float32, 11), b = Tensor::randn_seeded({k, n}, DType::Float32, 12);
     std::vector<float> ha = host_of(a), hb = host_of(b), hc = host_of(a.matmul(b));
     double num = 0.0, den = 0.0;
     for (int i = 0; i < m; i += 7) {
@@ -158,7 +158,7 @@ static void test_pool_and_events() {
     device_free(q);
     Stream s;
     Event e0, e1;
-    Tensor a = Tensor::randn({512, 512}, DType::Float32, 1);
+    Tensor a = Tensor::randn_seeded({512, 512}, DType::Float32, 1);
     a.set_stream(s.get());
     e0.record(s.get());
     Tensor c = a.matmul(a);
@@ -176,7 +176,7 @@ static void test_stream_aware_pool() {
     const size_t bytes = (4u << 20) + 512;                      // a size class of its own
     void* p = pool.allocate(bytes, s1.get());
     // A few milliseconds of work on s1, then the block is released behind it.
-    Tensor a = Tensor::randn({4096, 4096}, DType::Float32, 3);
+    Tensor a = Tensor::randn_seeded({4096, 4096}, DType::Float32, 3);
     a.set_stream(s1.get());
     Tensor c1 = a.matmul(a), c2 = a.matmul(a), c3 = a.matmul(a), c4 = a.matmul(a);
     pool.deallocate(p, s1.get());

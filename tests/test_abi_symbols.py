@@ -10,7 +10,7 @@ ROOT = Path(__file__).resolve().parents[1]
 HEADER = ROOT / "include" / "cudeep_b200.h"
 
 # Itanium-mangled launchers of the reference's C++ surface
-# (include/cudeep/kernels/matmul.cuh:8-44 and conv.cuh:8-16 in the cuDeep tree).
+# (include/cudeep/kernels/matmul.cuh:8-44 and conv.cuh:8-36 in the cuDeep tree).
 CXX_SYMBOLS = [
     "_ZN6cudeep7kernels20launch_matmul_kernelIfEEvPKT_S4_PS2_iiiP11CUstream_st",
     "_ZN6cudeep7kernels20launch_matmul_kernelIdEEvPKT_S4_PS2_iiiP11CUstream_st",
@@ -22,6 +22,10 @@ CXX_SYMBOLS = [
     "_ZN6cudeep7kernels23launch_matmul_fused_actEPKfS2_PfiiiNS0_12GemmEpilogueEP11CUstream_st",
     "_ZN6cudeep7kernels28launch_conv2d_forward_kernelIfEEvPKT_S4_S4_PS2_iiiiiiiiiiiP11CUstream_st",
     "_ZN6cudeep7kernels28launch_conv2d_forward_kernelIdEEvPKT_S4_S4_PS2_iiiiiiiiiiiP11CUstream_st",
+    "_ZN6cudeep7kernels34launch_conv2d_backward_data_kernelIfEEvPKT_S4_PS2_iiiiiiiiiiiP11CUstream_st",
+    "_ZN6cudeep7kernels34launch_conv2d_backward_data_kernelIdEEvPKT_S4_PS2_iiiiiiiiiiiP11CUstream_st",
+    "_ZN6cudeep7kernels36launch_conv2d_backward_weight_kernelIfEEvPKT_S4_PS2_iiiiiiiiiiiP11CUstream_st",
+    "_ZN6cudeep7kernels36launch_conv2d_backward_weight_kernelIdEEvPKT_S4_PS2_iiiiiiiiiiiP11CUstream_st",
 ]
 
 

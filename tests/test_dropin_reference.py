@@ -1,0 +1,122 @@
+"""The drop-in, proven with the reference's own sources and tests.
+
+oracle/Makefile's `dropin` target compiles cuDeep's UNMODIFIED src/bindings/module.cpp, its eight
+kernel files outside the dense-contraction path and its four C++ unit tests against this
+repository's include/cudeep headers, and links them to cudeep_b200/libcudeep_b200.so in place of the
+reference's own tensor.cu / memory.cu / stream.cu / matmul_kernel.cu / conv_kernel.cu
+(CMakeLists.txt:26-47,73 in the cuDeep tree).  The result, oracle/_ref/dropin/, also holds a staged
+copy of the reference's Python package and Python tests so that a GPU machine without the checkout
+can run them.
+
+CPU tests: the build succeeds with no unresolved symbol and the module imports with every name the
+reference's python/cuDeep/_core.py:3-34 asks for.  GPU tests: the reference's C++ tests and its
+whole Python test suite run, unedited, on top of this library.
+"""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+
+# what python/cuDeep/_core.py:3-34 imports from _cudeep_core
+CORE_NAMES = """Tensor DType Layout Stream Event MemoryPool relu sigmoid tanh_act gelu silu leaky_relu
+broadcast_add scalar_mul div_op neg exp_op log_op sqrt_op pow_op abs_op clamp_op gt_mask sum mean max min
+sum_reduce_rows softmax mse_loss cross_entropy_loss conv2d_forward conv2d_backward_data
+conv2d_backward_weight max_pool2d avg_pool2d batchnorm_forward layernorm_forward activation_backward
+sgd_update adam_update adamw_update device_info""".split()
+
+
+@pytest.fixture(scope="module")
+def dropin(lib):
+    """oracle/_ref/dropin, (re)built when a cuDeep checkout is at hand and the library or the public
+    headers are newer than the last build; used as found otherwise."""
+    from cudeep_b200 import _lib
+    from oracle import oracle as o
+    import sysconfig
+    module = o.DROPIN_DIR / ("_cudeep_core" + sysconfig.get_config_var("EXT_SUFFIX"))
+    if o.reference_dir() is not None:
+        inputs = [_lib.LIB_PATH, *(ROOT / "include" / "cudeep").rglob("*.cuh"), ROOT / "oracle" / "Makefile"]
+        if not module.exists() or module.stat().st_mtime < max(p.stat().st_mtime for p in inputs):
+            o.build(dropin=True)
+    if not module.exists():
+        pytest.skip("oracle/_ref/dropin not built (needs a cuDeep checkout at build time)")
+    return o.DROPIN_DIR, module
+
+
+def run_python(dropin_dir, args, timeout=1200):
+    env = dict(os.environ)
+    env["PYTHONPATH"] = os.pathsep.join([str(dropin_dir), str(dropin_dir / "python")])
+    return subprocess.run([sys.executable, *args], cwd=dropin_dir, env=env, capture_output=True, text=True,
+                          timeout=timeout)
+
+
+def test_reference_module_needs_this_library_and_nothing_is_unresolved(dropin):
+    from cudeep_b200 import _lib
+    _, module = dropin
+    needed = subprocess.run(["readelf", "-d", str(module)], capture_output=True, text=True, check=True).stdout
+    assert "libcudeep_b200.so" in needed
+    assert "libcudeep.so" not in needed
+    ours = subprocess.run(["nm", "-D", "--defined-only", str(_lib.LIB_PATH)], capture_output=True, text=True,
+                          check=True).stdout
+    exported = {line.split()[-1] for line in ours.splitlines() if line.strip()}
+    wanted = subprocess.run(["nm", "-D", "--undefined-only", str(module)], capture_output=True, text=True,
+                            check=True).stdout
+    cudeep_syms = [line.split()[-1] for line in wanted.splitlines() if "6cudeep" in line]
+    assert len(cudeep_syms) >= 30                      # Tensor, MemoryPool, Stream, Event, launchers
+    missing = [s for s in cudeep_syms if s not in exported]
+    assert not missing, f"reference module wants symbols this library does not export: {missing}"
+    assert any("launch_conv2d_backward_weight_kernelIf" in s for s in cudeep_syms)
+    assert any("6Tensor6matmul" in s for s in cudeep_syms)
+
+
+def test_reference_package_imports_on_the_module(dropin):
+    """`import cuDeep` (the reference's package, unedited) on the module built above; no GPU needed."""
+    d, module = dropin
+    code = ("import _cudeep_core as c, cuDeep, cuDeep._core as k;"
+            f"names = {CORE_NAMES!r};"
+            "missing = [n for n in names if not hasattr(c, n)];"
+            "assert not missing, missing;"
+            "assert k.Tensor is c.Tensor;"
+            "print(c.__file__); print(cuDeep.__file__)")
+    proc = run_python(d, ["-c", code], timeout=300)
+    assert proc.returncode == 0, proc.stdout + proc.stderr
+    first, second = proc.stdout.split()[:2]
+    assert Path(first) == module
+    assert Path(second).parent == d / "python" / "cuDeep"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["test_matmul", "test_tensor", "test_kernels", "test_advanced_kernels"])
+def test_reference_cxx_unit_tests_pass(dropin, cuda, name):
+    """tests/unit/{test_matmul,test_tensor,test_kernels,test_advanced_kernels}.cu of the cuDeep tree:
+    plain executables whose asserts abort on a wrong answer (tests/CMakeLists.txt:3-21)."""
+    d, _ = dropin
+    proc = subprocess.run([str(d / "bin" / name)], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-4000:] + proc.stderr[-4000:]
+
+
+@pytest.mark.gpu
+def test_reference_on_path_python_tests_pass(dropin, cuda):
+    """The cases that pin this path in the reference: tests/unit/test_tensor_ops.py:210-262 (matmul),
+    test_nn.py:29-82 (Linear, Conv2d), test_layers.py:58-75."""
+    d, _ = dropin
+    proc = run_python(d, ["-m", "pytest", "-q", "-p", "no:cacheprovider",
+                          "pytests/unit/test_tensor_ops.py", "pytests/unit/test_nn.py",
+                          "pytests/unit/test_layers.py"])
+    assert proc.returncode == 0, proc.stdout[-6000:] + proc.stderr[-3000:]
+    assert " passed" in proc.stdout and " failed" not in proc.stdout
+
+
+@pytest.mark.gpu
+def test_reference_whole_python_suite_passes(dropin, cuda):
+    """Everything else the reference tests from Python (autograd, optimisers, functional ops, the
+    training-loop integration tests, its loose performance gates): those kernels are the reference's
+    own, but they allocate, copy and synchronise through this library's Tensor / MemoryPool / Stream."""
+    d, _ = dropin
+    proc = run_python(d, ["-m", "pytest", "-q", "-p", "no:cacheprovider", "pytests/unit", "pytests/integration",
+                          "pytests/performance"], timeout=2400)
+    assert proc.returncode == 0, proc.stdout[-8000:] + proc.stderr[-3000:]
+    assert " passed" in proc.stdout and " failed" not in proc.stdout

@@ -499,6 +499,40 @@ def test_c3_linear_stack_reduced_batch(dev, oracle):
     assert oracle.rel_frobenius(y, y_ref) <= TF32_TOL
 
 
+def test_c3_linear_stack_full_batch_sampled_rows(dev, oracle):
+    """C3 as specified: X[8192, 4096] -> Linear(4096 -> 16384, bias, GELU) -> Linear(16384 -> 4096, bias),
+    both layers through the fused launch the benchmark times.  The float64 oracle checks 64 sampled rows
+    (all columns) of the hidden activation and of the output; column checksums cover every tile."""
+    x, w1, b1, w2, b2 = workloads.c3_linear_stack()
+    m = x.shape[0]
+    h = dev.linear(x, w1, b1, act=2)
+    y = dev.linear(h, w2, b2)
+    assert h.shape == (8192, 16384) and y.shape == (8192, 4096)
+    assert not np.isnan(h).any() and not np.isnan(y).any()
+    rows = np.sort(np.random.default_rng(33).choice(m, size=64, replace=False))
+    check_tf32(oracle, h, x, w1, 4096, b_is_nk=True, bias=b1, act=2, rows=rows)
+    # layer 2 on the hidden rows the GPU produced (isolates the second launch) ...
+    check_tf32(oracle, y, h, w2, 16384, b_is_nk=True, bias=b2, rows=rows)
+    # ... and the whole stack against float64 from the inputs
+    h_ref = oracle.linear(x[rows], w1, b1, act=2)
+    y_ref = oracle.linear(h_ref.astype(np.float32), w2, b2)
+    assert oracle.rel_frobenius(y[rows], y_ref) <= TF32_TOL
+    # column checksums over all 8192 rows: sum_i (H W2^T + b2)[i, :] = (sum_i H[i, :]) W2^T + m b2,
+    # and the same identity for layer 1 launched without its activation
+    want = h.sum(axis=0, dtype=np.float64) @ w2.astype(np.float64).T + m * b2.astype(np.float64)
+    got = y.sum(axis=0, dtype=np.float64)
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= TF32_TOL
+    del y
+    pre = dev.linear(x, w1, b1, act=0)
+    want = x.sum(axis=0, dtype=np.float64) @ w1.astype(np.float64).T + m * b1.astype(np.float64)
+    got = pre.sum(axis=0, dtype=np.float64)
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= TF32_TOL
+    # GELU applied where it should be: the fused output equals the oracle's activation of the
+    # pre-activation values this library produced (sampled rows)
+    sample = pre[rows[:4]]
+    assert np.max(np.abs(h[rows[:4]] - oracle.activation(sample, 2))) <= 2e-5 * max(1.0, float(np.max(np.abs(sample))))
+
+
 # ---- host-buffer entry point ---------------------------------------------------------------
 
 def test_matmul_host_buffers(lib, cuda, oracle):
