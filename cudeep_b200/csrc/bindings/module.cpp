@@ -19,6 +19,7 @@
 #include "cudeep/tensor.cuh"
 #include "cudeep_b200.h"
 
+#include <cstdint>
 #include <stdexcept>
 #include <string>
 
@@ -36,8 +37,7 @@ Tensor contiguous_of(const Tensor& t) { return t.contiguous(); }
 Tensor activation(const Tensor& t, int code, const char* name) {
     if (t.dtype() != DType::Float32) throw std::runtime_error(std::string(name) + ": float32 only");
     Tensor in = contiguous_of(t);
-    Tensor out(in.shape(), in.dtype());
-    out.set_stream(in.stream());
+    Tensor out(in.shape(), in.dtype(), in.stream());
     check_abi(cudeep_b200_activation_f32(static_cast<const float*>(in.data()), static_cast<float*>(out.data()),
                                          in.numel(), code, in.stream()));
     return out;
@@ -47,19 +47,45 @@ struct ConvDims {
     int B, IC, IH, IW, OC, KH, KW, SH, SW, PH, PW, OH, OW;
 };
 
-ConvDims conv_dims(const std::vector<int64_t>& ishape, const std::vector<int64_t>& wshape,
+// Extents of a convolution from the shapes of its operands.  Everything the kernels and their
+// tensor maps will assume is checked here, before any launch: a mismatch must be a Python
+// RuntimeError, never a read past the smaller buffer.
+ConvDims conv_dims(const char* op, const std::vector<int64_t>& ishape, const std::vector<int64_t>& wshape,
                    const std::vector<int>& stride, const std::vector<int>& padding) {
+    const std::string who(op);
     if (ishape.size() != 4 || wshape.size() != 4 || stride.size() != 2 || padding.size() != 2)
-        throw std::runtime_error("conv2d: expected 4-D input and weight, 2 strides and 2 paddings");
+        throw std::runtime_error(who + ": expected 4-D input and weight, 2 strides and 2 paddings");
+    for (int64_t v : ishape)
+        if (v < 1 || v > INT32_MAX) throw std::runtime_error(who + ": input extents must be positive 32-bit values");
+    for (int64_t v : wshape)
+        if (v < 1 || v > INT32_MAX) throw std::runtime_error(who + ": weight extents must be positive 32-bit values");
+    if (wshape[1] != ishape[1])
+        throw std::runtime_error(who + ": weight has " + std::to_string(wshape[1]) + " input channels, input has " +
+                                 std::to_string(ishape[1]));
     ConvDims d{};
     d.B = static_cast<int>(ishape[0]); d.IC = static_cast<int>(ishape[1]);
     d.IH = static_cast<int>(ishape[2]); d.IW = static_cast<int>(ishape[3]);
     d.OC = static_cast<int>(wshape[0]); d.KH = static_cast<int>(wshape[2]); d.KW = static_cast<int>(wshape[3]);
     d.SH = stride[0]; d.SW = stride[1]; d.PH = padding[0]; d.PW = padding[1];
-    if (d.SH <= 0 || d.SW <= 0) throw std::runtime_error("conv2d: stride must be positive");
+    if (d.SH <= 0 || d.SW <= 0) throw std::runtime_error(who + ": stride must be positive");
+    if (d.PH < 0 || d.PW < 0) throw std::runtime_error(who + ": padding must not be negative");
+    if (d.IH + 2 * d.PH < d.KH || d.IW + 2 * d.PW < d.KW)
+        throw std::runtime_error(who + ": kernel larger than the padded input");
     d.OH = (d.IH + 2 * d.PH - d.KH) / d.SH + 1;
     d.OW = (d.IW + 2 * d.PW - d.KW) / d.SW + 1;
     return d;
+}
+
+void require_same_dtype(const char* op, const Tensor& a, const Tensor& b, const char* what) {
+    if (a.dtype() != b.dtype()) throw std::runtime_error(std::string(op) + ": " + what + " must have the input's dtype");
+}
+
+void require_grad_output_shape(const char* op, const Tensor& go, const ConvDims& d) {
+    const std::vector<int64_t> want{d.B, d.OC, d.OH, d.OW};
+    if (go.shape() != want)
+        throw std::runtime_error(std::string(op) + ": grad_output must be [" + std::to_string(d.B) + ", " +
+                                 std::to_string(d.OC) + ", " + std::to_string(d.OH) + ", " + std::to_string(d.OW) +
+                                 "] for these shapes");
 }
 
 // A name the reference's Python layer imports but that lies outside this library.
@@ -163,8 +189,7 @@ PYBIND11_MODULE(_cudeep_core, m) {
         if (mat.shape().size() != 2 || r.shape().size() != 1 || mat.shape()[1] != r.shape()[0] ||
             mat.dtype() != r.dtype())
             throw std::runtime_error("broadcast_add: requires matrix [N,M] and row [M], got incompatible shapes");
-        Tensor out(mat.shape(), mat.dtype());
-        out.set_stream(mat.stream());
+        Tensor out(mat.shape(), mat.dtype(), mat.stream());
         const long long rows = mat.shape()[0];
         const int cols = static_cast<int>(mat.shape()[1]);
         if (mat.dtype() == DType::Float32)
@@ -189,8 +214,7 @@ PYBIND11_MODULE(_cudeep_core, m) {
         const int mrows = static_cast<int>(xc.numel() / k);
         std::vector<int64_t> oshape(xc.shape().begin(), xc.shape().end() - 1);
         oshape.push_back(n);
-        Tensor out(oshape, xc.dtype());
-        out.set_stream(xc.stream());
+        Tensor out(oshape, xc.dtype(), xc.stream());
         Tensor bias;
         const void* bptr = nullptr;
         if (!bias_obj.is_none()) {
@@ -223,8 +247,7 @@ PYBIND11_MODULE(_cudeep_core, m) {
         const int64_t nn = tn ? b.shape()[1] : b.shape()[0];
         if (kk != (tn ? b.shape()[0] : b.shape()[1]))
             throw std::runtime_error("matmul_nt / matmul_tn: inner dimensions do not match");
-        Tensor out({mm, nn}, DType::Float32);
-        out.set_stream(a.stream());
+        Tensor out({mm, nn}, DType::Float32, a.stream());
         auto fn = tn ? kernels::launch_matmul_tn : kernels::launch_matmul_nt;
         fn(static_cast<const float*>(a.data()), static_cast<const float*>(b.data()), static_cast<float*>(out.data()),
            static_cast<int>(mm), static_cast<int>(nn), static_cast<int>(kk), a.stream());
@@ -236,15 +259,17 @@ PYBIND11_MODULE(_cudeep_core, m) {
     m.def("conv2d_forward", [](const Tensor& input, const Tensor& weight, py::object bias_obj,
                                std::vector<int> stride, std::vector<int> padding) {
         Tensor inp = contiguous_of(input), w = contiguous_of(weight);
-        const ConvDims d = conv_dims(inp.shape(), w.shape(), stride, padding);
-        Tensor out({d.B, d.OC, d.OH, d.OW}, inp.dtype());
-        out.set_stream(inp.stream());
+        const ConvDims d = conv_dims("conv2d_forward", inp.shape(), w.shape(), stride, padding);
+        require_same_dtype("conv2d_forward", inp, w, "weight");
         Tensor bias;
         const void* bptr = nullptr;
         if (!bias_obj.is_none()) {
             bias = contiguous_of(bias_obj.cast<Tensor>());
+            require_same_dtype("conv2d_forward", inp, bias, "bias");
+            if (bias.numel() != d.OC) throw std::runtime_error("conv2d_forward: bias must have out_channels elements");
             bptr = bias.data();
         }
+        Tensor out({d.B, d.OC, d.OH, d.OW}, inp.dtype(), inp.stream());
         if (inp.dtype() == DType::Float32)
             kernels::launch_conv2d_forward_kernel<float>(
                 static_cast<const float*>(inp.data()), static_cast<const float*>(w.data()),
@@ -265,10 +290,11 @@ PYBIND11_MODULE(_cudeep_core, m) {
                                      std::vector<int64_t> input_shape, std::vector<int> stride,
                                      std::vector<int> padding) {
         Tensor go = contiguous_of(grad_output), w = contiguous_of(weight);
-        const ConvDims d = conv_dims(input_shape, w.shape(), stride, padding);
+        const ConvDims d = conv_dims("conv2d_backward_data", input_shape, w.shape(), stride, padding);
         if (go.dtype() != DType::Float32) throw std::runtime_error("conv2d_backward_data: float32 only");
-        Tensor gi(input_shape, go.dtype());
-        gi.set_stream(go.stream());
+        require_same_dtype("conv2d_backward_data", go, w, "weight");
+        require_grad_output_shape("conv2d_backward_data", go, d);
+        Tensor gi(input_shape, go.dtype(), go.stream());
         kernels::launch_conv2d_backward_data_kernel<float>(
             static_cast<const float*>(go.data()), static_cast<const float*>(w.data()),
             static_cast<float*>(gi.data()), d.B, d.IC, d.OC, d.IH, d.IW, d.KH, d.KW, d.SH, d.SW, d.PH, d.PW,
@@ -281,10 +307,11 @@ PYBIND11_MODULE(_cudeep_core, m) {
                                        std::vector<int64_t> weight_shape, std::vector<int> stride,
                                        std::vector<int> padding) {
         Tensor go = contiguous_of(grad_output), inp = contiguous_of(input);
-        const ConvDims d = conv_dims(inp.shape(), weight_shape, stride, padding);
+        const ConvDims d = conv_dims("conv2d_backward_weight", inp.shape(), weight_shape, stride, padding);
         if (go.dtype() != DType::Float32) throw std::runtime_error("conv2d_backward_weight: float32 only");
-        Tensor gw(weight_shape, go.dtype());
-        gw.set_stream(go.stream());
+        require_same_dtype("conv2d_backward_weight", go, inp, "input");
+        require_grad_output_shape("conv2d_backward_weight", go, d);
+        Tensor gw(weight_shape, go.dtype(), go.stream());
         kernels::launch_conv2d_backward_weight_kernel<float>(
             static_cast<const float*>(go.data()), static_cast<const float*>(inp.data()),
             static_cast<float*>(gw.data()), d.B, d.IC, d.OC, d.IH, d.IW, d.KH, d.KW, d.SH, d.SW, d.PH, d.PW,

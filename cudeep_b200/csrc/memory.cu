@@ -1,4 +1,6 @@
 #include "cudeep/memory.cuh"
+
+#include <new>
 #include "cudeep/stream.cuh"
 #include "runtime.h"
 
@@ -72,6 +74,10 @@ struct DeviceGuard {
             switched = true;
         }
     }
+    // Non-throwing form for release paths: on failure the current device is left as it is.
+    DeviceGuard(int device, std::nothrow_t) noexcept {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != device) switched = cudaSetDevice(device) == cudaSuccess;
+    }
     ~DeviceGuard() {
         if (switched) cudaSetDevice(prev);
     }
@@ -138,28 +144,41 @@ void* MemoryPool::allocate(size_t nbytes, cudaStream_t stream) {
     return ptr;
 }
 
+// Never throws: it runs from destructors (Tensor storage), possibly while another exception
+// unwinds.  When the release event cannot be created or recorded (a context already in error)
+// the block goes straight back to the driver, which waits for the device itself.
 void MemoryPool::deallocate(void* ptr, cudaStream_t stream) {
     if (ptr == nullptr) return;
     std::lock_guard<std::mutex> lock(mutex_);
     auto it = live_blocks_.find(ptr);
     if (it == live_blocks_.end()) return;     // not ours: ignore, as the reference does
     const size_t bin = it->second;
+    live_blocks_.erase(it);
+    allocated_bytes_ -= bin;
     cudaEvent_t ready = nullptr;
+    cudaError_t err = cudaSuccess;
     {
-        DeviceGuard guard(device_);
+        DeviceGuard guard(device_, std::nothrow);
         if (!spare_events_.empty()) {
             ready = spare_events_.back();
             spare_events_.pop_back();
         } else {
-            CB200_CUDA(cudaEventCreateWithFlags(&ready, cudaEventDisableTiming));
+            err = cudaEventCreateWithFlags(&ready, cudaEventDisableTiming);
+            if (err != cudaSuccess) ready = nullptr;
         }
         // A stream of this library that is gone was drained when it was destroyed: nothing is
         // pending on the block.  (Streams created elsewhere must outlive the storage used on them.)
         if (stream_is_dead(stream)) stream = nullptr;
-        CB200_CUDA(cudaEventRecord(ready, stream));
+        if (err == cudaSuccess) err = cudaEventRecord(ready, stream);
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            if (ready != nullptr) spare_events_.push_back(ready);
+            cudaFree(ptr);
+            std::lock_guard<std::mutex> owner_lock(g_owner_mu);
+            g_owner.erase(ptr);
+            return;
+        }
     }
-    live_blocks_.erase(it);
-    allocated_bytes_ -= bin;
     free_blocks_[bin].push_back(FreeBlock{ptr, stream, ready});
     cached_bytes_ += bin;
 }

@@ -17,7 +17,12 @@ struct Tensor::Buffer {
     void* ptr = nullptr;
     cudaStream_t stream = nullptr;
     Buffer(size_t bytes, cudaStream_t s) : ptr(device_malloc(bytes > 0 ? bytes : 1, s)), stream(s) {}
-    ~Buffer() { device_free(ptr, stream); }
+    ~Buffer() {
+        try {
+            device_free(ptr, stream);
+        } catch (...) {      // a destructor must not throw; the pool's release path does not, this is belt and braces
+        }
+    }
     Buffer(const Buffer&) = delete;
     Buffer& operator=(const Buffer&) = delete;
 };

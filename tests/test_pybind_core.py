@@ -169,6 +169,50 @@ def test_conv2d_forward_and_backward(core, cuda, oracle, shape):
 
 
 @pytest.mark.gpu
+def test_conv_bindings_reject_mismatched_operands_before_any_launch(core, cuda):
+    """Every extent the kernels and their tensor maps assume is checked against the operands:
+    a mismatch is a RuntimeError, not a read past the smaller buffer."""
+    T = core.Tensor
+    f32 = lambda *shape: T.from_numpy(np.zeros(shape, np.float32))
+    f64 = lambda *shape: T.from_numpy(np.zeros(shape, np.float64))
+    x, w, b = f32(2, 8, 10, 10), f32(16, 8, 3, 3), f32(16)
+    core.conv2d_forward(x, w, b, [1, 1], [1, 1])                       # the well-formed call works
+    with pytest.raises(RuntimeError, match="input channels"):
+        core.conv2d_forward(x, f32(16, 4, 3, 3), b, [1, 1], [1, 1])
+    with pytest.raises(RuntimeError, match="dtype"):
+        core.conv2d_forward(x, f64(16, 8, 3, 3), None, [1, 1], [1, 1])
+    with pytest.raises(RuntimeError, match="dtype"):
+        core.conv2d_forward(x, w, f64(16), [1, 1], [1, 1])
+    with pytest.raises(RuntimeError, match="out_channels"):
+        core.conv2d_forward(x, w, f32(8), [1, 1], [1, 1])
+    with pytest.raises(RuntimeError, match="kernel larger"):
+        core.conv2d_forward(f32(1, 8, 2, 2), w, None, [1, 1], [0, 0])
+    with pytest.raises(RuntimeError, match="stride"):
+        core.conv2d_forward(x, w, None, [0, 1], [1, 1])
+    with pytest.raises(RuntimeError, match="padding"):
+        core.conv2d_forward(x, w, None, [1, 1], [-1, 1])
+    with pytest.raises(RuntimeError, match="4-D"):
+        core.conv2d_forward(f32(8, 10, 10), w, None, [1, 1], [1, 1])
+    go = f32(2, 16, 10, 10)
+    core.conv2d_backward_data(go, w, [2, 8, 10, 10], [1, 1], [1, 1])
+    core.conv2d_backward_weight(go, x, [16, 8, 3, 3], [1, 1], [1, 1])
+    with pytest.raises(RuntimeError, match="grad_output must be"):
+        core.conv2d_backward_data(f32(2, 16, 9, 10), w, [2, 8, 10, 10], [1, 1], [1, 1])
+    with pytest.raises(RuntimeError, match="grad_output must be"):
+        core.conv2d_backward_data(go, w, [2, 8, 20, 20], [1, 1], [1, 1])
+    with pytest.raises(RuntimeError, match="dtype"):
+        core.conv2d_backward_data(go, f64(16, 8, 3, 3), [2, 8, 10, 10], [1, 1], [1, 1])
+    with pytest.raises(RuntimeError, match="input channels"):
+        core.conv2d_backward_data(go, w, [2, 4, 10, 10], [1, 1], [1, 1])
+    with pytest.raises(RuntimeError, match="grad_output must be"):
+        core.conv2d_backward_weight(f32(2, 8, 10, 10), x, [16, 8, 3, 3], [1, 1], [1, 1])
+    with pytest.raises(RuntimeError, match="dtype"):
+        core.conv2d_backward_weight(go, f64(2, 8, 10, 10), [16, 8, 3, 3], [1, 1], [1, 1])
+    with pytest.raises(RuntimeError, match="input channels"):
+        core.conv2d_backward_weight(go, x, [16, 4, 3, 3], [1, 1], [1, 1])
+
+
+@pytest.mark.gpu
 def test_broadcast_add_rejects_bad_shapes(core, cuda):
     m = core.Tensor.from_numpy(np.ones((4, 6), dtype=np.float32))
     with pytest.raises(RuntimeError, match="broadcast_add"):

@@ -92,8 +92,11 @@ def test_conv_3x3_both_within_bounds(ref, dev, oracle):
 # fast_gelu_ptx / fast_silu_ptx / fast_sigmoid_ptx, include/cudeep/ptx_intrinsics.cuh:531-554) --------------
 
 @pytest.mark.parametrize("act", [0, 1, 2, 3, 4])
-@pytest.mark.parametrize("m,n,k", [(512, 512, 256), (1024, 768, 512)])   # multiples of the reference's 128 x 128 x 32 tile
+@pytest.mark.parametrize("m,n,k", [(512, 512, 256), (1024, 1024, 512)])
 def test_fused_activation_matches_the_reference_kernel(ref, dev, oracle, lib, act, m, n, k):
+    """Shapes are multiples of the reference's 128 x 128 x 32 tile (the fused kernel is its unguarded
+    aligned one) with N / 128 a multiple of 4: its tile raster walks columns in groups of 4
+    (matmul_kernel.cu:1565-1576) and covers C only then."""
     rng = np.random.default_rng(100 * act + m)
     a = rng.standard_normal((m, k), dtype=np.float32)
     b = (rng.standard_normal((k, n), dtype=np.float32) * np.float32(4.0 / np.sqrt(k)))   # pre-activations ~ N(0, 4)
