@@ -71,6 +71,24 @@ PROTOTYPES = {
     "cudeep_b200_pool_free_on_stream": (c_int, [c_void_p, c_void_p]),
     "cudeep_b200_pool_release_cached": (c_int, []),
     "cudeep_b200_pool_stats": (c_int, [POINTER(c_size_t), POINTER(c_size_t)]),
+    "cudeep_b200_sharded_gemm_create_local": (c_int, [POINTER(c_int), c_int, ctypes.c_longlong, c_int, c_int, c_int,
+                                                      c_int, c_int, POINTER(c_void_p)]),
+    "cudeep_b200_sharded_gemm_create_rank": (c_int, [c_int, c_int, c_int, ctypes.c_longlong, c_int, c_int, c_int,
+                                                     c_int, c_int, POINTER(c_void_p)]),
+    "cudeep_b200_sharded_gemm_destroy": (c_int, [c_void_p]),
+    "cudeep_b200_sharded_gemm_rows": (c_int, [c_void_p, c_int, c_int, POINTER(ctypes.c_longlong),
+                                              POINTER(ctypes.c_longlong)]),
+    "cudeep_b200_sharded_gemm_buffers": (c_int, [c_void_p, c_int, POINTER(c_void_p), POINTER(c_void_p),
+                                                 POINTER(c_void_p)]),
+    "cudeep_b200_sharded_gemm_comm_id": (c_int, [c_void_p]),
+    "cudeep_b200_sharded_gemm_init_comm": (c_int, [c_void_p, c_void_p]),
+    "cudeep_b200_sharded_gemm_export_c": (c_int, [c_void_p, c_void_p]),
+    "cudeep_b200_sharded_gemm_open_peers": (c_int, [c_void_p, c_void_p]),
+    "cudeep_b200_sharded_gemm_run": (c_int, [c_void_p, c_int, _stream]),
+    "cudeep_b200_sharded_gemm_synchronize": (c_int, [c_void_p]),
+    "cudeep_b200_sharded_gemm_time": (c_int, [c_void_p, c_int, c_int, c_int, POINTER(c_float)]),
+    "cudeep_b200_sharded_gemm_steps": (c_int, [c_void_p, c_int, POINTER(ctypes.c_longlong)]),
+    "cudeep_b200_sharded_gemm_inject_failure": (c_int, [c_void_p, c_int]),
 }
 
 _lib = None

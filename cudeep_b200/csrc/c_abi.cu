@@ -12,6 +12,7 @@
 #include "abi_error.h"
 #include "tensor_ops.h"
 #include "cudeep/stream.cuh"
+#include "cudeep/dist/sharded_gemm.cuh"
 
 #include <string>
 #include <vector>
@@ -531,6 +532,108 @@ int cudeep_b200_pool_stats(size_t* allocated_bytes, size_t* cached_bytes) {
         if (allocated_bytes) *allocated_bytes = pool.allocated_bytes();
         if (cached_bytes) *cached_bytes = pool.cached_bytes();
     });
+}
+
+// ---------------------------------------------------------------- row-sharded GEMM
+
+namespace {
+cudeep::dist::ShardedGemm& sharded(cudeep_b200_sharded_gemm_t g) {
+    CB200_REQUIRE(g != nullptr, "sharded GEMM handle is null");
+    return *reinterpret_cast<cudeep::dist::ShardedGemm*>(g);
+}
+cudeep::dist::ShardedGemmOptions sharded_options(int bands, int comm_sms, int dry_run) {
+    cudeep::dist::ShardedGemmOptions opt;
+    if (bands > 0) opt.bands = bands;
+    if (comm_sms >= 0) opt.comm_sms = comm_sms;
+    opt.dry_run = dry_run != 0;
+    return opt;
+}
+}  // namespace
+
+int cudeep_b200_sharded_gemm_create_local(const int* devices, int n_devices, long long M, int N, int K,
+                                          int bands, int comm_sms, int dry_run,
+                                          cudeep_b200_sharded_gemm_t* out) {
+    return guarded([&] {
+        CB200_REQUIRE(devices != nullptr && n_devices > 0 && out != nullptr, "sharded_gemm_create_local: bad arguments");
+        const std::vector<int> list(devices, devices + n_devices);
+        *out = reinterpret_cast<cudeep_b200_sharded_gemm_t>(
+            new cudeep::dist::ShardedGemm(list, M, N, K, sharded_options(bands, comm_sms, dry_run)));
+    });
+}
+
+int cudeep_b200_sharded_gemm_create_rank(int rank, int world, int device, long long M, int N, int K,
+                                         int bands, int comm_sms, int dry_run,
+                                         cudeep_b200_sharded_gemm_t* out) {
+    return guarded([&] {
+        CB200_REQUIRE(out != nullptr, "sharded_gemm_create_rank: null result pointer");
+        *out = reinterpret_cast<cudeep_b200_sharded_gemm_t>(
+            new cudeep::dist::ShardedGemm(rank, world, device, M, N, K, sharded_options(bands, comm_sms, dry_run)));
+    });
+}
+
+int cudeep_b200_sharded_gemm_destroy(cudeep_b200_sharded_gemm_t g) {
+    return guarded([&] { delete reinterpret_cast<cudeep::dist::ShardedGemm*>(g); });
+}
+
+int cudeep_b200_sharded_gemm_rows(cudeep_b200_sharded_gemm_t g, int rank, int band, long long* row0,
+                                  long long* rows) {
+    return guarded([&] {
+        const cudeep::dist::RowRange r = band < 0 ? sharded(g).rows_of(rank) : sharded(g).band_of(rank, band);
+        if (row0) *row0 = r.row0;
+        if (rows) *rows = r.rows;
+    });
+}
+
+int cudeep_b200_sharded_gemm_buffers(cudeep_b200_sharded_gemm_t g, int local, float** a_shard, float** b,
+                                     float** c) {
+    return guarded([&] {
+        if (a_shard) *a_shard = sharded(g).a_shard(local);
+        if (b) *b = sharded(g).b(local);
+        if (c) *c = sharded(g).c(local);
+    });
+}
+
+int cudeep_b200_sharded_gemm_comm_id(void* id_out) {
+    return guarded([&] { cudeep::dist::ShardedGemm::new_comm_id(id_out); });
+}
+
+int cudeep_b200_sharded_gemm_init_comm(cudeep_b200_sharded_gemm_t g, const void* id) {
+    return guarded([&] { sharded(g).init_comm(id); });
+}
+
+int cudeep_b200_sharded_gemm_export_c(cudeep_b200_sharded_gemm_t g, void* handle_out) {
+    return guarded([&] { sharded(g).export_c(handle_out); });
+}
+
+int cudeep_b200_sharded_gemm_open_peers(cudeep_b200_sharded_gemm_t g, const void* handles) {
+    return guarded([&] { sharded(g).open_peers(handles); });
+}
+
+int cudeep_b200_sharded_gemm_run(cudeep_b200_sharded_gemm_t g, int gather, cudeep_b200_stream_t stream) {
+    return guarded([&] { sharded(g).run(static_cast<cudeep::dist::Gather>(gather), as_stream(stream)); });
+}
+
+int cudeep_b200_sharded_gemm_synchronize(cudeep_b200_sharded_gemm_t g) {
+    return guarded([&] { sharded(g).synchronize(); });
+}
+
+int cudeep_b200_sharded_gemm_time(cudeep_b200_sharded_gemm_t g, int gather, int steps, int warmup,
+                                  float* ms_per_step) {
+    return guarded([&] {
+        CB200_REQUIRE(ms_per_step != nullptr, "sharded_gemm_time: null result pointer");
+        *ms_per_step = sharded(g).time_steps(static_cast<cudeep::dist::Gather>(gather), steps, warmup);
+    });
+}
+
+int cudeep_b200_sharded_gemm_steps(cudeep_b200_sharded_gemm_t g, int local, long long* steps) {
+    return guarded([&] {
+        CB200_REQUIRE(steps != nullptr, "sharded_gemm_steps: null result pointer");
+        *steps = sharded(g).steps_enqueued(local);
+    });
+}
+
+int cudeep_b200_sharded_gemm_inject_failure(cudeep_b200_sharded_gemm_t g, int rank) {
+    return guarded([&] { sharded(g).inject_failure(rank); });
 }
 
 }  // extern "C"

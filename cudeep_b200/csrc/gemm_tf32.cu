@@ -15,6 +15,8 @@
 #include "gemm_output.cuh"
 #include "umma_gemm.cuh"
 
+#include <type_traits>
+
 namespace cudeep_b200 {
 
 namespace {
@@ -101,6 +103,25 @@ struct GemmProblem : GemmOutput {
     }
 };
 
+// The same problem for one rank of a row-sharded product whose result every rank wants whole: each
+// staged 32 x 32 block is stored into this GPU's C and into the same place of the other ranks' C
+// (tensor maps over peer-mapped device memory).  Bulk stores only; nothing is loaded from a peer.
+template <int CTAS, int BN, bool B_MN_MAJOR>
+struct GemmPushProblem : GemmProblem<CTAS, BN, B_MN_MAJOR, false> {
+    static constexpr bool kPeerStore = true;
+    static constexpr bool kClusterSplit = false;       // every tile is whole: partial sums are never pushed
+    CUtensorMap peer_c[kMaxGemmPeers];
+    int n_peers;
+
+    __device__ __forceinline__ void prefetch_maps() const {
+        GemmProblem<CTAS, BN, B_MN_MAJOR, false>::prefetch_maps();
+        for (int i = 0; i < n_peers; ++i) ptx::prefetch_tensormap(&peer_c[i]);
+    }
+    __device__ __forceinline__ void push(uint32_t block, int x, int y) const {
+        for (int i = 0; i < n_peers; ++i) ptx::tma_store_2d(&peer_c[i], block, x, y);
+    }
+};
+
 // Zeroes the C region of tiles [first_tile, first_tile + gridDim.x) (raster order); blockIdx.y
 // selects a band of 16 rows inside the tile.
 __global__ void zero_tiles_kernel(float* __restrict__ c, long long ldc, int m, int n, int tile_m, int tile_n,
@@ -128,11 +149,14 @@ __global__ void zero_tiles_kernel(float* __restrict__ c, long long ldc, int m, i
 // Whether a CTA's last tile stages its results in the idle stage ring (see umma_gemm.cuh).
 constexpr bool kRingStagingDefault = true;
 
-template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, bool A_MN_MAJOR = false>
+template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, bool A_MN_MAJOR = false, bool PUSH = false>
 void launch_variant(const float* a, const float* b, float* c, int m, int n, int k,
-                    const UmmaEpilogueArgs& epi, const GemmTuning& tune, cudaStream_t stream) {
+                    const UmmaEpilogueArgs& epi, const GemmTuning& tune, cudaStream_t stream,
+                    const GemmPeerOutputs* peers = nullptr) {
     using Cfg = UmmaConfig<CTAS, BN, B_MN_MAJOR, KATOMS>;
-    using Prob = GemmProblem<CTAS, BN, B_MN_MAJOR, A_MN_MAJOR>;
+    using Prob = std::conditional_t<PUSH, GemmPushProblem<CTAS, BN, B_MN_MAJOR>,
+                                    GemmProblem<CTAS, BN, B_MN_MAJOR, A_MN_MAJOR>>;
+    static_assert(!(PUSH && A_MN_MAJOR), "peer stores are built for the forward layouts only");
     const DeviceInfo& dev = device_info();
 
     Prob prob;
@@ -177,6 +201,21 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
         encode_tensor_map(&prob.map_b, b, 2, dims, strides, box, TmaSwizzle::B128);
     }
     const bool tma_store = prob.set_output(c, m, n, tune.tma_store >= 0);
+    if constexpr (PUSH) {
+        CB200_REQUIRE(peers != nullptr && peers->count >= 0 && peers->count <= kMaxGemmPeers, "bad peer output list");
+        CB200_REQUIRE(tma_store, "peer stores need bulk tensor stores: N % 4 == 0 and a 16-byte aligned C");
+        prob.n_peers = peers->count;
+        for (int i = 0; i < peers->count; ++i) {
+            CB200_REQUIRE(peers->c[i] != nullptr && (reinterpret_cast<uintptr_t>(peers->c[i]) & 15u) == 0,
+                          "peer C pointers must be 16-byte aligned");
+            // The same view as map_c (this rank's rows only, so tiles that hang over the shard's
+            // last row are clipped in every copy).
+            const uint64_t dims[2] = {uint64_t(n), uint64_t(m)};
+            const uint64_t strides[1] = {uint64_t(n) * 4};
+            const uint32_t box[2] = {32, 32};
+            encode_tensor_map(&prob.peer_c[i], peers->c[i], 2, dims, strides, box, TmaSwizzle::B128);
+        }
+    }
 
     UmmaSchedule sched = whole_tile_schedule(
         (m + UMMA_BM * CTAS - 1) / (UMMA_BM * CTAS), (n + BN - 1) / BN, (k + UMMA_BK - 1) / UMMA_BK, BN,
@@ -255,6 +294,9 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     sched.ring_staging = (uint32_t(sched.stages) * Cfg::STAGE_BYTES >= 131072u && ring_wanted) ? 1 : 0;
     const uint32_t smem_bytes = uint32_t(sched.stages) * Cfg::STAGE_BYTES + exchange_bytes + staging_bytes + 1024;
 
+    if constexpr (PUSH)
+        CB200_REQUIRE(sched.split == 1 && sched.cluster_split == 1 && sched.tma_store == 1,
+                      "peer stores need whole tiles written by bulk tensor stores");
     auto kernel = umma_tf32_kernel<CTAS, BN, B_MN_MAJOR, KATOMS, Prob, A_MN_MAJOR>;
     // `groups` counts CTA groups (a CTA or a pair); a cluster holds cluster_split of them.
     launch_umma(kernel, prob, sched, epi, groups / sched.cluster_split, CTAS * sched.cluster_split, smem_bytes,
@@ -431,6 +473,21 @@ void gemm_tf32_tn(const float* a, const float* b, float* c, int m, int n, int k,
     if (t.bn == 0) t.bn = 256;                        // only the 256-wide tiles are built for this layout
     CB200_REQUIRE(t.bn == 256, "transposed-A GEMM supports 256-wide tiles only");
     dispatch<true, true>(a, b, c, m, n, k, epi, t, stream);
+}
+
+void gemm_tf32_push(const float* a, const float* b, bool b_is_nk, float* c, int m, int n, int k,
+                    const GemmPeerOutputs& peers, const GemmTuning& tune, cudaStream_t stream) {
+    CB200_REQUIRE(gemm_tf32_supported(a, b, c, m, n, k, b_is_nk) && n % 4 == 0,
+                  "TF32 tensor-core GEMM with peer stores needs an sm_100 device, 16-byte aligned operands and "
+                  "row lengths that are multiples of 4");
+    UmmaEpilogueArgs epi{nullptr, 0, EPI_NONE};
+    GemmTuning t = tune;
+    t.split_k = 1;            // whole tiles only
+    t.cluster_split = 1;
+    t.tma_store = 0;
+    // One tile shape: the CTA pair with a 256 x 256 tile (shards are large, that is what they take anyway).
+    if (b_is_nk) launch_variant<2, 256, false, 2, false, true>(a, b, c, m, n, k, epi, t, stream, &peers);
+    else launch_variant<2, 256, true, 2, false, true>(a, b, c, m, n, k, epi, t, stream, &peers);
 }
 
 void gemm_tf32(const float* a, const float* b, bool b_is_nk, float* c, int m, int n, int k,

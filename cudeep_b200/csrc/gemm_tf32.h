@@ -38,6 +38,20 @@ void gemm_tf32(const float* a, const float* b, bool b_is_nk, float* c, int m, in
                const float* bias, bool bias_per_row, int act, const GemmTuning& tune,
                cudaStream_t stream);
 
+// One rank's share of a row-sharded product, written into this GPU's C and, by the same kernel,
+// into the other GPUs' copies of C: c[i] are peer-mapped device pointers to the place this rank's
+// rows have in peer i's C (same row pitch N).  Tile by tile the epilogue repeats its bulk tensor
+// store once per peer, so the all-gather of C overlaps the GEMM instead of following it.  The
+// caller makes the result visible across ranks (this launch must have completed on every rank
+// before any rank reads rows it did not compute).  No activation, no bias, whole tiles only.
+constexpr int kMaxGemmPeers = 7;
+struct GemmPeerOutputs {
+    int count = 0;
+    float* c[kMaxGemmPeers] = {};
+};
+void gemm_tf32_push(const float* a, const float* b, bool b_is_nk, float* c, int m, int n, int k,
+                    const GemmPeerOutputs& peers, const GemmTuning& tune, cudaStream_t stream);
+
 // The tile shape the launcher would pick for a problem on a device with `num_sms` SMs (host
 // arithmetic only: no device is touched): CTAs per MMA, tile columns, K ranges per cluster,
 // K blocks per stage, and the estimated time in microseconds.

@@ -153,6 +153,23 @@ constexpr uint32_t UMMA_STORE_STAGING_BYTES = 4 * 2 * 4096;     // 4 epilogue wa
 constexpr int UMMA_KIND_TF32 = 0;
 constexpr int UMMA_KIND_F16 = 1;
 
+// Optional part of the problem contract, for a row-sharded product whose every rank needs all of C:
+//   static constexpr bool kPeerStore = true;
+//   __device__ void push(uint32_t block, int x, int y) const;
+// push() repeats the bulk tensor store of a staged 32 x 32 block into the copies of C that live in
+// the other GPUs' memory (tensor maps over peer-mapped addresses): the all-gather of C rides on the
+// epilogue, tile by tile, instead of following the GEMM as a collective.  Stores only - no load in
+// this kernel ever names peer memory.
+template <class P, class = void>
+struct has_peer_store { static constexpr bool value = false; };
+template <class P>
+struct has_peer_store<P, decltype((void)P::kPeerStore)> { static constexpr bool value = P::kPeerStore; };
+
+template <class P>
+__device__ __forceinline__ void push_to_peers(const P& prob, uint32_t block, int x, int y) {
+    if constexpr (has_peer_store<P>::value) prob.push(block, x, y);
+}
+
 template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, class Problem, bool A_MN_MAJOR = false,
           int KIND = UMMA_KIND_TF32>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
@@ -441,6 +458,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                             int x, y;
                             prob.out_coords(tile, int(quarter) * 32, c, x, y);
                             ptx::tma_store_2d(prob.out_map(), block, x, y);
+                            push_to_peers(prob, block, x, y);
                             ptx::bulk_commit_group();
                         }
                         return;
@@ -548,6 +566,8 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                             prob.out_coords(tile, int(quarter) * 32, c, x, y);
                             ptx::tma_store_2d(prob.out_map(), block0, x, y);
                             if (two) ptx::tma_store_2d(prob.out_map(), block0 + 4096u, x + 32, y);
+                            push_to_peers(prob, block0, x, y);
+                            if (two) push_to_peers(prob, block0 + 4096u, x + 32, y);
                             ptx::bulk_commit_group();
                         }
                         if (in_ring) block0 += 8192u;
@@ -577,7 +597,16 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
         }
         // Bulk stores read shared memory asynchronously: the reads must be over before the CTA
         // gives its shared memory back (the writes themselves complete with the kernel).
-        if (lane == 0) ptx::bulk_wait_group_read<0>();
+        if (lane == 0) {
+            if constexpr (has_peer_store<Problem>::value) {
+                // Stores into other GPUs' memory: wait for the writes themselves, then order them
+                // system-wide before the kernel ends (the peers read C after this launch completes).
+                ptx::bulk_wait_group<0>();
+                __threadfence_system();
+            } else {
+                ptx::bulk_wait_group_read<0>();
+            }
+        }
         __syncwarp();
     }
 

@@ -1,20 +1,32 @@
 """Row-sharded GEMM over the GPUs of one node: C[M,N] = A[M,K] @ B[K,N], A and C split by rows.
 
-One process per GPU (torchrun); each rank owns rows [row0, row0 + rows) of A and C and a full
-replica of B, so no exchange is needed to compute.  The only collective is the optional
-all-gather of C (NCCL over NVLink) for callers that need the whole product on every rank.
-The reference is single-device (device 0 is hard-coded in its capability queries,
-src/kernels/matmul_kernel.cu:1745); this module is the multi-GPU form of its
+The work is done by `cudeep::dist::ShardedGemm` inside libcudeep_b200.so
+(include/cudeep/dist/sharded_gemm.cuh); this module is its ctypes face and needs neither torch nor
+any other framework.  The reference is single-device (device 0 is hard-coded in its capability
+queries, src/kernels/matmul_kernel.cu:1745); this is the multi-GPU form of its
 launch_matmul_kernel<float>.
 
-torch is used here for what it is good at: device buffers, streams and torch.distributed.
-The product itself is computed by libcudeep_b200.so.
+Each rank owns rows [row0, row0 + rows) of A and C and a replica of B, so computing needs no
+exchange.  The optional all-gather of C comes in the forms `GATHER_*` below; GATHER_PEER_STORE is
+the fused one (the GEMM's epilogue stores every tile into all GPUs' C).
+
+One process may drive all GPUs (`ShardedGemm.local`), or one process per GPU (`ShardedGemm.rank`);
+in the second form the caller moves two small byte strings between the processes (`connect`), with
+whatever transport it has: a torch.distributed store, MPI, files.
 """
 from __future__ import annotations
 
 import ctypes
 from dataclasses import dataclass
-from typing import Callable, Optional
+from typing import Callable, Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+
+GATHER_NONE, GATHER_AFTER_GEMM, GATHER_BANDED, GATHER_PEER_STORE, GATHER_COLLECTIVE_ONLY = range(5)
+COMM_ID_BYTES = 128
+MEM_HANDLE_BYTES = 64
 
 
 @dataclass(frozen=True)
@@ -27,7 +39,8 @@ class RowShard:
 
 def row_partition(m: int, world: int, align: int = 1) -> list[RowShard]:
     """Split m rows over `world` ranks as evenly as possible in units of `align` rows; the last
-    ranks get the shorter shares, a rank may get zero rows when m < world * align."""
+    ranks get the shorter shares, a rank may get zero rows when m < world * align.  With
+    align = 128 this is the partition the library uses (ShardedGemm.rows_of)."""
     if m < 0 or world < 1 or align < 1:
         raise ValueError("row_partition: m >= 0, world >= 1 and align >= 1 required")
     units = -(-m // align)
@@ -40,27 +53,19 @@ def row_partition(m: int, world: int, align: int = 1) -> list[RowShard]:
     return shards
 
 
-def _device_matmul(a, b, c, stream) -> None:
-    from . import _lib
-    m, k = a.shape
-    n = b.shape[1]
-    _lib.check(_lib.load().cudeep_b200_matmul_f32(ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(b.data_ptr()),
-                                                  ctypes.c_void_p(c.data_ptr()), m, n, k, stream))
-
-
 class PeerFailure(RuntimeError):
     """Another rank of the sharded product reported an error, or did not report in time."""
 
 
 class StepGuard:
-    """Host-side liveness check, so that a rank that failed is noticed before the others enter a
-    collective they would hang in.
+    """Host-side liveness check between processes, so that a rank that failed is noticed before the
+    others enqueue anything that would wait for it.
 
-    Every rank calls report(step) when its kernels for that step are queued (or report(step,
-    ok=False, message=...) from its exception handler), then wait_all(step) before the collective.
-    Reports go through a torch.distributed store (the TCP store of the process group, or any other
-    `Store`); nothing here touches a GPU.  A rank that leaves does so between steps, with none of
-    its kernels or collectives in flight."""
+    Every rank calls report(step) when its host-side preparation for that step is done (or
+    report(step, ok=False, message=...) from its exception handler), then wait_all(step) before it
+    enqueues the step.  Reports go through a key-value store with set / wait / get (a
+    torch.distributed store, for one); nothing here touches a GPU.  A rank that leaves does so
+    between steps, with none of its kernels or collectives in flight."""
 
     def __init__(self, store, rank: int, world: int, timeout_s: float = 30.0, prefix: str = "cudeep_b200/step"):
         self.store, self.rank, self.world = store, rank, world
@@ -88,7 +93,8 @@ class StepGuard:
             except Exception:
                 missing.append(r)
                 continue
-            value = self.store.get(key).decode("utf-8", "replace")
+            value = self.store.get(key)
+            value = value.decode("utf-8", "replace") if isinstance(value, bytes) else str(value)
             if value != "ok":
                 failed[r] = value
         if failed or missing:
@@ -98,51 +104,149 @@ class StepGuard:
 
 
 class ShardedGemm:
-    """This rank's share of a row-sharded product.
+    """A row-sharded product held by libcudeep_b200.so; see the module docstring."""
 
-    a_shard: [rows, K] and b: [K, N] are torch tensors on this rank's device (CPU tensors are
-    accepted when a `compute` callback is given, which is how the host logic is tested without GPUs).
-    """
+    def __init__(self, handle: ctypes.c_void_p, m: int, n: int, k: int, world: int, local_ranks: Sequence[int]):
+        self._h, self.m, self.n, self.k, self.world = handle, m, n, k, world
+        self.local_ranks = list(local_ranks)
 
-    def __init__(self, shard: RowShard, a_shard, b, *, compute: Optional[Callable] = None):
-        import torch
-        if a_shard.shape[0] != shard.rows or a_shard.shape[1] != b.shape[0]:
-            raise ValueError("ShardedGemm: a_shard must be [shard.rows, K] and b [K, N]")
-        self.shard = shard
-        self.a, self.b = a_shard, b
-        self.c = torch.empty((shard.rows, b.shape[1]), dtype=a_shard.dtype, device=a_shard.device)
-        self._compute = compute
+    # ---- construction -----------------------------------------------------------------------
 
-    def run(self):
-        """Compute this rank's rows of C (asynchronous on the current CUDA stream)."""
-        if self.shard.rows == 0:
-            return self.c
-        if self._compute is not None:
-            self._compute(self.a, self.b, self.c)
-        else:
-            import torch
-            _device_matmul(self.a, self.b, self.c, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
-        return self.c
+    @classmethod
+    def local(cls, devices: Sequence[int], m: int, n: int, k: int, *, bands: int = 4, comm_sms: int = 20,
+              dry_run: bool = False) -> "ShardedGemm":
+        """One process drives all of `devices` (rank i on devices[i])."""
+        lib = _lib.load()
+        arr = (ctypes.c_int * len(devices))(*devices)
+        h = ctypes.c_void_p()
+        _lib.check(lib.cudeep_b200_sharded_gemm_create_local(arr, len(devices), m, n, k, bands, comm_sms,
+                                                             int(dry_run), ctypes.byref(h)))
+        return cls(h, m, n, k, len(devices), range(len(devices)))
 
-    def gather(self, shards: list[RowShard], group=None, guard: Optional[StepGuard] = None, step: int = 0):
-        """All-gather the row shards into the full C on every rank (shards may differ in size).
-        With a guard, every rank first confirms that all ranks reached this step: a failed or
-        absent peer raises PeerFailure here instead of leaving the collective to hang."""
-        import torch
-        import torch.distributed as dist
-        if guard is not None:
-            guard.report(step)
-            guard.wait_all(step)
-        n = self.b.shape[1]
-        if all(s.rows == shards[0].rows for s in shards):
-            full = torch.empty((sum(s.rows for s in shards), n), dtype=self.c.dtype, device=self.c.device)
-            dist.all_gather_into_tensor(full, self.c.contiguous(), group=group)
-            return full
-        # Collectives want equal contributions: pad every shard to the longest one, gather,
-        # then drop the padding rows.
-        longest = max(s.rows for s in shards)
-        padded = torch.zeros((longest, n), dtype=self.c.dtype, device=self.c.device)
-        padded[:self.shard.rows] = self.c
-        stacked = torch.empty((len(shards) * longest, n), dtype=self.c.dtype, device=self.c.device)
-        dist.all_gather_into_tensor(stacked, padded, group=group)
-        return torch.cat([stacked[i * longest:i * longest + s.rows] for i, s in enumerate(shards)], dim=0)
+    @classmethod
+    def rank(cls, rank: int, world: int, device: int, m: int, n: int, k: int, *, bands: int = 4,
+             comm_sms: int = 20, dry_run: bool = False) -> "ShardedGemm":
+        """This process is rank `rank` of `world` and drives `device`."""
+        lib = _lib.load()
+        h = ctypes.c_void_p()
+        _lib.check(lib.cudeep_b200_sharded_gemm_create_rank(rank, world, device, m, n, k, bands, comm_sms,
+                                                            int(dry_run), ctypes.byref(h)))
+        return cls(h, m, n, k, world, [rank])
+
+    def close(self) -> None:
+        if self._h:
+            _lib.check(_lib.load().cudeep_b200_sharded_gemm_destroy(self._h))
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    # ---- plan and buffers -------------------------------------------------------------------
+
+    def rows_of(self, rank: int, band: int = -1) -> RowShard:
+        row0, rows = ctypes.c_longlong(), ctypes.c_longlong()
+        _lib.check(_lib.load().cudeep_b200_sharded_gemm_rows(self._h, rank, band, ctypes.byref(row0),
+                                                             ctypes.byref(rows)))
+        return RowShard(rank, self.world, row0.value, rows.value)
+
+    def buffers(self, local: int = 0) -> tuple[int, int, int]:
+        """Device addresses of local rank `local`: its rows of A, its replica of B, the whole C."""
+        a, b, c = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()
+        _lib.check(_lib.load().cudeep_b200_sharded_gemm_buffers(self._h, local, ctypes.byref(a), ctypes.byref(b),
+                                                                ctypes.byref(c)))
+        return a.value or 0, b.value or 0, c.value or 0
+
+    def _h2d(self, dst: int, array: np.ndarray) -> None:
+        src = np.ascontiguousarray(array, dtype=np.float32)
+        _lib.check(_lib.load().cudeep_b200_memcpy_h2d(ctypes.c_void_p(dst), src.ctypes.data_as(ctypes.c_void_p),
+                                                      src.nbytes, None))
+
+    def set_a(self, local: int, rows: np.ndarray) -> None:
+        shard = self.rows_of(self.local_ranks[local])
+        if rows.shape != (shard.rows, self.k):
+            raise ValueError(f"set_a: expected {(shard.rows, self.k)}, got {rows.shape}")
+        if shard.rows:
+            self._h2d(self.buffers(local)[0], rows)
+
+    def set_b(self, b: np.ndarray) -> None:
+        if b.shape != (self.k, self.n):
+            raise ValueError(f"set_b: expected {(self.k, self.n)}, got {b.shape}")
+        for local in range(len(self.local_ranks)):
+            self._h2d(self.buffers(local)[1], b)
+
+    def read_c(self, local: int = 0, row0: int = 0, rows: Optional[int] = None) -> np.ndarray:
+        """Rows [row0, row0 + rows) of local rank `local`'s copy of C (blocking)."""
+        rows = self.m - row0 if rows is None else rows
+        out = np.empty((rows, self.n), dtype=np.float32)
+        if rows:
+            src = self.buffers(local)[2] + row0 * self.n * 4
+            _lib.check(_lib.load().cudeep_b200_memcpy_d2h(out.ctypes.data_as(ctypes.c_void_p), ctypes.c_void_p(src),
+                                                          out.nbytes, None))
+        return out
+
+    # ---- one process per GPU: the two exchanges ----------------------------------------------
+
+    @staticmethod
+    def new_comm_id() -> bytes:
+        buf = ctypes.create_string_buffer(COMM_ID_BYTES)
+        _lib.check(_lib.load().cudeep_b200_sharded_gemm_comm_id(buf))
+        return buf.raw
+
+    def init_comm(self, comm_id: bytes) -> None:
+        if len(comm_id) != COMM_ID_BYTES:
+            raise ValueError("init_comm: a communicator id has 128 bytes")
+        _lib.check(_lib.load().cudeep_b200_sharded_gemm_init_comm(self._h, comm_id))
+
+    def export_c(self) -> bytes:
+        buf = ctypes.create_string_buffer(MEM_HANDLE_BYTES)
+        _lib.check(_lib.load().cudeep_b200_sharded_gemm_export_c(self._h, buf))
+        return buf.raw
+
+    def open_peers(self, handles: Sequence[bytes]) -> None:
+        if len(handles) != self.world or any(len(h) != MEM_HANDLE_BYTES for h in handles):
+            raise ValueError("open_peers: one 64-byte handle per rank, in rank order")
+        _lib.check(_lib.load().cudeep_b200_sharded_gemm_open_peers(self._h, b"".join(handles)))
+
+    def connect(self, broadcast_from_0: Callable[[Optional[bytes]], bytes],
+                all_gather: Callable[[bytes], Sequence[bytes]], *, peers: bool = True) -> None:
+        """The whole hand-shake of the one-process-per-GPU form.  `broadcast_from_0(x)` returns
+        rank 0's `x` on every rank (other ranks pass None); `all_gather(x)` returns every rank's `x`
+        in rank order."""
+        me = self.local_ranks[0]
+        self.init_comm(broadcast_from_0(self.new_comm_id() if me == 0 else None))
+        if peers and self.world > 1:
+            self.open_peers(list(all_gather(self.export_c())))
+
+    # ---- steps --------------------------------------------------------------------------------
+
+    def run(self, gather: int = GATHER_NONE, stream: Optional[int] = None) -> None:
+        """Enqueue one step; asynchronous.  `stream` (a cudaStream_t as an integer) only in the
+        one-process-per-GPU form."""
+        _lib.check(_lib.load().cudeep_b200_sharded_gemm_run(self._h, gather, ctypes.c_void_p(stream or 0)))
+
+    def run_guarded(self, gather: int, guard: StepGuard, step: int, stream: Optional[int] = None) -> None:
+        """The two-phase step between processes: report, wait for every rank's report, and only then
+        enqueue.  Raises PeerFailure (and enqueues nothing) when a rank failed or is absent."""
+        guard.report(step)
+        guard.wait_all(step)
+        self.run(gather, stream)
+
+    def synchronize(self) -> None:
+        _lib.check(_lib.load().cudeep_b200_sharded_gemm_synchronize(self._h))
+
+    def time_steps(self, gather: int, steps: int, warmup: int) -> float:
+        """Mean device milliseconds per step (slowest local rank)."""
+        ms = ctypes.c_float()
+        _lib.check(_lib.load().cudeep_b200_sharded_gemm_time(self._h, gather, steps, warmup, ctypes.byref(ms)))
+        return ms.value
+
+    def steps_enqueued(self, local: int = 0) -> int:
+        out = ctypes.c_longlong()
+        _lib.check(_lib.load().cudeep_b200_sharded_gemm_steps(self._h, local, ctypes.byref(out)))
+        return out.value
+
+    def inject_failure(self, rank: int) -> None:
+        _lib.check(_lib.load().cudeep_b200_sharded_gemm_inject_failure(self._h, rank))

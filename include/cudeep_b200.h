@@ -284,6 +284,68 @@ int cudeep_b200_pool_free_on_stream(void* ptr, cudeep_b200_stream_t stream);
 int cudeep_b200_pool_release_cached(void);                 /* MemoryPool::release_cached */
 int cudeep_b200_pool_stats(size_t* allocated_bytes, size_t* cached_bytes);
 
+/* ---- row-sharded GEMM over the GPUs of one node (cudeep::dist::ShardedGemm) ---------------- */
+
+/* C[M,N] = A[M,K] * B[K,N] with A and C split by rows over `world` GPUs and B replicated; each
+ * rank's product is cudeep_b200_matmul_f32's.  No counterpart in the reference, which is
+ * single-device (src/kernels/matmul_kernel.cu:1745 queries device 0 only): this is the multi-GPU
+ * form of launch_matmul_kernel<float> (include/cudeep/kernels/matmul.cuh:8-12).  The object owns
+ * its device buffers (per rank: its rows of A, a replica of B, the whole C).
+ *
+ * gather modes (what happens to C after / while it is computed):
+ *   0 none            every GPU keeps only the rows it computed
+ *   1 after GEMM      one in-place ncclAllGather behind the GEMM, same stream
+ *   2 banded          row bands; band i's NCCL transfer on a second stream overlaps band i+1's GEMM
+ *   3 peer store      the GEMM's epilogue stores each tile into every GPU's C (peer-mapped memory,
+ *                     bulk tensor stores; no load ever touches a peer, no collective is called)
+ *   4 collective only the all-gather alone (for timing)
+ * A step whose host-side preparation fails on any rank enqueues nothing on any GPU, returns an
+ * error naming the rank, and the object refuses further steps. */
+typedef struct cudeep_b200_sharded_gemm* cudeep_b200_sharded_gemm_t;
+
+#define CUDEEP_B200_GATHER_NONE 0
+#define CUDEEP_B200_GATHER_AFTER_GEMM 1
+#define CUDEEP_B200_GATHER_BANDED 2
+#define CUDEEP_B200_GATHER_PEER_STORE 3
+#define CUDEEP_B200_GATHER_COLLECTIVE_ONLY 4
+#define CUDEEP_B200_COMM_ID_BYTES 128
+#define CUDEEP_B200_MEM_HANDLE_BYTES 64
+
+/* One process drives all of devices[0..n_devices): one host thread and stream pair per device,
+ * communicators from ncclCommInitAll.  dry_run != 0: host logic only, no CUDA or NCCL call. */
+int cudeep_b200_sharded_gemm_create_local(const int* devices, int n_devices, long long M, int N, int K,
+                                          int bands, int comm_sms, int dry_run,
+                                          cudeep_b200_sharded_gemm_t* out);
+/* This process is rank `rank` of `world` (one process per GPU) and drives `device`. */
+int cudeep_b200_sharded_gemm_create_rank(int rank, int world, int device, long long M, int N, int K,
+                                         int bands, int comm_sms, int dry_run,
+                                         cudeep_b200_sharded_gemm_t* out);
+int cudeep_b200_sharded_gemm_destroy(cudeep_b200_sharded_gemm_t g);
+/* Rows of A and C owned by `rank`; band `band` of them (band < 0: the whole share). */
+int cudeep_b200_sharded_gemm_rows(cudeep_b200_sharded_gemm_t g, int rank, int band, long long* row0,
+                                  long long* rows);
+/* Device buffers of local rank `local` (0 in the one-process-per-GPU form). */
+int cudeep_b200_sharded_gemm_buffers(cudeep_b200_sharded_gemm_t g, int local, float** a_shard, float** b,
+                                     float** c);
+/* One process per GPU: rank 0 makes a communicator id (128 bytes) and ships it; every rank then
+ * calls init_comm with it.  export_c writes the 64-byte handle of this rank's C; open_peers takes
+ * all ranks' handles in rank order (world * 64 bytes) and maps the others' C for peer stores. */
+int cudeep_b200_sharded_gemm_comm_id(void* id_out);
+int cudeep_b200_sharded_gemm_init_comm(cudeep_b200_sharded_gemm_t g, const void* id);
+int cudeep_b200_sharded_gemm_export_c(cudeep_b200_sharded_gemm_t g, void* handle_out);
+int cudeep_b200_sharded_gemm_open_peers(cudeep_b200_sharded_gemm_t g, const void* handles);
+/* Enqueue one step (asynchronous).  One process per GPU: on `stream` (NULL: the object's own);
+ * the collective's stream is joined back into it.  One process for all GPUs: `stream` is ignored. */
+int cudeep_b200_sharded_gemm_run(cudeep_b200_sharded_gemm_t g, int gather, cudeep_b200_stream_t stream);
+int cudeep_b200_sharded_gemm_synchronize(cudeep_b200_sharded_gemm_t g);
+/* Mean device time of a step in milliseconds, the slowest local rank's, over `steps` after `warmup`. */
+int cudeep_b200_sharded_gemm_time(cudeep_b200_sharded_gemm_t g, int gather, int steps, int warmup,
+                                  float* ms_per_step);
+/* Steps enqueued so far on local rank `local`; and a test hook that makes `rank`'s host-side
+ * preparation fail at the next step. */
+int cudeep_b200_sharded_gemm_steps(cudeep_b200_sharded_gemm_t g, int local, long long* steps);
+int cudeep_b200_sharded_gemm_inject_failure(cudeep_b200_sharded_gemm_t g, int rank);
+
 #ifdef __cplusplus
 }
 #endif
