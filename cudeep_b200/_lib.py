@@ -71,6 +71,7 @@ PROTOTYPES = {
     "cudeep_b200_pool_free_on_stream": (c_int, [c_void_p, c_void_p]),
     "cudeep_b200_pool_release_cached": (c_int, []),
     "cudeep_b200_pool_stats": (c_int, [POINTER(c_size_t), POINTER(c_size_t)]),
+    "cudeep_b200_scratch_trim": (c_int, [c_size_t]),
     "cudeep_b200_sharded_gemm_create_local": (c_int, [POINTER(c_int), c_int, ctypes.c_longlong, c_int, c_int, c_int,
                                                       c_int, c_int, POINTER(c_void_p)]),
     "cudeep_b200_sharded_gemm_create_rank": (c_int, [c_int, c_int, c_int, ctypes.c_longlong, c_int, c_int, c_int,

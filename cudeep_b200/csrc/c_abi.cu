@@ -534,6 +534,10 @@ int cudeep_b200_pool_stats(size_t* allocated_bytes, size_t* cached_bytes) {
     });
 }
 
+int cudeep_b200_scratch_trim(size_t keep_bytes) {
+    return guarded([&] { cudeep_b200::scratch_trim(keep_bytes); });
+}
+
 // ---------------------------------------------------------------- row-sharded GEMM
 
 namespace {

@@ -95,6 +95,8 @@ unsigned grid_for(long long total) {
 template <typename T>
 void backward_data_direct(const T* dy, const T* w, T* dx, const ConvShape& s, cudaStream_t stream) {
     const long long total = static_cast<long long>(s.batch) * s.in_c * s.in_h * s.in_w;
+    CB200_TRACE("conv2d grad_input direct strict %s: N=%d C=%d %dx%d OC=%d, %dx%d stride %dx%d",
+                sizeof(T) == 8 ? "FP64" : "FP32", s.batch, s.in_c, s.in_h, s.in_w, s.out_c, s.k_h, s.k_w, s.s_h, s.s_w);
     conv2d_backward_data_direct_kernel<T><<<grid_for(total), 256, 0, stream>>>(dy, w, dx, s, s.out_h(),
                                                                                s.out_w(), total);
     CB200_CHECK_LAUNCH();
@@ -170,6 +172,8 @@ static void backward_weight(const T* grad_output, const T* input, T* grad_weight
                   "conv2d backward: null tensor pointer");
     cudeep_b200::check_conv_shape(s);
     const long long total = static_cast<long long>(s.out_c) * s.in_c * s.k_h * s.k_w;
+    CB200_TRACE("conv2d grad_weight direct strict %s: N=%d C=%d %dx%d OC=%d, %dx%d stride %dx%d",
+                sizeof(T) == 8 ? "FP64" : "FP32", s.batch, s.in_c, s.in_h, s.in_w, s.out_c, s.k_h, s.k_w, s.s_h, s.s_w);
     cudeep_b200::conv2d_backward_weight_direct_kernel<T>
         <<<cudeep_b200::grid_for(total), 256, 0, stream>>>(grad_output, input, grad_weight, s, s.out_h(),
                                                            s.out_w(), total);

@@ -78,6 +78,9 @@ void conv2d_direct(const T* input, const T* weight, const T* bias, T* output, co
     long long blocks = (total + threads - 1) / threads;
     const long long cap = static_cast<long long>(device_info().num_sms) * 32;
     if (blocks > cap) blocks = cap;
+    CB200_TRACE("conv2d direct strict %s: N=%d C=%d %dx%d -> OC=%d %dx%d, %dx%d stride %dx%d pad %dx%d, blocks=%lld",
+                sizeof(T) == 8 ? "FP64" : "FP32", s.batch, s.in_c, s.in_h, s.in_w, s.out_c, oh, ow, s.k_h, s.k_w, s.s_h,
+                s.s_w, s.p_h, s.p_w, blocks);
     conv2d_direct_kernel<T><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
         input, weight, bias, output, s, oh, ow, total, act);
     CB200_CHECK_LAUNCH();

@@ -496,6 +496,11 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     if (groups < 1) groups = 1;
     if (groups > num_tiles) groups = num_tiles;
 
+    CB200_TRACE("conv2d implicit GEMM tcgen05: N=%d C=%d %dx%d -> OC=%d %dx%d, %dx%d stride %dx%d pad %dx%d; pixel box "
+                "%d x %d x %d images = %d columns, ctas/mma=%d katoms=%d stages=%d clusters=%lld, K blocks=%d, store=%s",
+                s.batch, s.in_c, s.in_h, s.in_w, s.out_c, oh, ow, s.k_h, s.k_w, s.s_h, s.s_w, s.p_h, s.p_w, plan.box_w,
+                plan.box_h, plan.box_n, umma_n, CTAS, KATOMS, sched.stages, groups, sched.k_blocks,
+                bulk_store ? "bulk-tensor" : "registers");
     auto kernel = umma_tf32_kernel<CTAS, 256, false, KATOMS, Prob>;
     UmmaEpilogueArgs epi{bias, 1, act};
     launch_umma(kernel, prob, sched, epi, groups, CTAS, smem_bytes, Cfg::SMEM_MAX, stream);

@@ -7,10 +7,19 @@
 // copy of the input and the packed filters) from the stream-ordered allocator; this
 // entry point takes it from a fixed array that is part of the library image instead.
 //
-// The array is a file-scope __device__ object: every GPU that loads the library holds
-// its 32 MiB until the process exits.  In host code the array's name is only a handle;
+// The array is a file-scope __device__ object: every GPU that loads this part of the library
+// holds its 32 MiB until the process exits.  In host code the array's name is only a handle;
 // the device address is looked up once per device with cudaGetSymbolAddress, with that
 // device current, and that address is what the kernels receive.
+//
+// "Loads" is literal: with CUDA's default lazy module loading the array's module is loaded -
+// and its 32 MiB taken from the device - by that first look-up, and each kernel variant
+// (tile shape, re-layout kernel) is loaded and has its shared-memory limit raised at its first
+// launch.  So the calls that must not allocate are the second and later ones of a shape class.
+// A caller with a fixed memory plan warms up at start-up, before it hands the free memory to
+// its own allocator and before any stream capture: cudeep_b200_conv2d_noalloc_capacity() on
+// each device resolves the array, one call per layer shape it will use loads the kernels
+// (or the process runs with CUDA_MODULE_LOADING=EAGER).
 #include "cudeep_b200.h"
 
 #include "abi_error.h"
@@ -45,7 +54,17 @@ void* static_scratch() {
 
 }  // namespace
 
-extern "C" size_t cudeep_b200_conv2d_noalloc_capacity(void) { return kStaticScratchBytes; }
+// Also the warm-up for the current device: resolving the array here loads its module, so the
+// 32 MiB are taken now and not inside the first convolution.  Without a usable device it only
+// reports the size.
+extern "C" size_t cudeep_b200_conv2d_noalloc_capacity(void) {
+    try {
+        static_scratch();
+    } catch (...) {
+        cudaGetLastError();
+    }
+    return kStaticScratchBytes;
+}
 
 extern "C" int cudeep_b200_conv2d_forward_noalloc_f32(const float* input, const float* weight,
                                                       const float* bias, float* output, int batch,
@@ -62,7 +81,8 @@ extern "C" int cudeep_b200_conv2d_forward_noalloc_f32(const float* input, const 
         cudeep_b200::check_conv_shape(shape);
         cudaStream_t s = static_cast<cudaStream_t>(stream);
         if (!cudeep_b200::conv2d_igemm_supported(shape)) {
-            // Strided, tiny or few-channel shapes run the direct kernel, which needs no scratch.
+            // Shapes the tensor-core path does not take (under 32 output channels or 64 output
+            // pixels, strides above 8) run the direct kernel, which needs no scratch.
             cudeep_b200::conv2d_direct<float>(input, weight, bias, output, shape, epilogue, s);
             return CUDEEP_B200_OK;
         }

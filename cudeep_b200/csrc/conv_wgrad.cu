@@ -322,6 +322,10 @@ void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, c
     if (groups < 1) groups = 1;
     if (groups > num_tiles) groups = num_tiles;
 
+    CB200_TRACE("conv2d grad_weight implicit GEMM tcgen05: N=%d C=%d %dx%d OC=%d, %dx%d stride %dx%d; %d columns, "
+                "K ranges=%d of %d blocks, ctas/mma=%d stages=%d clusters=%lld",
+                s.batch, s.in_c, s.in_h, s.in_w, s.out_c, s.k_h, s.k_w, s.s_h, s.s_w, p.n_cols, p.ranges,
+                p.kb_per_range, CTAS, sched.stages, groups);
     auto kernel = umma_tf32_kernel<CTAS, 256, true, KATOMS, Prob>;
     UmmaEpilogueArgs epi{nullptr, 0, EPI_NONE};
     launch_umma(kernel, prob, sched, epi, groups, CTAS, smem_bytes, Cfg::SMEM_MAX, stream);

@@ -111,6 +111,8 @@ void launch_f16(const __half* a, const __half* b, float* c, int m, int n, int k,
     if (groups < 1) groups = 1;
     if (groups > num_tiles) groups = num_tiles;
 
+    CB200_TRACE("gemm f16 tcgen05: M=%d N=%d K=%d tile=%dx%d ctas/mma=%d stages=%d clusters=%lld store=%s", m, n, k,
+                UMMA_BM * CTAS, BN, CTAS, sched.stages, groups, tma_store ? "bulk-tensor" : "registers");
     auto kernel = umma_tf32_kernel<CTAS, BN, true, KATOMS, Prob, false, UMMA_KIND_F16>;
     UmmaEpilogueArgs epi{nullptr, 0, EPI_NONE};
     launch_umma(kernel, prob, sched, epi, groups, CTAS, smem_bytes, Cfg::SMEM_MAX, stream);

@@ -223,6 +223,8 @@ void launch_aligned(const float* a, const float* b, float* c, int m, int n, int 
     auto kernel = sgemm_aligned_kernel<BM, BN, TM, TN, STAGES>;
     ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     dim3 grid(n / BN, m / BM);
+    CB200_TRACE("gemm strict FP32 (cp.async, aligned): M=%d N=%d K=%d tile=%dx%d stages=%d grid=%ux%u", m, n, k, BM,
+                BN, STAGES, grid.x, grid.y);
     kernel<<<grid, (BM / TM) * (BN / TN), smem, stream>>>(a, b, c, m, n, k, bias, bias_per_row ? 1 : 0, act);
     CB200_CHECK_LAUNCH();
 }
@@ -232,6 +234,8 @@ void launch(const TI* a, const TI* b, bool b_is_nk, T* c, int m, int n, int k, c
             bool bias_per_row, int act, cudaStream_t stream) {
     dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
     dim3 block((BM / TM) * (BN / TN));
+    CB200_TRACE("gemm strict %s (SIMT, any shape): M=%d N=%d K=%d B=%s tile=%dx%d grid=%ux%u",
+                sizeof(T) == 8 ? "FP64" : "FP32", m, n, k, b_is_nk ? "[N,K]" : "[K,N]", BM, BN, grid.x, grid.y);
     if (b_is_nk)
         gemm_simt_kernel<TI, T, BM, BN, BK, TM, TN, true><<<grid, block, 0, stream>>>(
             a, b, c, m, n, k, bias, bias_per_row ? 1 : 0, act);

@@ -297,6 +297,12 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     if constexpr (PUSH)
         CB200_REQUIRE(sched.split == 1 && sched.cluster_split == 1 && sched.tma_store == 1,
                       "peer stores need whole tiles written by bulk tensor stores");
+    CB200_TRACE("gemm tf32 tcgen05: M=%d N=%d K=%d A=%s B=%s tile=%dx%d ctas/mma=%d katoms=%d stages=%d "
+                "clusters=%d x %d CTAs tail_split=%d cluster_split=%d store=%s peers=%d act=%d bias=%d",
+                m, n, k, A_MN_MAJOR ? "[K,M]" : "[M,K]", B_MN_MAJOR ? "[K,N]" : "[N,K]", UMMA_BM * CTAS, BN, CTAS,
+                KATOMS, sched.stages, groups / sched.cluster_split, CTAS * sched.cluster_split, sched.split,
+                sched.cluster_split, sched.tma_store ? "bulk-tensor" : "registers",
+                PUSH ? (peers ? peers->count : 0) : 0, epi.act, epi.bias != nullptr);
     auto kernel = umma_tf32_kernel<CTAS, BN, B_MN_MAJOR, KATOMS, Prob, A_MN_MAJOR>;
     // `groups` counts CTA groups (a CTA or a pair); a cluster holds cluster_split of them.
     launch_umma(kernel, prob, sched, epi, groups / sched.cluster_split, CTAS * sched.cluster_split, smem_bytes,

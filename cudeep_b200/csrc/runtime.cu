@@ -1,5 +1,7 @@
 #include "runtime.h"
 
+#include <cstdarg>
+#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 #include <unordered_set>
@@ -35,6 +37,7 @@ struct DeviceState {
     DeviceInfo info;
     std::mutex mu;
     std::unordered_set<const void*> smem_done;
+    cudaMemPool_t scratch_pool = nullptr;      // created on first scratch_alloc
 };
 
 std::mutex g_mu;
@@ -94,6 +97,23 @@ void ensure_dynamic_smem(const void* func, size_t bytes) {
     st.smem_done.insert(func);
 }
 
+bool trace_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("CUDEEP_LOG");
+        return v != nullptr && v[0] != '\0' && v[0] != '0';
+    }();
+    return on;
+}
+
+void trace(const char* format, ...) {
+    char line[512];
+    va_list args;
+    va_start(args, format);
+    std::vsnprintf(line, sizeof(line), format, args);
+    va_end(args);
+    std::fprintf(stderr, "[cudeep_b200] %s\n", line);
+}
+
 bool programmatic_launch_enabled() {
     static const bool on = [] {
         const char* v = std::getenv("CUDEEP_B200_PDL");
@@ -102,19 +122,43 @@ bool programmatic_launch_enabled() {
     return on;
 }
 
-void* scratch_alloc(size_t bytes, cudaStream_t stream) {
-    static thread_local int pool_ready_device = -1;
-    const int dev = device_info().device;
-    if (pool_ready_device != dev) {
-        cudaMemPool_t pool;
-        CB200_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+namespace {
+// The library's own stream-ordered pool on the current device.  It is private so that its release
+// threshold (keep freed scratch cached across synchronisations) does not change how the device's
+// default pool behaves for other cudaMallocAsync users in the process.
+cudaMemPool_t scratch_pool() {
+    DeviceState& st = state();
+    std::lock_guard<std::mutex> lock(st.mu);
+    if (st.scratch_pool == nullptr) {
+        cudaMemPoolProps props{};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = st.info.device;
+        cudaMemPool_t pool = nullptr;
+        CB200_CUDA(cudaMemPoolCreate(&pool, &props));
         uint64_t keep = UINT64_MAX;
         CB200_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
-        pool_ready_device = dev;
+        st.scratch_pool = pool;
     }
+    return st.scratch_pool;
+}
+}  // namespace
+
+void* scratch_alloc(size_t bytes, cudaStream_t stream) {
     void* ptr = nullptr;
-    CB200_CUDA(cudaMallocAsync(&ptr, bytes, stream));
+    CB200_CUDA(cudaMallocFromPoolAsync(&ptr, bytes, scratch_pool(), stream));
     return ptr;
+}
+
+void scratch_trim(size_t keep_bytes) {
+    DeviceState& st = state();
+    cudaMemPool_t pool = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(st.mu);
+        pool = st.scratch_pool;
+    }
+    if (pool != nullptr) CB200_CUDA(cudaMemPoolTrimTo(pool, keep_bytes));
 }
 
 void scratch_free(void* ptr, cudaStream_t stream) noexcept {

@@ -30,6 +30,16 @@ namespace cudeep_b200 {
 
 #define CB200_CHECK_LAUNCH() CB200_CUDA(cudaGetLastError())
 
+// Dispatch trace: with CUDEEP_LOG=1 in the environment (read once) every launcher writes one line
+// to stderr saying which kernel a call took and with what tile / cluster / pipeline shape - the way
+// to see that a shape went to the strict-precision or the direct kernel instead of the tensor cores.
+bool trace_enabled();
+void trace(const char* format, ...) __attribute__((format(printf, 1, 2)));
+#define CB200_TRACE(...)                                                        \
+    do {                                                                        \
+        if (::cudeep_b200::trace_enabled()) ::cudeep_b200::trace(__VA_ARGS__);  \
+    } while (0)
+
 struct DeviceInfo {
     int device = -1;
     int num_sms = 0;
@@ -44,11 +54,13 @@ const DeviceInfo& device_info();
 // Raise the dynamic shared-memory limit of `func` on the current device once.
 void ensure_dynamic_smem(const void* func, size_t bytes);
 
-// Stream-ordered scratch (cudaMallocAsync / cudaFreeAsync on `stream`) from the device's default
-// memory pool, whose release threshold is raised once so that freed scratch stays cached instead
-// of going back to the driver at every synchronisation.
+// Stream-ordered scratch (cudaMallocFromPoolAsync / cudaFreeAsync on `stream`) from a memory pool
+// of the library's own on the current device; freed scratch stays cached in that pool instead of
+// going back to the driver at every synchronisation.  scratch_trim returns all but `keep_bytes` of
+// the cached memory to the driver (memory in use is not touched).
 void* scratch_alloc(size_t bytes, cudaStream_t stream);
 void scratch_free(void* ptr, cudaStream_t stream) noexcept;
+void scratch_trim(size_t keep_bytes);
 
 // Read-and-clear the current device's kernel status word (synchronises the device).
 uint32_t read_device_status(bool clear);

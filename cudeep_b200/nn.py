@@ -20,50 +20,63 @@ from .tensor import DType, Tensor, conv2d, linear
 
 
 class Parameter(Tensor):
+    """A tensor a Module owns: shares the storage of the tensor it was made from (reference nn.py:20-30)."""
+
     def __init__(self, data: Tensor):
         super().__init__(data.shape(), data.dtype(), _storage=data._storage, _strides=data.strides())
 
     def __repr__(self):
-        return f"Parameter(shape={self.shape()}, dtype={self.dtype()})"
+        return "Parameter(shape={}, dtype={})".format(self.shape(), self.dtype())
 
 
 class Module:
+    """Container of parameters and sub-modules with the reference's public surface (nn.py:33-90):
+    forward / __call__, register_parameter / register_module, parameters / named_parameters,
+    train / eval / training, state_dict / load_state_dict.  Parameter names are dotted paths,
+    a module's own parameters before those of its children, children in registration order.
+    Every query is one depth-first walk (`_owned`)."""
+
     def __init__(self):
         self._parameters: dict[str, Parameter] = {}
         self._modules: dict[str, "Module"] = {}
         self._training = True
 
+    # -- calling ------------------------------------------------------------------------------
     def forward(self, *args, **kwargs):
-        raise NotImplementedError
+        raise NotImplementedError(f"{type(self).__name__} does not define forward()")
 
     def __call__(self, *args, **kwargs):
         return self.forward(*args, **kwargs)
 
-    def register_parameter(self, name: str, tensor):
-        if not isinstance(tensor, Parameter):
-            tensor = Parameter(tensor)
-        self._parameters[name] = tensor
+    # -- registration ---------------------------------------------------------------------------
+    def register_parameter(self, name: str, tensor) -> None:
+        self._parameters[name] = tensor if isinstance(tensor, Parameter) else Parameter(tensor)
 
-    def register_module(self, name: str, module: "Module"):
+    def register_module(self, name: str, module: "Module") -> None:
         self._modules[name] = module
 
-    def parameters(self) -> list:
-        params = list(self._parameters.values())
-        for mod in self._modules.values():
-            params.extend(mod.parameters())
-        return params
+    # -- traversal ------------------------------------------------------------------------------
+    def _owned(self, prefix: str = ""):
+        """(dotted name, owning module, key) of every parameter below this module."""
+        for key in self._parameters:
+            yield prefix + key, self, key
+        for child_name, child in self._modules.items():
+            yield from child._owned(f"{prefix}{child_name}.")
 
     def named_parameters(self):
-        for name, p in self._parameters.items():
-            yield name, p
-        for mod_name, mod in self._modules.items():
-            for pname, p in mod.named_parameters():
-                yield f"{mod_name}.{pname}", p
+        for name, owner, key in self._owned():
+            yield name, owner._parameters[key]
 
+    def parameters(self) -> list:
+        return [p for _, p in self.named_parameters()]
+
+    # -- mode -----------------------------------------------------------------------------------
     def train(self, mode=True):
-        self._training = mode
-        for m in self._modules.values():
-            m.train(mode)
+        stack = [self]
+        while stack:
+            module = stack.pop()
+            module._training = mode
+            stack.extend(module._modules.values())
         return self
 
     def eval(self):
@@ -73,22 +86,15 @@ class Module:
     def training(self):
         return self._training
 
+    # -- state ----------------------------------------------------------------------------------
     def state_dict(self) -> dict:
         return {name: p.numpy() for name, p in self.named_parameters()}
 
     def load_state_dict(self, sd: dict):
-        owners = {}
-        self._collect_owners("", owners)
-        for name, arr in sd.items():
-            if name in owners:
-                module, key = owners[name]
-                module._parameters[key] = Parameter(Tensor.from_numpy(np.ascontiguousarray(arr)))
-
-    def _collect_owners(self, prefix: str, out: dict):
-        for key in self._parameters:
-            out[prefix + key] = (self, key)
-        for mod_name, mod in self._modules.items():
-            mod._collect_owners(f"{prefix}{mod_name}.", out)
+        """Replaces every parameter named in `sd`; names this module does not have are ignored."""
+        for name, owner, key in list(self._owned()):
+            if name in sd:
+                owner._parameters[key] = Parameter(Tensor.from_numpy(np.ascontiguousarray(sd[name])))
 
 
 class Linear(Module):

@@ -7,13 +7,19 @@
 // The operation is a cross-correlation with zero padding, no dilation, no
 // groups.  Launches are asynchronous on `stream`; errors are std::runtime_error.
 //
-// Dispatch of the float launcher:
-//   * implicit-GEMM on tcgen05 (TF32 multiply, FP32 accumulate) for stride 1
-//     with C % 4 == 0 and an output row of at most 256 pixels; the input is
-//     re-laid as NHWC once per call and gathered tap by tap with TMA, filters
-//     are packed [OC][KH][KW][C]; no im2col matrix is materialised;
-//   * direct strict-FP32 convolution otherwise.
-// The double instantiation is a direct FP64 convolution.
+// Which launchers return TF32-rounded results (operands truncated to TF32 by the tensor core,
+// FP32 accumulation - what the reference's own GEMM-based paths produce) and which strict FP32:
+//   * forward, float: implicit GEMM on tcgen05 (TF32) when strides are 1..8, padding is smaller
+//     than the filter, OC >= 32, one image has at least 64 output pixels, and C >= 3 (or fewer
+//     channels when a filter row fits one 32-wide K block: KW > 1 and KW * ceil4(C) <= 32).  The
+//     input is re-laid as NHWC once per call and gathered tap by tap with TMA, filters are packed
+//     [OC][KH*KW][C]; no im2col matrix is materialised.  Every other shape: direct strict FP32.
+//   * grad_input, float: the same implicit GEMM applied to grad_output with flipped filters (TF32)
+//     under the same conditions with the roles of C and OC exchanged (stride_h * stride_w <= 16:
+//     a strided layer's grad_output gets zeros inserted between its pixels); otherwise strict FP32.
+//   * grad_weight, float: implicit GEMM over output pixels (TF32) for strides 1..8, OC >= 32 and at
+//     least 256 output pixels in the batch; otherwise strict FP32.
+//   * every double instantiation: direct FP64.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -31,17 +37,15 @@ void launch_conv2d_forward_kernel(const T* input, const T* weight, const T* bias
                                   int pad_w, cudaStream_t stream = nullptr);
 
 // Gradient w.r.t. the input, grad_input [N, C, H, W] from grad_output [N, OC, OH, OW]
-// (reference conv.cuh:18-26).  Stride 1 with enough channels runs as a forward implicit-GEMM
-// convolution of grad_output with flipped filters (TF32); everything else, and double, runs a
-// direct strict-precision kernel.
+// (reference conv.cuh:18-26; precision per shape as listed at the top of this file).
 template <typename T>
 void launch_conv2d_backward_data_kernel(const T* grad_output, const T* weight, T* grad_input, int batch,
                                         int in_channels, int out_channels, int in_h, int in_w,
                                         int kernel_h, int kernel_w, int stride_h, int stride_w, int pad_h,
                                         int pad_w, cudaStream_t stream = nullptr);
 
-// Gradient w.r.t. the filters, grad_weight [OC, C, KH, KW] (reference conv.cuh:28-36); a direct
-// strict-precision kernel.
+// Gradient w.r.t. the filters, grad_weight [OC, C, KH, KW] (reference conv.cuh:28-36; TF32 on the
+// tensor cores for the shapes listed at the top of this file, strict FP32 otherwise).
 template <typename T>
 void launch_conv2d_backward_weight_kernel(const T* grad_output, const T* input, T* grad_weight, int batch,
                                           int in_channels, int out_channels, int in_h, int in_w,

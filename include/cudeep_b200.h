@@ -172,8 +172,13 @@ int cudeep_b200_conv2d_forward_fused_f32(const float* input, const float* weight
  *     with an error that states both sizes (C*H*(W + 2*pad_w)*batch*4 bytes, channels
  *     rounded up to 4, plus the filters with channels rounded up to 32).  Shapes the
  *     tensor-core path does not take (tiny, stride > 8) run the direct kernel and need no scratch.
- *   - The first call on each device looks up the array's device address; make that
- *     call before starting any stream capture.
+ *   - "Allocates nothing" holds from the second call of a shape class on.  With CUDA's lazy
+ *     module loading the first look-up of the array on a device loads it (that is when the
+ *     32 MiB are taken), and the first launch of each kernel variant loads that kernel and
+ *     raises its shared-memory limit.  Warm up at start-up, before giving the free memory
+ *     away and before any stream capture: cudeep_b200_conv2d_noalloc_capacity() on each device
+ *     resolves the array, one call per layer shape loads the kernels (or run the process with
+ *     CUDA_MODULE_LOADING=EAGER).
  *   - All calls on a device share the one array and it keeps the previous call's
  *     contents; each call rewrites every byte it later reads, so nothing needs
  *     clearing, but two calls that overlap on the GPU (different streams, no
@@ -184,7 +189,8 @@ int cudeep_b200_conv2d_forward_noalloc_f32(const float* input, const float* weig
                                            int kernel_w, int stride_h, int stride_w, int pad_h,
                                            int pad_w, int epilogue, cudeep_b200_stream_t stream);
 
-/* Bytes of built-in scratch behind cudeep_b200_conv2d_forward_noalloc_f32. */
+/* Bytes of built-in scratch behind cudeep_b200_conv2d_forward_noalloc_f32.  On a machine with a
+ * GPU it also resolves the array on the current device (the per-device warm-up, see above). */
 size_t cudeep_b200_conv2d_noalloc_capacity(void);
 
 /* FP64 convolution.  Replaces launch_conv2d_forward_kernel<double>. */
@@ -283,6 +289,12 @@ int cudeep_b200_pool_alloc_on_stream(size_t nbytes, cudeep_b200_stream_t stream,
 int cudeep_b200_pool_free_on_stream(void* ptr, cudeep_b200_stream_t stream);
 int cudeep_b200_pool_release_cached(void);                 /* MemoryPool::release_cached */
 int cudeep_b200_pool_stats(size_t* allocated_bytes, size_t* cached_bytes);
+/* The launchers' temporaries (conv re-layouts, packed filters, split-K partial sums) come from a
+ * stream-ordered pool of the library's own on each device, as the reference takes its temporaries
+ * from cudaMallocAsync (src/kernels/conv_kernel.cu:282,314,748-754); unlike the reference it leaves
+ * the device's default pool untouched and keeps freed scratch cached.  This call gives all but
+ * `keep_bytes` of that cache on the current device back to the driver. */
+int cudeep_b200_scratch_trim(size_t keep_bytes);
 
 /* ---- row-sharded GEMM over the GPUs of one node (cudeep::dist::ShardedGemm) ---------------- */
 

@@ -57,6 +57,27 @@ def test_noalloc_matches_regular_on_two_calls_in_a_row(dev, lib, oracle):
     assert oracle.rel_frobenius(fixed, regular) <= TOL
 
 
+def test_noalloc_takes_no_device_memory_once_a_shape_class_is_warm(dev, lib):
+    """The array and the kernels of a shape class are loaded at their first use; from then on a call
+    leaves the device's free memory exactly where it was."""
+    from cudeep_b200 import _lib
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((2, 32, 14, 14), dtype=np.float32)
+    w = rng.standard_normal((64, 32, 3, 3), dtype=np.float32)
+    tx, tw = dev.to_dev(x), dev.to_dev(w)
+    ty = dev.empty((2, 64, 14, 14))
+    args = (2, 32, 64, 14, 14, 3, 3, 1, 1, 1, 1, 0, None)
+    assert lib.cudeep_b200_conv2d_noalloc_capacity() == 32 << 20          # resolves the array on this device
+    _lib.check(lib.cudeep_b200_conv2d_forward_noalloc_f32(dev.ptr(tx), dev.ptr(tw), None, dev.ptr(ty), *args))
+    dev.torch.cuda.synchronize()
+    free_before, _ = dev.torch.cuda.mem_get_info()
+    for _ in range(3):
+        _lib.check(lib.cudeep_b200_conv2d_forward_noalloc_f32(dev.ptr(tx), dev.ptr(tw), None, dev.ptr(ty), *args))
+    dev.torch.cuda.synchronize()
+    free_after, _ = dev.torch.cuda.mem_get_info()
+    assert free_after == free_before
+
+
 def test_noalloc_refuses_shapes_beyond_its_scratch(dev, lib):
     cap = lib.cudeep_b200_conv2d_noalloc_capacity()
     assert cap == 32 << 20
@@ -68,7 +89,8 @@ def test_noalloc_refuses_shapes_beyond_its_scratch(dev, lib):
     assert "built-in scratch" in msg and str(cap) in msg
 
 
-def test_noalloc_runs_direct_kernel_for_strided_shapes(dev, lib, oracle):
+def test_noalloc_runs_direct_kernel_for_shapes_off_the_tensor_core_path(dev, lib, oracle):
+    """Six output channels: under the 32 the implicit GEMM needs, so the direct kernel runs (no scratch)."""
     from cudeep_b200 import _lib
     rng = np.random.default_rng(5)
     x = rng.standard_normal((2, 8, 12, 12), dtype=np.float32)
