@@ -12,7 +12,17 @@ data path.  At N = 8 that is the 65536 x 8192 x 8192 sharded configuration.
 
 Prints one JSON line (rank 0).  `value` is device-resident throughput (CUDA events,
 max over ranks); `e2e` is the same product through the host-buffer entry point with
-pinned host inputs and outputs, copies inside the timed region.
+pinned host inputs and outputs, copies inside the timed region.  Timed after the headline and
+reported in the same line:
+  * `value_burst` / `value_sustained`: the headline over a 20-step and a 200-step region (the
+    GPU settles under its power cap within a few hundred milliseconds);
+  * `parity`: every rank checks sampled rows of its own C against a float64 product on the
+    host (the run fails above 5e-3);
+  * `c5_strong`: the sharded configurations at FIXED total size - 65536 x 8192 x 8192 and
+    16384^3, rows split evenly over the N ranks (cudeep::dist::ShardedGemm, one process per GPU);
+  * `with_gather` (N > 1): the optional all-gather of C on 65536 x 8192 x 8192 - compute alone,
+    the collective alone, GEMM followed by ncclAllGather, the band-pipelined NCCL form, and the
+    fused form in which the GEMM's epilogue stores every tile into all ranks' C.
 
 --impl reference times the reference's own CUDA kernels (cuDeep's matmul sources
 rebuilt unmodified for sm_100, oracle/_ref) on the same GPU, inputs and protocol; the
@@ -46,6 +56,10 @@ NOMINAL_TF32_TFLOPS = 1125.0        # half the nominal dense bf16 rate of a B200
 # DRAM bytes one 8192^3 launch moves (dram__bytes_read.sum + dram__bytes_write.sum from the
 # ncu capture summarised in profiles/); None until a capture exists.
 NCU_DRAM_BYTES_PER_LAUNCH = 2.54e9
+NCU_DRAM_SOURCE = ("a constant, not re-measured by this run: one ncu capture of the 8192^3 launch on 1 GPU "
+                   "(profiles/gemm_tf32_8192_umma_kernel.md)")
+PARITY_TOL = 5e-3                   # relative Frobenius error of the TF32 path against float64
+PARITY_ROWS = 16
 
 
 def parse_args():
@@ -56,9 +70,10 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--gather", action="store_true",
-                    help="with --gpus N > 1: additionally time steps that end with the optional NCCL "
-                         "all-gather of C's row shards (reported under \"with_gather\")")
+    ap.add_argument("--no-gather", action="store_true",
+                    help="with --gpus N > 1: skip the timings of the optional all-gather of C (\"with_gather\")")
+    ap.add_argument("--no-c5", action="store_true", help="skip the fixed-size sharded configurations (\"c5_strong\")")
+    ap.add_argument("--c5-steps", type=int, default=10)
     ap.add_argument("--suite", action="store_true",
                     help="instead of the headline line, time every benchmark configuration next to "
                          "cuBLAS / cuDNN (through torch) and the reference's kernels; one JSON line each")
@@ -236,6 +251,135 @@ def cpu_baseline_leg():
             "sample": f"rows 0..{rows - 1} of the 8192^3 product, FP32 sgemm (NumPy/OpenBLAS), best of ~12 s"}
 
 
+
+# ---------------------------------------------------------------------------- parity
+
+def all_reduce_max(dist, value: float) -> float:
+    return max_over_ranks(dist, value)
+
+
+def headline_parity(a_np, b_np, c, dist):
+    """Every rank: PARITY_ROWS sampled rows (all columns) of its own C against the float64 product of
+    its own A rows and B, on the host, outside any timed region.  The worst rank's figures."""
+    import torch
+    from oracle import oracle as o
+    rank = dist.get_rank() if dist is not None else 0
+    rows = np.sort(np.random.default_rng([77, rank]).choice(a_np.shape[0], size=PARITY_ROWS, replace=False))
+    got = c[torch.from_numpy(rows).cuda()].cpu().numpy()
+    err = o.rel_frobenius(got, o.gemm(a_np[rows], b_np))
+    model = o.rel_frobenius(got, o.gemm(a_np[rows], b_np, input_mode=o.INPUT_TF32_TRUNC))
+    err, model = all_reduce_max(dist, float(err)), all_reduce_max(dist, float(model))
+    if not (err <= PARITY_TOL):
+        raise RuntimeError(f"parity: relative error {err} of the 8192^3 product exceeds {PARITY_TOL}")
+    return {"max_rel_err": err, "max_rel_err_vs_tf32_truncated_operands": model, "rows_per_rank": PARITY_ROWS,
+            "tolerance": PARITY_TOL, "checked": "sampled rows of every rank's C against a float64 host product"}
+
+
+# ---------------------------------------------------------------------------- C5: fixed-size sharded GEMM
+
+def run_c5(args, rank, world, local, dist, gather: bool):
+    """65536 x 8192 x 8192 and 16384^3 with the rows split evenly over the ranks (strong scaling),
+    through cudeep::dist::ShardedGemm in its one-process-per-GPU form; on the first shape also the
+    optional all-gather of C in all its forms."""
+    import torch
+    from cudeep_b200 import workloads
+    from cudeep_b200 import sharded as sh
+    from oracle import oracle as o
+    # A stream of its own (not the legacy default stream): the steps are enqueued on it, the
+    # collective's stream is joined back into it, and the timing events are recorded on it.
+    side = torch.cuda.Stream()
+    stream = side.cuda_stream
+    out = {"strong": [], "with_gather": None}
+
+    def exchange_id(x):
+        box = [x]
+        dist.broadcast_object_list(box, src=0)
+        return box[0]
+
+    def exchange_handles(x):
+        box = [None] * world
+        dist.all_gather_object(box, x)
+        return box
+
+    def timed(g, mode, steps):
+        with torch.cuda.stream(side):
+            seconds, _, _ = time_device_steps(lambda: g.run(mode, stream), steps, 3, dist, local)
+        return max_over_ranks(dist, seconds) / steps * 1e3
+
+    def check_rows(g, rows_global, b_np, k, what):
+        """float64 check of the given global rows of this rank's copy of C."""
+        worst = 0.0
+        for r in rows_global:
+            band = int(r) // workloads.C5_BAND_ROWS
+            a_row = workloads.c5_a_band(band, k)[int(r) % workloads.C5_BAND_ROWS][None, :]
+            got = g.read_c(0, int(r), 1)
+            worst = max(worst, float(o.rel_frobenius(got, o.gemm(a_row, b_np))))
+        worst = all_reduce_max(dist, worst)
+        if not (worst <= PARITY_TOL):
+            raise RuntimeError(f"parity ({what}): relative error {worst} exceeds {PARITY_TOL}")
+        return worst
+
+    for m, n, k in workloads.C5_SHAPES:
+        if m % (world * workloads.C5_BAND_ROWS) != 0:
+            continue
+        g = sh.ShardedGemm.rank(rank, world, local, m, n, k, bands=4)
+        try:
+            if world > 1:
+                g.connect(exchange_id, exchange_handles)
+            mine = g.rows_of(rank)
+            b_np = workloads.c5_b(n, k)
+            g.set_b(b_np)
+            a_ptr = g.buffers(0)[0]
+            for i in range(mine.rows // workloads.C5_BAND_ROWS):       # band by band: no multi-GB host copy of A
+                band = workloads.c5_a_band(mine.row0 // workloads.C5_BAND_ROWS + i, k)
+                g._h2d(a_ptr + i * workloads.C5_BAND_ROWS * k * 4, band)
+            ms = timed(g, sh.GATHER_NONE, args.c5_steps)
+            flops = 2.0 * m * n * k
+            rng = np.random.default_rng([55, rank, m])
+            own = mine.row0 + np.sort(rng.choice(mine.rows, size=min(PARITY_ROWS, mine.rows), replace=False))
+            err = check_rows(g, own, b_np, k, f"C5 {m}x{n}x{k}, own rows")
+            out["strong"].append({
+                "workload": f"C[{m},{n}] = A[{m},{k}] @ B[{k},{n}], {mine.rows} rows per GPU", "flop_per_step": flops,
+                "rows_per_gpu": mine.rows, "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+                "tflops_per_gpu": flops / (ms * 1e-3) / 1e12 / world, "steps": args.c5_steps,
+                "scaling": "strong", "parity_max_rel_err": err})
+            if gather and out["with_gather"] is None:
+                t_compute = ms
+                t_gather = timed(g, sh.GATHER_COLLECTIVE_ONLY, args.c5_steps)
+                t_after = timed(g, sh.GATHER_AFTER_GEMM, args.c5_steps)
+                t_banded = timed(g, sh.GATHER_BANDED, args.c5_steps)
+                t_fused = timed(g, sh.GATHER_PEER_STORE, args.c5_steps)
+                # the fused form's result, checked on rows this rank did NOT compute
+                barrier_sync(dist)
+                others = [r for r in range(world) if r != rank]
+                foreign = []
+                for j in range(PARITY_ROWS):
+                    s_ = g.rows_of(others[j % len(others)])
+                    foreign.append(s_.row0 + int(rng.integers(s_.rows)))
+                err_fused = check_rows(g, foreign, b_np, k, "gathered C, peer-store form, rows of other ranks")
+                barrier_sync(dist)
+                g.run(sh.GATHER_BANDED, stream)
+                barrier_sync(dist)
+                err_banded = check_rows(g, foreign, b_np, k, "gathered C, banded NCCL form, rows of other ranks")
+                longer = max(t_compute, t_gather)
+                best = min(t_banded, t_fused)
+                out["with_gather"] = {
+                    "workload": f"C[{m},{n}] gathered on every GPU ({(world - 1) * mine.rows * n * 4} bytes received per GPU)",
+                    "t_compute_ms": t_compute, "t_gather_alone_ms": t_gather,
+                    "t_gemm_then_ncclAllGather_ms": t_after, "t_banded_nccl_ms": t_banded,
+                    "t_fused_peer_store_ms": t_fused, "t_both_ms": best,
+                    "form": "fused peer-store epilogue" if t_fused <= t_banded else "banded NCCL",
+                    "overlap": best / longer, "overlap_banded_nccl": t_banded / longer,
+                    "overlap_fused_peer_store": t_fused / longer, "plain_sum_ms": t_compute + t_gather,
+                    "tflops_with_gather": flops / (best * 1e-3) / 1e12,
+                    "parity_max_rel_err_fused": err_fused, "parity_max_rel_err_banded": err_banded,
+                    "steps": args.c5_steps,
+                    "note": "overlap = step time / max(compute alone, collective alone); 1.0 = the shorter leg is fully hidden"}
+            barrier_sync(dist)
+        finally:
+            g.close()
+    return out
+
 # ---------------------------------------------------------------------------- arms
 
 def run_ours(args):
@@ -278,24 +422,21 @@ def run_ours(args):
     e2e_value = flops_step * args.e2e_steps / e2e_seconds / 1e12
     checksum = float(hc[0, :8].sum())      # the step's result is read on the host
 
-    gather_info = None
-    if dist is not None and args.gather:
-        # The optional collective of the sharded GEMM: every rank ends up with all of C.
-        full = torch.empty((SIZE * world, SIZE), device="cuda", dtype=torch.float32)
+    # the headline again over a short and a long region: burst and power-capped figures side by side
+    other_steps = 200 if args.steps < 100 else 20
+    other_seconds, _, _ = time_device_steps(launch, other_steps, 3, dist, local)
+    other_seconds = max_over_ranks(dist, other_seconds)
+    other_value = flops_step * other_steps / other_seconds / 1e12
+    burst, sustained = (value, other_value) if args.steps < 100 else (other_value, value)
 
-        def launch_and_gather():
-            launch()
-            dist.all_gather_into_tensor(full, c)
+    parity = headline_parity(a_np, b_np, c, dist)
+    del a, b, c, ha, hb, hc
+    torch.cuda.empty_cache()
 
-        g_steps = max(5, args.steps // 10)
-        g_seconds, _, _ = time_device_steps(launch_and_gather, g_steps, 3, dist, local)
-        g_seconds = max_over_ranks(dist, g_seconds)
-        payload = (world - 1) * SIZE * SIZE * 4          # bytes each rank receives per step
-        gather_info = {"value": flops_step * g_steps / g_seconds / 1e12, "unit": "TFLOP/s",
-                       "ms_per_step": g_seconds / g_steps * 1e3, "steps": g_steps,
-                       "bytes_received_per_rank": payload,
-                       "note": "GEMM then ncclAllGather of C on the same stream, not overlapped"}
-        del full
+    c5 = None if args.no_c5 else run_c5(args, rank, world, local, dist, gather=(world > 1 and not args.no_gather))
+    status = _lib.device_status(True)
+    if status != 0:
+        raise RuntimeError(f"kernel status word {status}: a pipeline wait was abandoned")
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -319,19 +460,25 @@ def run_ours(args):
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * SIZE * SIZE * 4 * world,
                 "d2h_bytes_per_step": SIZE * SIZE * 4 * world, "steps": args.e2e_steps,
                 "result_probe": checksum},
+        "value_burst": burst, "value_sustained": sustained,
+        "burst_sustained_note": "same launch over a 20-step region and a 200-step region; `value` is the one with --steps",
+        "parity": parity,
         "gpu_launches": args.steps,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak,
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                     "traffic_source": NCU_DRAM_SOURCE,
                      "peak_source": f"{peak_kind} dense bf16 cuBLAS {'sustained' if long_region else 'burst'} "
                                     f"({bf16_peak} TFLOP/s) / 2: TF32 issues at half the bf16 rate; the timed "
                                     f"region lasted {seconds * 1e3:.0f} ms (sustained figure from {SUSTAINED_REGION_MS:.0f} ms on)",
                      "frac_of_burst_peak": achieved / (bf16_burst / 2.0),
                      "kernel": "umma_tf32_kernel", "kernel_ms": kernel_ms},
     }
-    if gather_info is not None:
-        line["with_gather"] = gather_info
+    if c5 is not None:
+        line["c5_strong"] = c5["strong"]
+        if c5.get("with_gather") is not None:
+            line["with_gather"] = c5["with_gather"]
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_leg()
     print(json.dumps(line), flush=True)

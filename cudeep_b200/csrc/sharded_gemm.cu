@@ -315,6 +315,12 @@ struct ShardedGemm::Impl {
         if (peers_ready || opt.dry_run) return;
         CB200_REQUIRE(in_process, "open_peers() must be called before a step with Gather::PeerStore");
         CB200_REQUIRE(world - 1 <= cudeep_b200::kMaxGemmPeers, "Gather::PeerStore supports at most 8 ranks");
+        int prev = 0;
+        CB200_CUDA(cudaGetDevice(&prev));
+        struct Restore {
+            int device;
+            ~Restore() { cudaSetDevice(device); }
+        } restore{prev};
         for (RankState& r : ranks) {
             CB200_CUDA(cudaSetDevice(r.device));
             r.peer_c.assign(size_t(world), nullptr);
