@@ -717,6 +717,9 @@ def run_c4(lib, ref, timed, emit, ok, P, stream, trim):
             "cudnn_tf32_torch": timed(lambda: F.relu(F.conv2d(xc, wc, bc, padding=1)), 15, cmp=True)}
     xl = xc.contiguous(memory_format=torch.channels_last)
     rows["cudnn_tf32_torch_nhwc_input"] = timed(lambda: F.relu(F.conv2d(xl, wc, bc, padding=1)), 15, cmp=True)
+    xh = xc.permute(0, 2, 3, 1).contiguous()           # [N, H, W, C] for the channels-last entry point
+    rows["ours_nhwc_input"] = timed(lambda: ok(lib.cudeep_b200_conv2d_forward_fused_nhwc_f32(
+        P(xh), P(wc), P(bc), P(yc), nb, ch, oc, size, size, 3, 3, 1, 1, 1, 1, 1, stream)), 15)
     if ref is not None:
         rows["reference_no_relu"] = timed(lambda: ref.cudeep_ref_conv2d_forward_f32(
             P(xc), P(wc), P(bc), P(yc), nb, ch, oc, size, size, 3, 3, 1, 1, 1, 1, stream), 5, cmp=True)

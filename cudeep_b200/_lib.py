@@ -31,6 +31,7 @@ PROTOTYPES = {
                                             c_int, c_int, c_int, c_int, c_uint32, c_uint32, _stream]),
     "cudeep_b200_conv2d_forward_f32": (c_int, [_fp, _fp, _fp, _fp] + [c_int] * 11 + [_stream]),
     "cudeep_b200_conv2d_forward_fused_f32": (c_int, [_fp, _fp, _fp, _fp] + [c_int] * 12 + [_stream]),
+    "cudeep_b200_conv2d_forward_fused_nhwc_f32": (c_int, [_fp, _fp, _fp, _fp] + [c_int] * 12 + [_stream]),
     "cudeep_b200_conv2d_forward_f64": (c_int, [_fp, _fp, _fp, _fp] + [c_int] * 11 + [_stream]),
     "cudeep_b200_conv2d_forward_noalloc_f32": (c_int, [_fp, _fp, _fp, _fp] + [c_int] * 12 + [_stream]),
     "cudeep_b200_conv2d_noalloc_capacity": (c_size_t, []),
@@ -63,6 +64,7 @@ PROTOTYPES = {
     "cudeep_b200_gemm_tf32_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int),
                                            POINTER(c_int), POINTER(c_int), POINTER(c_double)]),
     "cudeep_b200_matmul_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "cudeep_b200_matmul_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "cudeep_b200_matmul_f16_tuned": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                              ctypes.c_uint32, ctypes.c_uint32, c_void_p]),
     "cudeep_b200_pool_alloc": (c_int, [c_size_t, POINTER(c_void_p)]),

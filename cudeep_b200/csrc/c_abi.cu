@@ -181,6 +181,14 @@ int cudeep_b200_matmul_f16(const void* A, const void* B, float* C, int M, int N,
     });
 }
 
+int cudeep_b200_matmul_bf16(const void* A, const void* B, float* C, int M, int N, int K,
+                            cudeep_b200_stream_t stream) {
+    return guarded([&] {
+        cudeep::kernels::launch_matmul_kernel_bf16(static_cast<const __nv_bfloat16*>(A),
+                                                   static_cast<const __nv_bfloat16*>(B), C, M, N, K, as_stream(stream));
+    });
+}
+
 int cudeep_b200_matmul_f16_tuned(const void* A, const void* B, float* C, int M, int N, int K, int ctas,
                                  uint32_t b_lbo, uint32_t b_sbo, cudeep_b200_stream_t stream) {
     return guarded([&] {
@@ -199,6 +207,19 @@ int cudeep_b200_conv2d_forward_f32(const float* input, const float* weight, cons
                                                              out_channels, in_h, in_w, kernel_h, kernel_w,
                                                              stride_h, stride_w, pad_h, pad_w,
                                                              as_stream(stream));
+    });
+}
+
+int cudeep_b200_conv2d_forward_fused_nhwc_f32(const float* input_nhwc, const float* weight,
+                                              const float* bias, float* output, int batch,
+                                              int in_channels, int out_channels, int in_h, int in_w,
+                                              int kernel_h, int kernel_w, int stride_h, int stride_w,
+                                              int pad_h, int pad_w, int epilogue,
+                                              cudeep_b200_stream_t stream) {
+    return guarded([&] {
+        cudeep::kernels::launch_conv2d_forward_fused_layout(
+            input_nhwc, cudeep::Layout::NHWC, weight, bias, output, batch, in_channels, out_channels, in_h, in_w,
+            kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, as_epilogue(epilogue), as_stream(stream));
     });
 }
 

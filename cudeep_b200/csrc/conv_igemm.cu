@@ -600,10 +600,18 @@ size_t conv2d_igemm_scratch_bytes(const ConvShape& s, size_t* nhwc_bytes, size_t
     return a_pad + b_pad;
 }
 
+bool conv2d_igemm_takes_nhwc_input(const float* input, const ConvShape& s) {
+    // The kernel's own input layout is NHWC with the channel count a multiple of 4 and 16-byte
+    // aligned pixels; the row-packed form (a first layer's few channels) re-lays its input with
+    // padding columns and has no use for it.
+    return conv2d_igemm_supported(s) && s.in_c % 4 == 0 && (reinterpret_cast<uintptr_t>(input) & 15u) == 0 &&
+           !conv2d_igemm_row_packed(s);
+}
+
 void conv2d_igemm_with_scratch(const float* input, const float* weight, const float* bias,
                                float* output, const ConvShape& s, int act, void* scratch,
                                int force_ctas, cudaStream_t stream, bool flipped_filters,
-                               const InputDilation* dilation) {
+                               const InputDilation* dilation, bool input_is_nhwc) {
     check_conv_shape(s);
     CB200_REQUIRE(conv2d_igemm_supported(s), "conv2d: shape not supported by the tensor-core path");
     CB200_REQUIRE(scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0,
@@ -618,9 +626,17 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
     float* wp = reinterpret_cast<float*>(static_cast<char*>(scratch) + nhwc_bytes);
 
     const bool row_packed = !flipped_filters && dilation == nullptr && conv2d_igemm_row_packed(s);
+    if (input_is_nhwc) {
+        CB200_REQUIRE(!flipped_filters && dilation == nullptr && conv2d_igemm_takes_nhwc_input(input, s),
+                      "conv2d: an NHWC input needs C % 4 == 0, a 16-byte aligned pointer and a shape on the "
+                      "tensor-core path");
+        xt = const_cast<float*>(input);        // read in place: no re-layout pass, no copy
+    }
     const FilterPack filters{weight, wp, s.out_c, s.in_c, s.k_h, s.k_w, cp, flipped_filters ? 1 : 0,
                              row_packed ? cx : 0};
-    if (row_packed) {
+    if (input_is_nhwc) {
+        prepare_operands(nullptr, nullptr, /*batch=*/0, s.in_c, hw, cx, &filters, stream);      // filters only
+    } else if (row_packed) {
         // The copy gets pad_w zero pixels on either side of every row, so that each output
         // column's window of KW pixels is contiguous in it.
         const int wp_pixels = s.in_w + 2 * s.p_w;
@@ -669,14 +685,14 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
 
 void conv2d_igemm(const float* input, const float* weight, const float* bias, float* output,
                   const ConvShape& s, int act, cudaStream_t stream, bool flipped_filters,
-                  const InputDilation* dilation) {
+                  const InputDilation* dilation, bool input_is_nhwc) {
     const size_t bytes = conv2d_igemm_scratch_bytes(s, nullptr, nullptr);
     // Stream-ordered scratch, as the reference does for its temporaries
     // (conv_kernel.cu:282,314,748-754): safe when calls on several streams overlap.
     void* scratch = scratch_alloc(bytes, stream);
     try {
         conv2d_igemm_with_scratch(input, weight, bias, output, s, act, scratch, 0, stream, flipped_filters,
-                                  dilation);
+                                  dilation, input_is_nhwc);
     } catch (...) {
         scratch_free(scratch, stream);
         throw;

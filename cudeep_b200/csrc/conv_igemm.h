@@ -31,15 +31,18 @@ struct InputDilation {
 // flipped_filters: `weight` is [C][OC][KH][KW] as seen from `s` (the forward filters of the
 // convolution whose grad_input this call computes) and is used with both spatial axes reversed
 // and the channel axes swapped.
+// input_is_nhwc: `input` is [N][H][W][C] (the layout the kernel gathers from) and is read in place,
+// which saves the re-layout pass; needs conv2d_igemm_takes_nhwc_input.  The output is NCHW either way.
 void conv2d_igemm_with_scratch(const float* input, const float* weight, const float* bias,
                                float* output, const ConvShape& s, int act, void* scratch,
                                int force_ctas, cudaStream_t stream, bool flipped_filters = false,
-                               const InputDilation* dilation = nullptr);
+                               const InputDilation* dilation = nullptr, bool input_is_nhwc = false);
+bool conv2d_igemm_takes_nhwc_input(const float* input, const ConvShape& s);
 
 // Convolution with stream-ordered scratch (cudaMallocAsync / cudaFreeAsync on `stream`).
 void conv2d_igemm(const float* input, const float* weight, const float* bias, float* output,
                   const ConvShape& s, int act, cudaStream_t stream, bool flipped_filters = false,
-                  const InputDilation* dilation = nullptr);
+                  const InputDilation* dilation = nullptr, bool input_is_nhwc = false);
 
 // x[N][C][HW] -> xt[N][HW][cx] with cx >= C a multiple of 4 (channels past C are zero).
 void nchw_to_nhwc(const float* input, float* xt, int batch, int c, int hw, int cx, cudaStream_t stream);

@@ -66,8 +66,10 @@ struct GemmProblemF16 : GemmOutput {
     }
 };
 
-template <int CTAS, int KATOMS>
-void launch_f16(const __half* a, const __half* b, float* c, int m, int n, int k, uint32_t b_lbo, uint32_t b_sbo,
+// KIND: UMMA_KIND_F16 or UMMA_KIND_BF16; the operands are 2-byte words either way (the tensor maps
+// only move them), the MMA's instruction descriptor says how to read them.
+template <int CTAS, int KATOMS, int KIND = UMMA_KIND_F16>
+void launch_f16(const void* a, const void* b, float* c, int m, int n, int k, uint32_t b_lbo, uint32_t b_sbo,
                 cudaStream_t stream) {
     constexpr int BN = 256;
     using Cfg = UmmaConfig<CTAS, BN, true, KATOMS>;
@@ -111,16 +113,16 @@ void launch_f16(const __half* a, const __half* b, float* c, int m, int n, int k,
     if (groups < 1) groups = 1;
     if (groups > num_tiles) groups = num_tiles;
 
-    CB200_TRACE("gemm f16 tcgen05: M=%d N=%d K=%d tile=%dx%d ctas/mma=%d stages=%d clusters=%lld store=%s", m, n, k,
-                UMMA_BM * CTAS, BN, CTAS, sched.stages, groups, tma_store ? "bulk-tensor" : "registers");
-    auto kernel = umma_tf32_kernel<CTAS, BN, true, KATOMS, Prob, false, UMMA_KIND_F16>;
+    CB200_TRACE("gemm %s tcgen05: M=%d N=%d K=%d tile=%dx%d ctas/mma=%d stages=%d clusters=%lld store=%s",
+                KIND == UMMA_KIND_BF16 ? "bf16" : "f16", m, n, k, UMMA_BM * CTAS, BN, CTAS, sched.stages, groups, tma_store ? "bulk-tensor" : "registers");
+    auto kernel = umma_tf32_kernel<CTAS, BN, true, KATOMS, Prob, false, KIND>;
     UmmaEpilogueArgs epi{nullptr, 0, EPI_NONE};
     launch_umma(kernel, prob, sched, epi, groups, CTAS, smem_bytes, Cfg::SMEM_MAX, stream);
 }
 
 }  // namespace
 
-bool gemm_f16_supported(const __half* a, const __half* b, int m, int n, int k) {
+bool gemm_f16_supported(const void* a, const void* b, int m, int n, int k) {
     if (m < 64 || n < 64 || k < 64) return false;
     if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(b) & 15u)) return false;
     if (k % 8 != 0 || n % 8 != 0) return false;
@@ -138,6 +140,19 @@ void gemm_f16(const __half* a, const __half* b, float* c, int m, int n, int k, i
     }
     if (ctas == 2) launch_f16<2, 2>(a, b, c, m, n, k, b_lbo, b_sbo, stream);
     else launch_f16<1, 1>(a, b, c, m, n, k, b_lbo, b_sbo, stream);
+}
+
+void gemm_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, float* c, int m, int n, int k, int ctas,
+               cudaStream_t stream) {
+    CB200_REQUIRE(gemm_f16_supported(a, b, m, n, k),
+                  "BF16 tensor-core GEMM needs an sm_100 device, 16-byte aligned operands, K and N multiples "
+                  "of 8 and M, N, K of at least 64");
+    if (ctas == 0) {
+        const long long pair_tiles = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
+        ctas = pair_tiles * 2 >= device_info().num_sms / 2 ? 2 : 1;
+    }
+    if (ctas == 2) launch_f16<2, 2, UMMA_KIND_BF16>(a, b, c, m, n, k, 0, 0, stream);
+    else launch_f16<1, 1, UMMA_KIND_BF16>(a, b, c, m, n, k, 0, 0, stream);
 }
 
 }  // namespace cudeep_b200

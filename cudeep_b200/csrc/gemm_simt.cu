@@ -10,6 +10,7 @@
 #include "gemm_simt.h"
 #include "epilogue_math.cuh"
 
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 namespace cudeep_b200 {
@@ -34,6 +35,7 @@ template <> __device__ __forceinline__ double act_t<double>(double x, int act) {
 
 template <typename T, typename TI> __device__ __forceinline__ T widen(TI x) { return static_cast<T>(x); }
 template <> __device__ __forceinline__ float widen<float, __half>(__half x) { return __half2float(x); }
+template <> __device__ __forceinline__ float widen<float, __nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
 
 // TI: element type of A and B in memory; T: accumulate / output type.
 template <typename TI, typename T, int BM, int BN, int BK, int TM, int TN, bool B_NK, bool A_KM = false>
@@ -294,6 +296,12 @@ void gemm_simt_half(const __half* a, const __half* b, float* c, int m, int n, in
                     cudaStream_t stream) {
     CB200_REQUIRE(m > 0 && n > 0 && k > 0, "GEMM extents must be positive");
     launch<__half, float, 64, 64, 16, 4, 4>(a, b, false, c, m, n, k, nullptr, false, EPI_NONE, stream);
+}
+
+void gemm_simt_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, float* c, int m, int n, int k,
+                    cudaStream_t stream) {
+    CB200_REQUIRE(m > 0 && n > 0 && k > 0, "GEMM extents must be positive");
+    launch<__nv_bfloat16, float, 64, 64, 16, 4, 4>(a, b, false, c, m, n, k, nullptr, false, EPI_NONE, stream);
 }
 
 }  // namespace cudeep_b200

@@ -3,6 +3,7 @@
 
 #include "runtime.h"
 
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 namespace cudeep_b200 {
@@ -19,6 +20,8 @@ void gemm_simt_tn(const float* a, const float* b, float* c, int m, int n, int k,
 
 // C[M,N] = A[M,K] * B[K,N] with half inputs widened to FP32 and FP32 accumulation.
 void gemm_simt_half(const __half* a, const __half* b, float* c, int m, int n, int k,
+                    cudaStream_t stream);
+void gemm_simt_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, float* c, int m, int n, int k,
                     cudaStream_t stream);
 
 }  // namespace cudeep_b200

@@ -33,6 +33,30 @@ void launch_conv2d_forward_fused(const float* input, const float* weight, const 
         cudeep_b200::conv2d_direct<float>(input, weight, bias, output, s, act, stream);
 }
 
+void launch_conv2d_forward_fused_layout(const float* input, Layout input_layout, const float* weight,
+                                        const float* bias, float* output, int batch, int in_channels,
+                                        int out_channels, int in_h, int in_w, int kernel_h, int kernel_w,
+                                        int stride_h, int stride_w, int pad_h, int pad_w, GemmEpilogue epilogue,
+                                        cudaStream_t stream) {
+    if (input_layout == Layout::NCHW) {
+        launch_conv2d_forward_fused(input, weight, bias, output, batch, in_channels, out_channels, in_h, in_w,
+                                    kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, epilogue, stream);
+        return;
+    }
+    CB200_REQUIRE(input_layout == Layout::NHWC, "conv2d: unknown input layout");
+    CB200_REQUIRE(input != nullptr && weight != nullptr && output != nullptr, "conv2d: null tensor pointer");
+    const int act = static_cast<int>(epilogue);
+    CB200_REQUIRE(act >= 0 && act <= 4, "conv2d: unknown epilogue");
+    const cudeep_b200::ConvShape s = make_shape(batch, in_channels, out_channels, in_h, in_w, kernel_h,
+                                                kernel_w, stride_h, stride_w, pad_h, pad_w);
+    cudeep_b200::check_conv_shape(s);
+    CB200_REQUIRE(cudeep_b200::conv2d_igemm_takes_nhwc_input(input, s),
+                  "conv2d: an NHWC input needs C % 4 == 0, a 16-byte aligned pointer and a shape the tensor-core "
+                  "path takes (OC >= 32, at least 64 output pixels, strides 1..8, padding smaller than the filter, "
+                  "more channels than a row-packed first layer)");
+    cudeep_b200::conv2d_igemm(input, weight, bias, output, s, act, stream, false, nullptr, /*input_is_nhwc=*/true);
+}
+
 template <>
 void launch_conv2d_forward_kernel<float>(const float* input, const float* weight, const float* bias,
                                          float* output, int batch, int in_channels, int out_channels,

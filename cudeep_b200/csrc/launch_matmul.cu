@@ -80,6 +80,15 @@ void launch_matmul_kernel_fp16(const __half* A, const __half* B, float* C, int M
         cudeep_b200::gemm_simt_half(A, B, C, M, N, K, stream);
 }
 
+void launch_matmul_kernel_bf16(const __nv_bfloat16* A, const __nv_bfloat16* B, float* C, int M, int N, int K,
+                               cudaStream_t stream) {
+    check_dims(A, B, C, M, N, K);
+    if (cudeep_b200::gemm_f16_supported(A, B, M, N, K))
+        cudeep_b200::gemm_bf16(A, B, C, M, N, K, 0, stream);
+    else
+        cudeep_b200::gemm_simt_bf16(A, B, C, M, N, K, stream);
+}
+
 void launch_matmul_fused_act(const float* A, const float* B, float* C, int M, int N, int K,
                              GemmEpilogue epilogue, cudaStream_t stream) {
     check_dims(A, B, C, M, N, K);

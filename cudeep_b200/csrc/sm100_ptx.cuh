@@ -392,10 +392,10 @@ __host__ __device__ constexpr uint32_t idesc_tf32(int m, int n, int a_mn_major, 
            (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
 }
 
-// The same for kind::f16 with FP16 operands (A and B format 0), FP32 accumulate.
-__host__ __device__ constexpr uint32_t idesc_f16(int m, int n, int a_mn_major, int b_mn_major) {
-    return (1u << 4) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) |
-           (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+// The same for kind::f16, FP32 accumulate: A and B format 0 = FP16, 1 = BF16.
+__host__ __device__ constexpr uint32_t idesc_f16(int m, int n, int a_mn_major, int b_mn_major, int bf16 = 0) {
+    return (1u << 4) | (uint32_t(bf16) << 7) | (uint32_t(bf16) << 10) | (uint32_t(a_mn_major) << 15) |
+           (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
 }
 
 }  // namespace ptx

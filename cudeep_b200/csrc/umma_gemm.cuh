@@ -147,11 +147,12 @@ struct UmmaConfig {
 //   __device__ const CUtensorMap* out_map() const;      C as {N, M}, box {32, 32}, 128-byte swizzle
 //   __device__ void out_coords(tile, row_in_cta, col0, int& x, int& y) const;
 constexpr uint32_t UMMA_STORE_STAGING_BYTES = 4 * 2 * 4096;     // 4 epilogue warps x 2 blocks of 32 x 32 floats
-// KIND: 0 = FP32 operands multiplied as TF32 (K block of 32 elements), 1 = FP16 operands (K block of
-// 64 elements); a K block is 128 bytes per operand row either way, so stages, barriers and the
-// epilogue do not change.
+// KIND: 0 = FP32 operands multiplied as TF32 (K block of 32 elements), 1 = FP16 operands, 2 = BF16
+// operands (K block of 64 elements); a K block is 128 bytes per operand row either way, so stages,
+// barriers and the epilogue do not change.
 constexpr int UMMA_KIND_TF32 = 0;
 constexpr int UMMA_KIND_F16 = 1;
+constexpr int UMMA_KIND_BF16 = 2;
 
 // Optional part of the problem contract, for a row-sharded product whose every rank needs all of C:
 //   static constexpr bool kPeerStore = true;
@@ -214,8 +215,8 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
             ptx::mbar_init(ptx::smem_u32(&bar_acc_full[a]), 1);
             ptx::mbar_init(ptx::smem_u32(&bar_acc_empty[a]), 4 * CTAS);
         }
-        // One arrival per epilogue thread of every other K range.
-        ptx::mbar_init(ptx::smem_u32(&bar_exchange), ksplit > 1 ? (ksplit - 1) * UMMA_BM : 1);
+        // One arrival per epilogue warp of every other K range.
+        ptx::mbar_init(ptx::smem_u32(&bar_exchange), ksplit > 1 ? (ksplit - 1) * 4 : 1);
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
@@ -311,8 +312,9 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
             // addresses in the uniform datapath the tensor-core instructions read from); one
             // elected lane issues the MMAs and commits.
             const uint32_t idesc =
-                KIND == UMMA_KIND_F16
-                    ? ptx::idesc_f16(UMMA_BM * CTAS, sched.umma_n, A_MN_MAJOR ? 1 : 0, B_MN_MAJOR ? 1 : 0)
+                KIND != UMMA_KIND_TF32
+                    ? ptx::idesc_f16(UMMA_BM * CTAS, sched.umma_n, A_MN_MAJOR ? 1 : 0, B_MN_MAJOR ? 1 : 0,
+                                     KIND == UMMA_KIND_BF16 ? 1 : 0)
                     : ptx::idesc_tf32(UMMA_BM * CTAS, sched.umma_n, /*a_mn=*/A_MN_MAJOR ? 1 : 0,
                                       /*b_mn=*/B_MN_MAJOR ? 1 : 0);
             // K-major operand: rows are 128 B, 8-row swizzle atoms 1024 B apart.
@@ -329,7 +331,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
             // MN-major 16-bit B: the plain 128-byte swizzle; TMA boxes of 64 columns x 64 K rows
             // (8192 B): column chunks 8192 B apart, 8-row K groups 1024 B apart, and one MMA
             // (K = 16) advances by 16 rows = 2048 B.
-            constexpr bool b_mn16 = B_MN_MAJOR && KIND == UMMA_KIND_F16;
+            constexpr bool b_mn16 = B_MN_MAJOR && KIND != UMMA_KIND_TF32;
             const uint32_t b_lbo = sched.b_lbo ? sched.b_lbo : (b_mn16 ? 8192u : B_MN_MAJOR ? 4096u : 16u);
             const uint32_t b_sbo = sched.b_sbo ? sched.b_sbo : (b_mn16 ? 1024u : B_MN_MAJOR ? 512u : 1024u);
             const uint64_t b_base = ptx::smem_desc(
@@ -378,7 +380,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                             for (int kk = 0; kk < UMMA_BK / UMMA_K; ++kk) {
                                 const uint64_t a_desc = a_stage + ((j * Cfg::ATOM_BYTES + kk * a_kstep) >> 4);
                                 const uint64_t b_desc = b_stage + ((j * Cfg::ATOM_BYTES + kk * b_kstep) >> 4);
-                                if constexpr (KIND == UMMA_KIND_F16)
+                                if constexpr (KIND != UMMA_KIND_TF32)
                                     ptx::umma_f16<CTAS>(d_tmem, a_desc, b_desc, idesc, (ks | j | kk) != 0);
                                 else
                                     ptx::umma_tf32<CTAS>(d_tmem, a_desc, b_desc, idesc, (ks | j | kk) != 0);
@@ -490,9 +492,15 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                         ptx::st_cluster_v4(dst + q * (UMMA_BM * 16u), r0[4 * q], r0[4 * q + 1], r0[4 * q + 2],
                                            r0[4 * q + 3]);
                 }
-                for (uint32_t g = 0; g < ksplit; ++g)
-                    if (g != kgroup)
-                        ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bar_exchange), g * CTAS + cta_rank));
+                // One lane signals for the warp: the warp barrier orders every lane's stores before
+                // lane 0's release, which is cumulative, so the owner's acquire sees all of them.
+                // (128 arrivals per peer barrier, one per thread, took longer than the stores.)
+                __syncwarp();
+                if (lane == 0) {
+                    for (uint32_t g = 0; g < ksplit; ++g)
+                        if (g != kgroup)
+                            ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bar_exchange), g * CTAS + cta_rank));
+                }
                 ok = ptx::mbar_wait<true>(ptx::smem_u32(&bar_exchange), 0, wctx, UMMA_TIMEOUT_EXCHANGE);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;

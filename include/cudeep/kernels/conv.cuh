@@ -24,6 +24,7 @@
 
 #include <cuda_runtime.h>
 
+#include "../common.cuh"
 #include "matmul.cuh"
 
 namespace cudeep {
@@ -59,6 +60,19 @@ void launch_conv2d_forward_fused(const float* input, const float* weight, const 
                                  int in_h, int in_w, int kernel_h, int kernel_w, int stride_h,
                                  int stride_w, int pad_h, int pad_w, GemmEpilogue epilogue,
                                  cudaStream_t stream = nullptr);
+
+// Addition: the fused convolution for an input already stored channels-last.  `input_layout` is the
+// reference's own enum (include/cudeep/common.cuh:10-19): Layout::NCHW is launch_conv2d_forward_fused;
+// Layout::NHWC reads input [N, H, W, C] in place - the layout the tensor-core kernel gathers from - and
+// so skips the re-layout pass of the NCHW form (about a sixth of that call on a 64 x 256 x 56 x 56
+// layer).  Weights stay [OC, C, KH, KW] and the output stays [N, OC, OH, OW].  NHWC needs C % 4 == 0,
+// a 16-byte aligned input and a shape the tensor-core path takes (see the top of this file); anything
+// else throws instead of falling back.
+void launch_conv2d_forward_fused_layout(const float* input, Layout input_layout, const float* weight,
+                                        const float* bias, float* output, int batch, int in_channels,
+                                        int out_channels, int in_h, int in_w, int kernel_h, int kernel_w,
+                                        int stride_h, int stride_w, int pad_h, int pad_w, GemmEpilogue epilogue,
+                                        cudaStream_t stream = nullptr);
 
 }  // namespace kernels
 }  // namespace cudeep

@@ -16,6 +16,7 @@
 #pragma once
 
 #include <cuda_runtime.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 namespace cudeep {
@@ -52,6 +53,12 @@ void launch_matmul_fused_act(const float* A, const float* B, float* C, int M, in
                              GemmEpilogue epilogue, cudaStream_t stream = nullptr);
 
 // ---- additions ------------------------------------------------------------------------
+
+// BF16 inputs, float output: launch_matmul_kernel_fp16's sibling (the reference has FP16 only).
+// Tensor cores (kind::f16 with BF16 operand format) for aligned shapes of at least a tile, the
+// SIMT kernel otherwise; products of BF16 values are exact, accumulation is FP32.
+void launch_matmul_kernel_bf16(const __nv_bfloat16* A, const __nv_bfloat16* B, float* C, int M, int N, int K,
+                               cudaStream_t stream = nullptr);
 
 // y[M,N] = act(x[M,K] * W[N,K]^T + bias[N]) in one kernel.  W is consumed as
 // nn.Linear stores it ([out_features, in_features] row-major); bias may be

@@ -109,6 +109,9 @@ int cudeep_b200_matmul_f16(const void* A, const void* B, float* C, int M, int N,
                            cudeep_b200_stream_t stream);
 /* The same on the tensor-core path only (fails instead of falling back), for benchmarks and
  * bring-up: ctas 0 | 1 | 2; b_lbo / b_sbo as in cudeep_b200_gemm_tf32_tuned (bits 0-15 only). */
+/* The same with BF16 operands (an addition: the reference has FP16 only). */
+int cudeep_b200_matmul_bf16(const void* A, const void* B, float* C, int M, int N, int K,
+                            cudeep_b200_stream_t stream);
 int cudeep_b200_matmul_f16_tuned(const void* A, const void* B, float* C, int M, int N, int K, int ctas,
                                  uint32_t b_lbo, uint32_t b_sbo, cudeep_b200_stream_t stream);
 
@@ -160,6 +163,18 @@ int cudeep_b200_conv2d_forward_fused_f32(const float* input, const float* weight
                                          int out_channels, int in_h, int in_w, int kernel_h,
                                          int kernel_w, int stride_h, int stride_w, int pad_h,
                                          int pad_w, int epilogue, cudeep_b200_stream_t stream);
+
+/* The same for an input already stored channels-last, input[N,H,W,C] (Layout::NHWC of
+ * include/cudeep/common.cuh:10-19; the reference declares the enum and has no kernel for it): the
+ * tensor-core kernel gathers from that layout, so the re-layout pass of the NCHW form is skipped.
+ * Filters stay OIHW, the output stays NCHW.  Needs C % 4 == 0, a 16-byte aligned input and a shape
+ * on the tensor-core path; fails otherwise (no fallback). */
+int cudeep_b200_conv2d_forward_fused_nhwc_f32(const float* input_nhwc, const float* weight,
+                                              const float* bias, float* output, int batch,
+                                              int in_channels, int out_channels, int in_h, int in_w,
+                                              int kernel_h, int kernel_w, int stride_h, int stride_w,
+                                              int pad_h, int pad_w, int epilogue,
+                                              cudeep_b200_stream_t stream);
 
 /* Conv2d forward (+ bias + activation) that allocates nothing.  No counterpart in the
  * reference: it exists for callers with a fixed device-memory plan - a serving process

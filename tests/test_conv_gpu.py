@@ -148,6 +148,45 @@ def test_strided_tensor_core_path_shapes(dev, lib, oracle, shape, oc, k, stride,
             assert oracle.rel_frobenius(dx, model) <= TF32_MODEL_TOL
 
 
+@pytest.mark.parametrize("shape,oc,k,stride,padding", [
+    ((2, 64, 28, 28), 128, 3, 1, 1),       # single-image tiles, bulk tensor stores
+    ((3, 36, 19, 23), 40, 3, 1, 1),        # ragged everything; channels padded to one K block
+    ((4, 128, 7, 7), 256, 3, 1, 1),        # several images per tile
+    ((2, 64, 30, 30), 96, 3, 2, 1),        # strided
+    ((2, 256, 14, 14), 64, 1, 1, 0),       # 1 x 1
+])
+@pytest.mark.parametrize("act", [0, 1])
+def test_nhwc_input_matches_the_nchw_call_bit_for_bit(dev, lib, oracle, shape, oc, k, stride, padding, act):
+    """The channels-last entry reads its input in place; everything after the (skipped) re-layout is the
+    same kernel on the same bytes, so the result equals the NCHW call's exactly - and the oracle's."""
+    rng = np.random.default_rng(sum(shape) + oc + k)
+    n, c, h, w_ = shape
+    x = rng.standard_normal(shape, dtype=np.float32)
+    w = (rng.standard_normal((oc, c, k, k), dtype=np.float32) * np.float32(0.1))
+    bias = rng.uniform(-0.5, 0.5, oc).astype(np.float32)
+    want = dev.conv2d(x, w, bias, (stride, stride), (padding, padding), act=act)
+    tx = dev.to_dev(np.ascontiguousarray(x.transpose(0, 2, 3, 1)))          # [N, H, W, C]
+    tw, tb = dev.to_dev(w), dev.to_dev(bias)
+    ty = dev.empty(want.shape)
+    dev.check(lib.cudeep_b200_conv2d_forward_fused_nhwc_f32(dev.ptr(tx), dev.ptr(tw), dev.ptr(tb), dev.ptr(ty), n, c,
+                                                            oc, h, w_, k, k, stride, stride, padding, padding, act,
+                                                            None))
+    assert dev.sync_status() == 0
+    got = ty.cpu().numpy()
+    assert np.array_equal(got, want)
+    assert oracle.rel_frobenius(got, oracle.conv2d(x, w, bias, (stride, stride), (padding, padding), act=act)) <= 5e-3
+
+
+def test_nhwc_input_refuses_what_it_cannot_read_in_place(dev, lib):
+    p = dev.ptr(dev.empty((64,)))
+    # 6 channels: not a multiple of 4
+    rc = lib.cudeep_b200_conv2d_forward_fused_nhwc_f32(p, p, None, p, 2, 6, 64, 16, 16, 3, 3, 1, 1, 1, 1, 0, None)
+    assert rc != 0 and b"NHWC input needs" in lib.cudeep_b200_last_error()
+    # 8 output channels: off the tensor-core path
+    rc = lib.cudeep_b200_conv2d_forward_fused_nhwc_f32(p, p, None, p, 2, 64, 8, 16, 16, 3, 3, 1, 1, 1, 1, 0, None)
+    assert rc != 0 and b"NHWC input needs" in lib.cudeep_b200_last_error()
+
+
 def test_no_bias_and_bias_differ_by_bias(dev):
     rng = np.random.default_rng(3)
     x = rng.standard_normal((1, 32, 8, 8), dtype=np.float32)

@@ -390,6 +390,27 @@ def test_fp16_launcher_any_shape(dev, oracle, m, n, k):
     assert oracle.rel_frobenius(got, want) <= FP32_TOL
 
 
+@pytest.mark.parametrize("m,n,k", [
+    (256, 256, 64), (640, 768, 416), (300, 520, 1000), (2048, 2048, 2048),      # tensor cores: one CTA and CTA pairs
+    (2, 2, 3), (33, 17, 20), (100, 260, 36),                                      # SIMT: small or unaligned
+])
+def test_bf16_launcher(dev, lib, oracle, m, n, k):
+    """BF16 operands on the FP16 mainloop (the MMA's operand-format bits are the only difference).  BF16
+    products are exact in FP32, so the result is the float64 product of the BF16 values up to FP32
+    accumulation - the strict bar; a kernel that read the bits as FP16 would miss it by orders of magnitude."""
+    import torch
+    rng = np.random.default_rng(m * 7 + n + k)
+    ta = torch.from_numpy(rng.standard_normal((m, k), dtype=np.float32)).to(torch.bfloat16).to(dev.dev)
+    tb = torch.from_numpy(rng.standard_normal((k, n), dtype=np.float32)).to(torch.bfloat16).to(dev.dev)
+    tc = dev.empty((m, n))
+    dev.check(lib.cudeep_b200_matmul_bf16(dev.ptr(ta), dev.ptr(tb), dev.ptr(tc), m, n, k, None))
+    assert dev.sync_status() == 0
+    got = tc.cpu().numpy()
+    want = oracle.gemm(ta.float().cpu().numpy(), tb.float().cpu().numpy())
+    assert not np.isnan(got).any()
+    assert oracle.rel_frobenius(got, want) <= FP32_TOL * max(1.0, k / 4096.0)
+
+
 # ---- transposed operands (the products of matmul's backward pass) ---------------------------------
 
 @pytest.mark.parametrize("m,n,k", [
