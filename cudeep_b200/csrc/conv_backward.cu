@@ -6,7 +6,9 @@
 // (KH-1-pad_h, KW-1-pad_w) - so it runs on the forward implicit-GEMM path, whose filter
 // packing reads the filters in that order.  The reference instead forms weight^T x grad_output as one big
 // GEMM into a [C*KH*KW, N*OH*OW] temporary and scatters it back with col2im.  A strided
-// convolution takes the same path with zeros inserted between the pixels of grad_output.
+// convolution splits its input pixels into stride_h * stride_w parity classes, each the stride-1
+// convolution of grad_output with the sub-filter of the taps that reach it (conv_igemm.cu); shapes
+// that form does not take use the same path with zeros inserted between the pixels of grad_output.
 // FP64 and shapes the tensor-core path does not take use a direct gather kernel.
 //
 // grad_weight: an implicit GEMM over output pixels on the tensor cores (any stride up to 8)
@@ -141,6 +143,9 @@ void launch_conv2d_backward_data_kernel<float>(const float* grad_output, const f
         // channel axes swapped: no re-arranged copy is made.
         cudeep_b200::conv2d_igemm(grad_output, weight, nullptr, grad_input, as_forward, cudeep_b200::EPI_NONE,
                                   stream, /*flipped_filters=*/true);
+    } else if (!stride_one && cudeep_b200::conv2d_grad_input_by_parity_supported(s)) {
+        // One stride-1 convolution of grad_output per parity class of the input pixels.
+        cudeep_b200::conv2d_grad_input_by_parity(grad_output, weight, grad_input, s, stream);
     } else if (pad_fits && !stride_one && stride_h * stride_w <= 16 &&
                cudeep_b200::conv2d_igemm_supported(dilated)) {
         const cudeep_b200::InputDilation dilation{s.out_h(), s.out_w(), stride_h, stride_w};

@@ -23,6 +23,8 @@
 #include "conv_igemm.h"
 #include "umma_gemm.cuh"
 
+#include <vector>
+
 namespace cudeep_b200 {
 
 namespace {
@@ -38,10 +40,15 @@ namespace {
 //            wp[oc][kh*KW + kw][c] = w[c][oc][KH-1-kh][KW-1-kw].
 //   row-packed (row_cx > 0, few input channels): one 32-wide K block per filter row holds its
 //            KW taps of row_cx channels each, wp[oc][kh][kw * row_cx + c] = w[oc][c][kh][kw].
+//   flipped sub-filter (sub_sh > 0): the launch computes one parity class of a strided layer's
+//            grad_input; its k_h x k_w taps are every sub_sh-th / sub_sw-th tap of the forward filter
+//            (full_kh x full_kw) starting at (sub_a, sub_b), reversed:
+//            wp[oc][kh*KW + kw][c] = w[c][oc][sub_a + sub_sh*(KH-1-kh)][sub_b + sub_sw*(KW-1-kw)].
 struct FilterPack {
     const float* w;
     float* wp;
     int oc_n, c, k_h, k_w, cp, flipped, row_cx;
+    int sub_sh = 0, sub_sw = 0, sub_a = 0, sub_b = 0, full_kh = 0, full_kw = 0;
 };
 
 __device__ __forceinline__ void pack_filters(const FilterPack& f, long long block, long long blocks, int threads) {
@@ -66,7 +73,11 @@ __device__ __forceinline__ void pack_filters(const FilterPack& f, long long bloc
         const long long oc = r / taps;
         float v = 0.0f;
         if (ch < f.c) {
-            if (f.flipped) {
+            if (f.flipped && f.sub_sh > 0) {
+                const int kh = tap / f.k_w, kw = tap - kh * f.k_w;
+                const int fh = f.sub_a + f.sub_sh * (f.k_h - 1 - kh), fw = f.sub_b + f.sub_sw * (f.k_w - 1 - kw);
+                v = f.w[((static_cast<long long>(ch) * f.oc_n + oc) * f.full_kh + fh) * f.full_kw + fw];
+            } else if (f.flipped) {
                 const int kh = tap / f.k_w, kw = tap - kh * f.k_w;
                 v = f.w[((static_cast<long long>(ch) * f.oc_n + oc) * f.k_h + (f.k_h - 1 - kh)) * f.k_w +
                         (f.k_w - 1 - kw)];
@@ -202,6 +213,12 @@ struct ConvProblem {
     // ROW_PACKED: one K block per filter row (see launch_conv), map_x is the window view.
     int contig;            // box_w == OW: the tile's pixels are contiguous in the output plane
     int vec_ok;            // 128-bit stores are aligned for every tile
+    // Where output pixel (oh, ow) of plane (n, oc) goes: out + (n * OC + oc) * out_plane + out_off +
+    // oh * out_row + ow * out_col.  A plain convolution has out_plane = OH * OW, out_off = 0,
+    // out_row = OW, out_col = 1; a parity class of a strided grad_input writes every stride-th
+    // pixel of a larger plane (then contig == 0).
+    long long out_plane;
+    int out_off, out_row, out_col;
 
     struct Tile {
         int oc0;           // first output channel of this CTA
@@ -295,11 +312,12 @@ struct ConvProblem {
                 const int rem = col - img * per_image;
                 const int oh = rem / box_w, ow = rem - oh * box_w;
                 if (t.n + img < batch && oh < oh_n && ow < ow_n)
-                    out[((static_cast<long long>(t.n + img) * oc_n + oc) * oh_n + oh) * ow_n + ow] = v[j];
+                    out[(static_cast<long long>(t.n + img) * oc_n + oc) * out_plane + out_off + oh * out_row +
+                        ow * out_col] = v[j];
             }
             return;
         }
-        float* plane = out + (static_cast<long long>(t.n) * oc_n + oc) * oh_n * ow_n;
+        float* plane = out + (static_cast<long long>(t.n) * oc_n + oc) * out_plane + out_off;
         if (contig) {
             const int rows = min(box_h, oh_n - t.oh0);
             const int limit = rows * ow_n;                 // valid accumulator columns
@@ -320,7 +338,7 @@ struct ConvProblem {
                 const int r = col / box_w;
                 const int q = col - r * box_w;
                 const int oh = t.oh0 + r, ow = t.ow0 + q;
-                if (oh < oh_n && ow < ow_n) plane[static_cast<long long>(oh) * ow_n + ow] = v[j];
+                if (oh < oh_n && ow < ow_n) plane[static_cast<long long>(oh) * out_row + ow * out_col] = v[j];
             }
         }
     }
@@ -398,9 +416,19 @@ TilePlan plan_multi_image_tile(int oh, int ow, int batch, int ctas, int s_h, int
     return best;
 }
 
+// What a parity class of a strided grad_input changes about a launch: the input plane the tensor
+// map describes (rows and columns past it read as zeros, and `s` may claim a larger or smaller
+// plane so that its output size is the class's), and where the output pixels go.
+struct ConvExtras {
+    int map_h, map_w;                 // true extent of the input plane
+    long long out_plane;              // floats per output plane
+    int out_off, out_row, out_col;    // see ConvProblem
+};
+
 template <int CTAS, int KATOMS, bool ROW_PACKED, bool MULTI_IMAGE>
 void launch_conv(const float* xt, const float* wp, const float* bias, float* out, const ConvShape& s,
-                 int cx, int cp, const TilePlan& plan, int act, cudaStream_t stream) {
+                 int cx, int cp, const TilePlan& plan, int act, cudaStream_t stream,
+                 const ConvExtras* extras = nullptr) {
     using Cfg = UmmaConfig<CTAS, 256, false, KATOMS>;
     using Prob = ConvProblem<CTAS, ROW_PACKED, MULTI_IMAGE>;
     // Rows and images of the pixel box one CTA stages.
@@ -432,9 +460,10 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
         const uint32_t steps[4] = {1, 1, uint32_t(s.s_h), 1};
         encode_tensor_map(&prob.map_x, xt, 4, dims, strides, box, TmaSwizzle::B128, steps);
     } else {
-        const uint64_t dims[4] = {uint64_t(cx), uint64_t(s.in_w), uint64_t(s.in_h), uint64_t(s.batch)};
-        const uint64_t strides[3] = {uint64_t(cx) * 4, uint64_t(s.in_w) * cx * 4,
-                                     uint64_t(s.in_h) * s.in_w * cx * 4};
+        const int map_h = extras ? extras->map_h : s.in_h, map_w = extras ? extras->map_w : s.in_w;
+        const uint64_t dims[4] = {uint64_t(cx), uint64_t(map_w), uint64_t(map_h), uint64_t(s.batch)};
+        const uint64_t strides[3] = {uint64_t(cx) * 4, uint64_t(map_w) * cx * 4,
+                                     uint64_t(map_h) * map_w * cx * 4};
         // A strided convolution reads every s-th input pixel: the box spans box * s input pixels
         // and the TMA unit walks it in steps of s (element strides), so box_w x box_h pixels land.
         const uint32_t box[4] = {UMMA_BK, uint32_t(plan.box_w * s.s_w), cta_rows * s.s_h, cta_images};
@@ -458,7 +487,11 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     prob.s_w = s.s_w;
     prob.total_kb = taps * prob.c_blocks;
     prob.batch = s.batch;
-    prob.contig = (plan.box_w == ow && !MULTI_IMAGE) ? 1 : 0;
+    prob.out_plane = extras ? extras->out_plane : static_cast<long long>(oh) * ow;
+    prob.out_off = extras ? extras->out_off : 0;
+    prob.out_row = extras ? extras->out_row : ow;
+    prob.out_col = extras ? extras->out_col : 1;
+    prob.contig = (plan.box_w == ow && !MULTI_IMAGE && extras == nullptr) ? 1 : 0;
     prob.vec_ok = (prob.contig && ((plan.box_h * ow) % 4 == 0) && ((oh * ow) % 4 == 0) &&
                    ((reinterpret_cast<uintptr_t>(out) & 15u) == 0)) ? 1 : 0;
     // Bulk stores: contiguous tiles, plane rows of 16-byte multiples, chunk starts on 16-byte
@@ -600,6 +633,40 @@ size_t conv2d_igemm_scratch_bytes(const ConvShape& s, size_t* nhwc_bytes, size_t
     return a_pad + b_pad;
 }
 
+namespace {
+// Picks the pixel box (one image's rows, or several whole images for small maps) and the CTA
+// grouping, and launches the matching kernel instantiation.
+void plan_and_launch(const float* xt, const float* wp, const float* bias, float* output, const ConvShape& s,
+                     int cx, int cp, int act, int force_ctas, bool row_packed, cudaStream_t stream,
+                     const ConvExtras* extras) {
+    const int oh = s.out_h(), ow = s.out_w();
+    int ctas = force_ctas;
+    if (ctas == 0) ctas = (s.out_c > UMMA_BM) ? 2 : 1;
+    TilePlan plan = plan_tile(oh, ow, ctas, s.s_h, s.s_w);
+    if (plan.box_w == 0 && ctas == 2) {
+        ctas = 1;
+        plan = plan_tile(oh, ow, 1, s.s_h, s.s_w);
+    }
+    CB200_REQUIRE(plan.box_w > 0, "conv2d: no tile shape fits this output size");
+    // A CTA pair stages at most 32 KB per K block, so two blocks share a pipeline
+    // stage and the barrier handshake is paid half as often.
+    if (!row_packed)
+        plan = plan_multi_image_tile(oh, ow, s.batch, ctas, s.s_h, s.s_w, (s.out_c + UMMA_BM * ctas - 1) / (UMMA_BM * ctas),
+                                     device_info().num_sms, plan);
+    CB200_REQUIRE(plan.box_w > 0, "conv2d: no tile shape fits this output size");
+    if (row_packed) {
+        if (ctas == 2) launch_conv<2, 2, true, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream, extras);
+        else launch_conv<1, 1, true, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream, extras);
+    } else if (plan.box_n > 1) {
+        if (ctas == 2) launch_conv<2, 2, false, true>(xt, wp, bias, output, s, cx, cp, plan, act, stream, extras);
+        else launch_conv<1, 1, false, true>(xt, wp, bias, output, s, cx, cp, plan, act, stream, extras);
+    } else {
+        if (ctas == 2) launch_conv<2, 2, false, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream, extras);
+        else launch_conv<1, 1, false, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream, extras);
+    }
+}
+}  // namespace
+
 bool conv2d_igemm_takes_nhwc_input(const float* input, const ConvShape& s) {
     // The kernel's own input layout is NHWC with the channel count a multiple of 4 and 16-byte
     // aligned pixels; the row-packed form (a first layer's few channels) re-lays its input with
@@ -656,31 +723,7 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
         prepare_operands(input, xt, s.batch, s.in_c, hw, cx, &filters, stream);
     }
 
-    const int oh = s.out_h(), ow = s.out_w();
-    int ctas = force_ctas;
-    if (ctas == 0) ctas = (s.out_c > UMMA_BM) ? 2 : 1;
-    TilePlan plan = plan_tile(oh, ow, ctas, s.s_h, s.s_w);
-    if (plan.box_w == 0 && ctas == 2) {
-        ctas = 1;
-        plan = plan_tile(oh, ow, 1, s.s_h, s.s_w);
-    }
-    CB200_REQUIRE(plan.box_w > 0, "conv2d: no tile shape fits this output size");
-    // A CTA pair stages at most 32 KB per K block, so two blocks share a pipeline
-    // stage and the barrier handshake is paid half as often.
-    if (!row_packed)
-        plan = plan_multi_image_tile(oh, ow, s.batch, ctas, s.s_h, s.s_w, (s.out_c + UMMA_BM * ctas - 1) / (UMMA_BM * ctas),
-                                     device_info().num_sms, plan);
-    CB200_REQUIRE(plan.box_w > 0, "conv2d: no tile shape fits this output size");
-    if (row_packed) {
-        if (ctas == 2) launch_conv<2, 2, true, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
-        else launch_conv<1, 1, true, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
-    } else if (plan.box_n > 1) {
-        if (ctas == 2) launch_conv<2, 2, false, true>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
-        else launch_conv<1, 1, false, true>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
-    } else {
-        if (ctas == 2) launch_conv<2, 2, false, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
-        else launch_conv<1, 1, false, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream);
-    }
+    plan_and_launch(xt, wp, bias, output, s, cx, cp, act, force_ctas, row_packed, stream, nullptr);
 }
 
 void conv2d_igemm(const float* input, const float* weight, const float* bias, float* output,
@@ -693,6 +736,135 @@ void conv2d_igemm(const float* input, const float* weight, const float* bias, fl
     try {
         conv2d_igemm_with_scratch(input, weight, bias, output, s, act, scratch, 0, stream, flipped_filters,
                                   dilation, input_is_nhwc);
+    } catch (...) {
+        scratch_free(scratch, stream);
+        throw;
+    }
+    scratch_free(scratch, stream);
+}
+
+// ------------------------------------------------------------------ grad_input of a strided layer
+//
+// dx[n,c,ih,iw] = sum over (oc, kh, kw) with (ih + p - kh) divisible by s of
+//                 dy[n,oc,(ih + p - kh) / s, ...] * w[oc,c,kh,kw].
+// Input pixels fall into s_h * s_w classes by ((ih + p_h) mod s_h, (iw + p_w) mod s_w).  Class (a, b)
+// is reached only by the taps kh = a + s_h * j, kw = b + s_w * l, and with ih = s_h * u + a - p_h its
+// values are  sum_{oc,j,l} dy[n,oc,u - j,v - l] * w[oc,c,a + s_h*j,b + s_w*l]:  a stride-1
+// convolution of dy itself with the reversed sub-filter, written to every s-th pixel of dx.  No zeros
+// are inserted anywhere, so the tensor cores do 1 / (s_h * s_w) of the work of the dilated form.
+namespace {
+struct ParityClass {
+    int a, b;          // class
+    int kh, kw;        // taps of its sub-filter (0: the class receives nothing)
+    int u0, v0;        // first output index (the first u with s*u + a - p >= 0)
+    int rows, cols;    // its pixels in dx
+    int pad_h, pad_w;  // padding of the equivalent stride-1 forward convolution over dy
+    ConvShape sub;     // that convolution: input dy (OC channels), output the class's pixels (C channels)
+};
+
+int ceil_div_int(int a, int b) { return (a + b - 1) / b; }
+
+ParityClass make_class(const ConvShape& s, int a, int b) {
+    ParityClass c{};
+    c.a = a;
+    c.b = b;
+    c.kh = a < s.k_h ? ceil_div_int(s.k_h - a, s.s_h) : 0;
+    c.kw = b < s.k_w ? ceil_div_int(s.k_w - b, s.s_w) : 0;
+    c.u0 = s.p_h > a ? ceil_div_int(s.p_h - a, s.s_h) : 0;
+    c.v0 = s.p_w > b ? ceil_div_int(s.p_w - b, s.s_w) : 0;
+    const int u_last = (s.in_h - 1 + s.p_h - a) >= 0 ? (s.in_h - 1 + s.p_h - a) / s.s_h : -1;
+    const int v_last = (s.in_w - 1 + s.p_w - b) >= 0 ? (s.in_w - 1 + s.p_w - b) / s.s_w : -1;
+    c.rows = u_last - c.u0 + 1;
+    c.cols = v_last - c.v0 + 1;
+    c.pad_h = c.kh - 1 - c.u0;
+    c.pad_w = c.kw - 1 - c.v0;
+    // Input extent chosen so that the stride-1 output size is exactly the class's pixel count; the
+    // tensor map keeps dy's true extent, so whatever lies outside it reads as zero.
+    c.sub = ConvShape{s.batch, s.out_c, s.in_c, c.rows + c.kh - 1 - 2 * c.pad_h, c.cols + c.kw - 1 - 2 * c.pad_w,
+                      c.kh, c.kw, 1, 1, c.pad_h, c.pad_w};
+    return c;
+}
+
+bool class_is_empty(const ParityClass& c) { return c.rows <= 0 || c.cols <= 0; }
+bool class_has_taps(const ParityClass& c) { return c.kh > 0 && c.kw > 0; }
+
+size_t round_1k(size_t v) { return (v + 1023) / 1024 * 1024; }
+}  // namespace
+
+bool conv2d_grad_input_by_parity_supported(const ConvShape& s) {
+    if (device_info().cc_major != 10) return false;
+    if (s.s_h < 1 || s.s_w < 1 || (s.s_h == 1 && s.s_w == 1) || s.s_h > 8 || s.s_w > 8) return false;
+    if (s.p_h > s.k_h - 1 || s.p_w > s.k_w - 1) return false;
+    if (s.out_c < 32 || s.out_c % 4 != 0) return false;          // dy's channels are the reduction: whole K blocks' worth
+    bool any = false;
+    for (int a = 0; a < s.s_h; ++a)
+        for (int b = 0; b < s.s_w; ++b) {
+            const ParityClass c = make_class(s, a, b);
+            if (class_is_empty(c) || !class_has_taps(c)) continue;
+            if (c.pad_h < 0 || c.pad_w < 0 || c.sub.in_h < 1 || c.sub.in_w < 1) return false;
+            if (!conv2d_igemm_supported(c.sub) || conv2d_igemm_row_packed(c.sub)) return false;
+            any = true;
+        }
+    return any;
+}
+
+void conv2d_grad_input_by_parity(const float* grad_output, const float* weight, float* grad_input,
+                                 const ConvShape& s, cudaStream_t stream) {
+    CB200_REQUIRE(conv2d_grad_input_by_parity_supported(s), "conv2d grad_input: shape not supported by the parity form");
+    const int oh = s.out_h(), ow = s.out_w();
+    const int cx = round_up(s.out_c, 4);             // channels of the NHWC copy of dy
+    const int cp = round_up(s.out_c, UMMA_BK);
+    const size_t nhwc_bytes = round_1k(static_cast<size_t>(s.batch) * oh * ow * cx * sizeof(float));
+    std::vector<ParityClass> classes;
+    std::vector<size_t> filter_offset;
+    size_t bytes = nhwc_bytes;
+    bool needs_zero = false;
+    for (int a = 0; a < s.s_h; ++a)
+        for (int b = 0; b < s.s_w; ++b) {
+            const ParityClass c = make_class(s, a, b);
+            if (class_is_empty(c)) continue;
+            if (!class_has_taps(c)) {            // filter smaller than the stride: these pixels get no gradient
+                needs_zero = true;
+                continue;
+            }
+            classes.push_back(c);
+            filter_offset.push_back(bytes);
+            bytes += round_1k(static_cast<size_t>(s.in_c) * c.kh * c.kw * cp * sizeof(float));
+        }
+    if (needs_zero)
+        CB200_CUDA(cudaMemsetAsync(grad_input, 0,
+                                   static_cast<size_t>(s.batch) * s.in_c * s.in_h * s.in_w * sizeof(float), stream));
+    char* scratch = static_cast<char*>(scratch_alloc(bytes, stream));
+    try {
+        float* xt = reinterpret_cast<float*>(scratch);
+        for (size_t i = 0; i < classes.size(); ++i) {
+            const ParityClass& c = classes[i];
+            float* wp = reinterpret_cast<float*>(scratch + filter_offset[i]);
+            FilterPack filters{weight, wp, s.in_c, s.out_c, c.kh, c.kw, cp, 1, 0};
+            filters.sub_sh = s.s_h;
+            filters.sub_sw = s.s_w;
+            filters.sub_a = c.a;
+            filters.sub_b = c.b;
+            filters.full_kh = s.k_h;
+            filters.full_kw = s.k_w;
+            // The first class's launch also re-lays dy as NHWC; the others pack their filters only.
+            if (i == 0) prepare_operands(grad_output, xt, s.batch, s.out_c, oh * ow, cx, &filters, stream);
+            else prepare_operands(nullptr, nullptr, /*batch=*/0, s.out_c, oh * ow, cx, &filters, stream);
+        }
+        for (size_t i = 0; i < classes.size(); ++i) {
+            const ParityClass& c = classes[i];
+            const float* wp = reinterpret_cast<const float*>(scratch + filter_offset[i]);
+            ConvExtras extras;
+            extras.map_h = oh;
+            extras.map_w = ow;
+            extras.out_plane = static_cast<long long>(s.in_h) * s.in_w;
+            extras.out_off = (s.s_h * c.u0 + c.a - s.p_h) * s.in_w + (s.s_w * c.v0 + c.b - s.p_w);
+            extras.out_row = s.s_h * s.in_w;
+            extras.out_col = s.s_w;
+            CB200_TRACE("conv2d grad_input by parity: class (%d,%d) of stride %dx%d, %dx%d taps, %d x %d pixels", c.a, c.b,
+                        s.s_h, s.s_w, c.kh, c.kw, c.rows, c.cols);
+            plan_and_launch(xt, wp, nullptr, grad_input, c.sub, cx, cp, EPI_NONE, 0, false, stream, &extras);
+        }
     } catch (...) {
         scratch_free(scratch, stream);
         throw;

@@ -52,6 +52,16 @@ void nchw_to_nhwc(const float* input, float* xt, int batch, int c, int hw, int c
 void nchw_to_nhwc_padded(const float* input, float* xt, int batch, int c, int h, int w, int cx, int pad_w,
                          cudaStream_t stream);
 
+// grad_input of a strided layer (`s` is the forward layer's shape) as stride_h * stride_w stride-1
+// convolutions of grad_output, one per parity class of the input pixels, each with the sub-filter of
+// the taps that reach its class and each written to every stride-th pixel of grad_input: no zeros
+// are inserted, so the tensor cores do 1 / (stride_h * stride_w) of the work of the dilated form.
+// Needs at least 32 output channels (a multiple of 4), padding smaller than the filter, and every
+// class on the tensor-core path.
+bool conv2d_grad_input_by_parity_supported(const ConvShape& s);
+void conv2d_grad_input_by_parity(const float* grad_output, const float* weight, float* grad_input,
+                                 const ConvShape& s, cudaStream_t stream);
+
 // grad_weight as an implicit GEMM over output pixels (conv_wgrad.cu): strides 1..8, at least 32
 // output channels and 256 output pixels.
 bool conv2d_wgrad_igemm_supported(const ConvShape& s);

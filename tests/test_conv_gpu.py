@@ -149,6 +149,39 @@ def test_strided_tensor_core_path_shapes(dev, lib, oracle, shape, oc, k, stride,
 
 
 @pytest.mark.parametrize("shape,oc,k,stride,padding", [
+    ((2, 64, 56, 56), 128, (3, 3), (2, 2), (1, 1)),      # a down-sampling layer: classes of 4, 2, 2 and 1 taps
+    ((2, 32, 15, 17), 64, (3, 3), (3, 3), (1, 1)),       # stride = filter: nine classes of one tap each
+    ((2, 48, 20, 20), 64, (2, 2), (2, 2), (0, 0)),       # 2 x 2 stride 2, no padding
+    ((2, 64, 16, 16), 96, (1, 1), (2, 2), (0, 0)),       # filter smaller than the stride: three classes get no gradient
+    ((1, 32, 22, 23), 32, (3, 3), (2, 2), (0, 0)),       # the forward pass leaves the last row unread: zeros there
+    ((1, 32, 21, 21), 40, (5, 5), (2, 2), (2, 2)),       # 5 x 5: classes of 3 x 3, 3 x 2, 2 x 3, 2 x 2 taps
+    ((2, 32, 18, 30), 64, (3, 5), (1, 2), (1, 2)),       # stride 1 down, 2 across
+    ((3, 32, 13, 13), 64, (4, 4), (3, 2), (1, 0)),       # different strides, even filter
+    ((8, 64, 14, 14), 64, (3, 3), (2, 2), (1, 1)),       # 7 x 7 classes: several whole images per tile
+    ((1, 40, 40, 40), 36, (7, 7), (4, 4), (3, 3)),       # stride 4: sixteen classes; 36 channels of grad_output
+])
+def test_strided_grad_input_by_parity_classes(dev, lib, oracle, shape, oc, k, stride, padding):
+    """grad_input of a strided layer: one stride-1 convolution of grad_output per parity class of the input
+    pixels, each writing every stride-th pixel.  Every pixel of grad_input must be written (the output starts
+    as NaN), pixels no tap reaches must be zero, and the values follow the truncated-operand model."""
+    rng = np.random.default_rng(sum(shape) + oc + sum(k))
+    x = np.zeros(shape, dtype=np.float32)
+    w = rng.standard_normal((oc, shape[1], *k), dtype=np.float32) * np.float32(0.1)
+    oh = (shape[2] + 2 * padding[0] - k[0]) // stride[0] + 1
+    ow = (shape[3] + 2 * padding[1] - k[1]) // stride[1] + 1
+    dy = rng.standard_normal((shape[0], oc, oh, ow), dtype=np.float32)
+    dx, _ = conv_backward(dev, lib, dy, w, x, stride, padding)
+    assert dx.shape == x.shape and not np.isnan(dx).any()
+    exact = oracle.conv2d_backward_data_np(dy, w, shape[2:], stride, padding)
+    model = oracle.conv2d_backward_data_np(dy, w, shape[2:], stride, padding, input_mode=oracle.INPUT_TF32_TRUNC)
+    assert oracle.rel_frobenius(dx, exact) <= TF32_TOL
+    assert oracle.rel_frobenius(dx, model) <= TF32_MODEL_TOL
+    assert np.all(dx[exact == 0.0] == 0.0)                   # untouched pixels are exactly zero
+    again, _ = conv_backward(dev, lib, dy, w, x, stride, padding)
+    assert np.array_equal(dx, again)
+
+
+@pytest.mark.parametrize("shape,oc,k,stride,padding", [
     ((2, 64, 28, 28), 128, 3, 1, 1),       # single-image tiles, bulk tensor stores
     ((3, 36, 19, 23), 40, 3, 1, 1),        # ragged everything; channels padded to one K block
     ((4, 128, 7, 7), 256, 3, 1, 1),        # several images per tile
