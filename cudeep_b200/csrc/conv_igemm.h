@@ -52,12 +52,12 @@ void nchw_to_nhwc(const float* input, float* xt, int batch, int c, int hw, int c
 void nchw_to_nhwc_padded(const float* input, float* xt, int batch, int c, int h, int w, int cx, int pad_w,
                          cudaStream_t stream);
 
-// grad_input of a strided layer (`s` is the forward layer's shape) as stride_h * stride_w stride-1
-// convolutions of grad_output, one per parity class of the input pixels, each with the sub-filter of
-// the taps that reach its class and each written to every stride-th pixel of grad_input: no zeros
-// are inserted, so the tensor cores do 1 / (stride_h * stride_w) of the work of the dilated form.
-// Needs at least 32 output channels (a multiple of 4), padding smaller than the filter, and every
-// class on the tensor-core path.
+// grad_input of a strided layer (`s` is the forward layer's shape) in its sub-pixel form: the input
+// pixels fall into stride_h * stride_w parity classes, each the stride-1 convolution of grad_output
+// with the sub-filter of the taps that reach it; all classes are computed as ONE stride-1 convolution
+// with (class, channel) pairs as output channels, into dense planes that a second pass weaves into
+// grad_input.  No zeros are inserted into grad_output.  Needs at least 32 output channels, padding
+// smaller than the filter and the combined convolution on the tensor-core path.
 bool conv2d_grad_input_by_parity_supported(const ConvShape& s);
 void conv2d_grad_input_by_parity(const float* grad_output, const float* weight, float* grad_input,
                                  const ConvShape& s, cudaStream_t stream);
