@@ -131,10 +131,11 @@ void launch_conv2d_backward_data_kernel<float>(const float* grad_output, const f
     // of them the forward path would need its row-packed form, which flipped filters do not have.)
     const bool pad_fits = pad_h <= kernel_h - 1 && pad_w <= kernel_w - 1 && out_channels >= 3;
     const bool stride_one = stride_h == 1 && stride_w == 1;
-    // A strided convolution: grad_output with (stride - 1) zeros put between its pixels, and as
-    // many zero rows and columns behind it as the forward pass left unread, is the input of the
-    // same stride-1 convolution.  The tensor cores then multiply stride_h * stride_w times more
-    // zeros than data, which still beats the gather kernel by far up to that factor 16.
+    // The fallback form of a strided layer (when the sub-pixel form below does not take it):
+    // grad_output with (stride - 1) zeros put between its pixels, and as many zero rows and columns
+    // behind it as the forward pass left unread, is the input of the same stride-1 convolution.  The
+    // tensor cores then multiply stride_h * stride_w times more zeros than data, which still beats
+    // the gather kernel by far up to that factor 16.
     ConvShape dilated = as_forward;
     dilated.in_h = (s.out_h() - 1) * stride_h + 1 + (in_h + 2 * pad_h - kernel_h) % stride_h;
     dilated.in_w = (s.out_w() - 1) * stride_w + 1 + (in_w + 2 * pad_w - kernel_w) % stride_w;

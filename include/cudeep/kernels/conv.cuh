@@ -14,9 +14,12 @@
 //     channels when a filter row fits one 32-wide K block: KW > 1 and KW * ceil4(C) <= 32).  The
 //     input is re-laid as NHWC once per call and gathered tap by tap with TMA, filters are packed
 //     [OC][KH*KW][C]; no im2col matrix is materialised.  Every other shape: direct strict FP32.
-//   * grad_input, float: the same implicit GEMM applied to grad_output with flipped filters (TF32)
-//     under the same conditions with the roles of C and OC exchanged (stride_h * stride_w <= 16:
-//     a strided layer's grad_output gets zeros inserted between its pixels); otherwise strict FP32.
+//   * grad_input, float: at stride 1 the same implicit GEMM applied to grad_output with flipped filters
+//     (TF32), under the forward conditions with the roles of C and OC exchanged.  A strided layer with
+//     OC >= 32 runs in sub-pixel form: one stride-1 implicit GEMM over grad_output whose output
+//     channels are (parity class of the input pixel, channel) pairs, then a pass that weaves the
+//     classes into grad_input (TF32; no zeros are inserted).  Strided shapes that form does not take
+//     use the stride-1 kernel on a zero-inserted copy (stride_h * stride_w <= 16); otherwise strict FP32.
 //   * grad_weight, float: implicit GEMM over output pixels (TF32) for strides 1..8, OC >= 32 and at
 //     least 256 output pixels in the batch; otherwise strict FP32.
 //   * every double instantiation: direct FP64.

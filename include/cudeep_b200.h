@@ -219,8 +219,10 @@ int cudeep_b200_conv2d_forward_f64(const double* input, const double* weight, co
  * launch_conv2d_backward_weight_kernel<float> (include/cudeep/kernels/conv.cuh:18-36,
  * src/kernels/conv_kernel.cu:417-545).  in_h / in_w are the forward input's size.
  * Both run on the tensor cores (TF32) for layers with at least 32 output channels: grad_input
- * with at least 32 input channels and stride_h * stride_w <= 16, grad_weight with at least 256
- * output pixels and strides up to 8; strict FP32 kernels otherwise. */
+ * with at least 32 input channels (strided layers, strides up to 8, in sub-pixel form: one
+ * stride-1 implicit GEMM over grad_output for all parity classes of the input pixels, no zeros
+ * inserted), grad_weight with at least 256 output pixels and strides up to 8; strict FP32 kernels
+ * otherwise. */
 int cudeep_b200_conv2d_backward_data_f32(const float* grad_output, const float* weight, float* grad_input,
                                          int batch, int in_channels, int out_channels, int in_h, int in_w,
                                          int kernel_h, int kernel_w, int stride_h, int stride_w, int pad_h,
