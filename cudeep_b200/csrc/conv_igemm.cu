@@ -834,32 +834,34 @@ struct WeaveArgs {
     signed char lo_h[8], lo_w[8];
 };
 
-template <bool VEC>
+// SH, SW: the strides as compile-time constants (0: read them from the arguments), so that the
+// divisions by them are shifts or multiplications.  blockIdx.y is the (image, channel) plane.
+template <bool VEC, int SH, int SW>
 __global__ void __launch_bounds__(256)
-weave_parity_classes_kernel(const float* __restrict__ planes, float* __restrict__ dx, WeaveArgs t, long long total) {
+weave_parity_classes_kernel(const float* __restrict__ planes, float* __restrict__ dx, WeaveArgs t) {
+    const int s_h = SH > 0 ? SH : t.s_h, s_w = SW > 0 ? SW : t.s_w;
     const int groups = (t.w + 3) / 4;
+    const int work = t.h * groups;
     const long long plane_px = static_cast<long long>(t.rows) * t.pitch;
-    for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
-         idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int g = static_cast<int>(idx % groups);
-        long long r = idx / groups;
-        const int ih = static_cast<int>(r % t.h);
-        r /= t.h;
-        const int c = static_cast<int>(r % t.c);
-        const long long n = r / t.c;
-        const int a = (ih + t.p_h) % t.s_h;
-        const int u = (ih + t.p_h) / t.s_h - t.lo_h[a];
-        const long long image = n * (static_cast<long long>(t.s_h) * t.s_w * t.c);
+    const int n = blockIdx.y / t.c, c = blockIdx.y - n * t.c;
+    // planes of this image: [class][channel]; class stride is C planes
+    const float* src0 = planes + (static_cast<long long>(n) * s_h * s_w * t.c + c) * plane_px;
+    const long long class_stride = static_cast<long long>(t.c) * plane_px;
+    float* dst0 = dx + static_cast<long long>(blockIdx.y) * t.h * t.w;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < work; idx += gridDim.x * blockDim.x) {
+        const int ih = idx / groups, g = idx - ih * groups;
+        const int a = (ih + t.p_h) % s_h;
+        const int u = (ih + t.p_h) / s_h - t.lo_h[a];
+        const float* row = src0 + static_cast<long long>(a) * s_w * class_stride + static_cast<long long>(u) * t.pitch;
         float v[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int iw = g * 4 + j;
-            const int b = (iw + t.p_w) % t.s_w;
-            const int q = (iw + t.p_w) / t.s_w - t.lo_w[b];
-            const long long plane = image + static_cast<long long>(a * t.s_w + b) * t.c + c;
-            v[j] = iw < t.w ? __ldg(planes + plane * plane_px + static_cast<long long>(u) * t.pitch + q) : 0.0f;
+            const int b = (iw + t.p_w) % s_w;
+            const int q = (iw + t.p_w) / s_w - t.lo_w[b];
+            v[j] = iw < t.w ? __ldg(row + b * class_stride + q) : 0.0f;
         }
-        float* dst = dx + ((n * t.c + c) * t.h + ih) * t.w + g * 4;
+        float* dst = dst0 + static_cast<long long>(ih) * t.w + g * 4;
         if (VEC) {
             *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
         } else {
@@ -867,6 +869,28 @@ weave_parity_classes_kernel(const float* __restrict__ planes, float* __restrict_
             for (int j = 0; j < 4; ++j)
                 if (g * 4 + j < t.w) dst[j] = v[j];
         }
+    }
+}
+
+template <bool VEC>
+void launch_weave(const float* planes, float* dx, const WeaveArgs& t, long long n_planes, cudaStream_t stream) {
+    const int work = t.h * ((t.w + 3) / 4);
+    int bx = (work + 255) / 256;
+    if (bx > 64) bx = 64;
+    // gridDim.y is limited to 65535: whole images per launch (blockIdx.y = image * C + channel).
+    CB200_REQUIRE(t.c <= 65535, "conv2d grad_input: too many channels");
+    const long long chunk = static_cast<long long>(65535 / t.c) * t.c;
+    for (long long first = 0; first < n_planes; first += chunk) {
+        const long long count = n_planes - first < chunk ? n_planes - first : chunk;
+        const dim3 grid(static_cast<unsigned>(bx), static_cast<unsigned>(count));
+        const WeaveArgs& args = t;
+        const float* src = planes + (first / t.c) * t.s_h * t.s_w * t.c * static_cast<long long>(t.rows) * t.pitch;
+        float* dst = dx + first * static_cast<long long>(t.h) * t.w;
+        if (t.s_h == 2 && t.s_w == 2) weave_parity_classes_kernel<VEC, 2, 2><<<grid, 256, 0, stream>>>(src, dst, args);
+        else if (t.s_h == 3 && t.s_w == 3) weave_parity_classes_kernel<VEC, 3, 3><<<grid, 256, 0, stream>>>(src, dst, args);
+        else if (t.s_h == 4 && t.s_w == 4) weave_parity_classes_kernel<VEC, 4, 4><<<grid, 256, 0, stream>>>(src, dst, args);
+        else weave_parity_classes_kernel<VEC, 0, 0><<<grid, 256, 0, stream>>>(src, dst, args);
+        CB200_CHECK_LAUNCH();
     }
 }
 }  // namespace
@@ -928,14 +952,10 @@ void conv2d_grad_input_by_parity(const float* grad_output, const float* weight, 
         CB200_TRACE("conv2d grad_input by parity classes: stride %dx%d, %d classes x %d channels, %dx%d taps each, "
                     "planes of %d x %d", s.s_h, s.s_w, s.s_h * s.s_w, s.in_c, p.h.taps, p.w.taps, p.h.extent, p.cols_padded);
         plan_and_launch(xt, wp, nullptr, planes, p.sub, cx, cp, EPI_NONE, 0, false, stream, &extras);
-        const long long total = static_cast<long long>(s.batch) * s.in_c * s.in_h * ((s.in_w + 3) / 4);
-        long long blocks = (total + 255) / 256;
-        const long long cap = static_cast<long long>(device_info().num_sms) * 16;
-        if (blocks > cap) blocks = cap;
         const bool vec = s.in_w % 4 == 0 && (reinterpret_cast<uintptr_t>(grad_input) & 15u) == 0;
-        if (vec) weave_parity_classes_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(planes, grad_input, args, total);
-        else weave_parity_classes_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(planes, grad_input, args, total);
-        CB200_CHECK_LAUNCH();
+        const long long n_planes = static_cast<long long>(s.batch) * s.in_c;
+        if (vec) launch_weave<true>(planes, grad_input, args, n_planes, stream);
+        else launch_weave<false>(planes, grad_input, args, n_planes, stream);
     } catch (...) {
         scratch_free(scratch, stream);
         throw;
