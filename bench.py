@@ -830,6 +830,15 @@ def run_h1(lib, timed, emit, ok, P, stream, trim):
         ch = torch.empty((n, n), device="cuda", dtype=torch.half)
         rows = {"ours": timed(lambda: ok(lib.cudeep_b200_matmul_f16(P(a), P(b), P(c), n, n, n, stream)), 15),
                 "cublas_f16_result_torch": timed(lambda: torch.matmul(a, b, out=ch), 15, cmp=True)}
+        try:        # cuBLAS with the same FP32 result this library writes (torch versions that offer out_dtype)
+            torch.mm(a, b, out_dtype=torch.float32)
+            rows["cublas_f32_result_torch"] = timed(lambda: torch.mm(a, b, out_dtype=torch.float32), 15, cmp=True)
+        except Exception:
+            pass
+        ab, bb = a.to(torch.bfloat16), b.to(torch.bfloat16)
+        cb = torch.empty((n, n), device="cuda", dtype=torch.bfloat16)
+        rows["ours_bf16"] = timed(lambda: ok(lib.cudeep_b200_matmul_bf16(P(ab), P(bb), P(c), n, n, n, stream)), 15)
+        rows["cublas_bf16_result_torch"] = timed(lambda: torch.matmul(ab, bb, out=cb), 15, cmp=True)
         emit(f"H1 FP16 GEMM {n}^3, FP32 result", 2.0 * n ** 3, trim(rows))
 
 
