@@ -698,7 +698,8 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
     size_t nhwc_bytes = 0;
     conv2d_igemm_scratch_bytes(s, &nhwc_bytes, nullptr);
     float* xt = static_cast<float*>(scratch);
-    float* wp = reinterpret_cast<float*>(static_cast<char*>(scratch) + nhwc_bytes);
+    // With a channels-last input there is no copy of it: the scratch holds the packed filters only.
+    float* wp = reinterpret_cast<float*>(static_cast<char*>(scratch) + (input_is_nhwc ? 0 : nhwc_bytes));
 
     const bool row_packed = !flipped_filters && dilation == nullptr && conv2d_igemm_row_packed(s);
     if (input_is_nhwc) {
@@ -737,7 +738,9 @@ void conv2d_igemm_with_scratch(const float* input, const float* weight, const fl
 void conv2d_igemm(const float* input, const float* weight, const float* bias, float* output,
                   const ConvShape& s, int act, cudaStream_t stream, bool flipped_filters,
                   const InputDilation* dilation, bool input_is_nhwc) {
-    const size_t bytes = conv2d_igemm_scratch_bytes(s, nullptr, nullptr);
+    size_t filter_bytes = 0;
+    size_t bytes = conv2d_igemm_scratch_bytes(s, nullptr, &filter_bytes);
+    if (input_is_nhwc) bytes = filter_bytes;
     // Stream-ordered scratch, as the reference does for its temporaries
     // (conv_kernel.cu:282,314,748-754): safe when calls on several streams overlap.
     void* scratch = scratch_alloc(bytes, stream);
