@@ -322,7 +322,10 @@ def run_c5(args, rank, world, local, dist, gather: bool):
     for m, n, k in workloads.C5_SHAPES:
         if m % (world * workloads.C5_BAND_ROWS) != 0:
             continue
-        g = sh.ShardedGemm.rank(rank, world, local, m, n, k, bands=4)
+        # Row bands of the pipelined gather forms: eight where a band still holds several waves of tiles
+        # (2048 rows or more), else four.
+        bands = 8 if m // world // 8 >= 2048 else 4
+        g = sh.ShardedGemm.rank(rank, world, local, m, n, k, bands=bands)
         try:
             if world > 1:
                 g.connect(exchange_id, exchange_handles)
@@ -349,6 +352,7 @@ def run_c5(args, rank, world, local, dist, gather: bool):
                 t_after = timed(g, sh.GATHER_AFTER_GEMM, args.c5_steps)
                 t_banded = timed(g, sh.GATHER_BANDED, args.c5_steps)
                 t_fused = timed(g, sh.GATHER_PEER_STORE, args.c5_steps)
+                t_copy = timed(g, sh.GATHER_COPY_ENGINE, args.c5_steps)
                 # the fused form's result, checked on rows this rank did NOT compute
                 barrier_sync(dist)
                 others = [r for r in range(world) if r != rank]
@@ -361,19 +365,28 @@ def run_c5(args, rank, world, local, dist, gather: bool):
                 g.run(sh.GATHER_BANDED, stream)
                 barrier_sync(dist)
                 err_banded = check_rows(g, foreign, b_np, k, "gathered C, banded NCCL form, rows of other ranks")
+                barrier_sync(dist)
+                g.run(sh.GATHER_COPY_ENGINE, stream)
+                barrier_sync(dist)
+                err_copy = check_rows(g, foreign, b_np, k, "gathered C, copy-engine form, rows of other ranks")
                 longer = max(t_compute, t_gather)
-                best = min(t_banded, t_fused)
+                forms = {"fused peer-store epilogue": t_fused, "banded NCCL": t_banded,
+                         "banded copy-engine pushes": t_copy}
+                best_form = min(forms, key=forms.get)
+                best = forms[best_form]
                 out["with_gather"] = {
                     "workload": f"C[{m},{n}] gathered on every GPU ({(world - 1) * mine.rows * n * 4} bytes received per GPU)",
                     "t_compute_ms": t_compute, "t_gather_alone_ms": t_gather,
                     "t_gemm_then_ncclAllGather_ms": t_after, "t_banded_nccl_ms": t_banded,
-                    "t_fused_peer_store_ms": t_fused, "t_both_ms": best,
-                    "form": "fused peer-store epilogue" if t_fused <= t_banded else "banded NCCL",
+                    "t_fused_peer_store_ms": t_fused, "t_banded_copy_engine_ms": t_copy, "t_both_ms": best,
+                    "form": best_form,
                     "overlap": best / longer, "overlap_banded_nccl": t_banded / longer,
-                    "overlap_fused_peer_store": t_fused / longer, "plain_sum_ms": t_compute + t_gather,
+                    "overlap_fused_peer_store": t_fused / longer, "overlap_banded_copy_engine": t_copy / longer,
+                    "plain_sum_ms": t_compute + t_gather,
                     "tflops_with_gather": flops / (best * 1e-3) / 1e12,
                     "parity_max_rel_err_fused": err_fused, "parity_max_rel_err_banded": err_banded,
-                    "steps": args.c5_steps,
+                    "parity_max_rel_err_copy_engine": err_copy,
+                    "steps": args.c5_steps, "bands": bands,
                     "note": "overlap = step time / max(compute alone, collective alone); 1.0 = the shorter leg is fully hidden"}
             barrier_sync(dist)
         finally:

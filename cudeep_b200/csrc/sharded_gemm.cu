@@ -146,6 +146,8 @@ struct RankState {
     cudaStream_t comm = nullptr;
     std::vector<cudaEvent_t> band_done;
     cudaEvent_t comm_done = nullptr;
+    std::vector<cudaStream_t> copy_streams;    // Gather::CopyEngine: one per peer, made on first use
+    std::vector<cudaEvent_t> copy_done;
     cudaEvent_t t0 = nullptr, t1 = nullptr;
     NcclComm nccl_comm = nullptr;
     std::vector<float*> peer_c;        // every rank's C as seen from this device (own slot: c)
@@ -285,6 +287,39 @@ struct ShardedGemm::Impl {
             CB200_CUDA(cudaStreamWaitEvent(s, r.comm_done, 0));
             break;
         }
+        case Gather::CopyEngine: {
+            // Band by band: the GEMM of a band, then one device-to-device copy of that band into every
+            // peer's C, each on a stream of its own.  The copies run on the copy engines, so they take
+            // no SM from the next band's GEMM, and they move large contiguous blocks at link rate.
+            if (r.copy_streams.empty()) {
+                r.copy_streams.resize(size_t(world));
+                r.copy_done.resize(size_t(world));
+                for (int p = 0; p < world; ++p) {
+                    if (p == r.rank) continue;
+                    CB200_CUDA(cudaStreamCreateWithFlags(&r.copy_streams[size_t(p)], cudaStreamNonBlocking));
+                    CB200_CUDA(cudaEventCreateWithFlags(&r.copy_done[size_t(p)], cudaEventDisableTiming));
+                }
+            }
+            for (int band = 0; band < opt.bands; ++band) {
+                const RowRange part = band_of(r.rank, band);
+                if (part.rows <= 0) continue;
+                gemm(r, r.a + (part.row0 - own.row0) * k, r.c + part.row0 * n, part.rows, 0, s);
+                CB200_CUDA(cudaEventRecord(r.band_done[band], s));
+                for (int p = 0; p < world; ++p) {
+                    if (p == r.rank) continue;
+                    cudaStream_t cs = r.copy_streams[size_t(p)];
+                    CB200_CUDA(cudaStreamWaitEvent(cs, r.band_done[band], 0));
+                    CB200_CUDA(cudaMemcpyAsync(r.peer_c[size_t(p)] + part.row0 * n, r.c + part.row0 * n,
+                                               size_t(part.rows) * n * sizeof(float), cudaMemcpyDeviceToDevice, cs));
+                }
+            }
+            for (int p = 0; p < world; ++p) {
+                if (p == r.rank) continue;
+                CB200_CUDA(cudaEventRecord(r.copy_done[size_t(p)], r.copy_streams[size_t(p)]));
+                CB200_CUDA(cudaStreamWaitEvent(s, r.copy_done[size_t(p)], 0));
+            }
+            break;
+        }
         case Gather::PeerStore: {
             cudeep_b200::GemmPeerOutputs peers;
             for (int p = 0; p < world; ++p) {
@@ -341,8 +376,9 @@ struct ShardedGemm::Impl {
     void check_mode(Gather gather) {
         CB200_REQUIRE(!broken, "this ShardedGemm had a failed step; make a new one");
         const int g = int(gather);
-        CB200_REQUIRE(g >= 0 && g <= 4, "unknown gather mode");
+        CB200_REQUIRE(g >= 0 && g <= 5, "unknown gather mode");
         if (gather == Gather::AfterGemm || gather == Gather::Banded || gather == Gather::CollectiveOnly) ensure_comm();
+        if (gather == Gather::CopyEngine) ensure_peers();
         if (gather == Gather::PeerStore) {
             ensure_peers();
             CB200_REQUIRE(opt.dry_run || n % 4 == 0, "Gather::PeerStore needs N % 4 == 0");
@@ -467,6 +503,8 @@ ShardedGemm::~ShardedGemm() {
         }
         for (void* p : r.opened) cudaIpcCloseMemHandle(p);
         for (cudaEvent_t e : r.band_done) cudaEventDestroy(e);
+        for (cudaEvent_t e : r.copy_done) if (e) cudaEventDestroy(e);
+        for (cudaStream_t cs : r.copy_streams) if (cs) cudaStreamDestroy(cs);
         if (r.comm_done) cudaEventDestroy(r.comm_done);
         if (r.t0) cudaEventDestroy(r.t0);
         if (r.t1) cudaEventDestroy(r.t1);
@@ -597,6 +635,7 @@ void ShardedGemm::synchronize() {
         CB200_CUDA(cudaSetDevice(r.device));
         CB200_CUDA(cudaStreamSynchronize(r.compute));
         CB200_CUDA(cudaStreamSynchronize(r.comm));
+        for (cudaStream_t cs : r.copy_streams) if (cs) CB200_CUDA(cudaStreamSynchronize(cs));
     });
 }
 

@@ -7,12 +7,15 @@
 // the product each rank computes is exactly that launcher's.
 //
 // Rows are independent, so computing needs no exchange.  The only communication is the optional
-// all-gather of C for callers that need the whole product on every GPU, offered in three forms:
+// all-gather of C for callers that need the whole product on every GPU, offered in four forms:
 //
 //   Gather::AfterGemm   the GEMM, then one in-place ncclAllGather on the same stream (the baseline);
 //   Gather::Banded      the shard is cut into row bands; the NCCL transfer of band i runs on a second
 //                       stream behind an event recorded after band i's GEMM, so it overlaps the GEMM of
 //                       band i+1 (the GEMM leaves `comm_sms` SMs to NCCL's kernels);
+//   Gather::CopyEngine  row bands again, but band i travels as one device-to-device copy per peer on the
+//                       GPU's copy engines (peer-mapped memory, a stream per peer): no SM is taken from
+//                       band i+1's GEMM and the links carry large contiguous blocks;
 //   Gather::PeerStore   one kernel does both: the GEMM's epilogue stores every finished tile into all
 //                       GPUs' copies of C through peer-mapped memory (bulk tensor stores; nothing is
 //                       ever loaded from a peer), so the transfer overlaps the math tile by tile and no
@@ -48,6 +51,7 @@ enum class Gather : int {
     Banded = 2,
     PeerStore = 3,
     CollectiveOnly = 4,  // only the all-gather of whatever C holds (to time the collective by itself)
+    CopyEngine = 5,
 };
 
 struct RowRange {

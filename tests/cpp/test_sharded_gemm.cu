@@ -78,7 +78,7 @@ static void test_every_gather_mode(int world) {
         g.set_a(i, a.data() + own.row0 * k);
     }
     CHECK(covered == m);
-    const Gather modes[] = {Gather::AfterGemm, Gather::Banded, Gather::PeerStore};
+    const Gather modes[] = {Gather::AfterGemm, Gather::Banded, Gather::PeerStore, Gather::CopyEngine};
     std::vector<float> host(size_t(m) * n);
     for (Gather mode : modes) {
         for (int i = 0; i < world; ++i) {

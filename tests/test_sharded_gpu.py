@@ -12,8 +12,8 @@ import socket
 import numpy as np
 import pytest
 
-from cudeep_b200.sharded import (GATHER_AFTER_GEMM, GATHER_BANDED, GATHER_COLLECTIVE_ONLY, GATHER_NONE,
-                                 GATHER_PEER_STORE, ShardedGemm)
+from cudeep_b200.sharded import (GATHER_AFTER_GEMM, GATHER_BANDED, GATHER_COLLECTIVE_ONLY, GATHER_COPY_ENGINE,
+                                 GATHER_NONE, GATHER_PEER_STORE, ShardedGemm)
 
 pytestmark = pytest.mark.gpu
 
@@ -54,7 +54,7 @@ def test_world_of_one_every_gather_mode(lib, cuda, oracle, m, n, k):
     with ShardedGemm.local([0], m, n, k, bands=3) as g:
         assert g.rows_of(0).rows == m
         _load(g, a, b)
-        for mode in (GATHER_NONE, GATHER_AFTER_GEMM, GATHER_BANDED, GATHER_PEER_STORE):
+        for mode in (GATHER_NONE, GATHER_AFTER_GEMM, GATHER_BANDED, GATHER_PEER_STORE, GATHER_COPY_ENGINE):
             _poison(g, lib, [0])
             g.run(mode)
             g.synchronize()
@@ -67,7 +67,7 @@ def test_world_of_one_every_gather_mode(lib, cuda, oracle, m, n, k):
         assert oracle.rel_frobenius(g.read_c(), want) <= TF32_MODEL_TOL
         ms = g.time_steps(GATHER_BANDED, 3, 1)
         assert 0.0 < ms < 1000.0
-        assert g.steps_enqueued(0) == 5 + 4
+        assert g.steps_enqueued(0) == 6 + 4
 
 
 def _check_every_rank_has_all_of_c(g, want, oracle, only_own_rows=False):
@@ -97,7 +97,7 @@ def test_one_process_all_gpus(lib, cuda, oracle, m, n, k):
         g.run(GATHER_NONE)
         g.synchronize()
         _check_every_rank_has_all_of_c(g, want, oracle, only_own_rows=True)
-        for mode in (GATHER_AFTER_GEMM, GATHER_BANDED, GATHER_PEER_STORE):
+        for mode in (GATHER_AFTER_GEMM, GATHER_BANDED, GATHER_PEER_STORE, GATHER_COPY_ENGINE):
             _poison(g, lib, list(range(world)))
             g.run(mode)
             g.synchronize()
@@ -141,7 +141,7 @@ def _rank_worker(rank, world, port, out_dir):
         g.connect(broadcast_from_0, all_gather)
         _load(g, a, b)
         stream = torch.cuda.current_stream().cuda_stream
-        for mode in (GATHER_AFTER_GEMM, GATHER_BANDED, GATHER_PEER_STORE):
+        for mode in (GATHER_AFTER_GEMM, GATHER_BANDED, GATHER_PEER_STORE, GATHER_COPY_ENGINE):
             _poison(g, lib, [rank])
             barrier(f"poisoned{mode}")
             g.run(mode, stream)
