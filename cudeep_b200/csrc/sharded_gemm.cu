@@ -287,6 +287,7 @@ struct ShardedGemm::Impl {
             CB200_CUDA(cudaStreamWaitEvent(s, r.comm_done, 0));
             break;
         }
+        case Gather::CopyOnly:
         case Gather::CopyEngine: {
             // Band by band: the GEMM of a band, then one device-to-device copy of that band into every
             // peer's C, each on a stream of its own.  The copies run on the copy engines, so they take
@@ -303,7 +304,8 @@ struct ShardedGemm::Impl {
             for (int band = 0; band < opt.bands; ++band) {
                 const RowRange part = band_of(r.rank, band);
                 if (part.rows <= 0) continue;
-                gemm(r, r.a + (part.row0 - own.row0) * k, r.c + part.row0 * n, part.rows, 0, s);
+                if (gather == Gather::CopyEngine)
+                    gemm(r, r.a + (part.row0 - own.row0) * k, r.c + part.row0 * n, part.rows, 0, s);
                 CB200_CUDA(cudaEventRecord(r.band_done[band], s));
                 for (int p = 0; p < world; ++p) {
                     if (p == r.rank) continue;
@@ -376,9 +378,9 @@ struct ShardedGemm::Impl {
     void check_mode(Gather gather) {
         CB200_REQUIRE(!broken, "this ShardedGemm had a failed step; make a new one");
         const int g = int(gather);
-        CB200_REQUIRE(g >= 0 && g <= 5, "unknown gather mode");
+        CB200_REQUIRE(g >= 0 && g <= 6, "unknown gather mode");
         if (gather == Gather::AfterGemm || gather == Gather::Banded || gather == Gather::CollectiveOnly) ensure_comm();
-        if (gather == Gather::CopyEngine) ensure_peers();
+        if (gather == Gather::CopyEngine || gather == Gather::CopyOnly) ensure_peers();
         if (gather == Gather::PeerStore) {
             ensure_peers();
             CB200_REQUIRE(opt.dry_run || n % 4 == 0, "Gather::PeerStore needs N % 4 == 0");

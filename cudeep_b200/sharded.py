@@ -24,7 +24,8 @@ import numpy as np
 
 from . import _lib
 
-GATHER_NONE, GATHER_AFTER_GEMM, GATHER_BANDED, GATHER_PEER_STORE, GATHER_COLLECTIVE_ONLY, GATHER_COPY_ENGINE = range(6)
+(GATHER_NONE, GATHER_AFTER_GEMM, GATHER_BANDED, GATHER_PEER_STORE, GATHER_COLLECTIVE_ONLY, GATHER_COPY_ENGINE,
+ GATHER_COPY_ONLY) = range(7)
 COMM_ID_BYTES = 128
 MEM_HANDLE_BYTES = 64
 

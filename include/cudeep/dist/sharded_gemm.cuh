@@ -52,6 +52,7 @@ enum class Gather : int {
     PeerStore = 3,
     CollectiveOnly = 4,  // only the all-gather of whatever C holds (to time the collective by itself)
     CopyEngine = 5,
+    CopyOnly = 6,        // only the copy-engine pushes of whatever C holds (to time them by themselves)
 };
 
 struct RowRange {

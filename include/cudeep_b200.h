@@ -330,6 +330,7 @@ int cudeep_b200_scratch_trim(size_t keep_bytes);
  *   4 collective only the all-gather alone (for timing)
  *   5 copy engine     row bands; band i goes to every peer as a device-to-device copy on the copy
  *                     engines (peer-mapped memory) while band i+1 is computed
+ *   6 copy only       those copies alone (for timing)
  * A step whose host-side preparation fails on any rank enqueues nothing on any GPU, returns an
  * error naming the rank, and the object refuses further steps. */
 typedef struct cudeep_b200_sharded_gemm* cudeep_b200_sharded_gemm_t;
@@ -340,6 +341,7 @@ typedef struct cudeep_b200_sharded_gemm* cudeep_b200_sharded_gemm_t;
 #define CUDEEP_B200_GATHER_PEER_STORE 3
 #define CUDEEP_B200_GATHER_COLLECTIVE_ONLY 4
 #define CUDEEP_B200_GATHER_COPY_ENGINE 5
+#define CUDEEP_B200_GATHER_COPY_ONLY 6
 #define CUDEEP_B200_COMM_ID_BYTES 128
 #define CUDEEP_B200_MEM_HANDLE_BYTES 64
 
