@@ -87,6 +87,9 @@ PROTOTYPES = {
     "cudeep_b200_sharded_gemm_init_comm": (c_int, [c_void_p, c_void_p]),
     "cudeep_b200_sharded_gemm_export_c": (c_int, [c_void_p, c_void_p]),
     "cudeep_b200_sharded_gemm_open_peers": (c_int, [c_void_p, c_void_p]),
+    "cudeep_b200_sharded_gemm_multicast_fd": (c_int, [c_void_p, POINTER(c_int)]),
+    "cudeep_b200_sharded_gemm_multicast_join": (c_int, [c_void_p, c_int]),
+    "cudeep_b200_sharded_gemm_multicast_bind": (c_int, [c_void_p]),
     "cudeep_b200_sharded_gemm_run": (c_int, [c_void_p, c_int, _stream]),
     "cudeep_b200_sharded_gemm_synchronize": (c_int, [c_void_p]),
     "cudeep_b200_sharded_gemm_time": (c_int, [c_void_p, c_int, c_int, c_int, POINTER(c_float)]),

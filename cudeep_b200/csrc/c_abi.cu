@@ -570,7 +570,8 @@ cudeep::dist::ShardedGemmOptions sharded_options(int bands, int comm_sms, int dr
     cudeep::dist::ShardedGemmOptions opt;
     if (bands > 0) opt.bands = bands;
     if (comm_sms >= 0) opt.comm_sms = comm_sms;
-    opt.dry_run = dry_run != 0;
+    opt.dry_run = (dry_run & 1) != 0;        // `dry_run` is a flag word: bit 0 dry run, bit 1 multicast
+    opt.multicast = (dry_run & 2) != 0;
     return opt;
 }
 }  // namespace
@@ -632,6 +633,21 @@ int cudeep_b200_sharded_gemm_export_c(cudeep_b200_sharded_gemm_t g, void* handle
 
 int cudeep_b200_sharded_gemm_open_peers(cudeep_b200_sharded_gemm_t g, const void* handles) {
     return guarded([&] { sharded(g).open_peers(handles); });
+}
+
+int cudeep_b200_sharded_gemm_multicast_fd(cudeep_b200_sharded_gemm_t g, int* fd) {
+    return guarded([&] {
+        CB200_REQUIRE(fd != nullptr, "sharded_gemm_multicast_fd: null result pointer");
+        *fd = sharded(g).multicast_create_fd();
+    });
+}
+
+int cudeep_b200_sharded_gemm_multicast_join(cudeep_b200_sharded_gemm_t g, int fd) {
+    return guarded([&] { sharded(g).multicast_join(fd); });
+}
+
+int cudeep_b200_sharded_gemm_multicast_bind(cudeep_b200_sharded_gemm_t g) {
+    return guarded([&] { sharded(g).multicast_bind(); });
 }
 
 int cudeep_b200_sharded_gemm_run(cudeep_b200_sharded_gemm_t g, int gather, cudeep_b200_stream_t stream) {

@@ -122,6 +122,31 @@ struct GemmPushProblem : GemmProblem<CTAS, BN, B_MN_MAJOR, false> {
     }
 };
 
+// And the form for GPUs behind one NVSwitch: `mc_c` is this rank's rows of C seen through a multicast
+// address, so one multimem.st per 16 bytes writes them into every GPU's C (this GPU's included).  The
+// rank then sends each tile over NVLink once, whatever the number of peers.
+template <int CTAS, int BN, bool B_MN_MAJOR>
+struct GemmMultimemProblem : GemmProblem<CTAS, BN, B_MN_MAJOR, false> {
+    static constexpr bool kMultimemStore = true;
+    static constexpr bool kClusterSplit = false;
+    float* mc_c;
+
+    // Rows [y, y + 32), columns [x, x + 32) of this rank's C from the staged block (128-byte rows,
+    // 16-byte units XOR-swizzled by row): each instruction of the warp covers four rows.
+    __device__ __forceinline__ void multimem_store(uint32_t block, int x, int y, uint32_t lane) const {
+        const uint32_t unit = lane & 7u;
+        const int col = x + int(unit) * 4;
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i) {
+            const uint32_t row = i * 4u + (lane >> 3);
+            const float4 v = ptx::ld_shared_v4(block + row * 128u + ((unit ^ (row & 7u)) << 4));
+            const int gr = y + int(row);
+            if (gr < this->m && col < this->n)
+                ptx::multimem_st_v4(mc_c + static_cast<long long>(gr) * this->ldc + col, v);
+        }
+    }
+};
+
 // Zeroes the C region of tiles [first_tile, first_tile + gridDim.x) (raster order); blockIdx.y
 // selects a band of 16 rows inside the tile.
 __global__ void zero_tiles_kernel(float* __restrict__ c, long long ldc, int m, int n, int tile_m, int tile_n,
@@ -149,14 +174,18 @@ __global__ void zero_tiles_kernel(float* __restrict__ c, long long ldc, int m, i
 // Whether a CTA's last tile stages its results in the idle stage ring (see umma_gemm.cuh).
 constexpr bool kRingStagingDefault = true;
 
-template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, bool A_MN_MAJOR = false, bool PUSH = false>
+// OUT: 0 = C on this GPU; 1 = also stored into the peers' C (bulk tensor stores); 2 = stored through a
+// multicast address into every GPU's C.
+template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, bool A_MN_MAJOR = false, int OUT = 0>
 void launch_variant(const float* a, const float* b, float* c, int m, int n, int k,
                     const UmmaEpilogueArgs& epi, const GemmTuning& tune, cudaStream_t stream,
-                    const GemmPeerOutputs* peers = nullptr) {
+                    const GemmPeerOutputs* peers = nullptr, float* mc_c = nullptr) {
     using Cfg = UmmaConfig<CTAS, BN, B_MN_MAJOR, KATOMS>;
-    using Prob = std::conditional_t<PUSH, GemmPushProblem<CTAS, BN, B_MN_MAJOR>,
-                                    GemmProblem<CTAS, BN, B_MN_MAJOR, A_MN_MAJOR>>;
-    static_assert(!(PUSH && A_MN_MAJOR), "peer stores are built for the forward layouts only");
+    constexpr bool PUSH = OUT == 1;
+    using Prob = std::conditional_t<OUT == 1, GemmPushProblem<CTAS, BN, B_MN_MAJOR>,
+                                    std::conditional_t<OUT == 2, GemmMultimemProblem<CTAS, BN, B_MN_MAJOR>,
+                                                       GemmProblem<CTAS, BN, B_MN_MAJOR, A_MN_MAJOR>>>;
+    static_assert(!(OUT != 0 && A_MN_MAJOR), "peer stores are built for the forward layouts only");
     const DeviceInfo& dev = device_info();
 
     Prob prob;
@@ -294,9 +323,14 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     sched.ring_staging = (uint32_t(sched.stages) * Cfg::STAGE_BYTES >= 131072u && ring_wanted) ? 1 : 0;
     const uint32_t smem_bytes = uint32_t(sched.stages) * Cfg::STAGE_BYTES + exchange_bytes + staging_bytes + 1024;
 
-    if constexpr (PUSH)
+    if constexpr (OUT == 2) {
+        CB200_REQUIRE(tma_store && mc_c != nullptr && (reinterpret_cast<uintptr_t>(mc_c) & 15u) == 0,
+                      "multicast stores need N % 4 == 0 and a 16-byte aligned multicast address of C");
+        prob.mc_c = mc_c;
+    }
+    if constexpr (OUT != 0)
         CB200_REQUIRE(sched.split == 1 && sched.cluster_split == 1 && sched.tma_store == 1,
-                      "peer stores need whole tiles written by bulk tensor stores");
+                      "peer stores need whole tiles written through the staging blocks");
     CB200_TRACE("gemm tf32 tcgen05: M=%d N=%d K=%d A=%s B=%s tile=%dx%d ctas/mma=%d katoms=%d stages=%d "
                 "clusters=%d x %d CTAs tail_split=%d cluster_split=%d store=%s peers=%d act=%d bias=%d",
                 m, n, k, A_MN_MAJOR ? "[K,M]" : "[M,K]", B_MN_MAJOR ? "[K,N]" : "[N,K]", UMMA_BM * CTAS, BN, CTAS,
@@ -492,8 +526,22 @@ void gemm_tf32_push(const float* a, const float* b, bool b_is_nk, float* c, int 
     t.cluster_split = 1;
     t.tma_store = 0;
     // One tile shape: the CTA pair with a 256 x 256 tile (shards are large, that is what they take anyway).
-    if (b_is_nk) launch_variant<2, 256, false, 2, false, true>(a, b, c, m, n, k, epi, t, stream, &peers);
-    else launch_variant<2, 256, true, 2, false, true>(a, b, c, m, n, k, epi, t, stream, &peers);
+    if (b_is_nk) launch_variant<2, 256, false, 2, false, 1>(a, b, c, m, n, k, epi, t, stream, &peers);
+    else launch_variant<2, 256, true, 2, false, 1>(a, b, c, m, n, k, epi, t, stream, &peers);
+}
+
+void gemm_tf32_multimem(const float* a, const float* b, bool b_is_nk, float* c_local, float* c_multicast, int m, int n,
+                        int k, const GemmTuning& tune, cudaStream_t stream) {
+    CB200_REQUIRE(gemm_tf32_supported(a, b, c_local, m, n, k, b_is_nk) && n % 4 == 0,
+                  "TF32 tensor-core GEMM with multicast stores needs an sm_100 device, 16-byte aligned operands "
+                  "and row lengths that are multiples of 4");
+    UmmaEpilogueArgs epi{nullptr, 0, EPI_NONE};
+    GemmTuning t = tune;
+    t.split_k = 1;
+    t.cluster_split = 1;
+    t.tma_store = 0;
+    if (b_is_nk) launch_variant<2, 256, false, 2, false, 2>(a, b, c_local, m, n, k, epi, t, stream, nullptr, c_multicast);
+    else launch_variant<2, 256, true, 2, false, 2>(a, b, c_local, m, n, k, epi, t, stream, nullptr, c_multicast);
 }
 
 void gemm_tf32(const float* a, const float* b, bool b_is_nk, float* c, int m, int n, int k,

@@ -52,6 +52,14 @@ struct GemmPeerOutputs {
 void gemm_tf32_push(const float* a, const float* b, bool b_is_nk, float* c, int m, int n, int k,
                     const GemmPeerOutputs& peers, const GemmTuning& tune, cudaStream_t stream);
 
+// The same product with C behind a multicast address (GPUs of one NVSwitch domain, multicast.h):
+// `c_multicast` is the address of this rank's rows of C through which a store reaches every GPU's
+// copy, this GPU's included; `c_local` is their ordinary address on this GPU (used for alignment
+// checks only: the kernel writes through `c_multicast` alone).  The epilogue reads each staged block
+// back and writes it with multimem.st, so a tile crosses NVLink once however many GPUs receive it.
+void gemm_tf32_multimem(const float* a, const float* b, bool b_is_nk, float* c_local, float* c_multicast, int m, int n,
+                        int k, const GemmTuning& tune, cudaStream_t stream);
+
 // The tile shape the launcher would pick for a problem on a device with `num_sms` SMs (host
 // arithmetic only: no device is touched): CTAs per MMA, tile columns, K ranges per cluster,
 // K blocks per stage, and the estimated time in microseconds.

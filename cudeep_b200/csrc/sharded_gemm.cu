@@ -7,6 +7,7 @@
 
 #include "cudeep/kernels/matmul.cuh"
 #include "gemm_tf32.h"
+#include "multicast.h"
 #include "runtime.h"
 
 #include <dlfcn.h>
@@ -154,6 +155,7 @@ struct RankState {
     std::vector<void*> opened;         // inter-process mappings to close
     int num_sms = 0;
     int64_t steps_enqueued = 0;
+    cudeep_b200::MulticastShare share;  // C when the object was made with the multicast option
 };
 
 }  // namespace
@@ -168,6 +170,8 @@ struct ShardedGemm::Impl {
     std::vector<std::unique_ptr<Worker>> workers;      // one per local rank (in-process mode)
     bool comm_ready = false;
     bool peers_ready = false;
+    cudeep_b200::MulticastGroup group;                 // multicast option: the object all ranks' C is bound to
+    bool group_bound = false;
     bool broken = false;
     std::atomic<int> fail_rank{-1};
 
@@ -322,6 +326,14 @@ struct ShardedGemm::Impl {
             }
             break;
         }
+        case Gather::Multimem: {
+            if (own.rows > 0) {
+                float* through_switch = static_cast<float*>(r.share.group) + own.row0 * n;
+                cudeep_b200::GemmTuning tune;
+                cudeep_b200::gemm_tf32_multimem(r.a, r.b, false, c_own, through_switch, int(own.rows), n, k, tune, s);
+            }
+            break;
+        }
         case Gather::PeerStore: {
             cudeep_b200::GemmPeerOutputs peers;
             for (int p = 0; p < world; ++p) {
@@ -378,7 +390,15 @@ struct ShardedGemm::Impl {
     void check_mode(Gather gather) {
         CB200_REQUIRE(!broken, "this ShardedGemm had a failed step; make a new one");
         const int g = int(gather);
-        CB200_REQUIRE(g >= 0 && g <= 6, "unknown gather mode");
+        CB200_REQUIRE(g >= 0 && g <= 7, "unknown gather mode");
+        const bool peer_mapped = gather == Gather::PeerStore || gather == Gather::CopyEngine || gather == Gather::CopyOnly;
+        CB200_REQUIRE(!(peer_mapped && opt.multicast && !opt.dry_run),
+                      "an object made with the multicast option holds C in virtual-memory allocations, which the "
+                      "peer-mapped gather forms do not reach; use Gather::Multimem");
+        if (gather == Gather::Multimem)
+            CB200_REQUIRE(opt.dry_run || (opt.multicast && group_bound && n % 4 == 0),
+                          "Gather::Multimem needs an object made with the multicast option, bound (multicast_bind), and "
+                          "N % 4 == 0");
         if (gather == Gather::AfterGemm || gather == Gather::Banded || gather == Gather::CollectiveOnly) ensure_comm();
         if (gather == Gather::CopyEngine || gather == Gather::CopyOnly) ensure_peers();
         if (gather == Gather::PeerStore) {
@@ -416,14 +436,22 @@ struct ShardedGemm::Impl {
 // ---------------------------------------------------------------- construction
 
 namespace {
-void allocate_rank(RankState& r, int64_t rows, int64_t m, int n, int k, int bands) {
+void allocate_rank(RankState& r, int64_t rows, int64_t m, int n, int k, int bands, int world, bool multicast) {
     CB200_CUDA(cudaSetDevice(r.device));
     cudaDeviceProp prop{};
     CB200_CUDA(cudaGetDeviceProperties(&prop, r.device));
     r.num_sms = prop.multiProcessorCount;
     CB200_CUDA(cudaMalloc(&r.a, size_t(rows > 0 ? rows : 1) * k * sizeof(float)));
     CB200_CUDA(cudaMalloc(&r.b, size_t(k) * n * sizeof(float)));
-    CB200_CUDA(cudaMalloc(&r.c, size_t(m) * n * sizeof(float)));
+    if (multicast) {
+        // C comes from the virtual-memory API so that it can be bound into a multicast object.
+        CB200_REQUIRE(cudeep_b200::multicast_supported(), "this GPU cannot take part in a multicast object");
+        cudeep_b200::multicast_allocate(r.share, r.device,
+                                        cudeep_b200::multicast_round_size(world, size_t(m) * n * sizeof(float)));
+        r.c = static_cast<float*>(r.share.local);
+    } else {
+        CB200_CUDA(cudaMalloc(&r.c, size_t(m) * n * sizeof(float)));
+    }
     int least = 0, greatest = 0;
     CB200_CUDA(cudaDeviceGetStreamPriorityRange(&least, &greatest));
     CB200_CUDA(cudaStreamCreateWithFlags(&r.compute, cudaStreamNonBlocking));
@@ -462,7 +490,19 @@ ShardedGemm::ShardedGemm(const std::vector<int>& devices, int64_t m, int n, int 
     if (!options.dry_run) {
         int prev = 0;
         CB200_CUDA(cudaGetDevice(&prev));
-        for (RankState& r : s.ranks) allocate_rank(r, s.rows_of(r.rank).rows, m, n, k, options.bands);
+        for (RankState& r : s.ranks)
+            allocate_rank(r, s.rows_of(r.rank).rows, m, n, k, options.bands, s.world, options.multicast);
+        if (options.multicast) {
+            // One process: make the object, add every device, then bind every share.
+            CB200_REQUIRE(s.world >= 2, "the multicast option needs at least two GPUs");
+            s.group = cudeep_b200::multicast_create(s.world, s.ranks[0].share.size);
+            for (RankState& r : s.ranks) cudeep_b200::multicast_add_device(s.group, r.device);
+            for (RankState& r : s.ranks) {
+                CB200_CUDA(cudaSetDevice(r.device));
+                cudeep_b200::multicast_bind(s.group, r.share);
+            }
+            s.group_bound = true;
+        }
         CB200_CUDA(cudaSetDevice(prev));
     }
     for (size_t i = 0; i < devices.size(); ++i) s.workers.emplace_back(new Worker);
@@ -482,7 +522,8 @@ ShardedGemm::ShardedGemm(int rank, int world, int device, int64_t m, int n, int 
     s.ranks.resize(1);
     s.ranks[0].rank = rank;
     s.ranks[0].device = device;
-    if (!options.dry_run) allocate_rank(s.ranks[0], s.rows_of(rank).rows, m, n, k, options.bands);
+    if (!options.dry_run)
+        allocate_rank(s.ranks[0], s.rows_of(rank).rows, m, n, k, options.bands, world, options.multicast);
 }
 
 ShardedGemm::~ShardedGemm() {
@@ -514,8 +555,10 @@ ShardedGemm::~ShardedGemm() {
         if (r.comm) cudaStreamDestroy(r.comm);
         cudaFree(r.a);
         cudaFree(r.b);
-        cudaFree(r.c);
+        if (r.share.memory != 0) cudeep_b200::multicast_release(s.group, r.share);
+        else cudaFree(r.c);
     }
+    cudeep_b200::multicast_destroy(s.group);
     cudaSetDevice(prev);
     cudaGetLastError();
 }
@@ -585,6 +628,7 @@ void ShardedGemm::init_comm(const void* id_bytes) {
 void ShardedGemm::export_c(void* handle_out) const {
     const Impl& s = *impl_;
     CB200_REQUIRE(!s.in_process && handle_out != nullptr && !s.opt.dry_run, "export_c: one-process-per-GPU form only");
+    CB200_REQUIRE(!s.opt.multicast, "export_c: an object made with the multicast option shares C through multicast_join");
     static_assert(sizeof(cudaIpcMemHandle_t) == kHandleBytes, "unexpected handle size");
     cudaIpcMemHandle_t h{};
     CB200_CUDA(cudaSetDevice(s.ranks[0].device));
@@ -613,6 +657,37 @@ void ShardedGemm::open_peers(const void* handles) {
         r.peer_c[size_t(p)] = static_cast<float*>(mapped);
     }
     s.peers_ready = true;
+}
+
+int ShardedGemm::multicast_create_fd() {
+    Impl& s = *impl_;
+    CB200_REQUIRE(!s.in_process && s.opt.multicast && !s.opt.dry_run && s.ranks[0].rank == 0 && s.group.handle == 0,
+                  "multicast_create_fd: rank 0 of a one-process-per-GPU object made with the multicast option, once");
+    CB200_CUDA(cudaSetDevice(s.ranks[0].device));
+    s.group = cudeep_b200::multicast_create(s.world, s.ranks[0].share.size);
+    return cudeep_b200::multicast_export_fd(s.group);
+}
+
+void ShardedGemm::multicast_join(int fd) {
+    Impl& s = *impl_;
+    CB200_REQUIRE(!s.in_process && s.opt.multicast && !s.opt.dry_run, "multicast_join: one-process-per-GPU form with the multicast option");
+    RankState& r = s.ranks[0];
+    CB200_CUDA(cudaSetDevice(r.device));
+    if (r.rank != 0) {
+        CB200_REQUIRE(fd >= 0 && s.group.handle == 0, "multicast_join: a file descriptor from rank 0, once");
+        s.group = cudeep_b200::multicast_import_fd(fd, s.world, r.share.size);
+    }
+    CB200_REQUIRE(s.group.handle != 0, "multicast_join: rank 0 calls multicast_create_fd first");
+    cudeep_b200::multicast_add_device(s.group, r.device);
+}
+
+void ShardedGemm::multicast_bind() {
+    Impl& s = *impl_;
+    CB200_REQUIRE(!s.in_process && s.opt.multicast && !s.opt.dry_run && s.group.handle != 0 && !s.group_bound,
+                  "multicast_bind: after multicast_join on every rank, once");
+    CB200_CUDA(cudaSetDevice(s.ranks[0].device));
+    cudeep_b200::multicast_bind(s.group, s.ranks[0].share);
+    s.group_bound = true;
 }
 
 // ---------------------------------------------------------------- steps

@@ -197,6 +197,12 @@ template <int N>
 __device__ __forceinline__ void bulk_wait_group() {
     asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
+// 16-byte store through a multicast address: the switch writes it into every GPU's copy.
+__device__ __forceinline__ void multimem_st_v4(float* mc_addr, float4 v) {
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(v.x), "f"(v.y),
+                 "f"(v.z), "f"(v.w)
+                 : "memory");
+}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, float x, float y, float z, float w) {
     asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(x), "f"(y), "f"(z), "f"(w)
                  : "memory");

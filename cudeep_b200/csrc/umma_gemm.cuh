@@ -171,6 +171,17 @@ __device__ __forceinline__ void push_to_peers(const P& prob, uint32_t block, int
     if constexpr (has_peer_store<P>::value) prob.push(block, x, y);
 }
 
+// The other optional form of the same idea:
+//   static constexpr bool kMultimemStore = true;
+//   __device__ void multimem_store(uint32_t block, int x, int y, uint32_t lane) const;
+// The whole warp reads the staged 32 x 32 block back (4 rows of 128 bytes per instruction) and writes
+// it with multimem.st through a multicast address of C: one store travels over NVLink once and the
+// switch replicates it into every GPU's copy, this GPU's included, so no bulk tensor store is issued.
+template <class P, class = void>
+struct has_multimem_store { static constexpr bool value = false; };
+template <class P>
+struct has_multimem_store<P, decltype((void)P::kMultimemStore)> { static constexpr bool value = P::kMultimemStore; };
+
 template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, class Problem, bool A_MN_MAJOR = false,
           int KIND = UMMA_KIND_TF32>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
@@ -569,7 +580,13 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                         if (c + 96 < n_cols && !dbg_nold) ptx::tmem_ld_32x32(t_row + c + 96, r1);
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
-                        if (lane == 0 && !dbg_nost) {
+                        if constexpr (has_multimem_store<Problem>::value) {
+                            int x, y;
+                            prob.out_coords(tile, int(quarter) * 32, c, x, y);
+                            prob.multimem_store(block0, x, y, lane);
+                            if (two) prob.multimem_store(block0 + 4096u, x + 32, y, lane);
+                            __syncwarp();
+                        } else if (lane == 0 && !dbg_nost) {
                             int x, y;
                             prob.out_coords(tile, int(quarter) * 32, c, x, y);
                             ptx::tma_store_2d(prob.out_map(), block0, x, y);
@@ -605,6 +622,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
         }
         // Bulk stores read shared memory asynchronously: the reads must be over before the CTA
         // gives its shared memory back (the writes themselves complete with the kernel).
+        if constexpr (has_multimem_store<Problem>::value) __threadfence_system();
         if (lane == 0) {
             if constexpr (has_peer_store<Problem>::value) {
                 // Stores into other GPUs' memory: wait for the writes themselves, then order them

@@ -25,7 +25,7 @@ import numpy as np
 from . import _lib
 
 (GATHER_NONE, GATHER_AFTER_GEMM, GATHER_BANDED, GATHER_PEER_STORE, GATHER_COLLECTIVE_ONLY, GATHER_COPY_ENGINE,
- GATHER_COPY_ONLY) = range(7)
+ GATHER_COPY_ONLY, GATHER_MULTIMEM) = range(8)
 COMM_ID_BYTES = 128
 MEM_HANDLE_BYTES = 64
 
@@ -115,23 +115,24 @@ class ShardedGemm:
 
     @classmethod
     def local(cls, devices: Sequence[int], m: int, n: int, k: int, *, bands: int = 4, comm_sms: int = 20,
-              dry_run: bool = False) -> "ShardedGemm":
-        """One process drives all of `devices` (rank i on devices[i])."""
+              dry_run: bool = False, multicast: bool = False) -> "ShardedGemm":
+        """One process drives all of `devices` (rank i on devices[i]).  multicast: C is bound to an NVLink
+        multicast object, which GATHER_MULTIMEM writes through (the peer-mapped forms are then unavailable)."""
         lib = _lib.load()
         arr = (ctypes.c_int * len(devices))(*devices)
         h = ctypes.c_void_p()
         _lib.check(lib.cudeep_b200_sharded_gemm_create_local(arr, len(devices), m, n, k, bands, comm_sms,
-                                                             int(dry_run), ctypes.byref(h)))
+                                                             int(dry_run) | (2 if multicast else 0), ctypes.byref(h)))
         return cls(h, m, n, k, len(devices), range(len(devices)))
 
     @classmethod
     def rank(cls, rank: int, world: int, device: int, m: int, n: int, k: int, *, bands: int = 4,
-             comm_sms: int = 20, dry_run: bool = False) -> "ShardedGemm":
+             comm_sms: int = 20, dry_run: bool = False, multicast: bool = False) -> "ShardedGemm":
         """This process is rank `rank` of `world` and drives `device`."""
         lib = _lib.load()
         h = ctypes.c_void_p()
         _lib.check(lib.cudeep_b200_sharded_gemm_create_rank(rank, world, device, m, n, k, bands, comm_sms,
-                                                            int(dry_run), ctypes.byref(h)))
+                                                            int(dry_run) | (2 if multicast else 0), ctypes.byref(h)))
         return cls(h, m, n, k, world, [rank])
 
     def close(self) -> None:
@@ -221,6 +222,32 @@ class ShardedGemm:
         if peers and self.world > 1:
             self.open_peers(list(all_gather(self.export_c())))
 
+    def connect_multicast(self, share_fd: Callable[[Optional[int]], int], barrier: Callable[[], None]) -> None:
+        """The extra hand-shake of an object made with multicast=True (one process per GPU).
+        `share_fd(fd)`: rank 0 passes the descriptor of the multicast object and every other rank
+        (passing None) gets a descriptor of its own for the same object - descriptors cross processes
+        over a unix socket (socket.send_fds / recv_fds).  `barrier()` returns once every rank reached it."""
+        import os
+        lib = _lib.load()
+        me = self.local_ranks[0]
+        if me == 0:
+            fd = ctypes.c_int(-1)
+            _lib.check(lib.cudeep_b200_sharded_gemm_multicast_fd(self._h, ctypes.byref(fd)))
+            try:
+                share_fd(fd.value)
+            finally:
+                os.close(fd.value)
+            _lib.check(lib.cudeep_b200_sharded_gemm_multicast_join(self._h, -1))
+        else:
+            fd = share_fd(None)
+            try:
+                _lib.check(lib.cudeep_b200_sharded_gemm_multicast_join(self._h, fd))
+            finally:
+                os.close(fd)
+        barrier()                      # every device has been added
+        _lib.check(lib.cudeep_b200_sharded_gemm_multicast_bind(self._h))
+        barrier()
+
     # ---- steps --------------------------------------------------------------------------------
 
     def run(self, gather: int = GATHER_NONE, stream: Optional[int] = None) -> None:
@@ -251,3 +278,38 @@ class ShardedGemm:
 
     def inject_failure(self, rank: int) -> None:
         _lib.check(_lib.load().cudeep_b200_sharded_gemm_inject_failure(self._h, rank))
+
+
+def unix_socket_fd_sharing(rank: int, world: int, path: str):
+    """A `share_fd` for ShardedGemm.connect_multicast over a unix-domain socket at `path` (all ranks on
+    one host): rank 0 listens and sends the descriptor to each rank that connects."""
+    import socket
+    import time
+
+    def share_fd(fd):
+        if rank == 0:
+            with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as server:
+                server.bind(path)
+                server.listen(world)
+                try:
+                    for _ in range(world - 1):
+                        conn, _addr = server.accept()
+                        with conn:
+                            socket.send_fds(conn, [b"fd"], [fd])
+                finally:
+                    import os
+                    os.unlink(path)
+            return fd
+        deadline = time.monotonic() + 60.0
+        while True:
+            try:
+                with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as client:
+                    client.connect(path)
+                    _msg, fds, _flags, _addr = socket.recv_fds(client, 16, 1)
+                    return fds[0]
+            except (FileNotFoundError, ConnectionRefusedError):
+                if time.monotonic() > deadline:
+                    raise
+                time.sleep(0.05)
+
+    return share_fd

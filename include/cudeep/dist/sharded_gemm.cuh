@@ -16,6 +16,11 @@
 //   Gather::CopyEngine  row bands again, but band i travels as one device-to-device copy per peer on the
 //                       GPU's copy engines (peer-mapped memory, a stream per peer): no SM is taken from
 //                       band i+1's GEMM and the links carry large contiguous blocks;
+//   Gather::Multimem    one kernel does both, through the switch: C lives in memory bound to an NVLink
+//                       multicast object, and the GEMM's epilogue writes every tile with multimem.st, which
+//                       crosses NVLink once and is replicated into every GPU's C by the NVSwitch - the
+//                       rank sends its rows once instead of once per peer (objects made with
+//                       ShardedGemmOptions::multicast);
 //   Gather::PeerStore   one kernel does both: the GEMM's epilogue stores every finished tile into all
 //                       GPUs' copies of C through peer-mapped memory (bulk tensor stores; nothing is
 //                       ever loaded from a peer), so the transfer overlaps the math tile by tile and no
@@ -53,6 +58,7 @@ enum class Gather : int {
     CollectiveOnly = 4,  // only the all-gather of whatever C holds (to time the collective by itself)
     CopyEngine = 5,
     CopyOnly = 6,        // only the copy-engine pushes of whatever C holds (to time them by themselves)
+    Multimem = 7,
 };
 
 struct RowRange {
@@ -71,6 +77,11 @@ struct ShardedGemmOptions {
     int bands = 4;         // row bands per shard in Gather::Banded
     int comm_sms = 20;     // SMs the banded GEMM leaves to the collective's kernels
     bool dry_run = false;  // host logic only: no CUDA or NCCL call is made (plan and failure-path tests)
+    // C is allocated through the virtual-memory API and bound to an NVLink multicast object, which
+    // Gather::Multimem writes through (needs GPUs behind one NVSwitch and at least two of them).  Such
+    // an object offers None, AfterGemm, Banded and Multimem; the peer-mapped forms need the default.
+    // Every rank must be idle (a barrier after the last step) before any rank destroys its object.
+    bool multicast = false;
 };
 
 class ShardedGemm {
@@ -109,6 +120,14 @@ public:
     void init_comm(const void* id);
     void export_c(void* handle_out) const;
     void open_peers(const void* handles);
+
+    // The same for an object made with the multicast option: rank 0 makes the multicast object and
+    // gets a file descriptor for it, which the caller hands to the other processes (SCM_RIGHTS over a
+    // unix socket, or pidfd_getfd) and closes; every rank joins (rank 0 passes -1); after a barrier
+    // between the processes - every device must have joined - every rank binds its C.
+    int multicast_create_fd();
+    void multicast_join(int fd);
+    void multicast_bind();
 
     // Enqueues one step on every local rank and returns without waiting.  With one process for all
     // GPUs the work goes on the object's own streams; with one process per GPU on `stream` (nullptr:

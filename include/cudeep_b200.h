@@ -331,6 +331,9 @@ int cudeep_b200_scratch_trim(size_t keep_bytes);
  *   5 copy engine     row bands; band i goes to every peer as a device-to-device copy on the copy
  *                     engines (peer-mapped memory) while band i+1 is computed
  *   6 copy only       those copies alone (for timing)
+ *   7 multimem        the GEMM's epilogue writes each tile with multimem.st through an NVLink multicast
+ *                     object that all GPUs' C is bound to: the tile crosses NVLink once and the NVSwitch
+ *                     replicates it (objects created with the multicast flag)
  * A step whose host-side preparation fails on any rank enqueues nothing on any GPU, returns an
  * error naming the rank, and the object refuses further steps. */
 typedef struct cudeep_b200_sharded_gemm* cudeep_b200_sharded_gemm_t;
@@ -342,11 +345,16 @@ typedef struct cudeep_b200_sharded_gemm* cudeep_b200_sharded_gemm_t;
 #define CUDEEP_B200_GATHER_COLLECTIVE_ONLY 4
 #define CUDEEP_B200_GATHER_COPY_ENGINE 5
 #define CUDEEP_B200_GATHER_COPY_ONLY 6
+#define CUDEEP_B200_GATHER_MULTIMEM 7
+#define CUDEEP_B200_SHARDED_DRY_RUN 1        /* flag bits of the `dry_run` argument of the two create calls */
+#define CUDEEP_B200_SHARDED_MULTICAST 2
 #define CUDEEP_B200_COMM_ID_BYTES 128
 #define CUDEEP_B200_MEM_HANDLE_BYTES 64
 
 /* One process drives all of devices[0..n_devices): one host thread and stream pair per device,
- * communicators from ncclCommInitAll.  dry_run != 0: host logic only, no CUDA or NCCL call. */
+ * communicators from ncclCommInitAll.  `dry_run` is a flag word: CUDEEP_B200_SHARDED_DRY_RUN = host logic
+ * only, no CUDA or NCCL call; CUDEEP_B200_SHARDED_MULTICAST = C is bound to an NVLink multicast object
+ * (gather mode 7; the peer-mapped modes 3, 5 and 6 are then unavailable). */
 int cudeep_b200_sharded_gemm_create_local(const int* devices, int n_devices, long long M, int N, int K,
                                           int bands, int comm_sms, int dry_run,
                                           cudeep_b200_sharded_gemm_t* out);
@@ -368,6 +376,13 @@ int cudeep_b200_sharded_gemm_comm_id(void* id_out);
 int cudeep_b200_sharded_gemm_init_comm(cudeep_b200_sharded_gemm_t g, const void* id);
 int cudeep_b200_sharded_gemm_export_c(cudeep_b200_sharded_gemm_t g, void* handle_out);
 int cudeep_b200_sharded_gemm_open_peers(cudeep_b200_sharded_gemm_t g, const void* handles);
+/* One process per GPU with the multicast flag: rank 0 creates the multicast object and receives a file
+ * descriptor for it (multicast_fd), hands it to the other processes and closes it; every rank joins
+ * (rank 0 with fd = -1); after a barrier between the processes every rank binds.  Before any rank
+ * destroys its object all ranks must be idle (a barrier after the last step). */
+int cudeep_b200_sharded_gemm_multicast_fd(cudeep_b200_sharded_gemm_t g, int* fd);
+int cudeep_b200_sharded_gemm_multicast_join(cudeep_b200_sharded_gemm_t g, int fd);
+int cudeep_b200_sharded_gemm_multicast_bind(cudeep_b200_sharded_gemm_t g);
 /* Enqueue one step (asynchronous).  One process per GPU: on `stream` (NULL: the object's own);
  * the collective's stream is joined back into it.  One process for all GPUs: `stream` is ignored. */
 int cudeep_b200_sharded_gemm_run(cudeep_b200_sharded_gemm_t g, int gather, cudeep_b200_stream_t stream);

@@ -13,7 +13,8 @@ import numpy as np
 import pytest
 
 from cudeep_b200.sharded import (GATHER_AFTER_GEMM, GATHER_BANDED, GATHER_COLLECTIVE_ONLY, GATHER_COPY_ENGINE,
-                                 GATHER_NONE, GATHER_PEER_STORE, ShardedGemm)
+                                 GATHER_MULTIMEM, GATHER_NONE, GATHER_PEER_STORE, ShardedGemm,
+                                 unix_socket_fd_sharing)
 
 pytestmark = pytest.mark.gpu
 
@@ -106,6 +107,97 @@ def test_one_process_all_gpus(lib, cuda, oracle, m, n, k):
             cuda.cuda.set_device(dev)
             assert _lib.device_status(True) == 0
         cuda.cuda.set_device(0)
+
+
+@pytest.mark.parametrize("m,n,k", [(2048, 768, 512), (1900, 520, 260)])
+def test_one_process_all_gpus_through_the_switch(lib, cuda, oracle, m, n, k):
+    """C bound to an NVLink multicast object: the GEMM's epilogue writes each tile once with multimem.st
+    and the NVSwitch replicates it into every GPU's C.  NCCL's forms work on the same buffers."""
+    from cudeep_b200 import _lib
+    world = min(cuda.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs two GPUs")
+    a, b = _inputs(m, n, k, seed=17)
+    want = oracle.gemm(a, b, input_mode=oracle.INPUT_TF32_TRUNC)
+    with ShardedGemm.local(list(range(world)), m, n, k, bands=2, multicast=True) as g:
+        _load(g, a, b)
+        for mode in (GATHER_MULTIMEM, GATHER_AFTER_GEMM, GATHER_MULTIMEM):
+            _poison(g, lib, list(range(world)))
+            g.run(mode)
+            g.synchronize()
+            _check_every_rank_has_all_of_c(g, want, oracle)
+        with pytest.raises(_lib.CudeepError, match="multicast option"):
+            g.run(GATHER_PEER_STORE)
+        for dev in range(world):
+            cuda.cuda.set_device(dev)
+            assert _lib.device_status(True) == 0
+        cuda.cuda.set_device(0)
+    with ShardedGemm.local(list(range(world)), m, n, k) as g:
+        with pytest.raises(_lib.CudeepError, match="multicast option"):
+            g.run(GATHER_MULTIMEM)
+
+
+def _multicast_rank_worker(rank, world, port, out_dir):
+    """One process per GPU, C behind a multicast object; the descriptor travels over a unix socket."""
+    import datetime
+    import torch
+    import torch.distributed as dist
+    from cudeep_b200 import _lib
+    from oracle import oracle as o
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=datetime.timedelta(seconds=60))
+    counter = [0]
+
+    def barrier():
+        counter[0] += 1
+        store.set(f"b{counter[0]}/{rank}", "1")
+        store.wait([f"b{counter[0]}/{r}" for r in range(world)])
+
+    def broadcast_from_0(x):
+        if rank == 0:
+            store.set("id", x)
+        return store.get("id")
+
+    m, n, k = 2048, 1024, 512
+    a, b = _inputs(m, n, k, seed=19)
+    want = o.gemm(a, b, input_mode=o.INPUT_TF32_TRUNC)
+    lib = _lib.load()
+    errs = []
+    g = ShardedGemm.rank(rank, world, rank, m, n, k, bands=2, multicast=True)
+    try:
+        g.connect(broadcast_from_0, lambda x: [], peers=False)
+        g.connect_multicast(unix_socket_fd_sharing(rank, world, os.path.join(out_dir, "mc.sock")), barrier)
+        _load(g, a, b)
+        stream = torch.cuda.current_stream().cuda_stream
+        for mode in (GATHER_MULTIMEM, GATHER_AFTER_GEMM, GATHER_MULTIMEM):
+            _poison(g, lib, [rank])
+            barrier()
+            g.run(mode, stream)
+            torch.cuda.synchronize()
+            g.synchronize()
+            barrier()
+            got = g.read_c()
+            errs.append(float("inf") if np.isnan(got).any() else o.rel_frobenius(got, want))
+        status = _lib.device_status(True)
+    finally:
+        barrier()                      # nobody unbinds while another rank may still write through the switch
+        g.close()
+    np.save(os.path.join(out_dir, f"m_{rank}.npy"), np.array([status, *errs]))
+
+
+def test_one_process_per_gpu_through_the_switch(cuda, lib, tmp_path):
+    if cuda.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_multicast_rank_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for rank in range(2):
+        status, *errs = np.load(tmp_path / f"m_{rank}.npy")
+        assert status == 0
+        assert all(e <= TF32_MODEL_TOL for e in errs), errs
 
 
 def _rank_worker(rank, world, port, out_dir):
