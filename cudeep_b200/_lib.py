@@ -83,6 +83,7 @@ PROTOTYPES = {
                                               POINTER(ctypes.c_longlong)]),
     "cudeep_b200_sharded_gemm_buffers": (c_int, [c_void_p, c_int, POINTER(c_void_p), POINTER(c_void_p),
                                                  POINTER(c_void_p)]),
+    "cudeep_b200_sharded_gemm_read_c": (c_int, [c_void_p, c_int, ctypes.c_longlong, ctypes.c_longlong, c_void_p]),
     "cudeep_b200_sharded_gemm_comm_id": (c_int, [c_void_p]),
     "cudeep_b200_sharded_gemm_init_comm": (c_int, [c_void_p, c_void_p]),
     "cudeep_b200_sharded_gemm_export_c": (c_int, [c_void_p, c_void_p]),

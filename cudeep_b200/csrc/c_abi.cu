@@ -619,6 +619,11 @@ int cudeep_b200_sharded_gemm_buffers(cudeep_b200_sharded_gemm_t g, int local, fl
     });
 }
 
+int cudeep_b200_sharded_gemm_read_c(cudeep_b200_sharded_gemm_t g, int local, long long row0, long long rows,
+                                    float* host_dst) {
+    return guarded([&] { sharded(g).read_c(local, row0, rows, host_dst); });
+}
+
 int cudeep_b200_sharded_gemm_comm_id(void* id_out) {
     return guarded([&] { cudeep::dist::ShardedGemm::new_comm_id(id_out); });
 }

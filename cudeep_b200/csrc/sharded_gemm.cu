@@ -593,6 +593,20 @@ void ShardedGemm::set_a(int local, const float* host_rows) {
     CB200_CUDA(cudaSetDevice(prev));
 }
 
+void ShardedGemm::read_c(int local, int64_t row0, int64_t rows, float* host_dst) const {
+    CB200_REQUIRE(host_dst != nullptr && !impl_->opt.dry_run, "read_c: null pointer or dry run");
+    CB200_REQUIRE(row0 >= 0 && rows >= 0 && row0 + rows <= impl_->m, "read_c: rows out of range");
+    const RankState& r = impl_->at(local);
+    if (rows == 0) return;
+    int prev = 0;
+    CB200_CUDA(cudaGetDevice(&prev));
+    CB200_CUDA(cudaSetDevice(r.device));         // memory from the virtual-memory API is reachable from its own device only
+    const cudaError_t err = cudaMemcpy(host_dst, r.c + row0 * impl_->n, size_t(rows) * impl_->n * sizeof(float),
+                                       cudaMemcpyDeviceToHost);
+    cudaSetDevice(prev);
+    CB200_CUDA(err);
+}
+
 void ShardedGemm::set_b(const float* host_b) {
     CB200_REQUIRE(host_b != nullptr && !impl_->opt.dry_run, "set_b: null pointer or dry run");
     int prev = 0;

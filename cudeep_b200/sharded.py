@@ -184,9 +184,8 @@ class ShardedGemm:
         rows = self.m - row0 if rows is None else rows
         out = np.empty((rows, self.n), dtype=np.float32)
         if rows:
-            src = self.buffers(local)[2] + row0 * self.n * 4
-            _lib.check(_lib.load().cudeep_b200_memcpy_d2h(out.ctypes.data_as(ctypes.c_void_p), ctypes.c_void_p(src),
-                                                          out.nbytes, None))
+            _lib.check(_lib.load().cudeep_b200_sharded_gemm_read_c(self._h, local, row0, rows,
+                                                                   out.ctypes.data_as(ctypes.c_void_p)))
         return out
 
     # ---- one process per GPU: the two exchanges ----------------------------------------------

@@ -112,6 +112,8 @@ public:
     float* c(int local) const;
     void set_a(int local, const float* host_rows);      // blocking copies from host memory
     void set_b(const float* host_b);                    // into every local replica
+    // Rows [row0, row0 + rows) of local rank `local`'s copy of C into host memory (blocking).
+    void read_c(int local, int64_t row0, int64_t rows, float* host_dst) const;
 
     // One-process-per-GPU plumbing.  new_comm_id: rank 0 makes the id and ships it to the others;
     // init_comm: all ranks, collectively.  export_c / open_peers: every rank publishes the handle of

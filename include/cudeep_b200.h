@@ -369,6 +369,9 @@ int cudeep_b200_sharded_gemm_rows(cudeep_b200_sharded_gemm_t g, int rank, int ba
 /* Device buffers of local rank `local` (0 in the one-process-per-GPU form). */
 int cudeep_b200_sharded_gemm_buffers(cudeep_b200_sharded_gemm_t g, int local, float** a_shard, float** b,
                                      float** c);
+/* Rows [row0, row0 + rows) of local rank `local`'s copy of C into host memory (blocking). */
+int cudeep_b200_sharded_gemm_read_c(cudeep_b200_sharded_gemm_t g, int local, long long row0, long long rows,
+                                    float* host_dst);
 /* One process per GPU: rank 0 makes a communicator id (128 bytes) and ships it; every rank then
  * calls init_comm with it.  export_c writes the 64-byte handle of this rank's C; open_peers takes
  * all ranks' handles in rank order (world * 64 bytes) and maps the others' C for peer stores. */
