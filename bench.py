@@ -331,11 +331,15 @@ def run_c5(args, rank, world, local, dist, gather: bool):
                 g.connect(exchange_id, exchange_handles)
             mine = g.rows_of(rank)
             b_np = workloads.c5_b(n, k)
-            g.set_b(b_np)
-            a_ptr = g.buffers(0)[0]
-            for i in range(mine.rows // workloads.C5_BAND_ROWS):       # band by band: no multi-GB host copy of A
-                band = workloads.c5_a_band(mine.row0 // workloads.C5_BAND_ROWS + i, k)
-                g._h2d(a_ptr + i * workloads.C5_BAND_ROWS * k * 4, band)
+
+            def load_operands(obj):
+                obj.set_b(b_np)
+                a_ptr = obj.buffers(0)[0]
+                for i in range(mine.rows // workloads.C5_BAND_ROWS):   # band by band: no multi-GB host copy of A
+                    band = workloads.c5_a_band(mine.row0 // workloads.C5_BAND_ROWS + i, k)
+                    obj._h2d(a_ptr + i * workloads.C5_BAND_ROWS * k * 4, band)
+
+            load_operands(g)
             ms = timed(g, sh.GATHER_NONE, args.c5_steps)
             flops = 2.0 * m * n * k
             rng = np.random.default_rng([55, rank, m])
@@ -369,23 +373,48 @@ def run_c5(args, rank, world, local, dist, gather: bool):
                 g.run(sh.GATHER_COPY_ENGINE, stream)
                 barrier_sync(dist)
                 err_copy = check_rows(g, foreign, b_np, k, "gathered C, copy-engine form, rows of other ranks")
+                # The same product with C bound to an NVLink multicast object: the epilogue writes each tile
+                # once with multimem.st and the switch replicates it.
+                t_multimem, err_multimem, multimem_note = None, None, None
+                try:
+                    gm = sh.ShardedGemm.rank(rank, world, local, m, n, k, bands=bands, multicast=True)
+                except Exception as e:                      # no multicast support: the same on every rank
+                    gm, multimem_note = None, str(e)
+                if gm is not None:
+                    try:
+                        import tempfile
+                        path = exchange_id(os.path.join(tempfile.gettempdir(), f"cudeep_mc_{os.getpid()}.sock")
+                                           if rank == 0 else None)
+                        gm.connect_multicast(sh.unix_socket_fd_sharing(rank, world, path), lambda: barrier_sync(dist))
+                        load_operands(gm)
+                        t_multimem = timed(gm, sh.GATHER_MULTIMEM, args.c5_steps)
+                        barrier_sync(dist)
+                        err_multimem = check_rows(gm, foreign, b_np, k, "gathered C, multimem form, rows of other ranks")
+                    finally:
+                        barrier_sync(dist)        # nobody unbinds while another rank may still write through the switch
+                        gm.close()
                 longer = max(t_compute, t_gather)
                 forms = {"fused peer-store epilogue": t_fused, "banded NCCL": t_banded,
                          "banded copy-engine pushes": t_copy}
+                if t_multimem is not None:
+                    forms["fused multimem epilogue (NVSwitch multicast)"] = t_multimem
                 best_form = min(forms, key=forms.get)
                 best = forms[best_form]
                 out["with_gather"] = {
                     "workload": f"C[{m},{n}] gathered on every GPU ({(world - 1) * mine.rows * n * 4} bytes received per GPU)",
                     "t_compute_ms": t_compute, "t_gather_alone_ms": t_gather,
                     "t_gemm_then_ncclAllGather_ms": t_after, "t_banded_nccl_ms": t_banded,
-                    "t_fused_peer_store_ms": t_fused, "t_banded_copy_engine_ms": t_copy, "t_both_ms": best,
+                    "t_fused_peer_store_ms": t_fused, "t_banded_copy_engine_ms": t_copy,
+                    "t_fused_multimem_ms": t_multimem, "t_both_ms": best,
                     "form": best_form,
                     "overlap": best / longer, "overlap_banded_nccl": t_banded / longer,
                     "overlap_fused_peer_store": t_fused / longer, "overlap_banded_copy_engine": t_copy / longer,
+                    "overlap_fused_multimem": (t_multimem / longer) if t_multimem is not None else None,
+                    "multimem_unavailable": multimem_note,
                     "plain_sum_ms": t_compute + t_gather,
                     "tflops_with_gather": flops / (best * 1e-3) / 1e12,
                     "parity_max_rel_err_fused": err_fused, "parity_max_rel_err_banded": err_banded,
-                    "parity_max_rel_err_copy_engine": err_copy,
+                    "parity_max_rel_err_copy_engine": err_copy, "parity_max_rel_err_multimem": err_multimem,
                     "steps": args.c5_steps, "bands": bands,
                     "note": "overlap = step time / max(compute alone, collective alone); 1.0 = the shorter leg is fully hidden"}
             barrier_sync(dist)
