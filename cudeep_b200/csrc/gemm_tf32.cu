@@ -145,6 +145,20 @@ struct GemmMultimemProblem : GemmProblem<CTAS, BN, B_MN_MAJOR, false> {
                 ptx::multimem_st_v4(mc_c + static_cast<long long>(gr) * this->ldc + col, v);
         }
     }
+    // Two staged blocks side by side (columns [x, x + 64)): each instruction of the warp covers two
+    // rows of 256 contiguous bytes, the largest payload an NVLink write carries.
+    __device__ __forceinline__ void multimem_store_pair(uint32_t block, int x, int y, uint32_t lane) const {
+        const uint32_t u = lane & 15u, blk = u >> 3, unit = u & 7u;
+        const int col = x + int(u) * 4;
+#pragma unroll
+        for (uint32_t i = 0; i < 16; ++i) {
+            const uint32_t row = i * 2u + (lane >> 4);
+            const float4 v = ptx::ld_shared_v4(block + blk * 4096u + row * 128u + ((unit ^ (row & 7u)) << 4));
+            const int gr = y + int(row);
+            if (gr < this->m && col < this->n)
+                ptx::multimem_st_v4(mc_c + static_cast<long long>(gr) * this->ldc + col, v);
+        }
+    }
 };
 
 // Zeroes the C region of tiles [first_tile, first_tile + gridDim.x) (raster order); blockIdx.y

@@ -174,6 +174,7 @@ __device__ __forceinline__ void push_to_peers(const P& prob, uint32_t block, int
 // The other optional form of the same idea:
 //   static constexpr bool kMultimemStore = true;
 //   __device__ void multimem_store(uint32_t block, int x, int y, uint32_t lane) const;
+//   __device__ void multimem_store_pair(uint32_t block, int x, int y, uint32_t lane) const;   two blocks, 64 columns
 // The whole warp reads the staged 32 x 32 block back (4 rows of 128 bytes per instruction) and writes
 // it with multimem.st through a multicast address of C: one store travels over NVLink once and the
 // switch replicates it into every GPU's copy, this GPU's included, so no bulk tensor store is issued.
@@ -583,8 +584,8 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                         if constexpr (has_multimem_store<Problem>::value) {
                             int x, y;
                             prob.out_coords(tile, int(quarter) * 32, c, x, y);
-                            prob.multimem_store(block0, x, y, lane);
-                            if (two) prob.multimem_store(block0 + 4096u, x + 32, y, lane);
+                            if (two) prob.multimem_store_pair(block0, x, y, lane);
+                            else prob.multimem_store(block0, x, y, lane);
                             __syncwarp();
                         } else if (lane == 0 && !dbg_nost) {
                             int x, y;
