@@ -7,7 +7,7 @@
 // the product each rank computes is exactly that launcher's.
 //
 // Rows are independent, so computing needs no exchange.  The only communication is the optional
-// all-gather of C for callers that need the whole product on every GPU, offered in four forms:
+// all-gather of C for callers that need the whole product on every GPU, offered in these forms:
 //
 //   Gather::AfterGemm   the GEMM, then one in-place ncclAllGather on the same stream (the baseline);
 //   Gather::Banded      the shard is cut into row bands; the NCCL transfer of band i runs on a second
