@@ -56,13 +56,14 @@ static void test_plan_and_failure_path_without_a_gpu() {
     std::printf("[PASS] plan and failure path (dry run)\n");
 }
 
-static void test_every_gather_mode(int world) {
+static void test_every_gather_mode(int world, bool multicast = false) {
     const int64_t m = 1536 + 128;       // ragged over two or four ranks
     const int n = 768, k = 320;
     std::vector<int> devices(world);
     for (int i = 0; i < world; ++i) devices[i] = i;
     ShardedGemmOptions opt;
     opt.bands = 2;
+    opt.multicast = multicast;          // C bound to an NVLink multicast object: Gather::Multimem
     ShardedGemm g(devices, m, n, k, opt);
     std::mt19937 gen(3);
     std::normal_distribution<float> dist(0.0f, 1.0f);
@@ -78,7 +79,9 @@ static void test_every_gather_mode(int world) {
         g.set_a(i, a.data() + own.row0 * k);
     }
     CHECK(covered == m);
-    const Gather modes[] = {Gather::AfterGemm, Gather::Banded, Gather::PeerStore, Gather::CopyEngine};
+    const std::vector<Gather> modes = multicast
+        ? std::vector<Gather>{Gather::Multimem, Gather::AfterGemm, Gather::Multimem}
+        : std::vector<Gather>{Gather::AfterGemm, Gather::Banded, Gather::PeerStore, Gather::CopyEngine};
     std::vector<float> host(size_t(m) * n);
     for (Gather mode : modes) {
         for (int i = 0; i < world; ++i) {
@@ -89,7 +92,7 @@ static void test_every_gather_mode(int world) {
         g.run(mode);
         g.synchronize();
         for (int i = 0; i < world; ++i) {
-            cudaMemcpy(host.data(), g.c(i), host.size() * sizeof(float), cudaMemcpyDeviceToHost);
+            g.read_c(i, 0, m, host.data());
             for (int s = 0; s < 400; ++s) {
                 const int64_t row = (int64_t(s) * 7919 + i * 13) % m;
                 const int col = (s * 104729) % n;
@@ -101,9 +104,10 @@ static void test_every_gather_mode(int world) {
             }
         }
     }
-    const float ms = g.time_steps(Gather::PeerStore, 3, 1);
+    const float ms = g.time_steps(multicast ? Gather::Multimem : Gather::PeerStore, 3, 1);
     CHECK(ms > 0.0f);
-    std::printf("[PASS] every gather mode on %d GPU(s), %.3f ms per fused step\n", world, ms);
+    std::printf("[PASS] every gather mode on %d GPU(s)%s, %.3f ms per fused step\n", world,
+                multicast ? " through the switch" : "", ms);
 }
 
 int main(int argc, char** argv) {
@@ -117,7 +121,10 @@ int main(int argc, char** argv) {
         int count = 0;
         CHECK(cudaGetDeviceCount(&count) == cudaSuccess && count >= 1);
         test_every_gather_mode(1);
-        if (count >= 2) test_every_gather_mode(count >= 4 ? 4 : 2);
+        if (count >= 2) {
+            test_every_gather_mode(count >= 4 ? 4 : 2);
+            test_every_gather_mode(count >= 4 ? 4 : 2, /*multicast=*/true);
+        }
     } catch (const std::exception& e) {
         std::printf("FAILED with exception: %s\n", e.what());
         return 1;
