@@ -46,12 +46,24 @@ namespace {
 //            j = pad_h - kh + lo_h[a], l = pad_w - kw + lo_w[b] of class (a, b)'s sub-filter, i.e.
 //            forward tap (a + sub_sh * j, b + sub_sw * l), and zero where that tap does not exist:
 //            wp[oc][kh*KW + kw][c] = w[c][ci][a + sub_sh*j][b + sub_sw*l].
+// Eight small signed integers in one word, read by shifting.  (An array member indexed at run
+// time makes the compiler keep a copy of the whole kernel-parameter struct in local memory, which
+// every thread of the kernel then fills on entry: that doubled the time of the re-layout kernel.)
+struct PackedInts8 {
+    unsigned long long bits = 0;
+    __host__ __device__ void set(int i, int v) {
+        bits = (bits & ~(0xffull << (8 * i))) |
+               (static_cast<unsigned long long>(static_cast<unsigned char>(static_cast<signed char>(v))) << (8 * i));
+    }
+    __host__ __device__ int operator[](int i) const { return static_cast<signed char>(bits >> (8 * i)); }
+};
+
 struct FilterPack {
     const float* w;
     float* wp;
     int oc_n, c, k_h, k_w, cp, flipped, row_cx;
     int sub_sh = 0, sub_sw = 0, fwd_c = 0, full_kh = 0, full_kw = 0, pad_h = 0, pad_w = 0;
-    signed char lo_h[8] = {}, lo_w[8] = {};
+    PackedInts8 lo_h, lo_w;
 };
 
 __device__ __forceinline__ void pack_filters(const FilterPack& f, long long block, long long blocks, int threads) {
@@ -202,7 +214,13 @@ struct ConvProblem {
     // When a tile's pixels are contiguous in the output plane (box_w == OW) the output is the 2-D
     // tensor {OH*OW, N*OC} and goes out by bulk tensor stores like a GEMM's C; otherwise registers.
     static constexpr bool kTmaStore = true;
-    static constexpr bool kClusterSplit = false;
+    // Few tiles and a long reduction (small feature maps, many channels): the K blocks of a tile
+    // may be split over the CTA groups of a cluster.  Only the kernels for tiles of several images
+    // carry that code: in the others it was never chosen for a layer that was measured, and its
+    // presence alone costs the short tiles of large maps instruction-cache space.
+    static constexpr bool kClusterSplit = MULTI_IMAGE;
+    // Tiles of whole small planes may leave through compacted blocks (see has_plane_store).
+    static constexpr bool kPlaneStore = MULTI_IMAGE;
     CUtensorMap map_w;     // packed filters: dims {KH*KW*Cp, OC}, box {32, 128}
     CUtensorMap map_x;     // NHWC input: dims {Cx, W, H, N}, box {32, box_w, box_h / CTAS, 1}
     CUtensorMap map_out;   // output planes: dims {OH*OW, N*OC}, box {32, 32}
@@ -279,6 +297,26 @@ struct ConvProblem {
         t.nb0 = t.n;
         return t;
     }
+    __device__ __forceinline__ int plane_columns() const { return box_w * box_h; }
+    __device__ __forceinline__ uint32_t plane_bytes() const { return 32u * uint32_t(oh_n * ow_n) * 4u; }
+    __device__ __forceinline__ float* plane_dst(const Tile& t, int row0, int plane) const {
+        const int oc = t.oc0 + row0;
+        if (oc >= oc_n || t.n + plane >= batch) return nullptr;     // OC is a multiple of 32 in this mode
+        return out + (static_cast<long long>(t.n + plane) * oc_n + oc) * out_plane;
+    }
+    // Row `lane` of the block is that output channel's plane, OH * OW floats; columns of the pixel
+    // box past OW or OH are dropped.  (An odd plane size keeps the lanes on different banks.)
+    __device__ __forceinline__ void plane_stage(uint32_t staging, uint32_t lane, int col_in_plane,
+                                                const float (&v)[32]) const {
+        const uint32_t row = staging + lane * uint32_t(oh_n * ow_n) * 4u;
+        int oh = col_in_plane / box_w;
+        int ow = col_in_plane - oh * box_w;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (oh < oh_n && ow < ow_n) ptx::st_shared_f32(row + uint32_t(oh * ow_n + ow) * 4u, v[j]);
+            if (++ow == box_w) { ow = 0; ++oh; }
+        }
+    }
     template <int C>
     __device__ __forceinline__ void load(const Tile& t, int kb, uint32_t a_smem, uint32_t b_smem,
                                          uint32_t bar) const {
@@ -354,6 +392,7 @@ struct ConvProblem {
 struct TilePlan {
     int box_w = 0, box_h = 0;
     int box_n = 1;      // > 1: whole images per tile (small feature maps)
+    int ksplit = 1;     // > 1: the reduction is split over this many CTA groups of one cluster
 };
 
 // Output-pixel box of one tile: box_h rows of box_w pixels, box_w * box_h a
@@ -386,38 +425,70 @@ TilePlan plan_tile(int oh, int ow, int ctas, int s_h, int s_w) {
 
 // Small feature maps: a tile of box_n whole images (box_w >= OW, box_h >= OH, box_n a multiple of
 // the CTAs that split it), so that the filter slab a CTA stages per K block is used by more
-// accumulator columns than one image's 49 or 16.  Candidates are ranked by an estimate of the
-// time per K block - the slower of the tensor pipe (about 1.08 ns per accumulator column) and
-// the CTA's operand ingest (about 114 bytes per ns) - times the waves of tiles over the SMs:
-// few large tiles leave SMs idle, many small ones re-read the filters.
+// accumulator columns than one image's 49 or 16.  And few tiles with a long reduction: the K blocks
+// of a tile split over `ksplit` CTA groups of one cluster, which add their partial sums through
+// distributed shared memory (one tile per cluster, so every tile must find a cluster in one wave
+// for the split to pay).  Candidates are ranked by an estimate of the launch's K loop: per K block
+// the slower of the tensor pipe (about 1.08 ns per accumulator column) and the CTA's operand ingest
+// (about 114 bytes per ns), times the K blocks of a group, times the waves of tiles over the SMs,
+// plus what the exchange of partial sums costs.  Few large tiles leave SMs idle, many small ones
+// re-read the filters.
+constexpr double kExchangeNs = 3500.0, kExchangeDoublingNs = 750.0;
+
+// Whether `ksplit` groups of `ctas` CTAs can share a tile of n accumulator columns: a portable
+// cluster, whole 32-column chunks per group, and room for the exchange buffer beside two stages.
+bool cluster_split_fits(int n, int ctas, int ksplit, int k_blocks, int katoms, uint32_t staging_bytes) {
+    if (ksplit == 1) return true;
+    if (ctas * ksplit > 8 || n % (32 * ksplit) != 0) return false;
+    int per = (k_blocks + ksplit - 1) / ksplit;
+    per = (per + katoms - 1) / katoms * katoms;
+    if (per < 2 * katoms || (k_blocks + per - 1) / per != ksplit) return false;
+    const uint32_t stage = uint32_t(katoms) * (UMMA_BM * UMMA_BK * 4 + uint32_t(n / ctas) * UMMA_BK * 4);
+    const uint32_t exchange = uint32_t(ksplit - 1) * UMMA_BM * uint32_t(n / ksplit) * 4u;
+    return exchange + staging_bytes + 2 * stage <= 232448u - 1536u;     // the kernels' shared-memory budget
+}
+
 TilePlan plan_multi_image_tile(int oh, int ow, int batch, int ctas, int s_h, int s_w, int tiles_m, int num_sms,
-                               const TilePlan& single) {
+                               int k_blocks, const TilePlan& single) {
     TilePlan best = single;
-    if (oh * ow > 128 || batch < 2) return best;
-    const int slots = num_sms / ctas > 0 ? num_sms / ctas : 1;
-    auto cost_of = [&](int bw, int bh, int bn, long long pixel_tiles) {
+    const int katoms = ctas == 2 ? 2 : 1;
+    auto cost_of = [&](int bw, int bh, int bn, long long pixel_tiles, int ksplit) {
         const int n = bw * bh * bn;
         const double mma_ns = 1.08 * n;
         const double ingest_ns = (UMMA_BM * UMMA_BK * 4 + double(n / ctas) * UMMA_BK * 4) / 114.0;
-        const long long waves = (pixel_tiles * tiles_m + slots - 1) / slots;
-        return double(waves) * (mma_ns > ingest_ns ? mma_ns : ingest_ns);
+        const int slots = num_sms / (ctas * ksplit) > 0 ? num_sms / (ctas * ksplit) : 1;
+        const long long tiles = pixel_tiles * tiles_m;
+        const long long waves = (tiles + slots - 1) / slots;
+        double exchange_ns = 0.0;
+        if (ksplit > 1) {
+            if (waves > 1) return 1e30;
+            exchange_ns = kExchangeNs;
+            for (int k = ksplit; k > 2; k /= 2) exchange_ns += kExchangeDoublingNs;
+        }
+        const int per = (k_blocks + ksplit - 1) / ksplit;
+        return double(waves) * per * (mma_ns > ingest_ns ? mma_ns : ingest_ns) + exchange_ns;
     };
     double best_cost = 1e30;
     if (single.box_w > 0) {
         const long long tiles = static_cast<long long>((ow + single.box_w - 1) / single.box_w) *
                                 ((oh + single.box_h - 1) / single.box_h) * batch;
-        best_cost = cost_of(single.box_w, single.box_h, 1, tiles);
+        best_cost = cost_of(single.box_w, single.box_h, 1, tiles, 1);
     }
+    if (oh * ow > 128 || batch < 2) return best;
     for (int bw = ow; bw <= ow + 7 && bw * s_w <= 256; ++bw)
         for (int bh = oh; bh <= oh + 7 && bh * s_h <= 256; ++bh)
             for (int bn = ctas; bw * bh * bn <= 256; bn += ctas) {
                 if (bn < 2 || (bw * bh * bn) % 32 != 0) continue;
-                const double cost = cost_of(bw, bh, bn, (batch + bn - 1) / bn);
-                if (cost < best_cost * 0.999) {
-                    best_cost = cost;
-                    best.box_w = bw;
-                    best.box_h = bh;
-                    best.box_n = bn;
+                for (int ks = 1; ks <= 4; ks *= 2) {
+                    if (!cluster_split_fits(bw * bh * bn, ctas, ks, k_blocks, katoms, 0)) continue;
+                    const double cost = cost_of(bw, bh, bn, (batch + bn - 1) / bn, ks);
+                    if (cost < best_cost * 0.999) {
+                        best_cost = cost;
+                        best.box_w = bw;
+                        best.box_h = bh;
+                        best.box_n = bn;
+                        best.ksplit = ks;
+                    }
                 }
             }
     return best;
@@ -524,27 +595,57 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     // Consecutive tiles walk the output-channel tiles of one pixel block, so
     // concurrent CTAs read the same input pixels from L2.
     sched.raster_group = sched.tiles_m;
-    const uint32_t staging_bytes = bulk_store ? UMMA_STORE_STAGING_BYTES : 0u;
-    const int fit_stages = int((Cfg::SMEM_BUDGET - staging_bytes) / Cfg::STAGE_BYTES);
+    // Tiles of several whole planes: compacted blocks of 32 channels x one plane, when a block fits
+    // a warp's staging area, planes are dense and 16-byte aligned as blocks, and the plane size is
+    // odd (rows of the block then fall on different shared-memory banks).
+    const int plane = oh * ow, per_plane = plan.box_w * plan.box_h;
+    const bool dense_planes = prob.out_plane == plane && prob.out_off == 0 && prob.out_row == ow && prob.out_col == 1;
+    bool plane_store = MULTI_IMAGE && dense_planes && s.out_c % 32 == 0 && plane % 2 == 1 && plane <= 64 &&
+                       per_plane % 32 == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
+    uint32_t staging_bytes = (bulk_store || plane_store) ? UMMA_STORE_STAGING_BYTES : 0u;
+    const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;
+    CB200_REQUIRE(num_tiles < (1LL << 30), "conv2d: too many tiles");
+    // Split-K inside a cluster (one tile per cluster): see the GEMM launcher for the layout.
+    int ksplit = Prob::kClusterSplit ? plan.ksplit : 1;
+    // (A group's slice of the columns must hold whole planes for the compacted stores; the split
+    // matters more, so they give way.)
+    if (plane_store && ksplit > 1 &&
+        ((umma_n / ksplit) % per_plane != 0 ||
+         !cluster_split_fits(umma_n, CTAS, ksplit, sched.k_blocks, KATOMS, staging_bytes))) {
+        plane_store = false;
+        staging_bytes = 0;
+    }
+    while (ksplit > 1 && !cluster_split_fits(umma_n, CTAS, ksplit, sched.k_blocks, KATOMS, staging_bytes)) ksplit /= 2;
+    sched.plane_store = plane_store ? 1 : 0;
+    uint32_t exchange_bytes = 0;
+    if (ksplit > 1) {
+        int per = (sched.k_blocks + ksplit - 1) / ksplit;
+        per = (per + KATOMS - 1) / KATOMS * KATOMS;
+        sched.cluster_split = ksplit;
+        sched.kb_per_split = per;
+        exchange_bytes = uint32_t(ksplit - 1) * UMMA_BM * uint32_t(umma_n / ksplit) * 4u;
+    }
+    sched.exchange_bytes = exchange_bytes;
+    const int fit_stages = int((Cfg::SMEM_BUDGET - staging_bytes - exchange_bytes) / Cfg::STAGE_BYTES);
     if (sched.stages > fit_stages) sched.stages = fit_stages;
     sched.tma_store = bulk_store ? 1 : 0;
     sched.ring_staging = (bulk_store && uint32_t(sched.stages) * Cfg::STAGE_BYTES >= 131072u) ? 1 : 0;
-    const uint32_t smem_bytes = uint32_t(sched.stages) * Cfg::STAGE_BYTES + staging_bytes + 1024;
+    const uint32_t smem_bytes = uint32_t(sched.stages) * Cfg::STAGE_BYTES + exchange_bytes + staging_bytes + 1024;
 
-    const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;
-    CB200_REQUIRE(num_tiles < (1LL << 30), "conv2d: too many tiles");
     long long groups = dev.num_sms / CTAS;
     if (groups < 1) groups = 1;
     if (groups > num_tiles) groups = num_tiles;
+    if (ksplit > 1) groups = num_tiles;          // clusters: one per tile
 
     CB200_TRACE("conv2d implicit GEMM tcgen05: N=%d C=%d %dx%d -> OC=%d %dx%d, %dx%d stride %dx%d pad %dx%d; pixel box "
-                "%d x %d x %d images = %d columns, ctas/mma=%d katoms=%d stages=%d clusters=%lld, K blocks=%d, store=%s",
+                "%d x %d x %d images = %d columns, ctas/mma=%d katoms=%d stages=%d clusters=%lld, K blocks=%d, "
+                "cluster_split=%d, store=%s",
                 s.batch, s.in_c, s.in_h, s.in_w, s.out_c, oh, ow, s.k_h, s.k_w, s.s_h, s.s_w, s.p_h, s.p_w, plan.box_w,
-                plan.box_h, plan.box_n, umma_n, CTAS, KATOMS, sched.stages, groups, sched.k_blocks,
-                bulk_store ? "bulk-tensor" : "registers");
+                plan.box_h, plan.box_n, umma_n, CTAS, KATOMS, sched.stages, groups, sched.k_blocks, ksplit,
+                bulk_store ? "bulk-tensor" : plane_store ? "bulk planes" : "registers");
     auto kernel = umma_tf32_kernel<CTAS, 256, false, KATOMS, Prob>;
     UmmaEpilogueArgs epi{bias, 1, act};
-    launch_umma(kernel, prob, sched, epi, groups, CTAS, smem_bytes, Cfg::SMEM_MAX, stream);
+    launch_umma(kernel, prob, sched, epi, groups, CTAS * ksplit, smem_bytes, Cfg::SMEM_MAX, stream);
 }
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
@@ -660,7 +761,7 @@ void plan_and_launch(const float* xt, const float* wp, const float* bias, float*
     // stage and the barrier handshake is paid half as often.
     if (!row_packed)
         plan = plan_multi_image_tile(oh, ow, s.batch, ctas, s.s_h, s.s_w, (s.out_c + UMMA_BM * ctas - 1) / (UMMA_BM * ctas),
-                                     device_info().num_sms, plan);
+                                     device_info().num_sms, s.k_h * s.k_w * (cp / UMMA_BK), plan);
     CB200_REQUIRE(plan.box_w > 0, "conv2d: no tile shape fits this output size");
     if (row_packed) {
         if (ctas == 2) launch_conv<2, 2, true, false>(xt, wp, bias, output, s, cx, cp, plan, act, stream, extras);
@@ -834,7 +935,7 @@ size_t round_1k(size_t v) { return (v + 1023) / 1024 * 1024; }
 // store when rows are 16-byte multiples).
 struct WeaveArgs {
     int c, h, w, s_h, s_w, p_h, p_w, rows, pitch;
-    signed char lo_h[8], lo_w[8];
+    PackedInts8 lo_h, lo_w;
 };
 
 // SH, SW: the strides as compile-time constants (0: read them from the arguments), so that the
@@ -940,8 +1041,10 @@ void conv2d_grad_input_by_parity(const float* grad_output, const float* weight, 
         filters.pad_w = p.w.pad;
         WeaveArgs args{s.in_c, s.in_h, s.in_w, s.s_h, s.s_w, s.p_h, s.p_w, p.h.extent, p.cols_padded, {}, {}};
         for (int a = 0; a < 8; ++a) {
-            filters.lo_h[a] = args.lo_h[a] = static_cast<signed char>(a < s.s_h ? p.h.lo[a] : 0);
-            filters.lo_w[a] = args.lo_w[a] = static_cast<signed char>(a < s.s_w ? p.w.lo[a] : 0);
+            filters.lo_h.set(a, a < s.s_h ? p.h.lo[a] : 0);
+            filters.lo_w.set(a, a < s.s_w ? p.w.lo[a] : 0);
+            args.lo_h = filters.lo_h;
+            args.lo_w = filters.lo_w;
         }
         prepare_operands(grad_output, xt, s.batch, s.out_c, oh * ow, cx, &filters, stream);
         ConvExtras extras;

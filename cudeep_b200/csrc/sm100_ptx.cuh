@@ -197,6 +197,15 @@ template <int N>
 __device__ __forceinline__ void bulk_wait_group() {
     asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
+// Untiled bulk copy shared -> global of `bytes` contiguous bytes (a multiple of 16; both addresses
+// 16-byte aligned); completion is tracked by bulk groups like the tensor stores.
+__device__ __forceinline__ void bulk_store_1d(void* dst, uint32_t src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 : : "l"(reinterpret_cast<uint64_t>(dst)), "r"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void st_shared_f32(uint32_t addr, float x) {
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(x) : "memory");
+}
 // 16-byte store through a multicast address: the switch writes it into every GPU's copy.
 __device__ __forceinline__ void multimem_st_v4(float* mc_addr, float4 v) {
     asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(v.x), "f"(v.y),

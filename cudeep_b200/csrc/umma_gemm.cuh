@@ -77,6 +77,7 @@ struct UmmaSchedule {
     // buffer, and write it with one bulk tensor store: 8 KB (two blocks) per epilogue warp.
     int tma_store;
     int ring_staging;      // the stages in use span at least 128 KB: the last tile's epilogue may stage in them
+    int plane_store;       // Problem::kPlaneStore and the launch qualifies: see has_plane_store
     // Diagnostics for performance bring-up (results are then meaningless):
     //   bit 0: after the ring has been filled once the producer stops loading and only
     //          signals the stages, so the MMA side runs without memory traffic;
@@ -182,6 +183,22 @@ template <class P, class = void>
 struct has_multimem_store { static constexpr bool value = false; };
 template <class P>
 struct has_multimem_store<P, decltype((void)P::kMultimemStore)> { static constexpr bool value = P::kMultimemStore; };
+
+// A third optional form, for tiles whose columns are several whole small output planes (a
+// convolution over 7 x 7 maps): the accumulator columns of one plane, with the padding columns of
+// its pixel box dropped, form a run of contiguous floats per row, and 32 consecutive rows form one
+// contiguous block of the output.  So a warp compacts its 32 rows of one plane into its staging
+// block and writes them with a single untiled bulk copy.
+//   static constexpr bool kPlaneStore = true;
+//   __device__ int plane_columns() const;           accumulator columns per plane (a multiple of 32)
+//   __device__ uint32_t plane_bytes() const;        bytes of 32 rows of one compacted plane (<= 8192)
+//   __device__ void plane_stage(uint32_t staging, uint32_t lane, int col_in_plane, const float (&v)[32]) const;
+//   __device__ float* plane_dst(tile, int row0, int plane) const;    nullptr: nothing to write
+// UmmaSchedule::plane_store switches it on for a launch (the staging blocks must then exist).
+template <class P, class = void>
+struct has_plane_store { static constexpr bool value = false; };
+template <class P>
+struct has_plane_store<P, decltype((void)P::kPlaneStore)> { static constexpr bool value = P::kPlaneStore; };
 
 template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, class Problem, bool A_MN_MAJOR = false,
           int KIND = UMMA_KIND_TF32>
@@ -474,6 +491,29 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                             ptx::tma_store_2d(prob.out_map(), block, x, y);
                             push_to_peers(prob, block, x, y);
                             ptx::bulk_commit_group();
+                        }
+                        return;
+                    }
+                }
+                if constexpr (has_plane_store<Problem>::value) {
+                    if (sched.plane_store != 0) {
+                        prob.finish(tile, row_in_cta, c, v, epi);
+                        const int per_plane = prob.plane_columns();
+                        const int plane = c / per_plane;
+                        const int in_plane = c - plane * per_plane;
+                        if (in_plane == 0) {      // the copy of the previous plane must have read the block
+                            if (lane == 0) ptx::bulk_wait_group_read<0>();
+                            __syncwarp();
+                        }
+                        prob.plane_stage(staging, lane, in_plane, v);
+                        if (in_plane + 32 == per_plane) {
+                            ptx::fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                float* dst = prob.plane_dst(tile, int(quarter) * 32, plane);
+                                if (dst != nullptr) ptx::bulk_store_1d(dst, staging, prob.plane_bytes());
+                                ptx::bulk_commit_group();
+                            }
                         }
                         return;
                     }

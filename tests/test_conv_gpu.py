@@ -90,6 +90,10 @@ def test_direct_path_shapes(dev, oracle, shape, oc, k, stride, padding):
     ((7, 40, 9, 9), 64, (3, 3), (0, 0)),         # 7 x 7 outputs without padding
     ((2, 32, 12, 16), 160, (3, 3), (1, 1)),      # bulk-store tiles whose rows past OC = 160 must not reach image 1
     ((3, 32, 10, 8), 96, (3, 3), (1, 1)),        # bulk-store tiles taller than the image (rows past OH clipped)
+    ((6, 256, 7, 7), 512, (3, 3), (1, 1)),       # few tiles, 72 K blocks: the reduction split four ways in a cluster of 8
+    ((32, 192, 7, 7), 512, (3, 3), (1, 1)),      # 16 tiles of four images, 54 K blocks split two ways (clusters of 4)
+    ((7, 160, 7, 7), 96, (3, 3), (1, 1)),        # one CTA per tile, split reduction, last tile partly empty
+    ((16, 288, 4, 4), 128, (3, 3), (1, 1)),      # 4 x 4 maps (an even plane size: stored from registers), split reduction
 ])
 @pytest.mark.parametrize("act", [0, 1])
 def test_tensor_core_path_shapes(dev, oracle, shape, oc, k, padding, act):
