@@ -66,7 +66,63 @@ struct FilterPack {
     PackedInts8 lo_h, lo_w;
 };
 
-__device__ __forceinline__ void pack_filters(const FilterPack& f, long long block, long long blocks, int threads) {
+// `tile`: 32 x 65 floats of shared memory, or nullptr.  With it the plain and the flipped form go
+// through shared memory so that both the reads and the writes are runs of consecutive floats (the
+// direct loop below reads one float per KH * KW of them, or per C * KH * KW when flipped).
+__device__ __forceinline__ void pack_filters(const FilterPack& f, long long block, long long blocks, int threads,
+                                             float* tile = nullptr) {
+    const int taps_all = f.k_h * f.k_w;
+    if (tile != nullptr && f.row_cx == 0 && f.sub_sh == 0 && f.flipped) {
+        // Source [C][OC * taps]: 32 channels x 64 consecutive (oc, tap) entries per unit.
+        const long long entries = static_cast<long long>(f.oc_n) * taps_all;
+        const long long e_chunks = (entries + 63) / 64;
+        const long long units = e_chunks * (f.cp / 32);
+        for (long long u = block; u < units; u += blocks) {
+            const int c0 = static_cast<int>(u / e_chunks) * 32;
+            const long long e0 = (u % e_chunks) * 64;
+            for (int i = threadIdx.x; i < 32 * 64; i += threads) {
+                const int r = i >> 6, j = i & 63;
+                const int ch = c0 + r;
+                const long long e = e0 + j;
+                tile[r * 65 + j] = (ch < f.c && e < entries) ? f.w[ch * entries + e] : 0.0f;
+            }
+            __syncthreads();
+            for (int i = threadIdx.x; i < 32 * 64; i += threads) {
+                const int j = i >> 5, r = i & 31;
+                const long long e = e0 + j;
+                if (e < entries) {
+                    const long long oc = e / taps_all;
+                    const int tap = static_cast<int>(e - oc * taps_all);
+                    f.wp[(oc * taps_all + (taps_all - 1 - tap)) * f.cp + c0 + r] = tile[r * 65 + j];
+                }
+            }
+            __syncthreads();
+        }
+        return;
+    }
+    if (tile != nullptr && f.row_cx == 0 && f.sub_sh == 0 && !f.flipped && taps_all <= 65) {
+        // Source [OC][C * taps]: one output channel x `chunk` channels (all their taps) per unit.
+        int chunk = (32 * 65 / taps_all) / 32 * 32;
+        if (chunk > f.cp) chunk = f.cp;
+        const int chunks = (f.cp + chunk - 1) / chunk;
+        const long long units = static_cast<long long>(f.oc_n) * chunks;
+        for (long long u = block; u < units; u += blocks) {
+            const long long oc = u / chunks;
+            const int c0 = static_cast<int>(u - oc * chunks) * chunk;
+            const int real = min(chunk, f.c - c0);                     // channels that exist in w
+            const float* src = f.w + (oc * f.c + c0) * taps_all;
+            for (int i = threadIdx.x; i < real * taps_all; i += threads) tile[i] = src[i];
+            __syncthreads();
+            const int width = min(chunk, f.cp - c0);                   // channels written (zeros past C)
+            float* dst = f.wp + oc * taps_all * f.cp + c0;
+            for (int i = threadIdx.x; i < width * taps_all; i += threads) {
+                const int tap = i / width, cc = i - tap * width;
+                dst[static_cast<long long>(tap) * f.cp + cc] = cc < real ? tile[cc * taps_all + tap] : 0.0f;
+            }
+            __syncthreads();
+        }
+        return;
+    }
     if (f.row_cx > 0) {
         const long long total = static_cast<long long>(f.oc_n) * f.k_h * UMMA_BK;
         for (long long i = block * threads + threadIdx.x; i < total; i += blocks * threads) {
@@ -132,7 +188,7 @@ nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, 
     if (with_filters && int(blockIdx.z) >= batch) {
         const long long per_slice = static_cast<long long>(gridDim.x) * gridDim.y;
         pack_filters(filters, (int(blockIdx.z) - batch) * per_slice + blockIdx.y * gridDim.x + blockIdx.x,
-                     per_slice * (int(gridDim.z) - batch), 256);
+                     per_slice * (int(gridDim.z) - batch), 256, &tile[0][0]);
         return;
     }
     const int n = blockIdx.z;

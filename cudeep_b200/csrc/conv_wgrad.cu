@@ -131,10 +131,52 @@ __global__ void pad_rows_kernel(const float* __restrict__ src, float* __restrict
 }
 
 // dw[oc][c][tap] = sum over ranges of part[range][oc][tap * cp + c], ranges in ascending order.
-// Threads walk (oc, tap, c) with c fastest, so the reads of the partial tiles (ranges times the
-// size of dw) coalesce; the writes are strided by the tap count.
-__global__ void wgrad_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, int ranges, int oc_n,
-                                    int ocp, int c_n, int cp, int taps) {
+// A block takes one output channel and a chunk of channels with all their taps: it reads the
+// partial tiles along c, 128 bits per thread and range (few values per thread, so the bytes in
+// flight are what sets the speed), keeps the sums in shared memory as [tap][chunk + 4] and writes
+// its part of dw, which is one run of consecutive floats.
+constexpr int kReduceTile = 3072;
+__global__ void __launch_bounds__(256)
+wgrad_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, int ranges, int oc_n, int ocp,
+                    int c_n, int cp, int taps, int chunk) {
+    __shared__ __align__(16) float tile[kReduceTile];
+    const int chunks = (c_n + chunk - 1) / chunk;
+    const long long units = static_cast<long long>(oc_n) * chunks;
+    const long long row_len = static_cast<long long>(taps) * cp;
+    const long long range_stride = static_cast<long long>(ocp) * row_len;
+    const int pitch = chunk + 4;
+    for (long long u = blockIdx.x; u < units; u += gridDim.x) {
+        const long long oc = u / chunks;
+        const int c0 = static_cast<int>(u - oc * chunks) * chunk;
+        const int width = min(chunk, c_n - c0);
+        const int quads = (width + 3) / 4;          // columns up to cp exist in the partial tiles (zeros past C)
+        const float* src = part + oc * row_len + c0;
+        for (int i = threadIdx.x; i < quads * taps; i += blockDim.x) {
+            const int tap = i / quads, q4 = i - tap * quads;
+            const float4* q = reinterpret_cast<const float4*>(src + static_cast<long long>(tap) * cp) + q4;
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 4
+            for (int s = 0; s < ranges; ++s) {
+                const float4 v = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(q) + s * range_stride));
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            *reinterpret_cast<float4*>(&tile[tap * pitch + 4 * q4]) = acc;
+        }
+        __syncthreads();
+        float* dst = dw + (oc * c_n + c0) * taps;
+        for (int i = threadIdx.x; i < width * taps; i += blockDim.x) {
+            const int cc = i / taps, tap = i - cc * taps;
+            dst[i] = tile[tap * pitch + cc];
+        }
+        __syncthreads();
+    }
+}
+
+// The same sum for filters with more than 65 taps (a chunk of 32 channels would not fit the tile):
+// threads walk (oc, tap, c) with c fastest, so the reads coalesce; the writes are strided by the
+// tap count.
+__global__ void wgrad_reduce_wide_kernel(const float* __restrict__ part, float* __restrict__ dw, int ranges,
+                                         int oc_n, int ocp, int c_n, int cp, int taps) {
     const long long total = static_cast<long long>(oc_n) * taps * c_n;
     const long long row_len = static_cast<long long>(taps) * cp;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
@@ -384,8 +426,19 @@ void conv2d_wgrad_igemm(const float* grad_output, const float* input, float* gra
             nchw_to_nhwc(input, xt, s.batch, s.in_c, s.in_h * s.in_w, p.cp, stream);
             if (p.ctas == 2) launch_wgrad<2, 2>(dy, copy_dy ? dy_pitch : ow, xt, part, s, p, stream);
             else launch_wgrad<1, 1>(dy, copy_dy ? dy_pitch : ow, xt, part, s, p, stream);
-            wgrad_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-                part, grad_weight, p.ranges, s.out_c, p.ocp, s.in_c, p.cp, s.k_h * s.k_w);
+            const int taps = s.k_h * s.k_w;
+            if (taps <= 65) {
+                // Channels per block: as many 32-channel groups as fit the tile (all of them for 1 x 1).
+                int chunk = (kReduceTile / taps - 4) / 32 * 32;
+                if (chunk > p.cp) chunk = p.cp;
+                long long units = static_cast<long long>(s.out_c) * ((s.in_c + chunk - 1) / chunk);
+                if (units > 148 * 16) units = 148 * 16;
+                wgrad_reduce_kernel<<<static_cast<unsigned>(units), 256, 0, stream>>>(
+                    part, grad_weight, p.ranges, s.out_c, p.ocp, s.in_c, p.cp, taps, chunk);
+            } else {
+                wgrad_reduce_wide_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+                    part, grad_weight, p.ranges, s.out_c, p.ocp, s.in_c, p.cp, taps);
+            }
         }
         CB200_CHECK_LAUNCH();
     } catch (...) {
