@@ -449,18 +449,23 @@ def run_ours(args):
     flops_step = 2.0 * SIZE ** 3 * world
     value = flops_step * args.steps / seconds / 1e12
 
-    # end to end: pinned host buffers in, pinned host buffer out, through the host entry point
-    ha = torch.from_numpy(a_np).pin_memory()
-    hb = torch.from_numpy(b_np).pin_memory()
-    hc = torch.empty((SIZE, SIZE), dtype=torch.float32).pin_memory()
-    pha, phb, phc = (ctypes.c_void_p(t.data_ptr()) for t in (ha, hb, hc))
+    # end to end: pinned host buffers in, pinned host buffer out, through the host entry point.
+    # The buffers are allocated (and the copies enqueued) from a thread that runs on the GPU's NUMA
+    # node, so their pages sit on the socket the GPU's host link hangs off (a thread's CPU affinity,
+    # restored afterwards; nothing about the GPU changes).
+    from cudeep_b200 import hostmem
+    with hostmem.near_gpu(local) as placement:
+        ha = torch.from_numpy(a_np).pin_memory()
+        hb = torch.from_numpy(b_np).pin_memory()
+        hc = torch.empty((SIZE, SIZE), dtype=torch.float32).pin_memory()
+        pha, phb, phc = (ctypes.c_void_p(t.data_ptr()) for t in (ha, hb, hc))
 
-    def e2e_step():
-        rc = lib.cudeep_b200_matmul_host_f32(pha, phb, phc, SIZE, SIZE, SIZE, 0)
-        if rc != 0:
-            raise RuntimeError(lib.cudeep_b200_last_error().decode())
+        def e2e_step():
+            rc = lib.cudeep_b200_matmul_host_f32(pha, phb, phc, SIZE, SIZE, SIZE, 0)
+            if rc != 0:
+                raise RuntimeError(lib.cudeep_b200_last_error().decode())
 
-    e2e_seconds = max_over_ranks(dist, time_e2e_steps(e2e_step, args.e2e_steps, dist))
+        e2e_seconds = max_over_ranks(dist, time_e2e_steps(e2e_step, args.e2e_steps, dist))
     e2e_value = flops_step * args.e2e_steps / e2e_seconds / 1e12
     checksum = float(hc[0, :8].sum())      # the step's result is read on the host
 
@@ -501,6 +506,8 @@ def run_ours(args):
         "pct_of_nominal_tf32_peak": 100.0 * value / world / NOMINAL_TF32_TFLOPS,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * SIZE * SIZE * 4 * world,
                 "d2h_bytes_per_step": SIZE * SIZE * 4 * world, "steps": args.e2e_steps,
+                "host_placement": {"numa_node": placement["numa_node"], "bound": placement["bound"],
+                                   "cpus": placement["cpus"]},
                 "result_probe": checksum},
         "value_burst": burst, "value_sustained": sustained,
         "burst_sustained_note": "same launch over a 20-step region and a 200-step region; `value` is the one with --steps",
