@@ -493,7 +493,7 @@ constexpr double kExchangeNs = 3500.0, kExchangeDoublingNs = 750.0;
 
 // Whether `ksplit` groups of `ctas` CTAs can share a tile of n accumulator columns: a portable
 // cluster, whole 32-column chunks per group, and room for the exchange buffer beside two stages.
-bool cluster_split_fits(int n, int ctas, int ksplit, int k_blocks, int katoms, uint32_t staging_bytes) {
+bool cluster_split_fits(int n, int ctas, int ksplit, int k_blocks, int katoms) {
     if (ksplit == 1) return true;
     if (ctas * ksplit > 8 || n % (32 * ksplit) != 0) return false;
     int per = (k_blocks + ksplit - 1) / ksplit;
@@ -501,7 +501,8 @@ bool cluster_split_fits(int n, int ctas, int ksplit, int k_blocks, int katoms, u
     if (per < 2 * katoms || (k_blocks + per - 1) / per != ksplit) return false;
     const uint32_t stage = uint32_t(katoms) * (UMMA_BM * UMMA_BK * 4 + uint32_t(n / ctas) * UMMA_BK * 4);
     const uint32_t exchange = uint32_t(ksplit - 1) * UMMA_BM * uint32_t(n / ksplit) * 4u;
-    return exchange + staging_bytes + 2 * stage <= 232448u - 1536u;     // the kernels' shared-memory budget
+    // (A split tile stages its stores in the idle stage ring, which two stages always cover.)
+    return exchange + 2 * stage <= 232448u - 1536u;     // the kernels' shared-memory budget
 }
 
 TilePlan plan_multi_image_tile(int oh, int ow, int batch, int ctas, int s_h, int s_w, int tiles_m, int num_sms,
@@ -536,7 +537,7 @@ TilePlan plan_multi_image_tile(int oh, int ow, int batch, int ctas, int s_h, int
             for (int bn = ctas; bw * bh * bn <= 256; bn += ctas) {
                 if (bn < 2 || (bw * bh * bn) % 32 != 0) continue;
                 for (int ks = 1; ks <= 4; ks *= 2) {
-                    if (!cluster_split_fits(bw * bh * bn, ctas, ks, k_blocks, katoms, 0)) continue;
+                    if (!cluster_split_fits(bw * bh * bn, ctas, ks, k_blocks, katoms)) continue;
                     const double cost = cost_of(bw, bh, bn, (batch + bn - 1) / bn, ks);
                     if (cost < best_cost * 0.999) {
                         best_cost = cost;
@@ -665,13 +666,9 @@ void launch_conv(const float* xt, const float* wp, const float* bias, float* out
     int ksplit = Prob::kClusterSplit ? plan.ksplit : 1;
     // (A group's slice of the columns must hold whole planes for the compacted stores; the split
     // matters more, so they give way.)
-    if (plane_store && ksplit > 1 &&
-        ((umma_n / ksplit) % per_plane != 0 ||
-         !cluster_split_fits(umma_n, CTAS, ksplit, sched.k_blocks, KATOMS, staging_bytes))) {
-        plane_store = false;
-        staging_bytes = 0;
-    }
-    while (ksplit > 1 && !cluster_split_fits(umma_n, CTAS, ksplit, sched.k_blocks, KATOMS, staging_bytes)) ksplit /= 2;
+    while (ksplit > 1 && !cluster_split_fits(umma_n, CTAS, ksplit, sched.k_blocks, KATOMS)) ksplit /= 2;
+    if (plane_store && ksplit > 1 && (umma_n / ksplit) % per_plane != 0) plane_store = false;
+    if (ksplit > 1 || !(bulk_store || plane_store)) staging_bytes = 0;       // split tiles stage in the idle ring
     sched.plane_store = plane_store ? 1 : 0;
     uint32_t exchange_bytes = 0;
     if (ksplit > 1) {

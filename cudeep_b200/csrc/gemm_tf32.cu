@@ -269,7 +269,7 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     sched.tma_store = tma_store ? 1 : 0;
     sched.debug = tune.debug;
     if (tune.wait_limit_ms > 0) sched.wait_limit_ns = static_cast<unsigned long long>(tune.wait_limit_ms) * 1000000ull;
-    const uint32_t staging_bytes = tma_store ? UMMA_STORE_STAGING_BYTES : 0u;
+    const uint32_t whole_tile_staging = tma_store ? UMMA_STORE_STAGING_BYTES : 0u;
 
     const int num_tiles = sched.tiles_m * sched.tiles_n;
     int max_ctas = tune.max_ctas > 0 ? tune.max_ctas : dev.num_sms;
@@ -316,7 +316,8 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
         per = (sched.k_blocks + ksplit - 1) / ksplit;
         per = (per + KATOMS - 1) / KATOMS * KATOMS;
         exchange_bytes = uint32_t(ksplit - 1) * UMMA_BM * (BN / ksplit) * 4u;
-        const bool fits = exchange_bytes + staging_bytes + 2 * Cfg::STAGE_BYTES <= Cfg::SMEM_BUDGET;
+        // (A split tile stages its stores in the idle stage ring: no staging area of its own.)
+        const bool fits = exchange_bytes + 2 * Cfg::STAGE_BYTES <= Cfg::SMEM_BUDGET;
         if (CTAS * ksplit <= 8 && BN % (32 * ksplit) == 0 && (sched.k_blocks + per - 1) / per == ksplit && fits)
             break;
         ksplit /= 2;
@@ -331,6 +332,7 @@ void launch_variant(const float* a, const float* b, float* c, int m, int n, int 
     }
     sched.exchange_bytes = exchange_bytes;
     // Dynamic shared memory: [stages][exchange buffer][store staging], after up to 1 KB of alignment.
+    const uint32_t staging_bytes = ksplit > 1 ? 0u : whole_tile_staging;
     const int fit_stages = int((Cfg::SMEM_BUDGET - exchange_bytes - staging_bytes) / Cfg::STAGE_BYTES);
     if (sched.stages > fit_stages) sched.stages = fit_stages;
     const bool ring_wanted = kRingStagingDefault != (tune.ring_staging < 0);      // the tuning flag flips the default
@@ -376,7 +378,8 @@ struct TilePick { int ctas, bn, cluster_split, katoms; };
 inline int stages_for(int ctas, int bn, int katoms, int cluster_split) {
     const int stage = katoms * (int(UMMA_BM) * UMMA_BK * 4 + bn / ctas * UMMA_BK * 4);
     const int exchange = cluster_split > 1 ? (cluster_split - 1) * UMMA_BM * (bn / cluster_split) * 4 : 0;
-    const int budget = 232448 - 1024 - 512 - exchange - int(UMMA_STORE_STAGING_BYTES);
+    const int staging = cluster_split > 1 ? 0 : int(UMMA_STORE_STAGING_BYTES);      // split tiles stage in the ring
+    const int budget = 232448 - 1024 - 512 - exchange - staging;
     const int stages = budget / stage;
     return stages > 8 ? 8 : stages;
 }

@@ -464,8 +464,12 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
             // bulk tensor store where the problem has an output map, else straight from registers.
             bool use_tma = false;
             if constexpr (Problem::kTmaStore) use_tma = sched.tma_store != 0 && w.mode == 0;
-            const uint32_t staging = smem_base + uint32_t(sched.stages) * Cfg::STAGE_BYTES + sched.exchange_bytes +
-                                     quarter * 8192u;
+            // A tile split over a cluster is its CTA's only tile: when its epilogue starts the stage
+            // ring is idle (every load was consumed by an MMA that has completed), so the staging
+            // blocks lie at its start and no shared memory is set aside for them.
+            const uint32_t staging = ksplit > 1 ? smem_base + quarter * 8192u
+                                                : smem_base + uint32_t(sched.stages) * Cfg::STAGE_BYTES +
+                                                      sched.exchange_bytes + quarter * 8192u;
             auto emit = [&](int c, const uint32_t (&r)[32]) {
                 float v[32];
 #pragma unroll
@@ -530,20 +534,38 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 const int slice = sched.umma_n / int(ksplit);          // columns this group reduces
                 const int slice_chunks = slice / 32;
                 const uint32_t row_off = uint32_t(row_in_cta) * 16u;
-#pragma unroll 1
-                for (int c = 0; c < n_cols; c += 32) {
+                // Both loops keep the accumulator load of the next chunk in flight while the current
+                // chunk is stored or reduced (two register sets, bodies unrolled twice).
+                auto next_foreign = [&](int c) { return (c < n_cols && uint32_t(c / slice) == kgroup) ? c + slice : c; };
+                auto send = [&](int c, const uint32_t (&r)[32]) {
                     const uint32_t owner = uint32_t(c / slice);
-                    if (owner == kgroup) continue;
-                    ptx::tmem_ld_32x32(t_row + c, r0);
-                    ptx::tmem_ld_wait();
                     const uint32_t slot = kgroup > owner ? kgroup - 1 : kgroup;
                     const uint32_t chunk = slot * slice_chunks + uint32_t(c - int(owner) * slice) / 32u;
                     const uint32_t dst = ptx::mapa(xbuf + chunk * (UMMA_BM * 128u) + row_off, owner * CTAS + cta_rank);
 #pragma unroll
                     for (uint32_t q = 0; q < 8; ++q)
-                        ptx::st_cluster_v4(dst + q * (UMMA_BM * 16u), r0[4 * q], r0[4 * q + 1], r0[4 * q + 2],
-                                           r0[4 * q + 3]);
+                        ptx::st_cluster_v4(dst + q * (UMMA_BM * 16u), r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                };
+                {
+                    int c = next_foreign(0);
+                    if (c < n_cols) ptx::tmem_ld_32x32(t_row + c, r0);
+#pragma unroll 1
+                    while (c < n_cols) {
+                        ptx::tmem_ld_wait();
+                        const int c1 = next_foreign(c + 32);
+                        if (c1 < n_cols) ptx::tmem_ld_32x32(t_row + c1, r1);
+                        send(c, r0);
+                        if (c1 >= n_cols) break;
+                        ptx::tmem_ld_wait();
+                        c = next_foreign(c1 + 32);
+                        if (c < n_cols) ptx::tmem_ld_32x32(t_row + c, r0);
+                        send(c1, r1);
+                    }
                 }
+                // This group's own slice does not depend on the others: its first chunk is on its way
+                // out of TMEM while the partial sums cross the cluster.
+                const int own0 = int(kgroup) * slice;
+                if (n_cols > 0) ptx::tmem_ld_32x32(t_row + own0, r0);
                 // One lane signals for the warp: the warp barrier orders every lane's stores before
                 // lane 0's release, which is cumulative, so the owner's acquire sees all of them.
                 // (128 arrivals per peer barrier, one per thread, took longer than the stores.)
@@ -555,24 +577,31 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 }
                 ok = ptx::mbar_wait<true>(ptx::smem_u32(&bar_exchange), 0, wctx, UMMA_TIMEOUT_EXCHANGE);
                 ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-#pragma unroll 1
-                for (int cc = 0; cc < slice_chunks && n_cols > 0; ++cc) {
-                    const int c = int(kgroup) * slice + cc * 32;
-                    ptx::tmem_ld_32x32(t_row + c, r0);
-                    ptx::tmem_ld_wait();
+                if (!ok) { ptx::tmem_ld_wait(); break; }
+                auto reduce = [&](int cc, uint32_t (&r)[32]) {
                     for (uint32_t slot = 0; slot + 1 < ksplit; ++slot) {      // fixed order: reproducible
                         const uint32_t src = xbuf + (slot * slice_chunks + cc) * (UMMA_BM * 128u) + row_off;
 #pragma unroll
                         for (uint32_t q = 0; q < 8; ++q) {
                             const float4 p = ptx::ld_shared_v4(src + q * (UMMA_BM * 16u));
-                            r0[4 * q] = __float_as_uint(__uint_as_float(r0[4 * q]) + p.x);
-                            r0[4 * q + 1] = __float_as_uint(__uint_as_float(r0[4 * q + 1]) + p.y);
-                            r0[4 * q + 2] = __float_as_uint(__uint_as_float(r0[4 * q + 2]) + p.z);
-                            r0[4 * q + 3] = __float_as_uint(__uint_as_float(r0[4 * q + 3]) + p.w);
+                            r[4 * q] = __float_as_uint(__uint_as_float(r[4 * q]) + p.x);
+                            r[4 * q + 1] = __float_as_uint(__uint_as_float(r[4 * q + 1]) + p.y);
+                            r[4 * q + 2] = __float_as_uint(__uint_as_float(r[4 * q + 2]) + p.z);
+                            r[4 * q + 3] = __float_as_uint(__uint_as_float(r[4 * q + 3]) + p.w);
                         }
                     }
-                    emit(c, r0);
+                    emit(own0 + cc * 32, r);
+                };
+                if (n_cols == 0) ptx::tmem_ld_wait();
+#pragma unroll 1
+                for (int cc = 0; cc < slice_chunks && n_cols > 0; cc += 2) {
+                    ptx::tmem_ld_wait();
+                    if (cc + 1 < slice_chunks) ptx::tmem_ld_32x32(t_row + own0 + (cc + 1) * 32, r1);
+                    reduce(cc, r0);
+                    if (cc + 1 >= slice_chunks) break;
+                    ptx::tmem_ld_wait();
+                    if (cc + 2 < slice_chunks) ptx::tmem_ld_32x32(t_row + own0 + (cc + 2) * 32, r0);
+                    reduce(cc + 1, r1);
                 }
             }
             if (ksplit == 1 && use_tma) {
