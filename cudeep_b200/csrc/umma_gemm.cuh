@@ -590,6 +590,24 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                             r[4 * q + 3] = __float_as_uint(__uint_as_float(r[4 * q + 3]) + p.w);
                         }
                     }
+                    // With an output map every chunk of the slice gets a block of its own in the
+                    // idle stage ring, and one proxy fence and one group of bulk stores follow the
+                    // loop: a fence-and-store round costs about as much for four blocks as for one.
+                    if constexpr (Problem::kTmaStore) {
+                        if (use_tma) {
+                            float v[32];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                            prob.finish(tile, row_in_cta, own0 + cc * 32, v, epi);
+                            const uint32_t row_smem =
+                                smem_base + (quarter * uint32_t(slice_chunks) + uint32_t(cc)) * 4096u + lane * 128u;
+#pragma unroll
+                            for (uint32_t q = 0; q < 8; ++q)
+                                ptx::st_shared_v4(row_smem + ((q ^ (lane & 7u)) << 4), v[4 * q], v[4 * q + 1],
+                                                  v[4 * q + 2], v[4 * q + 3]);
+                            return;
+                        }
+                    }
                     emit(own0 + cc * 32, r);
                 };
                 if (n_cols == 0) ptx::tmem_ld_wait();
@@ -602,6 +620,21 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                     ptx::tmem_ld_wait();
                     if (cc + 2 < slice_chunks) ptx::tmem_ld_32x32(t_row + own0 + (cc + 2) * 32, r0);
                     reduce(cc + 1, r1);
+                }
+                if constexpr (Problem::kTmaStore) {
+                    if (use_tma && n_cols > 0) {
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            for (int cc = 0; cc < slice_chunks; ++cc) {
+                                int x, y;
+                                prob.out_coords(tile, int(quarter) * 32, own0 + cc * 32, x, y);
+                                ptx::tma_store_2d(prob.out_map(),
+                                                  smem_base + (quarter * uint32_t(slice_chunks) + uint32_t(cc)) * 4096u, x, y);
+                            }
+                            ptx::bulk_commit_group();
+                        }
+                    }
                 }
             }
             if (ksplit == 1 && use_tma) {
@@ -716,7 +749,11 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
         while (ptx::globaltimer_ns() - t0 < 2000000ull) { }
         __syncthreads();
     }
-    if (clustered) {             // no CTA leaves while a peer may still write to or signal it
+    // No CTA of a pair leaves (or frees the pair's TMEM) while its partner may still signal it or
+    // read accumulators.  Lone CTAs that only shared a split reduction need no such barrier: each
+    // one waited, on its exchange barrier, for everything any other CTA sends it, and the last
+    // thing it sent - its arrivals on the others' exchange barriers - is what they wait for.
+    if (CTAS == 2) {
         ptx::cluster_arrive();
         ptx::cluster_wait();
     }
