@@ -73,6 +73,16 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t x,
                  "r"(z), "r"(w)
                  : "memory");
 }
+// The same store, asynchronous: when its 16 bytes have landed in the other CTA's shared memory
+// they are counted on that CTA's mbarrier (complete_tx), so the receiver learns of data and
+// completion at once and the sender neither fences nor signals.  Both addresses come from mapa
+// and name the same CTA.
+__device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w,
+                                            uint32_t cluster_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(cluster_addr), "r"(x), "r"(y), "r"(z), "r"(w), "r"(cluster_bar)
+                 : "memory");
+}
 __device__ __forceinline__ float4 ld_shared_v4(uint32_t addr) {
     float4 v;
     asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"

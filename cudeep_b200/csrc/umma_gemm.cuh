@@ -244,9 +244,13 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
             ptx::mbar_init(ptx::smem_u32(&bar_acc_full[a]), 1);
             ptx::mbar_init(ptx::smem_u32(&bar_acc_empty[a]), 4 * CTAS);
         }
-        // One arrival per epilogue warp of every other K range.
-        ptx::mbar_init(ptx::smem_u32(&bar_exchange), ksplit > 1 ? (ksplit - 1) * 4 : 1);
+        // The exchange of a split tile: the other K ranges' partial sums arrive as asynchronous
+        // stores that count their bytes on this barrier, (ksplit - 1) slices of 128 rows.
+        ptx::mbar_init(ptx::smem_u32(&bar_exchange), 1);
         ptx::fence_mbar_init();
+        if (ksplit > 1)
+            ptx::mbar_arrive_expect_tx(ptx::smem_u32(&bar_exchange),
+                                       (ksplit - 1) * uint32_t(sched.umma_n) / ksplit * (UMMA_BM * 4u));
     }
     if (warp == 1) {
         ptx::tmem_alloc<CTAS>(ptx::smem_u32(&tmem_base_holder), Cfg::TMEM_COLS);
@@ -542,9 +546,11 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                     const uint32_t slot = kgroup > owner ? kgroup - 1 : kgroup;
                     const uint32_t chunk = slot * slice_chunks + uint32_t(c - int(owner) * slice) / 32u;
                     const uint32_t dst = ptx::mapa(xbuf + chunk * (UMMA_BM * 128u) + row_off, owner * CTAS + cta_rank);
+                    const uint32_t bar = ptx::mapa(ptx::smem_u32(&bar_exchange), owner * CTAS + cta_rank);
 #pragma unroll
                     for (uint32_t q = 0; q < 8; ++q)
-                        ptx::st_cluster_v4(dst + q * (UMMA_BM * 16u), r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                        ptx::st_async_v4(dst + q * (UMMA_BM * 16u), r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3],
+                                         bar);
                 };
                 {
                     int c = next_foreign(0);
@@ -566,16 +572,10 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 // out of TMEM while the partial sums cross the cluster.
                 const int own0 = int(kgroup) * slice;
                 if (n_cols > 0) ptx::tmem_ld_32x32(t_row + own0, r0);
-                // One lane signals for the warp: the warp barrier orders every lane's stores before
-                // lane 0's release, which is cumulative, so the owner's acquire sees all of them.
-                // (128 arrivals per peer barrier, one per thread, took longer than the stores.)
-                __syncwarp();
-                if (lane == 0) {
-                    for (uint32_t g = 0; g < ksplit; ++g)
-                        if (g != kgroup)
-                            ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bar_exchange), g * CTAS + cta_rank));
-                }
-                ok = ptx::mbar_wait<true>(ptx::smem_u32(&bar_exchange), 0, wctx, UMMA_TIMEOUT_EXCHANGE);
+                // Nothing to signal: every store counts its own bytes on the owner's barrier when it
+                // lands (a release fence and an arrival per warp cost a round trip through the
+                // cluster before the arrival could even leave, about 1900 cycles).
+                ok = n_cols == 0 || ptx::mbar_wait<true>(ptx::smem_u32(&bar_exchange), 0, wctx, UMMA_TIMEOUT_EXCHANGE);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) { ptx::tmem_ld_wait(); break; }
                 auto reduce = [&](int cc, uint32_t (&r)[32]) {
