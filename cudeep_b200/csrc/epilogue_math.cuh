@@ -56,7 +56,7 @@ static __device__ __noinline__ float4 activate4(float4 x, int act) {
 template <int N>
 __device__ __forceinline__ void apply_activation(float (&v)[N], int act) {
     static_assert(N % 4 == 0, "activations are applied four values at a time");
-    if (act == EPI_NONE) return;
+    if (__builtin_expect(act == EPI_NONE, 1)) return;      // the plain epilogue falls straight through
     if (act == EPI_RELU) {
 #pragma unroll
         for (int j = 0; j < N; ++j) v[j] = fmaxf(v[j], 0.0f);

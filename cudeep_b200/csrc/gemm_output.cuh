@@ -47,7 +47,7 @@ struct GemmOutput {
                                            const UmmaEpilogueArgs& epi) const {
         const int row = t.m0 + row_in_cta;
         const int col = t.n0 + c0;
-        if (epi.bias != nullptr && row < m && col < n) {
+        if (__builtin_expect(epi.bias != nullptr && row < m && col < n, 0)) {
             if (epi.bias_per_row) {
                 const float b = __ldg(epi.bias + row);
 #pragma unroll

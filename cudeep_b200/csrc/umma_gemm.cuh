@@ -265,8 +265,10 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
     ptx::tc_fence_after();
     const uint32_t tmem_base = tmem_base_holder;
     // Everything above touched only this launch's parameters and on-chip state, so it may overlap
-    // the tail of the previous kernel in the stream; operands, bias and C are touched from here on.
-    ptx::grid_dependency_wait();
+    // the tail of the previous kernel in the stream.  So may what follows, up to the first access
+    // to global memory of each role: the producer works out its first tile before it waits for the
+    // predecessors (just before its first load), the epilogue warps wait before they first read a
+    // bias or write C, and the MMA issuer touches only shared and tensor memory.
     ptx::grid_launch_dependents();
 
     const int num_tiles = sched.tiles_m * sched.tiles_n;
@@ -310,6 +312,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 tile_coords(w.tile, tm, tn);
                 const auto tile = prob.decode(tm, tn, cta_rank);
                 const int k_stages = (w.kb_count + KATOMS - 1) / KATOMS;
+                if (u == first_unit) ptx::grid_dependency_wait();
                 for (int ks = 0; ks < k_stages; ++ks) {
                     if (!ptx::mbar_wait(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, wctx,
                                         UMMA_TIMEOUT_PRODUCER))
@@ -338,6 +341,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
         }
     producer_done:
         __syncwarp();
+        if (CTAS == 2) ptx::cluster_arrive();      // see the teardown
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (is_leader) {
@@ -440,6 +444,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
         }
     mma_done:
         __syncwarp();
+        if (CTAS == 2) ptx::cluster_arrive();
     } else {
         // ------------------------------------------------------------ epilogue
         const uint32_t quarter = warp & 3u;            // TMEM lanes [32*quarter, +32) belong to this warp
@@ -458,6 +463,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                                 UMMA_TIMEOUT_EPILOGUE);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            if (it == 0) ptx::grid_dependency_wait();      // before the first bias read or store to C
             ptx::tc_fence_after();
             const uint32_t t_row = tmem_base + acc * BN + ((quarter * 32u) << 16);
             // Two register sets: the TMEM load of the next 32 columns is in flight while the
@@ -723,6 +729,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 else ptx::mbar_arrive(acce_local);
             }
         }
+        if (CTAS == 2) ptx::cluster_arrive();      // this warp is done with TMEM and with its partner: see the teardown
         // Bulk stores read shared memory asynchronously: the reads must be over before the CTA
         // gives its shared memory back (the writes themselves complete with the kernel).
         if constexpr (has_multimem_store<Problem>::value) __threadfence_system();
@@ -753,10 +760,10 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
     // read accumulators.  Lone CTAs that only shared a split reduction need no such barrier: each
     // one waited, on its exchange barrier, for everything any other CTA sends it, and the last
     // thing it sent - its arrivals on the others' exchange barriers - is what they wait for.
-    if (CTAS == 2) {
-        ptx::cluster_arrive();
-        ptx::cluster_wait();
-    }
+    // The barrier is split: every warp arrived when its own role ended (the epilogue warps before
+    // they waited for their bulk stores to drain), so by now the partner's warps have usually
+    // arrived too and the wait costs nothing, instead of a round trip after the drain.
+    if (CTAS == 2) ptx::cluster_wait();
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
