@@ -420,7 +420,10 @@ inline double estimate_us(const TileCost& t, int cluster_split, int m, int n, in
         return 0.0;
     const int katoms = default_katoms(t.ctas, t.bn, cluster_split);
     if (stages_for(t.ctas, t.bn, katoms, cluster_split) < 2) return 0.0;
-    double exchange_us = 3.5;
+    // The exchange: a fixed part, the 32-column chunks a CTA sends (and as many it adds up), and
+    // what wider clusters cost beyond that (fitted to graph-timed launches from 512^3 to
+    // 128 x 4096 x 4096 after the exchange became asynchronous stores).
+    double exchange_us = 1.0 + 0.45 * (t.bn / 32) * (cluster_split - 1) / cluster_split;
     for (int s = cluster_split; s > 2; s /= 2) exchange_us += 0.75;
     const double loop_us = 4.0 * per * t.step_ns * 1e-3;
     return t.base_us + (loop_us > dram_us ? loop_us : dram_us) + t.epi_us / cluster_split + exchange_us;
