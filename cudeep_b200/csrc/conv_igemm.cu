@@ -23,6 +23,7 @@
 #include "conv_igemm.h"
 #include "umma_gemm.cuh"
 
+#include <cstdlib>
 #include <vector>
 
 namespace cudeep_b200 {
@@ -30,6 +31,8 @@ namespace cudeep_b200 {
 namespace {
 
 // ------------------------------------------------------------------ layout transforms
+
+inline int round_up_int(int v, int m) { return (v + m - 1) / m * m; }
 
 // Filters -> wp[OC][KH*KW][Cp], the K-major A operand (zero for c >= C); OC and C are the output and
 // input channel counts of the convolution being launched.
@@ -445,6 +448,166 @@ struct ConvProblem {
     }
 };
 
+// Stride-1 convolutions with three taps per filter row over whole output rows, on CTA pairs: the form
+// umma_gemm.cuh describes under has_shared_b.  A stage is one filter row kh and one block of 32
+// channels: three filter slabs (kw = 0, 1, 2) and the input pixels under them - `rows_per_half`
+// image rows per CTA, OW + 2 pixels each, halo included - loaded once and read by the three taps at
+// offsets of 0, 1 and 2 pixels.  Operand column n of a CTA's half is pixel (n / pitch, n % pitch) of
+// its rows; the columns with n % pitch >= OW (and those past rows_per_half * pitch) are by-products.
+struct ConvRowProblem {
+    static constexpr bool kTmaStore = true;
+    static constexpr bool kClusterSplit = false;
+    static constexpr bool kSharedB = true;
+    CUtensorMap map_w;     // packed filters: dims {KH*3*Cp, OC}, box {32, 128}
+    CUtensorMap map_x;     // NHWC input: dims {Cx, W, H, N}, box {32, pitch, rows_per_half, 1}
+    CUtensorMap map_out;   // output: dims {OW, OH, N*OC}, box {OW, 1, 32}, not swizzled
+    int oc_n, oh_n, ow_n, batch;
+    int rows_per_half, pitch, half_cols;
+    int tiles_h;           // tiles per image
+    int c_blocks, cp, p_h, p_w;
+
+    struct Tile {
+        int oc0, n, oh0, hb0;
+    };
+    __device__ __forceinline__ void prefetch_maps() const {
+        ptx::prefetch_tensormap(&map_w);
+        ptx::prefetch_tensormap(&map_x);
+        ptx::prefetch_tensormap(&map_out);
+    }
+    __device__ __forceinline__ const CUtensorMap* out_map() const { return &map_out; }
+    __device__ __forceinline__ Tile decode(int tm, int tn, uint32_t cta_rank) const {
+        Tile t;
+        t.oc0 = (tm * 2 + int(cta_rank)) * UMMA_BM;
+        t.n = tn / tiles_h;
+        t.oh0 = (tn - t.n * tiles_h) * (2 * rows_per_half);
+        t.hb0 = t.oh0 + int(cta_rank) * rows_per_half;
+        return t;
+    }
+    template <int C>
+    __device__ __forceinline__ void load_stage(const Tile& t, int stage_index, uint32_t a_smem, uint32_t b_smem,
+                                               uint32_t bar) const {
+        static_assert(C == 2, "the row form runs on CTA pairs");
+        const int kh = stage_index / c_blocks;
+        const int c0 = (stage_index - kh * c_blocks) * UMMA_BK;
+#pragma unroll
+        for (int kw = 0; kw < 3; ++kw)
+            ptx::tma_load_2d_pair(a_smem + kw * (UMMA_BM * UMMA_BK * 4), &map_w, bar, (kh * 3 + kw) * cp + c0, t.oc0);
+        ptx::tma_load_4d_pair(b_smem, &map_x, bar, c0, -p_w, t.hb0 + kh - p_h, t.n);
+    }
+    __device__ __forceinline__ void finish(const Tile& t, int row_in_cta, int /*c0*/, float (&v)[32],
+                                           const UmmaEpilogueArgs& epi) const {
+        const int oc = t.oc0 + row_in_cta;
+        if (epi.bias != nullptr && oc < oc_n) {
+            const float b = __ldg(epi.bias + oc);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += b;
+        }
+        apply_activation(v, epi.act);
+    }
+    __device__ __forceinline__ int out_rows() const { return 2 * rows_per_half; }
+    __device__ __forceinline__ int row_values() const { return ow_n; }
+    __device__ __forceinline__ uint32_t row_column(int r) const {
+        const int half = r / rows_per_half;
+        return uint32_t(half * half_cols + (r - half * rows_per_half) * pitch);
+    }
+    // Rows past OH and blocks of channels past OC (a multiple of 32) are clipped by the store.
+    __device__ __forceinline__ void row_coords(const Tile& t, int row0, int r, int& x, int& y, int& z) const {
+        x = 0;
+        y = t.oh0 + r;
+        z = t.n * oc_n + t.oc0 + row0;
+        if (t.oc0 + row0 >= oc_n) z = batch * oc_n;
+    }
+    // Never used: every tile leaves through the row stores.
+    __device__ __forceinline__ void store(const Tile&, int, int, float (&)[32], const UmmaEpilogueArgs&, int) const {}
+    __device__ __forceinline__ void out_coords(const Tile&, int, int, int& x, int& y) const { x = y = 0; }
+};
+
+struct RowPlan {
+    int rows_per_half = 0, pitch = 0, half_cols = 0;
+};
+
+// Whether (and how) the row form takes a convolution: CTA pairs, three taps per filter row, stride 1,
+// whole output rows of 16-byte multiples, at most 120 operand columns per CTA.
+RowPlan plan_rows(const ConvShape& s, int ctas, const float* out, bool plain_output) {
+    RowPlan p;
+    const int oh = s.out_h(), ow = s.out_w();
+    if (ctas != 2 || !plain_output || s.k_w != 3 || s.s_h != 1 || s.s_w != 1) return p;
+    if (ow % 4 != 0 || ow < 24 || s.out_c % 32 != 0 || (reinterpret_cast<uintptr_t>(out) & 15u) != 0) return p;
+    const int pitch = ow + 2;
+    if (pitch > 120 || ow > 64) return p;
+    int rows = 120 / pitch;
+    if (rows > (oh + 1) / 2) rows = (oh + 1) / 2;
+    if (rows < 1) return p;
+    const int half_cols = round_up_int(rows * pitch, 8);
+    // The epilogue reads 32 or 64 accumulator columns from the start of a row: inside the buffer.
+    const int last_row = half_cols + (rows - 1) * pitch;
+    if (last_row + (ow > 32 ? 64 : 32) > 256) return p;
+    p.rows_per_half = rows;
+    p.pitch = pitch;
+    p.half_cols = half_cols;
+    return p;
+}
+
+void launch_conv_rows(const float* xt, const float* wp, const float* bias, float* out, const ConvShape& s, int cx,
+                      int cp, const RowPlan& plan, int act, cudaStream_t stream) {
+    constexpr int KW = 3;
+    using Cfg = UmmaConfig<2, 256, false, KW>;
+    const DeviceInfo& dev = device_info();
+    const int oh = s.out_h(), ow = s.out_w();
+    ConvRowProblem prob;
+    {
+        const uint64_t dims[2] = {uint64_t(s.k_h) * KW * cp, uint64_t(s.out_c)};
+        const uint64_t strides[1] = {uint64_t(s.k_h) * KW * cp * 4};
+        const uint32_t box[2] = {UMMA_BK, UMMA_BM};
+        encode_tensor_map(&prob.map_w, wp, 2, dims, strides, box, TmaSwizzle::B128);
+    }
+    {
+        const uint64_t dims[4] = {uint64_t(cx), uint64_t(s.in_w), uint64_t(s.in_h), uint64_t(s.batch)};
+        const uint64_t strides[3] = {uint64_t(cx) * 4, uint64_t(s.in_w) * cx * 4, uint64_t(s.in_h) * s.in_w * cx * 4};
+        const uint32_t box[4] = {UMMA_BK, uint32_t(plan.pitch), uint32_t(plan.rows_per_half), 1};
+        encode_tensor_map(&prob.map_x, xt, 4, dims, strides, box, TmaSwizzle::B128);
+    }
+    {
+        const uint64_t dims[3] = {uint64_t(ow), uint64_t(oh), uint64_t(s.batch) * s.out_c};
+        const uint64_t strides[2] = {uint64_t(ow) * 4, uint64_t(oh) * ow * 4};
+        const uint32_t box[3] = {uint32_t(ow), 1, 32};
+        encode_tensor_map(&prob.map_out, out, 3, dims, strides, box, TmaSwizzle::None);
+    }
+    prob.oc_n = s.out_c;
+    prob.oh_n = oh;
+    prob.ow_n = ow;
+    prob.batch = s.batch;
+    prob.rows_per_half = plan.rows_per_half;
+    prob.pitch = plan.pitch;
+    prob.half_cols = plan.half_cols;
+    prob.tiles_h = (oh + 2 * plan.rows_per_half - 1) / (2 * plan.rows_per_half);
+    prob.c_blocks = cp / UMMA_BK;
+    prob.cp = cp;
+    prob.p_h = s.p_h;
+    prob.p_w = s.p_w;
+
+    constexpr uint32_t stage_bytes = KW * Cfg::A_BYTES + Cfg::B_BYTES;
+    const int umma_n = 2 * plan.half_cols;
+    const uint32_t tx = 2u * (KW * Cfg::A_BYTES + uint32_t(plan.pitch) * plan.rows_per_half * UMMA_BK * 4);
+    const int stages = int((Cfg::SMEM_BUDGET - UMMA_STORE_STAGING_BYTES) / stage_bytes);
+    UmmaSchedule sched = whole_tile_schedule((s.out_c + 2 * UMMA_BM - 1) / (2 * UMMA_BM), s.batch * prob.tiles_h,
+                                             s.k_h * prob.c_blocks, umma_n, tx, stages, dev.status_word);
+    sched.raster_group = sched.tiles_m;
+    const uint32_t smem_bytes = uint32_t(stages) * stage_bytes + UMMA_STORE_STAGING_BYTES + 1024;
+    const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;
+    CB200_REQUIRE(num_tiles < (1LL << 30), "conv2d: too many tiles");
+    long long groups = dev.num_sms / 2;
+    if (groups > num_tiles) groups = num_tiles;
+    CB200_TRACE("conv2d implicit GEMM tcgen05, rows shared by the taps of a filter row: N=%d C=%d %dx%d -> OC=%d "
+                "%dx%d, %dx3 pad %dx%d; %d rows x %d pixels per CTA = %d columns per pair, stages=%d of %u KB, "
+                "clusters=%lld, stages per tile=%d",
+                s.batch, s.in_c, s.in_h, s.in_w, s.out_c, oh, ow, s.k_h, s.p_h, s.p_w, plan.rows_per_half, plan.pitch,
+                umma_n, stages, stage_bytes / 1024, groups, sched.k_blocks);
+    auto kernel = umma_tf32_kernel<2, 256, false, KW, ConvRowProblem>;
+    UmmaEpilogueArgs epi{bias, 1, act};
+    launch_umma(kernel, prob, sched, epi, groups, 2, smem_bytes, Cfg::SMEM_MAX, stream);
+}
+
 struct TilePlan {
     int box_w = 0, box_h = 0;
     int box_n = 1;      // > 1: whole images per tile (small feature maps)
@@ -796,6 +959,15 @@ size_t conv2d_igemm_scratch_bytes(const ConvShape& s, size_t* nhwc_bytes, size_t
 }
 
 namespace {
+// CUDEEP_B200_CONV_ROWS=0 keeps 3 x 3 layers on the tap-per-K-block form (read once).
+bool rows_form_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("CUDEEP_B200_CONV_ROWS");
+        return !(v != nullptr && v[0] == '0');
+    }();
+    return on;
+}
+
 // Picks the pixel box (one image's rows, or several whole images for small maps) and the CTA
 // grouping, and launches the matching kernel instantiation.
 void plan_and_launch(const float* xt, const float* wp, const float* bias, float* output, const ConvShape& s,
@@ -804,6 +976,13 @@ void plan_and_launch(const float* xt, const float* wp, const float* bias, float*
     const int oh = s.out_h(), ow = s.out_w();
     int ctas = force_ctas;
     if (ctas == 0) ctas = (s.out_c > UMMA_BM) ? 2 : 1;
+    if (!row_packed && rows_form_enabled()) {
+        const RowPlan rows = plan_rows(s, ctas, output, extras == nullptr);
+        if (rows.rows_per_half > 0) {
+            launch_conv_rows(xt, wp, bias, output, s, cx, cp, rows, act, stream);
+            return;
+        }
+    }
     TilePlan plan = plan_tile(oh, ow, ctas, s.s_h, s.s_w);
     if (plan.box_w == 0 && ctas == 2) {
         ctas = 1;

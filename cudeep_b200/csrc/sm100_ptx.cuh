@@ -194,6 +194,10 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src,
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                  : : "l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, uint32_t src, int32_t x, int32_t y, int32_t z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 : : "l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

@@ -200,6 +200,27 @@ struct has_plane_store { static constexpr bool value = false; };
 template <class P>
 struct has_plane_store<P, decltype((void)P::kPlaneStore)> { static constexpr bool value = P::kPlaneStore; };
 
+// One more optional form, for a 3 x 3 (or other KW-wide) stride-1 convolution over whole output rows:
+//   static constexpr bool kSharedB = true;
+// A pipeline stage then holds KATOMS A atoms - the filter slabs of the KATOMS taps of one filter row -
+// and ONE B block: the rows of input pixels under that filter row, halo columns included, loaded once.
+// Tap j's B operand is the same block read from j rows (pixels) further on: its descriptor starts
+// j * 128 bytes later and is otherwise unchanged, base-offset field included (measured: the tensor
+// core derives the 128-byte swizzle from the address bits, as TMA does when it writes the rows, so a
+// block can be read from any row on; a base offset of j gives wrong products).  The pixel gather, the costliest
+// requests of the TMA unit, shrinks by the filter width.  The schedule's K blocks count stages, the
+// problem loads a whole stage at once (`load_stage`), and tiles leave row by row (`kRowStore`):
+//   __device__ void load_stage(tile, int stage_index, uint32_t stage_smem, uint32_t b_smem, uint32_t bar) const;
+//   __device__ int out_rows() const;                     output rows per tile
+//   __device__ uint32_t row_column(int r) const;         first accumulator column of output row r
+//   __device__ int row_values() const;                   values per row (<= 64)
+//   __device__ void row_coords(tile, int row0, int r, int& x, int& y, int& z) const;   for out_map()
+//   finish() as for kTmaStore; out_map() is a 3-D map {OW, OH, planes}, box {OW, 1, 32}, no swizzle.
+template <class P, class = void>
+struct has_shared_b { static constexpr bool value = false; };
+template <class P>
+struct has_shared_b<P, decltype((void)P::kSharedB)> { static constexpr bool value = P::kSharedB; };
+
 template <int CTAS, int BN, bool B_MN_MAJOR, int KATOMS, class Problem, bool A_MN_MAJOR = false,
           int KIND = UMMA_KIND_TF32>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
@@ -208,7 +229,9 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM101_ALL) || \
     defined(__CUDA_ARCH_FEAT_SM103_ALL)
     using Cfg = UmmaConfig<CTAS, BN, B_MN_MAJOR, KATOMS>;
-    constexpr int STAGES = Cfg::STAGES;
+    constexpr bool SHARED_B = has_shared_b<Problem>::value;
+    constexpr uint32_t STAGE_BYTES = SHARED_B ? KATOMS * Cfg::A_BYTES + Cfg::B_BYTES : Cfg::STAGE_BYTES;
+    constexpr int STAGES = SHARED_B ? int(Cfg::SMEM_BUDGET / STAGE_BYTES) : Cfg::STAGES;
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[STAGES];
@@ -311,7 +334,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 int tm, tn;
                 tile_coords(w.tile, tm, tn);
                 const auto tile = prob.decode(tm, tn, cta_rank);
-                const int k_stages = (w.kb_count + KATOMS - 1) / KATOMS;
+                const int k_stages = SHARED_B ? w.kb_count : (w.kb_count + KATOMS - 1) / KATOMS;
                 if (u == first_unit) ptx::grid_dependency_wait();
                 for (int ks = 0; ks < k_stages; ++ks) {
                     if (!ptx::mbar_wait(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, wctx,
@@ -327,11 +350,17 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                         // of range, so they arrive as zeros and add nothing.  (A split unit
                         // that is not the last holds a whole number of stages, so it never
                         // reaches into its neighbour's K range.)
+                        if constexpr (SHARED_B) {
+                            const uint32_t stage_smem = smem_base + stage * STAGE_BYTES;
+                            prob.template load_stage<CTAS>(tile, w.kb0 + ks, stage_smem,
+                                                           stage_smem + KATOMS * Cfg::A_BYTES, full_bar);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < KATOMS; ++j) {
-                            const uint32_t a_smem = smem_base + stage * Cfg::STAGE_BYTES + j * Cfg::ATOM_BYTES;
-                            prob.template load<CTAS>(tile, w.kb0 + ks * KATOMS + j, a_smem,
-                                                     a_smem + Cfg::A_BYTES, full_bar);
+                            for (int j = 0; j < KATOMS; ++j) {
+                                const uint32_t a_smem = smem_base + stage * STAGE_BYTES + j * Cfg::ATOM_BYTES;
+                                prob.template load<CTAS>(tile, w.kb0 + ks * KATOMS + j, a_smem,
+                                                         a_smem + Cfg::A_BYTES, full_bar);
+                            }
                         }
                     }
                     ++issued;
@@ -375,12 +404,14 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 b_lbo, b_sbo, (B_MN_MAJOR && !b_mn16) ? ptx::SMEM_LAYOUT_SW128_ATOM32 : ptx::SMEM_LAYOUT_SW128);
             constexpr uint32_t b_kstep = b_mn16 ? 2048u : B_MN_MAJOR ? 1024u : UMMA_K * 4u;
             const uint64_t a_desc0 = ptx::smem_desc_at(a_base, smem_base);
-            const uint64_t b_desc0 = ptx::smem_desc_at(b_base, smem_base + Cfg::A_BYTES);
+            const uint64_t b_desc0 =
+                ptx::smem_desc_at(b_base, smem_base + (SHARED_B ? KATOMS * Cfg::A_BYTES : Cfg::A_BYTES));
 
             uint32_t stage = 0, phase = 0;
             int it = 0;
             for (int u = first_unit; u < num_units; u += unit_stride, ++it) {
-                const int k_stages = (decode_unit(u).kb_count + KATOMS - 1) / KATOMS;
+                const int kb_count = decode_unit(u).kb_count;
+                const int k_stages = SHARED_B ? kb_count : (kb_count + KATOMS - 1) / KATOMS;
                 const uint32_t acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
                 if (!__all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u,
@@ -409,14 +440,19 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                     if (issuer && !(sched.debug & 2u)) {
                         // Descriptors differ only in the start-address field (address >> 4),
                         // so each one is the stage's first descriptor plus a constant.
-                        const uint64_t a_stage = a_desc0 + ((stage * Cfg::STAGE_BYTES) >> 4);
-                        const uint64_t b_stage = b_desc0 + ((stage * Cfg::STAGE_BYTES) >> 4);
+                        const uint64_t a_stage = a_desc0 + ((stage * STAGE_BYTES) >> 4);
+                        const uint64_t b_stage = b_desc0 + ((stage * STAGE_BYTES) >> 4);
 #pragma unroll
                         for (int j = 0; j < KATOMS; ++j) {
 #pragma unroll
                             for (int kk = 0; kk < UMMA_BK / UMMA_K; ++kk) {
-                                const uint64_t a_desc = a_stage + ((j * Cfg::ATOM_BYTES + kk * a_kstep) >> 4);
-                                const uint64_t b_desc = b_stage + ((j * Cfg::ATOM_BYTES + kk * b_kstep) >> 4);
+                                // Shared B: atom j's A slab, and the one B block read from row j on
+                                // (the start address j * 128 bytes later, nothing else).
+                                const uint64_t a_desc =
+                                    a_stage + (((SHARED_B ? j * Cfg::A_BYTES : j * Cfg::ATOM_BYTES) + kk * a_kstep) >> 4);
+                                const uint64_t b_desc =
+                                    SHARED_B ? b_stage + ((j * 128u + kk * b_kstep) >> 4)
+                                             : b_stage + ((j * Cfg::ATOM_BYTES + kk * b_kstep) >> 4);
                                 if constexpr (KIND != UMMA_KIND_TF32)
                                     ptx::umma_f16<CTAS>(d_tmem, a_desc, b_desc, idesc, (ks | j | kk) != 0);
                                 else
@@ -478,7 +514,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
             // ring is idle (every load was consumed by an MMA that has completed), so the staging
             // blocks lie at its start and no shared memory is set aside for them.
             const uint32_t staging = ksplit > 1 ? smem_base + quarter * 8192u
-                                                : smem_base + uint32_t(sched.stages) * Cfg::STAGE_BYTES +
+                                                : smem_base + uint32_t(sched.stages) * STAGE_BYTES +
                                                       sched.exchange_bytes + quarter * 8192u;
             auto emit = [&](int c, const uint32_t (&r)[32]) {
                 float v[32];
@@ -534,13 +570,57 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 }
                 prob.store(tile, row_in_cta, c, v, epi, w.mode);
             };
+            if constexpr (SHARED_B) {
+                // ---- the tile leaves one output row at a time: its values are a run of accumulator
+                // columns (the halo columns between rows are dropped), staged as a dense
+                // [32 channels][values] block and written by one 3-D bulk tensor store.
+                if constexpr (Problem::kTmaStore) {
+                    const int out_rows = prob.out_rows();
+                    const int vals = prob.row_values();
+#pragma unroll 1
+                    for (int r = 0; r < out_rows && n_cols > 0; ++r) {
+                        const uint32_t col = prob.row_column(r);
+                        ptx::tmem_ld_32x32(t_row + col, r0);
+                        if (vals > 32) ptx::tmem_ld_32x32(t_row + col + 32, r1);
+                        ptx::tmem_ld_wait();
+                        float v0[32], v1[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            v0[j] = __uint_as_float(r0[j]);
+                            v1[j] = __uint_as_float(r1[j]);
+                        }
+                        prob.finish(tile, row_in_cta, 0, v0, epi);
+                        if (vals > 32) prob.finish(tile, row_in_cta, 32, v1, epi);
+                        if (lane == 0) ptx::bulk_wait_group_read<0>();      // the previous row's store has read the block
+                        __syncwarp();
+                        const uint32_t dst = staging + lane * uint32_t(vals) * 4u;
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            if (q * 4 < vals)
+                                ptx::st_shared_v4(dst + q * 16, v0[4 * q], v0[4 * q + 1], v0[4 * q + 2], v0[4 * q + 3]);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            if (32 + q * 4 < vals)
+                                ptx::st_shared_v4(dst + 128 + q * 16, v1[4 * q], v1[4 * q + 1], v1[4 * q + 2],
+                                                  v1[4 * q + 3]);
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            int x, y, z;
+                            prob.row_coords(tile, int(quarter) * 32, r, x, y, z);
+                            ptx::tma_store_3d(prob.out_map(), staging, x, y, z);
+                            ptx::bulk_commit_group();
+                        }
+                    }
+                }
+            } else {
             if (ksplit > 1) {
                 // ---- split-K inside the cluster: exchange partial sums, then reduce one slice
                 // Exchange buffer: [source group (own one skipped)][32-column chunk of the slice]
                 // [16-byte unit of the row (8)][row (128)][16 B]: one store instruction of a warp
                 // covers 512 contiguous bytes of the peer's shared memory, and the thread that
                 // reduces a row reads back exactly what its counterpart wrote.
-                const uint32_t xbuf = smem_base + uint32_t(sched.stages) * Cfg::STAGE_BYTES;
+                const uint32_t xbuf = smem_base + uint32_t(sched.stages) * STAGE_BYTES;
                 const int slice = sched.umma_n / int(ksplit);          // columns this group reduces
                 const int slice_chunks = slice / 32;
                 const uint32_t row_off = uint32_t(row_in_cta) * 16u;
@@ -721,6 +801,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                     }
                 }
             }
+            }      // !SHARED_B
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) {
