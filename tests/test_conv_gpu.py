@@ -110,6 +110,33 @@ def test_tensor_core_path_shapes(dev, oracle, shape, oc, k, padding, act):
     assert oracle.rel_frobenius(got, model) <= TF32_MODEL_TOL
 
 
+@pytest.mark.parametrize("shape,oc,k,padding", [
+    ((2, 64, 56, 56), 256, (3, 3), (1, 1)),      # C4's rows: 2 x 58 pixels per CTA, 240 accumulator columns
+    ((1, 40, 29, 28), 160, (3, 3), (1, 1)),      # 29 rows in tiles of 8: the last tile is mostly past OH; 160 channels
+    ((3, 32, 12, 64), 384, (3, 3), (1, 1)),      # 64-pixel rows: one row per CTA, two loads of 32 columns per row
+    ((2, 36, 30, 26), 256, (5, 3), (2, 0)),      # five filter rows, no horizontal padding: 24-pixel rows
+    ((2, 64, 26, 42), 256, (3, 3), (0, 1)),      # no vertical padding: 24 output rows of 40 pixels
+    ((5, 100, 32, 32), 512, (3, 3), (1, 1)),     # channels padded 100 -> 128, 512 output channels: two tile rows
+])
+@pytest.mark.parametrize("act", [0, 2])
+def test_rows_shared_by_the_taps_of_a_filter_row(dev, oracle, shape, oc, k, padding, act):
+    """Stride-1 layers with three taps per filter row and whole output rows of 24-64 pixels on CTA pairs:
+    one load of the input rows serves the three taps (shifted descriptors), rows leave by 3-D bulk
+    stores.  Same bars as every tensor-core convolution, plus bitwise equality with a second run."""
+    rng = np.random.default_rng(sum(shape) + oc + act)
+    x = rng.standard_normal(shape, dtype=np.float32)
+    w = rng.standard_normal((oc, shape[1], *k), dtype=np.float32) * np.float32(0.1)
+    bias = rng.standard_normal(oc, dtype=np.float32)
+    got = dev.conv2d(x, w, bias, (1, 1), padding, act=act)
+    assert not np.isnan(got).any()
+    exact = oracle.conv2d(x, w, bias, (1, 1), padding, act=act)
+    model = oracle.conv2d(x, w, bias, (1, 1), padding, act=act, input_mode=oracle.INPUT_TF32_TRUNC)
+    assert got.shape == exact.shape
+    assert oracle.rel_frobenius(got, exact) <= TF32_TOL
+    assert oracle.rel_frobenius(got, model) <= TF32_MODEL_TOL
+    assert np.array_equal(got, dev.conv2d(x, w, bias, (1, 1), padding, act=act))
+
+
 @pytest.mark.parametrize("shape,oc,k,stride,padding", [
     ((2, 64, 14, 14), 64, (3, 3), (2, 2), (1, 1)),       # 7 x 7 outputs, every second pixel in both directions
     ((2, 32, 28, 28), 128, (3, 3), (2, 2), (1, 1)),      # a ResNet down-sampling layer

@@ -25,6 +25,8 @@ x, w, y = torch.zeros((2, 64, 16, 16), device="cuda"), torch.zeros((64, 64, 3, 3
 _lib.check(lib.cudeep_b200_conv2d_forward_f32(P(x), P(w), None, P(y), 2, 64, 64, 16, 16, 3, 3, 1, 1, 1, 1, None))
 x, w, y = torch.zeros((1, 4, 6, 6), device="cuda"), torch.zeros((5, 4, 3, 3), device="cuda"), torch.zeros((1, 5, 4, 4), device="cuda")
 _lib.check(lib.cudeep_b200_conv2d_forward_f32(P(x), P(w), None, P(y), 1, 4, 5, 6, 6, 3, 3, 1, 1, 0, 0, None))
+x, w, y = torch.zeros((1, 32, 28, 28), device="cuda"), torch.zeros((256, 32, 3, 3), device="cuda"), torch.zeros((1, 256, 28, 28), device="cuda")
+_lib.check(lib.cudeep_b200_conv2d_forward_f32(P(x), P(w), None, P(y), 1, 32, 256, 28, 28, 3, 3, 1, 1, 1, 1, None))
 torch.cuda.synchronize()
 """
 
@@ -45,6 +47,7 @@ def test_trace_names_the_kernel_each_call_took(lib, cuda):
     assert any("gemm tf32 tcgen05" in l and "M=512 N=512 K=512" in l and "tile=" in l and "stages=" in l for l in lines)
     assert any("conv2d implicit GEMM tcgen05" in l and "OC=64" in l for l in lines)
     assert any("conv2d direct strict FP32" in l and "OC=5" in l for l in lines)
+    assert any("rows shared by the taps of a filter row" in l and "OC=256" in l and "4 rows x 30 pixels" in l for l in lines)
 
 
 def test_trace_is_silent_by_default(lib, cuda):
