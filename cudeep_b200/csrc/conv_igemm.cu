@@ -448,12 +448,15 @@ struct ConvProblem {
     }
 };
 
-// Stride-1 convolutions with three taps per filter row over whole output rows, on CTA pairs: the form
+// Stride-1 convolutions with three taps per filter row over whole output rows: the form
 // umma_gemm.cuh describes under has_shared_b.  A stage is one filter row kh and one block of 32
 // channels: three filter slabs (kw = 0, 1, 2) and the input pixels under them - `rows_per_half`
 // image rows per CTA, OW + 2 pixels each, halo included - loaded once and read by the three taps at
-// offsets of 0, 1 and 2 pixels.  Operand column n of a CTA's half is pixel (n / pitch, n % pitch) of
+// offsets of 0, 1 and 2 pixels.  Operand column n of a CTA's share is pixel (n / pitch, n % pitch) of
 // its rows; the columns with n % pitch >= OW (and those past rows_per_half * pitch) are by-products.
+// CTAS = 2: the CTAs of a pair stage half of the tile's rows each; CTAS = 1 (at most 128 output
+// channels): one CTA stages them all.
+template <int CTAS>
 struct ConvRowProblem {
     static constexpr bool kTmaStore = true;
     static constexpr bool kClusterSplit = false;
@@ -477,22 +480,26 @@ struct ConvRowProblem {
     __device__ __forceinline__ const CUtensorMap* out_map() const { return &map_out; }
     __device__ __forceinline__ Tile decode(int tm, int tn, uint32_t cta_rank) const {
         Tile t;
-        t.oc0 = (tm * 2 + int(cta_rank)) * UMMA_BM;
+        t.oc0 = (tm * CTAS + int(cta_rank)) * UMMA_BM;
         t.n = tn / tiles_h;
-        t.oh0 = (tn - t.n * tiles_h) * (2 * rows_per_half);
+        t.oh0 = (tn - t.n * tiles_h) * (CTAS * rows_per_half);
         t.hb0 = t.oh0 + int(cta_rank) * rows_per_half;
         return t;
     }
     template <int C>
     __device__ __forceinline__ void load_stage(const Tile& t, int stage_index, uint32_t a_smem, uint32_t b_smem,
                                                uint32_t bar) const {
-        static_assert(C == 2, "the row form runs on CTA pairs");
+        static_assert(C == CTAS, "loads follow the CTA grouping of the problem");
         const int kh = stage_index / c_blocks;
         const int c0 = (stage_index - kh * c_blocks) * UMMA_BK;
 #pragma unroll
-        for (int kw = 0; kw < 3; ++kw)
-            ptx::tma_load_2d_pair(a_smem + kw * (UMMA_BM * UMMA_BK * 4), &map_w, bar, (kh * 3 + kw) * cp + c0, t.oc0);
-        ptx::tma_load_4d_pair(b_smem, &map_x, bar, c0, -p_w, t.hb0 + kh - p_h, t.n);
+        for (int kw = 0; kw < 3; ++kw) {
+            const uint32_t dst = a_smem + kw * (UMMA_BM * UMMA_BK * 4);
+            if constexpr (C == 2) ptx::tma_load_2d_pair(dst, &map_w, bar, (kh * 3 + kw) * cp + c0, t.oc0);
+            else ptx::tma_load_2d(dst, &map_w, bar, (kh * 3 + kw) * cp + c0, t.oc0);
+        }
+        if constexpr (C == 2) ptx::tma_load_4d_pair(b_smem, &map_x, bar, c0, -p_w, t.hb0 + kh - p_h, t.n);
+        else ptx::tma_load_4d(b_smem, &map_x, bar, c0, -p_w, t.hb0 + kh - p_h, t.n);
     }
     __device__ __forceinline__ void finish(const Tile& t, int row_in_cta, int /*c0*/, float (&v)[32],
                                            const UmmaEpilogueArgs& epi) const {
@@ -504,7 +511,7 @@ struct ConvRowProblem {
         }
         apply_activation(v, epi.act);
     }
-    __device__ __forceinline__ int out_rows() const { return 2 * rows_per_half; }
+    __device__ __forceinline__ int out_rows() const { return CTAS * rows_per_half; }
     __device__ __forceinline__ int row_values() const { return ow_n; }
     __device__ __forceinline__ uint32_t row_column(int r) const {
         const int half = r / rows_per_half;
@@ -526,21 +533,23 @@ struct RowPlan {
     int rows_per_half = 0, pitch = 0, half_cols = 0;
 };
 
-// Whether (and how) the row form takes a convolution: CTA pairs, three taps per filter row, stride 1,
-// whole output rows of 16-byte multiples, at most 120 operand columns per CTA.
+// Whether (and how) the row form takes a convolution: three taps per filter row, stride 1, whole output
+// rows of 16-byte multiples; a CTA's share of the operand columns is at most 120 in a pair and 248 alone.
 RowPlan plan_rows(const ConvShape& s, int ctas, const float* out, bool plain_output) {
     RowPlan p;
     const int oh = s.out_h(), ow = s.out_w();
-    if (ctas != 2 || !plain_output || s.k_w != 3 || s.s_h != 1 || s.s_w != 1) return p;
-    if (ow % 4 != 0 || ow < 24 || s.out_c % 32 != 0 || (reinterpret_cast<uintptr_t>(out) & 15u) != 0) return p;
+    if (!plain_output || s.k_w != 3 || s.s_h != 1 || s.s_w != 1) return p;
+    if (ow % 4 != 0 || ow < 24 || ow > 64 || s.out_c % 32 != 0 || (reinterpret_cast<uintptr_t>(out) & 15u) != 0) return p;
     const int pitch = ow + 2;
-    if (pitch > 120 || ow > 64) return p;
-    int rows = 120 / pitch;
-    if (rows > (oh + 1) / 2) rows = (oh + 1) / 2;
+    const int share = ctas == 2 ? 120 : 248;
+    int rows = share / pitch;
+    const int rows_needed = (oh + ctas - 1) / ctas;
+    if (rows > rows_needed) rows = rows_needed;
     if (rows < 1) return p;
-    const int half_cols = round_up_int(rows * pitch, 8);
+    // A pair's MMA has N = 2 x share (a multiple of 16), a single CTA's N = share (likewise).
+    const int half_cols = round_up_int(rows * pitch, ctas == 2 ? 8 : 16);
     // The epilogue reads 32 or 64 accumulator columns from the start of a row: inside the buffer.
-    const int last_row = half_cols + (rows - 1) * pitch;
+    const int last_row = (ctas - 1) * half_cols + (rows - 1) * pitch;
     if (last_row + (ow > 32 ? 64 : 32) > 256) return p;
     p.rows_per_half = rows;
     p.pitch = pitch;
@@ -548,13 +557,14 @@ RowPlan plan_rows(const ConvShape& s, int ctas, const float* out, bool plain_out
     return p;
 }
 
+template <int CTAS>
 void launch_conv_rows(const float* xt, const float* wp, const float* bias, float* out, const ConvShape& s, int cx,
                       int cp, const RowPlan& plan, int act, cudaStream_t stream) {
     constexpr int KW = 3;
-    using Cfg = UmmaConfig<2, 256, false, KW>;
+    using Cfg = UmmaConfig<CTAS, 256, false, KW>;
     const DeviceInfo& dev = device_info();
     const int oh = s.out_h(), ow = s.out_w();
-    ConvRowProblem prob;
+    ConvRowProblem<CTAS> prob;
     {
         const uint64_t dims[2] = {uint64_t(s.k_h) * KW * cp, uint64_t(s.out_c)};
         const uint64_t strides[1] = {uint64_t(s.k_h) * KW * cp * 4};
@@ -580,32 +590,32 @@ void launch_conv_rows(const float* xt, const float* wp, const float* bias, float
     prob.rows_per_half = plan.rows_per_half;
     prob.pitch = plan.pitch;
     prob.half_cols = plan.half_cols;
-    prob.tiles_h = (oh + 2 * plan.rows_per_half - 1) / (2 * plan.rows_per_half);
+    prob.tiles_h = (oh + CTAS * plan.rows_per_half - 1) / (CTAS * plan.rows_per_half);
     prob.c_blocks = cp / UMMA_BK;
     prob.cp = cp;
     prob.p_h = s.p_h;
     prob.p_w = s.p_w;
 
     constexpr uint32_t stage_bytes = KW * Cfg::A_BYTES + Cfg::B_BYTES;
-    const int umma_n = 2 * plan.half_cols;
-    const uint32_t tx = 2u * (KW * Cfg::A_BYTES + uint32_t(plan.pitch) * plan.rows_per_half * UMMA_BK * 4);
+    const int umma_n = CTAS * plan.half_cols;
+    const uint32_t tx = uint32_t(CTAS) * (KW * Cfg::A_BYTES + uint32_t(plan.pitch) * plan.rows_per_half * UMMA_BK * 4);
     const int stages = int((Cfg::SMEM_BUDGET - UMMA_STORE_STAGING_BYTES) / stage_bytes);
-    UmmaSchedule sched = whole_tile_schedule((s.out_c + 2 * UMMA_BM - 1) / (2 * UMMA_BM), s.batch * prob.tiles_h,
+    UmmaSchedule sched = whole_tile_schedule((s.out_c + CTAS * UMMA_BM - 1) / (CTAS * UMMA_BM), s.batch * prob.tiles_h,
                                              s.k_h * prob.c_blocks, umma_n, tx, stages, dev.status_word);
     sched.raster_group = sched.tiles_m;
     const uint32_t smem_bytes = uint32_t(stages) * stage_bytes + UMMA_STORE_STAGING_BYTES + 1024;
     const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;
     CB200_REQUIRE(num_tiles < (1LL << 30), "conv2d: too many tiles");
-    long long groups = dev.num_sms / 2;
+    long long groups = dev.num_sms / CTAS;
     if (groups > num_tiles) groups = num_tiles;
     CB200_TRACE("conv2d implicit GEMM tcgen05, rows shared by the taps of a filter row: N=%d C=%d %dx%d -> OC=%d "
-                "%dx%d, %dx3 pad %dx%d; %d rows x %d pixels per CTA = %d columns per pair, stages=%d of %u KB, "
+                "%dx%d, %dx3 pad %dx%d; %d rows x %d pixels per CTA = %d columns per MMA, ctas/mma=%d, stages=%d of %u KB, "
                 "clusters=%lld, stages per tile=%d",
                 s.batch, s.in_c, s.in_h, s.in_w, s.out_c, oh, ow, s.k_h, s.p_h, s.p_w, plan.rows_per_half, plan.pitch,
-                umma_n, stages, stage_bytes / 1024, groups, sched.k_blocks);
-    auto kernel = umma_tf32_kernel<2, 256, false, KW, ConvRowProblem>;
+                umma_n, CTAS, stages, stage_bytes / 1024, groups, sched.k_blocks);
+    auto kernel = umma_tf32_kernel<CTAS, 256, false, KW, ConvRowProblem<CTAS>>;
     UmmaEpilogueArgs epi{bias, 1, act};
-    launch_umma(kernel, prob, sched, epi, groups, 2, smem_bytes, Cfg::SMEM_MAX, stream);
+    launch_umma(kernel, prob, sched, epi, groups, CTAS, smem_bytes, Cfg::SMEM_MAX, stream);
 }
 
 struct TilePlan {
@@ -979,7 +989,8 @@ void plan_and_launch(const float* xt, const float* wp, const float* bias, float*
     if (!row_packed && rows_form_enabled()) {
         const RowPlan rows = plan_rows(s, ctas, output, extras == nullptr);
         if (rows.rows_per_half > 0) {
-            launch_conv_rows(xt, wp, bias, output, s, cx, cp, rows, act, stream);
+            if (ctas == 2) launch_conv_rows<2>(xt, wp, bias, output, s, cx, cp, rows, act, stream);
+            else launch_conv_rows<1>(xt, wp, bias, output, s, cx, cp, rows, act, stream);
             return;
         }
     }

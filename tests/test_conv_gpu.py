@@ -117,6 +117,9 @@ def test_tensor_core_path_shapes(dev, oracle, shape, oc, k, padding, act):
     ((2, 36, 30, 26), 256, (5, 3), (2, 0)),      # five filter rows, no horizontal padding: 24-pixel rows
     ((2, 64, 26, 42), 256, (3, 3), (0, 1)),      # no vertical padding: 24 output rows of 40 pixels
     ((5, 100, 32, 32), 512, (3, 3), (1, 1)),     # channels padded 100 -> 128, 512 output channels: two tile rows
+    ((2, 64, 56, 56), 64, (3, 3), (1, 1)),       # one CTA per tile: 4 rows x 58 pixels, half of the 128 MMA rows are channels
+    ((3, 128, 28, 28), 128, (3, 3), (1, 1)),     # one CTA: 8 rows x 30 pixels = 240 columns
+    ((1, 48, 33, 32), 96, (3, 3), (1, 1)),       # one CTA, 33 rows in tiles of 7, 96 channels
 ])
 @pytest.mark.parametrize("act", [0, 2])
 def test_rows_shared_by_the_taps_of_a_filter_row(dev, oracle, shape, oc, k, padding, act):
