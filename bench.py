@@ -818,7 +818,8 @@ def run_b2(lib, ref, timed, emit, ok, P, stream, trim):
 
 def run_v1(lib, timed, emit, ok, P, stream, trim):
     """Convolution layers of a ResNet-style network other than C4, batch 64: a 7 x 7 stride-2 stem over
-    three channels, a stride-2 down-sampling layer and the 14 x 14 and 7 x 7 feature maps; forward
+    three channels, the 3 x 3 layers of the 56 x 56, 28 x 28, 14 x 14 and 7 x 7 feature maps and a stride-2
+    down-sampling layer; forward
     (bias, no activation), grad_input and grad_weight against cuDNN (TF32) through torch."""
     import torch
     import torch.nn.functional as F
@@ -826,8 +827,8 @@ def run_v1(lib, timed, emit, ok, P, stream, trim):
     torch.backends.cudnn.allow_tf32 = True
     torch.backends.cudnn.benchmark = True
     nb = 64
-    for ch, size, oc, k, s, p in [(3, 224, 64, 7, 2, 3), (64, 56, 128, 3, 2, 1), (256, 14, 256, 3, 1, 1),
-                                  (512, 7, 512, 3, 1, 1)]:
+    for ch, size, oc, k, s, p in [(3, 224, 64, 7, 2, 3), (64, 56, 64, 3, 1, 1), (64, 56, 128, 3, 2, 1),
+                                  (128, 28, 128, 3, 1, 1), (256, 14, 256, 3, 1, 1), (512, 7, 512, 3, 1, 1)]:
         out = (size + 2 * p - k) // s + 1
         x = torch.randn((nb, ch, size, size), device="cuda")
         w = torch.randn((oc, ch, k, k), device="cuda") * (2.0 / (ch * k * k)) ** 0.5

@@ -20,6 +20,8 @@
 // per 256 output channels but a very long K, so K is cut into ranges, one tile-sized partial
 // result per range goes to scratch (bulk tensor stores), and a small kernel adds the ranges in a
 // fixed order and writes the [OC][C][KH][KW] layout - bitwise reproducible, no atomics.
+#include <cstdlib>
+
 #include "conv_igemm.h"
 #include "umma_gemm.cuh"
 
@@ -31,7 +33,7 @@ namespace {
 // {KW * Cx, OW, H, N, 1} of the width-padded input copy, whose rows are the windows of KW pixels x Cx
 // channels the output columns read (the forward path's row-packed form), so the 32 columns of a
 // tile are a filter row's (tap, channel) pairs.
-template <int CTAS, bool ROW_PACKED = false>
+template <int CTAS, bool ROW_PACKED = false, bool MULTI_TAP = false>
 struct WgradProblem {
     static constexpr bool kTmaStore = true;
     static constexpr bool kClusterSplit = false;
@@ -43,7 +45,9 @@ struct WgradProblem {
     int c_tiles;            // channel tiles (of umma_n channels) per tap
     int taps, k_w, p_h, p_w;
     int s_h, s_w;           // convolution strides
-    int n_cols;             // channels per tile (umma_n)
+    int n_cols;             // accumulator columns per tile (umma_n)
+    int taps_per_tile;      // > 1 (few channels): a tile's columns are this many taps x all cp channels, so the
+                            // grad_output block a K step loads serves several taps (c_tiles == 1 then)
     int cp;                 // padded channels
     int ocp;                // padded output channels: rows of one K range in the scratch
     int dy_row_pitch;       // > 0: map_dy is {OH * pitch, 1, OC, N} over a copy with rows padded to `pitch`
@@ -67,12 +71,20 @@ struct WgradProblem {
     __device__ __forceinline__ Tile decode(int tm, int tn, uint32_t cta_rank) const {
         Tile t;
         t.oc0 = (tm * CTAS + int(cta_rank)) * UMMA_BM;
-        const int per_range = taps * c_tiles;
+        const int tap_tiles = (taps + taps_per_tile - 1) / taps_per_tile;
+        const int per_range = tap_tiles * c_tiles;
         t.range = tn / per_range;
         const int r = tn - t.range * per_range;
-        t.tap = r / c_tiles;
-        t.c0 = (r - t.tap * c_tiles) * n_cols;
-        t.cb0 = t.c0 + int(cta_rank) * (n_cols / CTAS);
+        const int tap_tile = r / c_tiles;
+        t.tap = tap_tile * taps_per_tile;
+        if constexpr (MULTI_TAP) {
+            // cb0: the first of the tile's taps this CTA stages (all channels of each).
+            t.c0 = 0;
+            t.cb0 = int(cta_rank) * (taps_per_tile / CTAS);
+        } else {
+            t.c0 = (r - tap_tile * c_tiles) * n_cols;
+            t.cb0 = t.c0 + int(cta_rank) * (n_cols / CTAS);
+        }
         return t;
     }
     template <int C>
@@ -88,17 +100,33 @@ struct WgradProblem {
         const int th = r / tiles_w;
         const int oh0 = th * box_h;
         const int ow0 = (r - th * tiles_w) * box_w;
-        const int kh = ROW_PACKED ? t.tap : t.tap / k_w;
-        const int x1 = ROW_PACKED ? ow0 : ow0 * s_w + (t.tap - kh * k_w) - p_w;
         const int dy_x = dy_row_pitch > 0 ? oh0 * dy_row_pitch : ow0;
         const int dy_y = dy_row_pitch > 0 ? 0 : oh0;
-        if constexpr (C == 1) {
-            ptx::tma_load_4d(a_smem, &map_dy, bar, dy_x, dy_y, t.oc0, n);
-            ptx::tma_load_5d(b_smem, &map_x, bar, 0, x1, oh0 * s_h + kh - p_h, n, t.cb0 / 32);
-        } else {
-            ptx::tma_load_4d_pair(a_smem, &map_dy, bar, dy_x, dy_y, t.oc0, n);
-            ptx::tma_load_5d_pair(b_smem, &map_x, bar, 0, x1, oh0 * s_h + kh - p_h, n, t.cb0 / 32);
+        if constexpr (C == 1) ptx::tma_load_4d(a_smem, &map_dy, bar, dy_x, dy_y, t.oc0, n);
+        else ptx::tma_load_4d_pair(a_smem, &map_dy, bar, dy_x, dy_y, t.oc0, n);
+        if constexpr (MULTI_TAP) {
+            {
+                // One box of all channels per tap, side by side as column groups; a tap past the
+                // filter's last one reads zeros (image index out of range), its columns are clipped.
+                const int mine = taps_per_tile / C;
+                const uint32_t group_bytes = uint32_t(cp / 32) * 4096u;
+                for (int tl = 0; tl < mine; ++tl) {
+                    const int tap = t.tap + t.cb0 + tl;
+                    const int kh = tap / k_w;
+                    const int x1 = ow0 * s_w + (tap - kh * k_w) - p_w;
+                    const int nn = tap < taps ? n : batch;
+                    if constexpr (C == 1)
+                        ptx::tma_load_5d(b_smem + tl * group_bytes, &map_x, bar, 0, x1, oh0 * s_h + kh - p_h, nn, 0);
+                    else
+                        ptx::tma_load_5d_pair(b_smem + tl * group_bytes, &map_x, bar, 0, x1, oh0 * s_h + kh - p_h, nn, 0);
+                }
+                return;
+            }
         }
+        const int kh = ROW_PACKED ? t.tap : t.tap / k_w;
+        const int x1 = ROW_PACKED ? ow0 : ow0 * s_w + (t.tap - kh * k_w) - p_w;
+        if constexpr (C == 1) ptx::tma_load_5d(b_smem, &map_x, bar, 0, x1, oh0 * s_h + kh - p_h, n, t.cb0 / 32);
+        else ptx::tma_load_5d_pair(b_smem, &map_x, bar, 0, x1, oh0 * s_h + kh - p_h, n, t.cb0 / 32);
     }
     __device__ __forceinline__ const CUtensorMap* out_map() const { return &map_part; }
     __device__ __forceinline__ void out_coords(const Tile& t, int row_in_cta, int c0, int& x, int& y) const {
@@ -218,6 +246,7 @@ struct WgradPlan {
     int dy_pitch;       // floats per row of the grad_output the kernel reads
     bool narrow;        // rows of at most 16 pixels: several rows per K block, always from a padded copy
     int ctas, box_w, box_h, n_cols, c_tiles, ranges, kb_per_range, tiles_w, tiles_h, cp, ocp;
+    int taps_per_tile;  // see WgradProblem
     size_t nhwc_bytes, part_bytes;
 };
 
@@ -243,6 +272,17 @@ WgradPlan plan_wgrad(const ConvShape& s, int num_sms) {
         p.n_cols = widest(32);
     }
     p.c_tiles = p.cp / p.n_cols;
+    // Few channels: the accumulator's 256 columns hold several taps of all channels, so that the
+    // grad_output block of a K step (128 requests of the TMA unit, whatever the channel count) is
+    // multiplied with 256 columns instead of 64 or 128.
+    p.taps_per_tile = 1;
+    static const bool several_taps = [] { const char* v = std::getenv("CUDEEP_B200_WGRAD_TAPS"); return !(v && v[0] == '0'); }();
+    if (several_taps && !p.row_packed && p.cp <= 128 && p.taps >= 2) {
+        p.taps_per_tile = 256 / p.cp;                 // 2, 4 or 8: even, so a pair splits it
+        p.n_cols = p.taps_per_tile * p.cp;
+        p.c_tiles = 1;
+        p.ctas = s.out_c > UMMA_BM ? 2 : 1;           // 128 columns per CTA of a pair again
+    }
     // A K block is 32 consecutive pixels of one output row.  A swizzled TMA box whose inner extent
     // is under 128 bytes is not packed densely in shared memory, so boxes of 16 x 2 or 8 x 4 pixels
     // cannot be read from grad_output in place; for rows of at most 16 pixels they are read from
@@ -261,7 +301,8 @@ WgradPlan plan_wgrad(const ConvShape& s, int num_sms) {
     const long long total_kb = static_cast<long long>(s.batch) * p.tiles_h * p.tiles_w;
     const int tiles_m = (s.out_c + UMMA_BM * p.ctas - 1) / (UMMA_BM * p.ctas);
     p.ocp = tiles_m * UMMA_BM * p.ctas;
-    const long long base_tiles = static_cast<long long>(tiles_m) * p.taps * p.c_tiles;
+    const int tap_tiles = (p.taps + p.taps_per_tile - 1) / p.taps_per_tile;
+    const long long base_tiles = static_cast<long long>(tiles_m) * tap_tiles * p.c_tiles;
     // Enough K ranges to give every CTA (pair) a unit, each at least 16 K blocks long.
     const long long slots = num_sms / p.ctas;
     long long ranges = slots / base_tiles;
@@ -282,11 +323,11 @@ WgradPlan plan_wgrad(const ConvShape& s, int num_sms) {
 
 // dy_pitch: floats between consecutive rows of grad_output as passed here (OW, or the plan's
 // pitch when a padded copy had to be made).
-template <int CTAS, int KATOMS, bool ROW_PACKED = false>
+template <int CTAS, int KATOMS, bool ROW_PACKED = false, bool MULTI_TAP = false>
 void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, const ConvShape& s,
                   const WgradPlan& p, cudaStream_t stream) {
     using Cfg = UmmaConfig<CTAS, 256, true, KATOMS>;
-    using Prob = WgradProblem<CTAS, ROW_PACKED>;
+    using Prob = WgradProblem<CTAS, ROW_PACKED, MULTI_TAP>;
     const DeviceInfo& dev = device_info();
     const int oh = s.out_h(), ow = s.out_w();
     const int taps = p.taps;
@@ -320,7 +361,7 @@ void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, c
                                      uint64_t(s.in_h) * s.in_w * p.cp * 4, 128};
         // With strides the box spans box * stride input pixels walked in steps of the stride.
         const uint32_t box[5] = {32, uint32_t(p.box_w * s.s_w), uint32_t(p.box_h * s.s_h), 1,
-                                 uint32_t(p.n_cols / CTAS / 32)};
+                                 uint32_t(p.taps_per_tile > 1 ? p.cp / 32 : p.n_cols / CTAS / 32)};
         const uint32_t steps[5] = {1, uint32_t(s.s_w), uint32_t(s.s_h), 1, 1};
         encode_tensor_map(&prob.map_x, xt, 5, dims, strides, box, TmaSwizzle::B128Atom32, steps);
     }
@@ -342,6 +383,7 @@ void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, c
     prob.s_h = s.s_h;
     prob.s_w = s.s_w;
     prob.n_cols = p.n_cols;
+    prob.taps_per_tile = p.taps_per_tile;
     prob.cp = p.cp;
     prob.ocp = p.ocp;
     prob.dy_row_pitch = p.narrow ? dy_pitch : 0;
@@ -351,7 +393,8 @@ void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, c
 
     const int fit_stages = int((Cfg::SMEM_BUDGET - UMMA_STORE_STAGING_BYTES) / Cfg::STAGE_BYTES);
     UmmaSchedule sched = whole_tile_schedule(
-        p.ocp / (UMMA_BM * CTAS), p.ranges * taps * p.c_tiles, p.kb_per_range, p.n_cols,
+        p.ocp / (UMMA_BM * CTAS), p.ranges * ((taps + p.taps_per_tile - 1) / p.taps_per_tile) * p.c_tiles,
+        p.kb_per_range, p.n_cols,
         (Cfg::A_BYTES + uint32_t(p.n_cols / CTAS) * UMMA_BK * 4) * CTAS * KATOMS,
         fit_stages < Cfg::STAGES ? fit_stages : Cfg::STAGES, dev.status_word);
     sched.raster_group = sched.tiles_m;
@@ -365,9 +408,9 @@ void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, c
     if (groups > num_tiles) groups = num_tiles;
 
     CB200_TRACE("conv2d grad_weight implicit GEMM tcgen05: N=%d C=%d %dx%d OC=%d, %dx%d stride %dx%d; %d columns, "
-                "K ranges=%d of %d blocks, ctas/mma=%d stages=%d clusters=%lld",
-                s.batch, s.in_c, s.in_h, s.in_w, s.out_c, s.k_h, s.k_w, s.s_h, s.s_w, p.n_cols, p.ranges,
-                p.kb_per_range, CTAS, sched.stages, groups);
+                "taps per tile=%d, K ranges=%d of %d blocks, ctas/mma=%d stages=%d clusters=%lld",
+                s.batch, s.in_c, s.in_h, s.in_w, s.out_c, s.k_h, s.k_w, s.s_h, s.s_w, p.n_cols, p.taps_per_tile,
+                p.ranges, p.kb_per_range, CTAS, sched.stages, groups);
     auto kernel = umma_tf32_kernel<CTAS, 256, true, KATOMS, Prob>;
     UmmaEpilogueArgs epi{nullptr, 0, EPI_NONE};
     launch_umma(kernel, prob, sched, epi, groups, CTAS, smem_bytes, Cfg::SMEM_MAX, stream);
@@ -424,8 +467,15 @@ void conv2d_wgrad_igemm(const float* grad_output, const float* input, float* gra
                 part, grad_weight, p.ranges, s.out_c, p.ocp, s.in_c, cx, s.k_h, s.k_w);
         } else {
             nchw_to_nhwc(input, xt, s.batch, s.in_c, s.in_h * s.in_w, p.cp, stream);
-            if (p.ctas == 2) launch_wgrad<2, 2>(dy, copy_dy ? dy_pitch : ow, xt, part, s, p, stream);
-            else launch_wgrad<1, 1>(dy, copy_dy ? dy_pitch : ow, xt, part, s, p, stream);
+            const int pitch = copy_dy ? dy_pitch : ow;
+            if (p.taps_per_tile > 1) {
+                if (p.ctas == 2) launch_wgrad<2, 2, false, true>(dy, pitch, xt, part, s, p, stream);
+                else launch_wgrad<1, 1, false, true>(dy, pitch, xt, part, s, p, stream);
+            } else if (p.ctas == 2) {
+                launch_wgrad<2, 2>(dy, pitch, xt, part, s, p, stream);
+            } else {
+                launch_wgrad<1, 1>(dy, pitch, xt, part, s, p, stream);
+            }
             const int taps = s.k_h * s.k_w;
             if (taps <= 65) {
                 // Channels per block: as many 32-channel groups as fit the tile (all of them for 1 x 1).
