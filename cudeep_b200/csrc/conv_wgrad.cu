@@ -278,10 +278,22 @@ WgradPlan plan_wgrad(const ConvShape& s, int num_sms) {
     p.taps_per_tile = 1;
     static const bool several_taps = [] { const char* v = std::getenv("CUDEEP_B200_WGRAD_TAPS"); return !(v && v[0] == '0'); }();
     if (several_taps && !p.row_packed && p.cp <= 128 && p.taps >= 2) {
-        p.taps_per_tile = 256 / p.cp;                 // 2, 4 or 8: even, so a pair splits it
+        // How many: the count (even for a pair, which splits the taps between its CTAs) that needs the
+        // fewest requests for all taps - per tile and K step 128 rows of grad_output and one row of
+        // 32 pixels per channel chunk and tap.  A 3 x 3 filter over 64 channels takes 3 tiles of
+        // 3 taps (192 columns), not 2 of 4 and one of 1.
+        p.ctas = s.out_c > UMMA_BM ? 2 : 1;           // 128 columns per CTA of a pair again
+        long long best_cost = -1;
+        for (int t = p.ctas; t * p.cp <= 256; t += p.ctas) {
+            const long long cost = static_cast<long long>((p.taps + t - 1) / t) * (128 + t * p.cp);
+            if (best_cost < 0 || cost < best_cost) {
+                best_cost = cost;
+                p.taps_per_tile = t;
+            }
+        }
         p.n_cols = p.taps_per_tile * p.cp;
         p.c_tiles = 1;
-        p.ctas = s.out_c > UMMA_BM ? 2 : 1;           // 128 columns per CTA of a pair again
+        if (p.taps_per_tile == 1) p.n_cols = p.cp;    // (a pair never gets here: its smallest count is 2)
     }
     // A K block is 32 consecutive pixels of one output row.  A swizzled TMA box whose inner extent
     // is under 128 bytes is not packed densely in shared memory, so boxes of 16 x 2 or 8 x 4 pixels
