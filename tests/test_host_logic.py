@@ -126,8 +126,12 @@ def test_plan_fills_the_machine_with_wide_pair_tiles(lib):
 
 
 def test_plan_narrows_tiles_for_small_problems(lib):
-    assert _plan(lib, 1024, 1024, 1024)[:3] == (1, 64, 1)       # 128 tiles of 128 x 64 on 148 SMs
-    assert _plan(lib, 256, 256, 256)[:3] == (1, 64, 1)
+    # Small cubes: narrow tiles, and the reduction split two ways inside a cluster so that both more SMs
+    # work and each takes in half the operand bytes (the exchange costs less than that saves).
+    assert _plan(lib, 1024, 1024, 1024)[:3] == (1, 128, 2)      # 64 tiles of 128 x 128, two CTAs each
+    assert _plan(lib, 512, 512, 512)[:3] == (1, 64, 2)          # 32 tiles of 128 x 64, two CTAs each
+    assert _plan(lib, 256, 256, 256)[:3] == (1, 64, 2)
+    assert _plan(lib, 128, 128, 64)[:3] == (1, 64, 1)           # two K blocks: nothing to split
     ctas, bn, split, _, _ = _plan(lib, 1536, 1536, 1536)
     assert (ctas, bn, split) == (2, 128, 1)                     # 72 CTA pairs of 256 x 128
 
