@@ -33,10 +33,15 @@ namespace {
 // {KW * Cx, OW, H, N, 1} of the width-padded input copy, whose rows are the windows of KW pixels x Cx
 // channels the output columns read (the forward path's row-packed form), so the 32 columns of a
 // tile are a filter row's (tap, channel) pairs.
-template <int CTAS, bool ROW_PACKED = false, bool MULTI_TAP = false>
+// TAP_SHIFT (one CTA per tile, stride 1, three taps per filter row, rows of more than 16 pixels): a
+// tile is one filter row kh and 64 channels; its 192 accumulator columns are [kw][channel], and the
+// K step loads 32 + 4 input pixels once for the three taps (tap_shift_of in umma_gemm.cuh).
+template <int CTAS, bool ROW_PACKED = false, bool MULTI_TAP = false, bool TAP_SHIFT = false>
 struct WgradProblem {
     static constexpr bool kTmaStore = true;
     static constexpr bool kClusterSplit = false;
+    static constexpr int kTapShift = TAP_SHIFT ? 3 : 0;
+    static constexpr int kTapColumns = 64;
     CUtensorMap map_dy;     // {OW, OH, OC, N}, box {box_w, box_h, 128, 1}
     CUtensorMap map_x;      // {32, W, H, N, Cp/32}, box {32, box_w, box_h, 1, chunks per CTA}
     CUtensorMap map_part;   // partial results [ranges * OCp][taps * Cp], box {32, 32}
@@ -77,7 +82,14 @@ struct WgradProblem {
         const int r = tn - t.range * per_range;
         const int tap_tile = r / c_tiles;
         t.tap = tap_tile * taps_per_tile;
-        if constexpr (MULTI_TAP) {
+        if constexpr (TAP_SHIFT) {
+            // tn enumerates (range, kh, 64-channel tile); t.tap is the row's first tap.
+            const int c64 = cp / 64;
+            const int kh = r / c64;
+            t.tap = kh * k_w;
+            t.c0 = (r - kh * c64) * 64;
+            t.cb0 = t.c0;
+        } else if constexpr (MULTI_TAP) {
             // cb0: the first of the tile's taps this CTA stages (all channels of each).
             t.c0 = 0;
             t.cb0 = int(cta_rank) * (taps_per_tile / CTAS);
@@ -104,6 +116,12 @@ struct WgradProblem {
         const int dy_y = dy_row_pitch > 0 ? 0 : oh0;
         if constexpr (C == 1) ptx::tma_load_4d(a_smem, &map_dy, bar, dy_x, dy_y, t.oc0, n);
         else ptx::tma_load_4d_pair(a_smem, &map_dy, bar, dy_x, dy_y, t.oc0, n);
+        if constexpr (TAP_SHIFT) {
+            // The pixels under filter row kh for all three taps: 36 from the first tap's start on.
+            const int kh = t.tap / k_w;
+            ptx::tma_load_5d(b_smem, &map_x, bar, 0, ow0 - p_w, oh0 + kh - p_h, n, t.cb0 / 32);
+            return;
+        }
         if constexpr (MULTI_TAP) {
             {
                 // One box of all channels per tap, side by side as column groups; a tap past the
@@ -130,7 +148,8 @@ struct WgradProblem {
     }
     __device__ __forceinline__ const CUtensorMap* out_map() const { return &map_part; }
     __device__ __forceinline__ void out_coords(const Tile& t, int row_in_cta, int c0, int& x, int& y) const {
-        x = t.tap * cp + t.c0 + c0;
+        if constexpr (TAP_SHIFT) x = (t.tap + c0 / 64) * cp + t.c0 + (c0 & 63);      // columns are [kw][64 channels]
+        else x = t.tap * cp + t.c0 + c0;
         y = t.range * ocp + t.oc0 + row_in_cta;
     }
     __device__ __forceinline__ void finish(const Tile&, int, int, float (&)[32], const UmmaEpilogueArgs&) const {}
@@ -247,6 +266,7 @@ struct WgradPlan {
     bool narrow;        // rows of at most 16 pixels: several rows per K block, always from a padded copy
     int ctas, box_w, box_h, n_cols, c_tiles, ranges, kb_per_range, tiles_w, tiles_h, cp, ocp;
     int taps_per_tile;  // see WgradProblem
+    bool tap_shift;     // one load of the input pixels serves the three taps of a filter row
     size_t nhwc_bytes, part_bytes;
 };
 
@@ -295,6 +315,15 @@ WgradPlan plan_wgrad(const ConvShape& s, int num_sms) {
         p.c_tiles = 1;
         if (p.taps_per_tile == 1) p.n_cols = p.cp;    // (a pair never gets here: its smallest count is 2)
     }
+    // One CTA per tile, stride 1, three taps per filter row, whole 64-channel tiles: the taps share the pixels.
+    p.tap_shift = several_taps && !p.row_packed && s.out_c <= UMMA_BM && s.k_w == 3 && s.s_h == 1 && s.s_w == 1 &&
+                  p.cp % 64 == 0 && ow > 16;
+    if (p.tap_shift) {
+        p.ctas = 1;
+        p.taps_per_tile = 3;
+        p.n_cols = 192;
+        p.c_tiles = p.cp / 64;
+    }
     // A K block is 32 consecutive pixels of one output row.  A swizzled TMA box whose inner extent
     // is under 128 bytes is not packed densely in shared memory, so boxes of 16 x 2 or 8 x 4 pixels
     // cannot be read from grad_output in place; for rows of at most 16 pixels they are read from
@@ -335,11 +364,11 @@ WgradPlan plan_wgrad(const ConvShape& s, int num_sms) {
 
 // dy_pitch: floats between consecutive rows of grad_output as passed here (OW, or the plan's
 // pitch when a padded copy had to be made).
-template <int CTAS, int KATOMS, bool ROW_PACKED = false, bool MULTI_TAP = false>
+template <int CTAS, int KATOMS, bool ROW_PACKED = false, bool MULTI_TAP = false, bool TAP_SHIFT = false>
 void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, const ConvShape& s,
                   const WgradPlan& p, cudaStream_t stream) {
     using Cfg = UmmaConfig<CTAS, 256, true, KATOMS>;
-    using Prob = WgradProblem<CTAS, ROW_PACKED, MULTI_TAP>;
+    using Prob = WgradProblem<CTAS, ROW_PACKED, MULTI_TAP, TAP_SHIFT>;
     const DeviceInfo& dev = device_info();
     const int oh = s.out_h(), ow = s.out_w();
     const int taps = p.taps;
@@ -372,8 +401,10 @@ void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, c
         const uint64_t strides[4] = {uint64_t(p.cp) * 4, uint64_t(s.in_w) * p.cp * 4,
                                      uint64_t(s.in_h) * s.in_w * p.cp * 4, 128};
         // With strides the box spans box * stride input pixels walked in steps of the stride.
-        const uint32_t box[5] = {32, uint32_t(p.box_w * s.s_w), uint32_t(p.box_h * s.s_h), 1,
-                                 uint32_t(p.taps_per_tile > 1 ? p.cp / 32 : p.n_cols / CTAS / 32)};
+        // (Tap shift: 32 pixels and the next 4, of which the taps reach 2; 36 rows keep every
+        // 32-channel chunk on a 512-byte boundary, the period of the swizzle.  Two chunks per tile.)
+        const uint32_t box[5] = {32, uint32_t(TAP_SHIFT ? 36 : p.box_w * s.s_w), uint32_t(p.box_h * s.s_h), 1,
+                                 uint32_t(TAP_SHIFT ? 2 : p.taps_per_tile > 1 ? p.cp / 32 : p.n_cols / CTAS / 32)};
         const uint32_t steps[5] = {1, uint32_t(s.s_w), uint32_t(s.s_h), 1, 1};
         encode_tensor_map(&prob.map_x, xt, 5, dims, strides, box, TmaSwizzle::B128Atom32, steps);
     }
@@ -407,9 +438,10 @@ void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, c
     UmmaSchedule sched = whole_tile_schedule(
         p.ocp / (UMMA_BM * CTAS), p.ranges * ((taps + p.taps_per_tile - 1) / p.taps_per_tile) * p.c_tiles,
         p.kb_per_range, p.n_cols,
-        (Cfg::A_BYTES + uint32_t(p.n_cols / CTAS) * UMMA_BK * 4) * CTAS * KATOMS,
+        TAP_SHIFT ? Cfg::A_BYTES + 2u * 36u * 128u : (Cfg::A_BYTES + uint32_t(p.n_cols / CTAS) * UMMA_BK * 4) * CTAS * KATOMS,
         fit_stages < Cfg::STAGES ? fit_stages : Cfg::STAGES, dev.status_word);
     sched.raster_group = sched.tiles_m;
+    if (TAP_SHIFT) sched.b_lbo = 36u * 128u;      // channel chunks lie one 36-row box apart
     sched.tma_store = 1;
     sched.ring_staging = uint32_t(sched.stages) * Cfg::STAGE_BYTES >= 131072u ? 1 : 0;
     const uint32_t smem_bytes = uint32_t(sched.stages) * Cfg::STAGE_BYTES + UMMA_STORE_STAGING_BYTES + 1024;
@@ -420,9 +452,9 @@ void launch_wgrad(const float* dy, int dy_pitch, const float* xt, float* part, c
     if (groups > num_tiles) groups = num_tiles;
 
     CB200_TRACE("conv2d grad_weight implicit GEMM tcgen05: N=%d C=%d %dx%d OC=%d, %dx%d stride %dx%d; %d columns, "
-                "taps per tile=%d, K ranges=%d of %d blocks, ctas/mma=%d stages=%d clusters=%lld",
+                "taps per tile=%d%s, K ranges=%d of %d blocks, ctas/mma=%d stages=%d clusters=%lld",
                 s.batch, s.in_c, s.in_h, s.in_w, s.out_c, s.k_h, s.k_w, s.s_h, s.s_w, p.n_cols, p.taps_per_tile,
-                p.ranges, p.kb_per_range, CTAS, sched.stages, groups);
+                TAP_SHIFT ? " sharing one load of the pixels" : "", p.ranges, p.kb_per_range, CTAS, sched.stages, groups);
     auto kernel = umma_tf32_kernel<CTAS, 256, true, KATOMS, Prob>;
     UmmaEpilogueArgs epi{nullptr, 0, EPI_NONE};
     launch_umma(kernel, prob, sched, epi, groups, CTAS, smem_bytes, Cfg::SMEM_MAX, stream);
@@ -480,7 +512,9 @@ void conv2d_wgrad_igemm(const float* grad_output, const float* input, float* gra
         } else {
             nchw_to_nhwc(input, xt, s.batch, s.in_c, s.in_h * s.in_w, p.cp, stream);
             const int pitch = copy_dy ? dy_pitch : ow;
-            if (p.taps_per_tile > 1) {
+            if (p.tap_shift) {
+                launch_wgrad<1, 1, false, false, true>(dy, pitch, xt, part, s, p, stream);
+            } else if (p.taps_per_tile > 1) {
                 if (p.ctas == 2) launch_wgrad<2, 2, false, true>(dy, pitch, xt, part, s, p, stream);
                 else launch_wgrad<1, 1, false, true>(dy, pitch, xt, part, s, p, stream);
             } else if (p.ctas == 2) {

@@ -216,6 +216,21 @@ struct has_plane_store<P, decltype((void)P::kPlaneStore)> { static constexpr boo
 //   __device__ int row_values() const;                   values per row (<= 64)
 //   __device__ void row_coords(tile, int row0, int r, int& x, int& y, int& z) const;   for out_map()
 //   finish() as for kTmaStore; out_map() is a 3-D map {OW, OH, planes}, box {OW, 1, 32}, no swizzle.
+// The mirror image for a grad_weight (B = input pixels as the K rows of an MN-major operand, A =
+// grad_output, shared by all taps): `static constexpr int kTapShift = T;` (and `kTapColumns`).
+// A stage is one ordinary atom whose B box is T - 1 pixels longer than the K block; tap t multiplies
+// the same A with the B rows from t on (start address t * 128 bytes later) into its own kTapColumns
+// accumulator columns, so one load of the input pixels serves the T taps of a filter row.  The B
+// descriptor's leading-dimension offset comes from the schedule (b_lbo: the box's rows x 128 bytes).
+template <class P, class = void>
+struct tap_shift_of { static constexpr int value = 0; };
+template <class P>
+struct tap_shift_of<P, decltype((void)P::kTapShift)> { static constexpr int value = P::kTapShift; };
+template <class P, class = void>
+struct tap_columns_of { static constexpr int value = 0; };
+template <class P>
+struct tap_columns_of<P, decltype((void)P::kTapColumns)> { static constexpr int value = P::kTapColumns; };
+
 template <class P, class = void>
 struct has_shared_b { static constexpr bool value = false; };
 template <class P>
@@ -442,6 +457,20 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                         // so each one is the stage's first descriptor plus a constant.
                         const uint64_t a_stage = a_desc0 + ((stage * STAGE_BYTES) >> 4);
                         const uint64_t b_stage = b_desc0 + ((stage * STAGE_BYTES) >> 4);
+                        constexpr int TAP_SHIFT = tap_shift_of<Problem>::value;
+                        if constexpr (TAP_SHIFT > 0) {
+                            constexpr int TAP_COLS = tap_columns_of<Problem>::value;
+                            const uint32_t idesc_tap =
+                                ptx::idesc_tf32(UMMA_BM * CTAS, TAP_COLS, A_MN_MAJOR ? 1 : 0, B_MN_MAJOR ? 1 : 0);
+#pragma unroll
+                            for (int t = 0; t < TAP_SHIFT; ++t) {
+#pragma unroll
+                                for (int kk = 0; kk < UMMA_BK / UMMA_K; ++kk)
+                                    ptx::umma_tf32<CTAS>(d_tmem + t * TAP_COLS, a_stage + ((kk * a_kstep) >> 4),
+                                                         b_stage + ((t * 128u + kk * b_kstep) >> 4), idesc_tap,
+                                                         (ks | kk) != 0);
+                            }
+                        } else {
 #pragma unroll
                         for (int j = 0; j < KATOMS; ++j) {
 #pragma unroll
@@ -459,6 +488,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                                     ptx::umma_tf32<CTAS>(d_tmem, a_desc, b_desc, idesc, (ks | j | kk) != 0);
                             }
                         }
+                        }      // !TAP_SHIFT
                     }
                     // Free the stage once these MMAs have read it (in both CTAs of a pair).
                     if (issuer && !free_run) {
