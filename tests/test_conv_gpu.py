@@ -360,6 +360,10 @@ def test_backward_against_oracle(dev, lib, oracle, shape, oc, k, stride, padding
     ((8, 8, 12, 12), 32, (3, 4), (1, 2)),       # row-packed and short rows (13 pixels padded to 16) together
     ((2, 1, 40, 40), 160, (5, 5), (2, 2)),      # a single input channel, 160 output channels
     ((2, 16, 6, 6), 32, (3, 3), (1, 1)),        # 72 output pixels: too few, the direct kernel
+    ((2, 64, 56, 56), 64, (3, 3), (1, 1)),      # the taps of a filter row share one load of 36 pixels; two boxes per row
+    ((3, 128, 20, 17), 96, (3, 3), (1, 1)),     # the same with two 64-channel tiles, 96 output channels, rows of 17 (padded copy)
+    ((2, 64, 18, 40), 128, (5, 3), (2, 0)),     # five filter rows, no horizontal padding: rows of 38 pixels
+    ((2, 64, 24, 24), 256, (3, 3), (1, 1)),     # 64 channels on a CTA pair: four taps per tile, loaded one by one
 ])
 def test_backward_weight_tensor_core_path(dev, lib, oracle, shape, oc, k, padding):
     """grad_weight as an implicit GEMM over output pixels (>= 32 output channels, >= 256 pixels): TF32
