@@ -529,6 +529,162 @@ struct ConvRowProblem {
     __device__ __forceinline__ void out_coords(const Tile&, int, int, int& x, int& y) const { x = y = 0; }
 };
 
+// The same sharing for small feature maps (7 x 7 and the like) on CTA pairs: a tile is four whole images,
+// two per CTA; a stage holds the three filter slabs of (kh, 32 channels) and, per image, the OH input
+// rows under filter row kh with OW + 2 pixels each (at most 63 pixels, in a slot of 64 operand rows).
+// Operand column n of an image is pixel (n / pitch, n % pitch).  The reduction may be split over the
+// pairs of a cluster, and the tile leaves as compacted planes (has_plane_store), both as for ConvProblem.
+struct ConvSmallMapProblem {
+    static constexpr bool kTmaStore = true;        // (finish() is used; no output map: tma_store stays 0)
+    static constexpr bool kClusterSplit = true;
+    static constexpr bool kSharedB = true;
+    static constexpr bool kPlaneStore = true;
+    CUtensorMap map_w;     // packed filters: dims {KH*3*Cp, OC}, box {32, 128}
+    CUtensorMap map_x;     // NHWC input: dims {Cx, W, H, N}, box {32, pitch, OH, 1}
+    float* out;
+    int oc_n, oh_n, ow_n, batch;
+    int pitch;             // OW + 2
+    int c_blocks, cp, p_h, p_w;
+    int total_stages;      // KH * c_blocks
+
+    struct Tile {
+        int oc0, n, nb0;
+    };
+    __device__ __forceinline__ void prefetch_maps() const {
+        ptx::prefetch_tensormap(&map_w);
+        ptx::prefetch_tensormap(&map_x);
+    }
+    __device__ __forceinline__ const CUtensorMap* out_map() const { return &map_w; }      // never used
+    __device__ __forceinline__ void out_coords(const Tile&, int, int, int& x, int& y) const { x = y = 0; }
+    __device__ __forceinline__ Tile decode(int tm, int tn, uint32_t cta_rank) const {
+        Tile t;
+        t.oc0 = (tm * 2 + int(cta_rank)) * UMMA_BM;
+        t.n = tn * 4;
+        t.nb0 = t.n + int(cta_rank) * 2;
+        return t;
+    }
+    template <int C>
+    __device__ __forceinline__ void load_stage(const Tile& t, int stage_index, uint32_t a_smem, uint32_t b_smem,
+                                               uint32_t bar) const {
+        static_assert(C == 2, "small maps run on CTA pairs");
+        const int kh = stage_index / c_blocks;
+        const int c0 = (stage_index - kh * c_blocks) * UMMA_BK;
+        // A stage past the end of a K range that is not a whole number of stages cannot occur: the
+        // ranges are counted in stages.
+#pragma unroll
+        for (int kw = 0; kw < 3; ++kw)
+            ptx::tma_load_2d_pair(a_smem + kw * (UMMA_BM * UMMA_BK * 4), &map_w, bar, (kh * 3 + kw) * cp + c0, t.oc0);
+#pragma unroll
+        for (int i = 0; i < 2; ++i)      // an image past the batch reads zeros
+            ptx::tma_load_4d_pair(b_smem + i * (64 * 128), &map_x, bar, c0, -p_w, kh - p_h, t.nb0 + i);
+    }
+    __device__ __forceinline__ void finish(const Tile& t, int row_in_cta, int /*c0*/, float (&v)[32],
+                                           const UmmaEpilogueArgs& epi) const {
+        const int oc = t.oc0 + row_in_cta;
+        if (epi.bias != nullptr && oc < oc_n) {
+            const float b = __ldg(epi.bias + oc);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += b;
+        }
+        apply_activation(v, epi.act);
+    }
+    __device__ __forceinline__ int plane_columns() const { return 64; }
+    __device__ __forceinline__ uint32_t plane_bytes() const { return 32u * uint32_t(oh_n * ow_n) * 4u; }
+    __device__ __forceinline__ float* plane_dst(const Tile& t, int row0, int plane) const {
+        const int oc = t.oc0 + row0;
+        if (oc >= oc_n || t.n + plane >= batch) return nullptr;
+        return out + (static_cast<long long>(t.n + plane) * oc_n + oc) * (oh_n * ow_n);
+    }
+    __device__ __forceinline__ void plane_stage(uint32_t staging, uint32_t lane, int col_in_plane,
+                                                const float (&v)[32]) const {
+        const uint32_t row = staging + lane * uint32_t(oh_n * ow_n) * 4u;
+        int oh = col_in_plane / pitch;
+        int ow = col_in_plane - oh * pitch;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (oh < oh_n && ow < ow_n) ptx::st_shared_f32(row + uint32_t(oh * ow_n + ow) * 4u, v[j]);
+            if (++ow == pitch) { ow = 0; ++oh; }
+        }
+    }
+    // Never used: every tile leaves as compacted planes.
+    __device__ __forceinline__ void store(const Tile&, int, int, float (&)[32], const UmmaEpilogueArgs&, int) const {}
+};
+
+// Whether that form takes a convolution: CTA pairs, three taps per filter row, stride 1, an image's
+// OH x (OW + 2) operand columns within 64, planes the compacted stores take (an odd number of floats,
+// at most 64), output the same size as the input (so the OH rows under filter row kh are one box).
+bool small_map_form_applies(const ConvShape& s, int ctas, const float* out, bool plain_output) {
+    const int oh = s.out_h(), ow = s.out_w();
+    if (ctas != 2 || !plain_output || s.k_w != 3 || s.s_h != 1 || s.s_w != 1 || s.batch < 4) return false;
+    if (oh * (ow + 2) > 64 || ow + 2 > 16 || (oh * ow) % 2 == 0 || oh * ow > 64) return false;
+    return s.out_c % 32 == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
+}
+
+void launch_conv_small_maps(const float* xt, const float* wp, const float* bias, float* out, const ConvShape& s,
+                            int cx, int cp, int act, cudaStream_t stream) {
+    constexpr int KW = 3;
+    using Cfg = UmmaConfig<2, 256, false, KW>;
+    const DeviceInfo& dev = device_info();
+    const int oh = s.out_h(), ow = s.out_w();
+    ConvSmallMapProblem prob;
+    {
+        const uint64_t dims[2] = {uint64_t(s.k_h) * KW * cp, uint64_t(s.out_c)};
+        const uint64_t strides[1] = {uint64_t(s.k_h) * KW * cp * 4};
+        const uint32_t box[2] = {UMMA_BK, UMMA_BM};
+        encode_tensor_map(&prob.map_w, wp, 2, dims, strides, box, TmaSwizzle::B128);
+    }
+    {
+        const uint64_t dims[4] = {uint64_t(cx), uint64_t(s.in_w), uint64_t(s.in_h), uint64_t(s.batch)};
+        const uint64_t strides[3] = {uint64_t(cx) * 4, uint64_t(s.in_w) * cx * 4, uint64_t(s.in_h) * s.in_w * cx * 4};
+        const uint32_t box[4] = {UMMA_BK, uint32_t(ow + 2), uint32_t(oh), 1};
+        encode_tensor_map(&prob.map_x, xt, 4, dims, strides, box, TmaSwizzle::B128);
+    }
+    prob.out = out;
+    prob.oc_n = s.out_c;
+    prob.oh_n = oh;
+    prob.ow_n = ow;
+    prob.batch = s.batch;
+    prob.pitch = ow + 2;
+    prob.c_blocks = cp / UMMA_BK;
+    prob.cp = cp;
+    prob.p_h = s.p_h;
+    prob.p_w = s.p_w;
+    prob.total_stages = s.k_h * prob.c_blocks;
+
+    constexpr uint32_t stage_bytes = KW * Cfg::A_BYTES + Cfg::B_BYTES;
+    const uint32_t tx = 2u * (KW * Cfg::A_BYTES + 2u * uint32_t(ow + 2) * oh * UMMA_BK * 4);
+    UmmaSchedule sched = whole_tile_schedule((s.out_c + 2 * UMMA_BM - 1) / (2 * UMMA_BM), (s.batch + 3) / 4,
+                                             prob.total_stages, 256, tx, 8, dev.status_word);
+    sched.raster_group = sched.tiles_m;
+    sched.plane_store = 1;
+    const long long num_tiles = static_cast<long long>(sched.tiles_m) * sched.tiles_n;
+    // Two K ranges per tile, on the two pairs of a cluster, when every tile finds its cluster at once
+    // and a range still has a few stages.
+    int ksplit = 1;
+    if (num_tiles * 4 <= dev.num_sms * 7 / 8 && prob.total_stages >= 8 && prob.total_stages % 2 == 0) ksplit = 2;
+    uint32_t exchange_bytes = 0, staging_bytes = UMMA_STORE_STAGING_BYTES;
+    if (ksplit > 1) {
+        sched.cluster_split = ksplit;
+        sched.kb_per_split = prob.total_stages / ksplit;
+        exchange_bytes = uint32_t(ksplit - 1) * UMMA_BM * uint32_t(256 / ksplit) * 4u;
+        staging_bytes = 0;                         // split tiles stage in the idle stage ring
+    }
+    sched.exchange_bytes = exchange_bytes;
+    sched.stages = int((Cfg::SMEM_BUDGET - exchange_bytes - staging_bytes) / stage_bytes);
+    const uint32_t smem_bytes = uint32_t(sched.stages) * stage_bytes + exchange_bytes + staging_bytes + 1024;
+    long long groups = dev.num_sms / 2;
+    if (groups > num_tiles) groups = num_tiles;
+    if (ksplit > 1) groups = num_tiles;
+    CB200_TRACE("conv2d implicit GEMM tcgen05, small maps with rows shared by the taps of a filter row: N=%d C=%d "
+                "%dx%d -> OC=%d %dx%d, %dx3 pad %dx%d; four images of %d x %d pixels per tile, stages=%d of %u KB, "
+                "clusters=%lld, stages per tile=%d, cluster_split=%d, store=bulk planes",
+                s.batch, s.in_c, s.in_h, s.in_w, s.out_c, oh, ow, s.k_h, s.p_h, s.p_w, oh, ow + 2, sched.stages,
+                stage_bytes / 1024, groups, sched.k_blocks, ksplit);
+    auto kernel = umma_tf32_kernel<2, 256, false, KW, ConvSmallMapProblem>;
+    UmmaEpilogueArgs epi{bias, 1, act};
+    launch_umma(kernel, prob, sched, epi, groups, 2 * ksplit, smem_bytes, Cfg::SMEM_MAX, stream);
+}
+
 struct RowPlan {
     int rows_per_half = 0, pitch = 0, half_cols = 0;
 };
@@ -986,6 +1142,10 @@ void plan_and_launch(const float* xt, const float* wp, const float* bias, float*
     const int oh = s.out_h(), ow = s.out_w();
     int ctas = force_ctas;
     if (ctas == 0) ctas = (s.out_c > UMMA_BM) ? 2 : 1;
+    if (!row_packed && rows_form_enabled() && small_map_form_applies(s, ctas, output, extras == nullptr)) {
+        launch_conv_small_maps(xt, wp, bias, output, s, cx, cp, act, stream);
+        return;
+    }
     if (!row_packed && rows_form_enabled()) {
         const RowPlan rows = plan_rows(s, ctas, output, extras == nullptr);
         if (rows.rows_per_half > 0) {

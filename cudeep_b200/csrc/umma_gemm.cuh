@@ -600,7 +600,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                 }
                 prob.store(tile, row_in_cta, c, v, epi, w.mode);
             };
-            if constexpr (SHARED_B) {
+            if constexpr (SHARED_B && !has_plane_store<Problem>::value) {
                 // ---- the tile leaves one output row at a time: its values are a run of accumulator
                 // columns (the halo columns between rows are dropped), staged as a dense
                 // [32 channels][values] block and written by one 3-D bulk tensor store.
@@ -831,7 +831,7 @@ umma_tf32_kernel(const __grid_constant__ Problem prob, const UmmaSchedule sched,
                     }
                 }
             }
-            }      // !SHARED_B
+            }      // not the row-store form
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) {
