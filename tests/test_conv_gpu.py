@@ -94,6 +94,10 @@ def test_direct_path_shapes(dev, oracle, shape, oc, k, stride, padding):
     ((32, 192, 7, 7), 512, (3, 3), (1, 1)),      # 16 tiles of four images, 54 K blocks split two ways (clusters of 4)
     ((7, 160, 7, 7), 96, (3, 3), (1, 1)),        # one CTA per tile, split reduction, last tile partly empty
     ((16, 288, 4, 4), 128, (3, 3), (1, 1)),      # 4 x 4 maps (an even plane size: stored from registers), split reduction
+    ((9, 64, 5, 5), 256, (3, 3), (1, 1)),        # 5 x 5 maps on a pair: taps share rows of 7 pixels, 6 stages unsplit, 9 images
+    ((10, 288, 3, 3), 512, (3, 3), (1, 1)),      # 3 x 3 maps: 15 of 64 operand rows per image are pixels; 27 stages, unsplit
+    ((5, 32, 7, 5), 160, (3, 3), (1, 1)),        # 7 x 5 maps, 160 channels (the second CTA's rows partly past OC), 3 stages
+    ((8, 128, 9, 7), 256, (5, 3), (2, 1)),       # five filter rows over 9 x 7 maps: 63 operand rows per image, the most
 ])
 @pytest.mark.parametrize("act", [0, 1])
 def test_tensor_core_path_shapes(dev, oracle, shape, oc, k, padding, act):
