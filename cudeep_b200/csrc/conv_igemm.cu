@@ -188,6 +188,10 @@ __global__ void __launch_bounds__(256)
 nchw_to_nhwc_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, int hw, int cx, int batch,
                     FilterPack filters, int with_filters, PixelScatter scatter = PixelScatter{}) {
     __shared__ float tile[32][65];
+    // The tensor-core kernel that follows is launched with programmatic stream serialization: once every
+    // block of this grid is running it may be set up (barriers, TMEM, descriptors) beside them; it waits
+    // for this grid's completion itself before it loads anything.
+    ptx::grid_launch_dependents();
     if (with_filters && int(blockIdx.z) >= batch) {
         const long long per_slice = static_cast<long long>(gridDim.x) * gridDim.y;
         pack_filters(filters, (int(blockIdx.z) - batch) * per_slice + blockIdx.y * gridDim.x + blockIdx.x,
@@ -244,6 +248,7 @@ template <bool SCATTER>
 __global__ void __launch_bounds__(256)
 nchw_to_nhwc4_kernel(const float* __restrict__ x, float* __restrict__ xt, int c, int hw, int batch,
                      FilterPack filters, int with_filters, PixelScatter scatter) {
+    ptx::grid_launch_dependents();      // see nchw_to_nhwc_kernel
     if (with_filters && int(blockIdx.z) >= batch) {
         const long long per_slice = static_cast<long long>(gridDim.x) * gridDim.y;
         pack_filters(filters, (int(blockIdx.z) - batch) * per_slice + blockIdx.y * gridDim.x + blockIdx.x,
