@@ -1348,11 +1348,12 @@ struct WeaveArgs {
 
 // SH, SW: the strides as compile-time constants (0: read them from the arguments), so that the
 // divisions by them are shifts or multiplications.  blockIdx.y is the (image, channel) plane.
-template <bool VEC, int SH, int SW>
+// PER: output pixels per thread (4, or 8 for rows that are multiples of 8: twice the loads in flight).
+template <bool VEC, int SH, int SW, int PER = 4>
 __global__ void __launch_bounds__(256)
 weave_parity_classes_kernel(const float* __restrict__ planes, float* __restrict__ dx, WeaveArgs t) {
     const int s_h = SH > 0 ? SH : t.s_h, s_w = SW > 0 ? SW : t.s_w;
-    const int groups = (t.w + 3) / 4;
+    const int groups = (t.w + PER - 1) / PER;
     const int work = t.h * groups;
     const long long plane_px = static_cast<long long>(t.rows) * t.pitch;
     const int n = blockIdx.y / t.c, c = blockIdx.y - n * t.c;
@@ -1365,28 +1366,31 @@ weave_parity_classes_kernel(const float* __restrict__ planes, float* __restrict_
         const int a = (ih + t.p_h) % s_h;
         const int u = (ih + t.p_h) / s_h - t.lo_h[a];
         const float* row = src0 + static_cast<long long>(a) * s_w * class_stride + static_cast<long long>(u) * t.pitch;
-        float v[4];
+        float v[PER];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int iw = g * 4 + j;
+        for (int j = 0; j < PER; ++j) {
+            const int iw = g * PER + j;
             const int b = (iw + t.p_w) % s_w;
             const int q = (iw + t.p_w) / s_w - t.lo_w[b];
             v[j] = iw < t.w ? __ldg(row + b * class_stride + q) : 0.0f;
         }
-        float* dst = dst0 + static_cast<long long>(ih) * t.w + g * 4;
+        float* dst = dst0 + static_cast<long long>(ih) * t.w + g * PER;
         if (VEC) {
-            *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+#pragma unroll
+            for (int j = 0; j < PER; j += 4)
+                *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
         } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (g * 4 + j < t.w) dst[j] = v[j];
+            for (int j = 0; j < PER; ++j)
+                if (g * PER + j < t.w) dst[j] = v[j];
         }
     }
 }
 
 template <bool VEC>
 void launch_weave(const float* planes, float* dx, const WeaveArgs& t, long long n_planes, cudaStream_t stream) {
-    const int work = t.h * ((t.w + 3) / 4);
+    const bool eight = VEC && t.w % 8 == 0 && t.s_h == 2 && t.s_w == 2;
+    const int work = t.h * ((t.w + (eight ? 7 : 3)) / (eight ? 8 : 4));
     int bx = (work + 255) / 256;
     if (bx > 64) bx = 64;
     // gridDim.y is limited to 65535: whole images per launch (blockIdx.y = image * C + channel).
@@ -1398,7 +1402,8 @@ void launch_weave(const float* planes, float* dx, const WeaveArgs& t, long long 
         const WeaveArgs& args = t;
         const float* src = planes + (first / t.c) * t.s_h * t.s_w * t.c * static_cast<long long>(t.rows) * t.pitch;
         float* dst = dx + first * static_cast<long long>(t.h) * t.w;
-        if (t.s_h == 2 && t.s_w == 2) weave_parity_classes_kernel<VEC, 2, 2><<<grid, 256, 0, stream>>>(src, dst, args);
+        if (eight) weave_parity_classes_kernel<VEC, 2, 2, 8><<<grid, 256, 0, stream>>>(src, dst, args);
+        else if (t.s_h == 2 && t.s_w == 2) weave_parity_classes_kernel<VEC, 2, 2><<<grid, 256, 0, stream>>>(src, dst, args);
         else if (t.s_h == 3 && t.s_w == 3) weave_parity_classes_kernel<VEC, 3, 3><<<grid, 256, 0, stream>>>(src, dst, args);
         else if (t.s_h == 4 && t.s_w == 4) weave_parity_classes_kernel<VEC, 4, 4><<<grid, 256, 0, stream>>>(src, dst, args);
         else weave_parity_classes_kernel<VEC, 0, 0><<<grid, 256, 0, stream>>>(src, dst, args);
